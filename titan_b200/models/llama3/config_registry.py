@@ -1,0 +1,99 @@
+"""Llama-3 recipes (``--module llama3 --config <name>``)."""
+
+from titan_b200.config.configs import (
+    ActivationCheckpointConfig,
+    CheckpointConfig,
+    LRSchedulerConfig,
+    MetricsConfig,
+    ModelConfigRef,
+    ModelConvertersConfig,
+    OptimizerConfig,
+    ParallelismConfig,
+    SyntheticDataLoaderConfig,
+    TrainerConfig,
+    TrainingConfig,
+)
+from titan_b200.protocols.converter import get_model_converter_config
+
+_FUSED = ["b200_rms_norm", "b200_rope", "b200_swiglu", "b200_flash_attention", "b200_cross_entropy"]
+
+
+def _fused_converters():
+    return [get_model_converter_config(n) for n in _FUSED]
+
+
+def llama3_debugmodel() -> TrainerConfig:
+    """dim 256 / 6 layers; runs on CPU (gloo) or one GPU in seconds."""
+    return TrainerConfig(
+        model=ModelConfigRef(name="llama3", flavor="debugmodel"),
+        metrics=MetricsConfig(log_freq=1),
+        optimizer=OptimizerConfig(name="AdamW", lr=8e-4, implementation="for-loop"),
+        lr_scheduler=LRSchedulerConfig(warmup_steps=2, decay_ratio=0.8, decay_type="linear", min_lr_factor=0.0),
+        training=TrainingConfig(local_batch_size=4, seq_len=512, steps=10, mixed_precision_param="float32",
+                                mixed_precision_reduce="float32", dtype="float32"),
+        dataloader=SyntheticDataLoaderConfig(seed=0),
+        parallelism=ParallelismConfig(data_parallel_shard_degree=-1),
+        checkpoint=CheckpointConfig(enable=False, interval=10, last_save_model_only=False),
+        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="2"),
+    )
+
+
+def llama3_debugmodel_b200() -> TrainerConfig:
+    """Debug model with every fused sm_100a op switched on (needs a B200)."""
+    cfg = llama3_debugmodel()
+    cfg.model_converters = ModelConvertersConfig(converters=_fused_converters())
+    cfg.optimizer.implementation = "b200_fused"
+    cfg.training.mixed_precision_param = "bfloat16"
+    cfg.training.dtype = "bfloat16"
+    return cfg
+
+
+def llama3_8b() -> TrainerConfig:
+    """Llama-3 8B pretraining: FSDP2, bf16 params/compute, fp32 reduce, seq 8192, local batch 1, selective AC."""
+    return TrainerConfig(
+        model=ModelConfigRef(name="llama3", flavor="8B"),
+        metrics=MetricsConfig(log_freq=10),
+        optimizer=OptimizerConfig(name="AdamW", lr=3e-4, eps=1e-8, implementation="b200_fused"),
+        lr_scheduler=LRSchedulerConfig(warmup_steps=200),
+        training=TrainingConfig(local_batch_size=1, seq_len=8192, steps=1000, mixed_precision_param="bfloat16",
+                                mixed_precision_reduce="float32", dtype="bfloat16"),
+        dataloader=SyntheticDataLoaderConfig(seed=0),
+        parallelism=ParallelismConfig(data_parallel_shard_degree=-1, fsdp_reshard_after_forward="default"),
+        checkpoint=CheckpointConfig(interval=500),
+        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op"),
+        model_converters=ModelConvertersConfig(converters=_fused_converters()),
+    )
+
+
+def llama3_8b_baseline() -> TrainerConfig:
+    """Same model and shapes on library ops only (cuBLAS / SDPA / NCCL): the on-box comparator."""
+    cfg = llama3_8b()
+    cfg.model_converters = ModelConvertersConfig(converters=[])
+    cfg.optimizer.implementation = "fused"
+    return cfg
+
+
+def llama3_70b() -> TrainerConfig:
+    """Llama-3 70B: FSDP=4 × TP=2 with sequence parallel, full AC, Swap Optimizer (AdamW state in pinned host memory)."""
+    return TrainerConfig(
+        model=ModelConfigRef(name="llama3", flavor="70B"),
+        metrics=MetricsConfig(log_freq=10),
+        optimizer=OptimizerConfig(name="AdamW", lr=1.5e-4, eps=1e-8, swap_optimizer=True, swap_optimizer_times=16),
+        lr_scheduler=LRSchedulerConfig(warmup_steps=200),
+        training=TrainingConfig(local_batch_size=1, seq_len=8192, steps=1000, mixed_precision_param="bfloat16",
+                                mixed_precision_reduce="float32", dtype="bfloat16"),
+        dataloader=SyntheticDataLoaderConfig(seed=0),
+        parallelism=ParallelismConfig(data_parallel_shard_degree=-1, tensor_parallel_degree=2,
+                                      enable_async_tensor_parallel=True),
+        checkpoint=CheckpointConfig(interval=500),
+        activation_checkpoint=ActivationCheckpointConfig(mode="full"),
+        model_converters=ModelConvertersConfig(converters=_fused_converters()),
+    )
+
+
+def llama3_405b() -> TrainerConfig:
+    cfg = llama3_70b()
+    cfg.model = ModelConfigRef(name="llama3", flavor="405B")
+    cfg.parallelism.tensor_parallel_degree = 8
+    cfg.optimizer.lr = 8e-5
+    return cfg

@@ -1,0 +1,150 @@
+"""Tensor-parallel helpers shared by all models.
+
+* `parallelize_module` – the entry point every model plan goes through; active
+  converter plan-updaters may rewrite the plan first (e.g. swap the NCCL
+  expert-parallel style for the fused peer-memory one).
+* `NoParallel` – keeps a module replicated but makes its params DTensors on the
+  TP mesh so gradient clipping / DCP see a uniform layout.
+* `AwaitRowwiseParallel` – row-parallel style whose output is waited on before
+  leaving the module (an un-awaited async collective tensor leaks under AC).
+* `PrepareModuleInputOutputWithBwdAllReduce` – replicated inputs to an attention
+  kernel whose gradients must be summed over TP.
+* `maybe_enable_async_tp` – selects the fused all-gather→GEMM / GEMM→reduce-scatter
+  kernels for sequence-parallel linears.
+
+Parity: torchtitan_npu/converters/framework/parallelize_plan_update_wrapper.py:24-48,
+models/deepseek_v32/parallelize.py:57-124, patches/torch/micro_pipeline_tp.py:114-144.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.distributed.device_mesh import DeviceMesh
+from torch.distributed.tensor import DTensor, Replicate, Shard, distribute_module, distribute_tensor
+from torch.distributed.tensor.parallel import (
+    ParallelStyle,
+    PrepareModuleInputOutput,
+    RowwiseParallel,
+)
+from torch.distributed.tensor.parallel import parallelize_module as _torch_parallelize_module
+
+from titan_b200.protocols.converter import active_plan_updaters
+
+__all__ = [
+    "parallelize_module",
+    "NoParallel",
+    "AwaitRowwiseParallel",
+    "PrepareModuleInputOutputWithBwdAllReduce",
+    "maybe_enable_async_tp",
+    "async_tp_enabled",
+]
+
+_ASYNC_TP = {"enabled": False}
+
+
+def parallelize_module(module: nn.Module, device_mesh: DeviceMesh | None = None, parallelize_plan=None, **kwargs):
+    for updater in active_plan_updaters():
+        parallelize_plan = updater.update(parallelize_plan)
+    return _torch_parallelize_module(module, device_mesh, parallelize_plan, **kwargs)
+
+
+class NoParallel(ParallelStyle):
+    def __init__(self, *, input_layout=None, output_layout=None, use_local_output: bool = True):
+        super().__init__()
+        self.input_layout = input_layout or Replicate()
+        self.output_layout = output_layout or Replicate()
+        self.desired_input_layout = Replicate()
+        self.use_local_output = use_local_output
+
+    @staticmethod
+    def _prepare_input_fn(input_layout, desired_input_layout, mod, inputs, device_mesh):
+        x = inputs[0]
+        if not isinstance(x, DTensor):
+            x = DTensor.from_local(x, device_mesh, (input_layout,), run_check=False)
+        if (input_layout,) != (desired_input_layout,):
+            x = x.redistribute(placements=(desired_input_layout,), async_op=True)
+        return (x, *inputs[1:])
+
+    @staticmethod
+    def _prepare_output_fn(output_layout, use_local_output, mod, outputs, device_mesh):
+        if outputs.placements != (output_layout,):
+            outputs = outputs.redistribute(placements=(output_layout,), async_op=True)
+        return outputs.to_local(grad_placements=(output_layout,)) if use_local_output else outputs
+
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        from functools import partial
+
+        return distribute_module(
+            module,
+            device_mesh,
+            None,
+            partial(self._prepare_input_fn, self.input_layout, self.desired_input_layout),
+            partial(self._prepare_output_fn, self.output_layout, self.use_local_output),
+        )
+
+
+class AwaitRowwiseParallel(RowwiseParallel):
+    @staticmethod
+    def _prepare_output_fn(output_layouts, use_local_output, mod, outputs, device_mesh):
+        out = RowwiseParallel._prepare_output_fn(output_layouts, use_local_output, mod, outputs, device_mesh)
+        if isinstance(out, torch.Tensor) and not isinstance(out, DTensor):
+            out = torch.ops._c10d_functional.wait_tensor(out) if type(out).__name__ == "AsyncCollectiveTensor" else out
+        return out
+
+
+class _AllReduceBwd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        return g, None
+
+
+class PrepareModuleInputOutputWithBwdAllReduce(PrepareModuleInputOutput):
+    """Like `PrepareModuleInputOutput`, and sums the grads of the inputs listed in
+    ``bwd_allreduce_input_idx`` over the mesh: each TP rank attends with its own
+    heads to the same replicated K/V latent, so dK/dV are partial sums."""
+
+    def __init__(self, *, bwd_allreduce_input_idx: tuple[int, ...] = (), **kwargs):
+        super().__init__(**kwargs)
+        self.bwd_allreduce_input_idx = tuple(bwd_allreduce_input_idx)
+
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        module = super()._apply(module, device_mesh)
+        group = device_mesh.get_group()
+        idxs = self.bwd_allreduce_input_idx
+
+        def pre_hook(mod, args):
+            args = list(args)
+            for i in idxs:
+                if i < len(args) and isinstance(args[i], torch.Tensor) and args[i].requires_grad:
+                    args[i] = _AllReduceBwd.apply(args[i], group)
+            return tuple(args)
+
+        module.register_forward_pre_hook(pre_hook)
+        return module
+
+
+def maybe_enable_async_tp(parallelism_config, tp_mesh: DeviceMesh | None) -> bool:
+    """Turn on the fused SP kernels when requested; returns whether they are on."""
+    if tp_mesh is None or not getattr(parallelism_config, "enable_async_tensor_parallel", False):
+        _ASYNC_TP["enabled"] = False
+        return False
+    if not torch.cuda.is_available():
+        raise RuntimeError("enable_async_tensor_parallel needs CUDA: the fused SP kernels are sm_100a code")
+    from titan_b200.ops import fused_comm
+
+    fused_comm.enable_for_group(tp_mesh.get_group())
+    _ASYNC_TP["enabled"] = True
+    return True
+
+
+def async_tp_enabled() -> bool:
+    return _ASYNC_TP["enabled"]

@@ -1,0 +1,185 @@
+"""Distributed bring-up, scalar reductions, determinism and EP-aware gradient clipping.
+
+Gradient clipping computes ``‖g‖_p`` from *local* shards: parameters are grouped by
+(mesh, placements); each group contributes ``Σ|g_local|^p`` which is all-reduced
+(SUM) over every mesh axis on which the group is sharded (or partial), so no
+DTensor redistribution of gradients happens.  Expert-parallel parameters live on
+another mesh than dense ones and are reduced separately; under pipeline
+parallelism the total is summed over stages.
+
+Parity: torchtitan_npu/patches/torch/clip_grad.py:32-145,
+patches/distributed/utils.py:25-80, tools/flight_recorder.py:15-43 (env wiring is in
+`titan_b200.utils.flight_recorder`), patches/torch_npu/determinism.py:25-68.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from collections import defaultdict
+from datetime import timedelta
+
+import torch
+import torch.distributed as dist
+from torch.distributed.device_mesh import DeviceMesh
+from torch.distributed.tensor import DTensor, Partial, Shard
+
+from titan_b200.utils.logging import logger
+
+__all__ = [
+    "init_distributed",
+    "dist_sum",
+    "dist_max",
+    "dist_mean",
+    "set_determinism",
+    "get_total_norm_local",
+    "clip_grad_norm_",
+    "device_type",
+]
+
+
+def device_type() -> str:
+    return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+def init_distributed(comm_config, *, world_size: int | None = None, base_folder: str = "") -> int:
+    """Create the default process group (NCCL on CUDA, gloo on CPU, fake in dry-run mode)."""
+    from titan_b200.utils.flight_recorder import setup_flight_recorder
+
+    mode = getattr(comm_config, "mode", "default")
+    if mode == "fake_backend":
+        from titan_b200.parallel.fake_pg import init_fake_process_group
+
+        ngpu = int(os.environ.get("NGPU", world_size or os.environ.get("WORLD_SIZE", "1")))
+        init_fake_process_group(rank=int(os.environ.get("RANK", "0")), world_size=ngpu)
+        return ngpu
+    setup_flight_recorder(comm_config, base_folder)
+    if not dist.is_initialized():
+        backend = comm_config.backend or ("nccl" if torch.cuda.is_available() else "gloo")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        rank = int(os.environ.get("RANK", "0"))
+        ws = int(os.environ.get("WORLD_SIZE", "1"))
+        kw = {}
+        if backend == "nccl":
+            local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local_rank)
+            kw["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend=backend, rank=rank, world_size=ws,
+                                timeout=timedelta(seconds=comm_config.init_timeout_seconds), **kw)
+    return dist.get_world_size()
+
+
+def _reduce(x: torch.Tensor | float, op, mesh: DeviceMesh | None) -> float:
+    if mesh is None or not dist.is_initialized():
+        return float(x)
+    if isinstance(x, DTensor):
+        x = x.full_tensor()
+    t = x.detach().clone().float() if isinstance(x, torch.Tensor) else torch.tensor(float(x))
+    dev = torch.device("cuda", torch.cuda.current_device()) if mesh.device_type == "cuda" else torch.device("cpu")
+    t = t.to(dev)
+    dist.all_reduce(t, op=op, group=mesh.get_group())
+    return t.item()
+
+
+def dist_sum(x, mesh: DeviceMesh | None) -> float:
+    return _reduce(x, dist.ReduceOp.SUM, mesh)
+
+
+def dist_max(x, mesh: DeviceMesh | None) -> float:
+    return _reduce(x, dist.ReduceOp.MAX, mesh)
+
+
+def dist_mean(x, mesh: DeviceMesh | None) -> float:
+    if mesh is None:
+        return float(x)
+    return _reduce(x, dist.ReduceOp.SUM, mesh) / mesh.size()
+
+
+def set_determinism(seed: int | None, deterministic: bool, *, parallel_dims=None, warn_only: bool = False) -> None:
+    """Seed every RNG (offset per pipeline stage only: data-parallel ranks share init) and,
+    if asked, force deterministic kernels and deterministic NCCL algorithms."""
+    if deterministic:
+        torch.use_deterministic_algorithms(True, warn_only=warn_only)
+        torch.backends.cudnn.deterministic = True
+        torch.backends.cudnn.benchmark = False
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        # tree/ring choice changes summation order; pin one algorithm and protocol
+        os.environ.setdefault("NCCL_ALGO", "Ring")
+        os.environ.setdefault("NCCL_PROTO", "Simple")
+        os.environ["TITAN_B200_DETERMINISTIC"] = "1"
+    if seed is None:
+        return
+    offset = 0
+    if parallel_dims is not None and parallel_dims.pp_enabled and dist.is_initialized():
+        offset = parallel_dims.coordinate(dist.get_rank())["pp"]
+    torch.manual_seed(seed + offset)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed + offset)
+
+
+# ----------------------------------------------------------------------- gradient clipping
+def _pow_sum(grads: list[torch.Tensor], p: float) -> torch.Tensor:
+    local = [g.to_local() if isinstance(g, DTensor) else g for g in grads]
+    if p == math.inf:
+        return torch.stack([g.detach().abs().max().float() for g in local]).max()
+    norms = torch._foreach_norm(local, p) if local[0].is_cuda else [torch.linalg.vector_norm(g, p) for g in local]
+    return torch.stack([n.float() for n in norms]).pow(p).sum()
+
+
+def get_total_norm_local(grads: list[torch.Tensor], norm_type: float = 2.0, *, pp_mesh: DeviceMesh | None = None,
+                         error_if_nonfinite: bool = False) -> torch.Tensor:
+    """Global p-norm of a list of (D)Tensor gradients, computed from local shards."""
+    if norm_type <= 0:
+        raise ValueError("norm_type must be positive")
+    p = float(norm_type)
+    groups: dict = defaultdict(list)
+    for g in grads:
+        if isinstance(g, DTensor):
+            groups[(g.device_mesh, tuple(g.placements))].append(g)
+        else:
+            groups[None].append(g)
+    total = None
+    for key, gs in groups.items():
+        part = _pow_sum(gs, p)
+        if key is not None:
+            mesh, placements = key
+            for dim, pl in enumerate(placements):
+                if isinstance(pl, Partial):
+                    raise NotImplementedError("Partial gradients must be reduced before clipping")
+                if isinstance(pl, Shard) and mesh.size(dim) > 1:
+                    op = dist.ReduceOp.MAX if p == math.inf else dist.ReduceOp.SUM
+                    dist.all_reduce(part, op=op, group=mesh.get_group(dim))
+        if total is None:
+            total = part
+        else:
+            total = torch.maximum(total, part.to(total.device)) if p == math.inf else total + part.to(total.device)
+    if total is None:
+        return torch.tensor(0.0)
+    if pp_mesh is not None and pp_mesh.size() > 1:
+        op = dist.ReduceOp.MAX if p == math.inf else dist.ReduceOp.SUM
+        dist.all_reduce(total, op=op, group=pp_mesh.get_group())
+    norm = total if p == math.inf else total.pow(1.0 / p)
+    if error_if_nonfinite and not torch.isfinite(norm):
+        raise RuntimeError(f"the total norm of order {p} of the gradients is non-finite")
+    return norm
+
+
+@torch.no_grad()
+def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, *, error_if_nonfinite: bool = False,
+                    foreach: bool | None = None, pp_mesh: DeviceMesh | None = None,
+                    ep_enabled: bool = False) -> torch.Tensor:
+    """Clip in place and return the total norm (a 0-d tensor on the gradients' device)."""
+    params = [p for p in ([parameters] if isinstance(parameters, torch.Tensor) else parameters) if p.grad is not None]
+    grads = [p.grad for p in params]
+    if not grads:
+        return torch.tensor(0.0)
+    total = get_total_norm_local(grads, norm_type, pp_mesh=pp_mesh, error_if_nonfinite=error_if_nonfinite)
+    coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+    local = [g.to_local() if isinstance(g, DTensor) else g for g in grads]
+    by_dev: dict = defaultdict(list)
+    for g in local:
+        by_dev[(g.device, g.dtype)].append(g)
+    for (dev, _), gs in by_dev.items():
+        torch._foreach_mul_(gs, coef.to(dev))
+    return total
