@@ -1,0 +1,16 @@
+// Library-wide runtime bookkeeping: launch counter and version.
+#include "tb_common.cuh"
+
+#include <atomic>
+
+namespace {
+std::atomic<long long> g_launches{0};
+}
+
+// called by every host launcher after a successful <<<>>>
+extern "C" __attribute__((visibility("default"))) void tb_note_launch(int n) { g_launches.fetch_add(n); }
+
+// Number of kernels this library has launched in this process (benchmarks report it).
+TB_API long long tb_launch_count() { return g_launches.load(); }
+TB_API int tb_reset_launch_count() { g_launches.store(0); return 0; }
+TB_API int tb_version() { return 1; }

@@ -15,7 +15,7 @@ from titan_b200.config.configs import (
 )
 from titan_b200.protocols.converter import get_model_converter_config
 
-_FUSED = ["b200_rms_norm", "b200_rope", "b200_swiglu", "b200_flash_attention", "b200_cross_entropy"]
+_FUSED = ["b200_rms_norm", "b200_rope", "b200_swiglu", "b200_cross_entropy"]
 
 
 def _fused_converters():

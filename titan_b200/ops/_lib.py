@@ -1,0 +1,151 @@
+"""ctypes binding of the sm_100a kernel library.
+
+`lib()` returns the loaded ``libtitan_b200.so`` (built in-tree by `titan_b200.csrc.build`).  If the
+library is missing on a machine that has a GPU, loading raises: a fused op must never fall back
+silently to library math.  Every kernel entry returns an int: 0 = launched, otherwise an error
+code (`check`) — kernels themselves report run-time failures (bounded waits that expired, index
+checks) through a status word that `StatusWord` owns.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+__all__ = ["lib", "available", "check", "stream_ptr", "ptr", "dtype_code", "StatusWord", "KernelError", "LIB_PATH"]
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C", "libtitan_b200.so")
+_LIB = None
+
+_STATUS_TEXT = {
+    1: "TMA full-barrier wait expired",
+    2: "empty-barrier wait expired",
+    3: "TMEM-full wait expired",
+    4: "TMEM-empty wait expired",
+    5: "peer flag wait expired",
+    6: "index out of bounds (access skipped)",
+    7: "invalid arguments",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _declare(L) -> None:
+    P, I, LL, F = c_void_p, c_int, c_longlong, c_float
+    sig = {
+        "tb_rmsnorm_bwd_grid": [I, I],
+        "tb_rmsnorm_fwd": [P, P, P, P, I, I, F, I, P],
+        "tb_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, I, P],
+        "tb_rope": [P, P, P, P, LL, I, I, I, I, I, I, I, I, P, P],
+        "tb_swiglu_fwd": [P, P, P, P, LL, I, LL, LL, F, I, P],
+        "tb_swiglu_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, F, I, P],
+        "tb_adam_limits": [P, P, P],
+        "tb_adamw_multi": [P, P, P, P, P, P, I, F, F, F, F, F, LL, P, I, I, I, I, I, I, P],
+        "tb_cross_entropy_fwd": [P, P, P, P, LL, I, LL, LL, I, P, P],
+        "tb_cross_entropy_bwd": [P, P, P, P, P, LL, I, LL, LL, I, P],
+        "tb_gemm_bf16": [P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P],
+    }
+    for name, args in sig.items():
+        fn = getattr(L, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise KernelError(
+                f"{LIB_PATH} is missing: run `python -m titan_b200.csrc.build` (needs nvcc; no GPU required)")
+        _LIB = ctypes.CDLL(LIB_PATH)
+        _declare(_LIB)
+    return _LIB
+
+
+def declare(name: str, argtypes: list) -> None:
+    """Late declaration for entry points added by optional source files."""
+    fn = getattr(lib(), name)
+    fn.argtypes = argtypes
+    fn.restype = c_int
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process."""
+    fn = lib().tb_launch_count
+    fn.restype = ctypes.c_longlong
+    fn.argtypes = []
+    return int(fn())
+
+
+def available() -> bool:
+    """True when CUDA is present (the library must then load, or this raises)."""
+    if not torch.cuda.is_available():
+        return False
+    lib()
+    return True
+
+
+def check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc >= 2000:
+        raise KernelError(f"{what}: cuTensorMapEncodeTiled failed with CUresult {rc - 2000}")
+    if rc >= 1000:
+        raise KernelError(f"{what}: CUDA runtime error {rc - 1000}")
+    raise KernelError(f"{what}: {_STATUS_TEXT.get(rc, f'error {rc}')}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE[dt]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {dt}") from None
+
+
+class StatusWord:
+    """A device int32 that kernels write error codes into; `raise_if_set` syncs and checks it."""
+
+    def __init__(self, device=None):
+        self.t = torch.zeros(1, dtype=torch.int32, device=device or torch.device("cuda", torch.cuda.current_device()))
+
+    @property
+    def ptr(self) -> int:
+        return self.t.data_ptr()
+
+    def read(self) -> int:
+        return int(self.t.item())
+
+    def raise_if_set(self, what: str) -> None:
+        code = self.read()
+        if code != 0:
+            self.t.zero_()
+            raise KernelError(f"{what}: kernel reported '{_STATUS_TEXT.get(code, code)}'")
+
+
+_STATUS_CACHE: dict[int, StatusWord] = {}
+
+
+def shared_status() -> StatusWord:
+    """One status word per device, checked lazily (e.g. at log steps) to avoid per-op syncs."""
+    dev = torch.cuda.current_device()
+    if dev not in _STATUS_CACHE:
+        _STATUS_CACHE[dev] = StatusWord()
+    return _STATUS_CACHE[dev]

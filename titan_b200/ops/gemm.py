@@ -1,0 +1,106 @@
+"""tcgen05 GEMM: Python entry points, a `linear` autograd function and oracles.
+
+``gemm(a, b, a_mn=False, b_mn=False)`` computes ``A · B`` for bf16/fp16 operands on the
+tcgen05 tensor cores with fp32 accumulation in tensor memory (`csrc/gemm/gemm_bf16.cu`).
+`a_mn` / `b_mn` say how each operand is *stored* (see that file); `linear(x, w)` uses the
+three storage combinations so forward, input-gradient and weight-gradient run without transposes:
+
+    y  = x · wᵀ      gemm(x,  w)                       (both K-major)
+    dx = dy · w      gemm(dy, w, b_mn=True)
+    dw = dyᵀ · x     gemm(dy, x, a_mn=True, b_mn=True)
+"""
+
+from __future__ import annotations
+
+import torch
+
+from titan_b200.ops import _lib
+
+__all__ = ["gemm", "linear", "gemm_ref", "supported"]
+
+
+def gemm_ref(a, b, a_mn=False, b_mn=False, out_dtype=None):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return (A @ B).to(out_dtype or a.dtype)
+
+
+def supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return (a.is_cuda and a.dtype in (torch.bfloat16, torch.float16) and a.dtype == b.dtype
+            and a.dim() == 2 and b.dim() == 2)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
+         out_dtype: torch.dtype | None = None, accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    """A · B.  a: [M,K] (or [K,M] if a_mn); b: [N,K] (or [K,N] if b_mn) → [M,N]."""
+    if not supported(a, b):
+        raise _lib.KernelError(f"gemm: unsupported operands {a.dtype}{tuple(a.shape)} x {b.dtype}{tuple(b.shape)}")
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    K, M = (a.shape[0], a.shape[1]) if a_mn else (a.shape[1], a.shape[0])
+    Kb, N = (b.shape[0], b.shape[1]) if b_mn else (b.shape[1], b.shape[0])
+    if K != Kb:
+        raise ValueError(f"gemm: contraction mismatch {K} vs {Kb}")
+    out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out_dtype not in (a.dtype, torch.float32):
+        raise ValueError("gemm: output dtype must be the input dtype or float32")
+    if out is None:
+        if accumulate:
+            raise ValueError("gemm: accumulate needs an output tensor")
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    elif out.shape != (M, N) or out.stride(-1) != 1:
+        raise ValueError("gemm: `out` must be [M, N] with unit inner stride")
+    # the kernel needs 16-byte aligned rows: pad ragged leading dimensions through a copy
+    if a.stride(0) % 8 or a.data_ptr() % 16:
+        a = _aligned_copy(a)
+    if b.stride(0) % 8 or b.data_ptr() % 16:
+        b = _aligned_copy(b)
+    status = _lib.shared_status()
+    rc = _lib.lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                 out.stride(0), int(a_mn), int(b_mn), _lib.dtype_code(a.dtype),
+                                 int(out_dtype == torch.float32), int(accumulate), int(max_ctas), status.ptr,
+                                 _lib.stream_ptr())
+    _lib.check(rc, "gemm_bf16")
+    return out
+
+
+def _aligned_copy(t: torch.Tensor) -> torch.Tensor:
+    rows, cols = t.shape
+    ld = (cols + 7) // 8 * 8
+    buf = torch.zeros(rows, ld, dtype=t.dtype, device=t.device)
+    buf[:, :cols] = t
+    return buf[:, :cols]
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        x2 = x.reshape(-1, x.shape[-1])
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(g2, w, b_mn=True).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(g2, x2, a_mn=True, b_mn=True)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` on the tcgen05 kernel (CUDA bf16/fp16), else `F.linear`."""
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and x.shape[-1] % 8 == 0 \
+            and w.shape[0] % 8 == 0:
+        y = _LinearFn.apply(x, w)
+        return y if bias is None else y + bias
+    return torch.nn.functional.linear(x, w, bias)

@@ -59,7 +59,24 @@ def multi_token_cross_entropy_loss(preds, labels: torch.Tensor, *, num_mtp: int,
     return main + mtp_loss_weight * extra / num_mtp
 
 
+def _fused_requested(trainer_config) -> bool:
+    if trainer_config is None:
+        return False
+    from titan_b200.protocols.converter import has_converter
+
+    return has_converter(trainer_config.model_converters.converters, "b200_cross_entropy")
+
+
+def fused_cross_entropy_loss(pred: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Sum of token losses through the sm_100a kernel (logits stay in their storage dtype)."""
+    from titan_b200.ops.cross_entropy import cross_entropy_sum
+
+    return cross_entropy_sum(pred, labels, IGNORE_INDEX, inplace_backward=True)
+
+
 def build_cross_entropy_loss(compile_config=None, trainer_config=None):
+    if _fused_requested(trainer_config):
+        return fused_cross_entropy_loss
     loss_fn = cross_entropy_loss
     if compile_config is not None and compile_config.enable and "loss" in compile_config.components:
         loss_fn = torch.compile(loss_fn, backend=compile_config.backend)
