@@ -1,0 +1,170 @@
+"""Per-kernel timings against the library baseline and the measured roofline.
+
+    python benchmarks/kernel_bench.py [--only gemm,rmsnorm,...] [--iters 20]
+
+Each line is JSON: kernel, shape, our time, baseline (PyTorch / cuBLAS) time, achieved TFLOP/s or
+GB/s, and the fraction of the measured peak (cuBLAS bf16 burst throughput / copy bandwidth from
+MEASURED_PEAKS.json when present, else the stated fallback).  Timing: CUDA events on the launching
+stream, 5 warm-up iterations, an L2 flush (write of a 256 MB buffer) before every timed iteration.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from titan_b200.utils.device import measured_peaks  # noqa: E402
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def timeit(fn, iters=20, warmup=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]  # median, ms
+
+
+def peaks():
+    p = measured_peaks()
+    if p:
+        return p["bf16_tflops"], p["hbm_gbs"], "of measured"
+    return 1590.0, 6650.0, "of fallback"
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def bench_gemm(iters):
+    from titan_b200.ops.gemm import gemm
+
+    tf_peak, _, tag = peaks()
+    shapes = [  # (M, N, K, a_mn, b_mn, label)
+        (8192, 4096, 4096, 0, 0, "llama8b wq/wo fwd"),
+        (8192, 6144, 4096, 0, 0, "llama8b qkv fwd"),
+        (8192, 14336, 4096, 0, 0, "llama8b w1/w3 fwd"),
+        (8192, 4096, 14336, 0, 0, "llama8b w2 fwd"),
+        (8192, 4096, 14336, 0, 1, "llama8b w1 dgrad"),
+        (14336, 4096, 8192, 1, 1, "llama8b w1 wgrad"),
+        (8192, 128256, 4096, 0, 0, "llama8b output fwd"),
+        (8192, 8192, 8192, 0, 0, "square 8192"),
+    ]
+    for M, N, K, a_mn, b_mn, label in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ours = timeit(lambda: gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out), iters)
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        base = timeit(lambda: torch.matmul(A, B, out=out), iters)
+        fl = 2.0 * M * N * K
+        emit(kernel="gemm_tcgen05", label=label, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, ms=ours, cublas_ms=base,
+             tflops=fl / ours / 1e9, cublas_tflops=fl / base / 1e9, frac_of_peak=fl / ours / 1e9 / tf_peak, peak=tag,
+             speedup_vs_cublas=base / ours)
+
+
+def bench_elementwise(iters):
+    from titan_b200.ops.cross_entropy import cross_entropy_sum
+    from titan_b200.ops.norm import rms_norm_bwd, rms_norm_fwd
+    from titan_b200.ops.rope import rope_apply
+    from titan_b200.ops.swiglu import swiglu
+    from titan_b200.models.common import rope as rope_ref
+
+    _, bw_peak, tag = peaks()
+    rows, dim = 8192, 4096
+    x = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(dim, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn_like(x)
+    ours = timeit(lambda: rms_norm_fwd(x, w, 1e-5), iters)
+    base = timeit(lambda: torch.nn.functional.rms_norm(x, (dim,), w, 1e-5), iters)
+    byt = 2 * x.numel() * 2
+    emit(kernel="rmsnorm_fwd", shape=[rows, dim], ms=ours, torch_ms=base, gbs=byt / ours / 1e6,
+         frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
+    _, rstd = rms_norm_fwd(x, w, 1e-5)
+    ours = timeit(lambda: rms_norm_bwd(g, x, w, rstd), iters)
+    byt = 3 * x.numel() * 2
+    emit(kernel="rmsnorm_bwd", shape=[rows, dim], ms=ours, gbs=byt / ours / 1e6,
+         frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
+
+    q = torch.randn(1, 8192, 32, 128, device="cuda", dtype=torch.bfloat16)
+    cache = rope_ref.precompute_freqs_cis(128, 8192, 500000.0).cuda()
+    ours = timeit(lambda: rope_apply(q, cache), iters)
+    base = timeit(lambda: rope_ref.apply_rotary_emb_single_complex(q, cache), iters)
+    byt = 2 * q.numel() * 2
+    emit(kernel="rope", shape=list(q.shape), ms=ours, torch_ms=base, gbs=byt / ours / 1e6,
+         frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
+
+    a = torch.randn(8192, 14336, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn_like(a)
+    ours = timeit(lambda: swiglu(a, b), iters)
+    base = timeit(lambda: torch.nn.functional.silu(a) * b, iters)
+    byt = 3 * a.numel() * 2
+    emit(kernel="swiglu_fwd", shape=list(a.shape), ms=ours, torch_ms=base, gbs=byt / ours / 1e6,
+         frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
+
+    T, V = 8192, 128256
+    logits = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    ours = timeit(lambda: cross_entropy_sum(logits, labels), max(5, iters // 4))
+    byt = logits.numel() * 2
+    emit(kernel="cross_entropy_fwd", shape=[T, V], ms=ours, gbs=byt / ours / 1e6,
+         frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
+    del logits
+
+    from titan_b200.optim.fused_adamw import adamw_multi_tensor
+
+    n = 256 * 1024 * 1024
+    p = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    gr = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    ours = timeit(lambda: adamw_multi_tensor([p], [gr], [m], [v], lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8,
+                                             weight_decay=0.1, step=3), max(5, iters // 4))
+    base = timeit(lambda: torch._fused_adamw_([p], [gr], [m], [v], [], [torch.tensor(3.0, device="cuda")],
+                                              lr=1e-3, beta1=0.9, beta2=0.95, weight_decay=0.1, eps=1e-8,
+                                              amsgrad=False, maximize=False), max(5, iters // 4))
+    byt = n * (2 + 2 + 4 + 4 + 2 + 4 + 4)
+    emit(kernel="adamw_multi", numel=n, ms=ours, torch_ms=base, gbs=byt / ours / 1e6,
+         frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="gemm,elementwise")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    which = set(args.only.split(","))
+    if "gemm" in which:
+        bench_gemm(args.iters)
+    if "elementwise" in which:
+        bench_elementwise(args.iters)
+
+
+if __name__ == "__main__":
+    main()

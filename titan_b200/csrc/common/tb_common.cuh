@@ -304,6 +304,20 @@ inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   }
   return fn;
 }
+// Driver calls (tensor-map encoding) need a current context on the calling thread.  Threads that have
+// not made a runtime call yet (autograd worker threads) have none: bind the device that owns `ptr`.
+inline int ensure_context(const void* ptr) {
+  static thread_local bool bound = false;
+  if (bound) return 0;
+  cudaPointerAttributes attr;
+  int dev = 0;
+  if (cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice) dev = attr.device;
+  else (void)cudaGetLastError();
+  TB_CUDA_CHECK(cudaSetDevice(dev));
+  TB_CUDA_CHECK(cudaFree(nullptr));
+  bound = true;
+  return 0;
+}
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements, row pitch `ld_bytes`; box = [box_rows, box_cols].
 // swizzle: 0 none, 1 = 32B, 2 = 64B, 3 = 128B (CUtensorMapSwizzle values).
 inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes, uint64_t rows,
@@ -311,6 +325,7 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   auto fn = encode_fn();
   if (fn == nullptr) return TB_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld_bytes & 15) != 0) return TB_ERR_ARG;
+  if (int rc = ensure_context(base)) return rc;
   cuuint64_t gdim[2] = {cols, rows};
   cuuint64_t gstride[1] = {ld_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
@@ -327,6 +342,7 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   if (fn == nullptr) return TB_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (stride1_bytes & 15) != 0 || (stride2_bytes & 15) != 0)
     return TB_ERR_ARG;
+  if (int rc = ensure_context(base)) return rc;
   cuuint64_t gdim[3] = {d0, d1, d2};
   cuuint64_t gstride[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {box0, box1, box2};

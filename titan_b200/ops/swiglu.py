@@ -61,13 +61,14 @@ class _SwiGLUFn(torch.autograd.Function):
     def backward(ctx, gout):
         rows, H, pitch, limit, fused, has_score = ctx.meta
         gout = gout.contiguous()
+        saved = ctx.saved_tensors  # read once: activation checkpointing forbids a second unpack
         if fused:
-            x = ctx.saved_tensors[0]
+            x = saved[0]
             gate, up = x, x[:, H:]
             dx = torch.empty_like(x)
             dgate, dup = dx, dx[:, H:]
         else:
-            gate, up = ctx.saved_tensors[0], ctx.saved_tensors[1]
+            gate, up = saved[0], saved[1]
             dgate, dup = torch.empty_like(gate), torch.empty_like(up)
         dscore = torch.empty(rows, dtype=torch.float32, device=gout.device) if has_score else None
         rc = _lib.lib().tb_swiglu_bwd(gout.data_ptr(), gate.data_ptr(), up.data_ptr(), dgate.data_ptr(), dup.data_ptr(),
@@ -76,7 +77,7 @@ class _SwiGLUFn(torch.autograd.Function):
         _lib.check(rc, "swiglu_bwd")
         ds = None
         if has_score:
-            orig = ctx.saved_tensors[-1]
+            orig = saved[-1]
             ds = dscore.to(orig.dtype).view(orig.shape)
         if fused:
             return dx, None, ds, None, None
