@@ -56,8 +56,8 @@ class SyntheticDataLoader(Stateful):
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         if not state_dict:
             return
-        if state_dict.get("dp_world_size", self.dp_world_size) != self.dp_world_size:
-            raise ValueError("dataloader state was saved with a different data-parallel degree")
+        # the stream is a pure function of (seed, dp_rank, step): a different data-parallel degree on
+        # resume continues at the same step with its own rank streams
         self._step = int(state_dict["step"])
 
 

@@ -31,7 +31,7 @@ class Linear(nn.Linear, Module):
         self.init_std = init_std
 
     def init_states(self, *, init_std: float | None = None, **kwargs) -> None:
-        std = self.init_std if init_std is None else init_std
+        std = getattr(self, "init_std", 0.02) if init_std is None else init_std
         nn.init.trunc_normal_(self.weight, mean=0.0, std=std, a=-3 * std, b=3 * std)
         if self.bias is not None:
             nn.init.zeros_(self.bias)

@@ -1,0 +1,294 @@
+"""Meta-device memory and communication simulator: per-rank HBM of a recipe without any GPU.
+
+The model named by a `TrainerConfig` is built on the **meta** device and converted exactly as the
+trainer would; one forward + backward of a local batch then runs on meta tensors under
+`MetaMemoryTracker`, a dispatch mode that follows every tensor storage created by an operator until
+it is freed — the peak of that curve is the activation footprint under the chosen activation-
+checkpoint mode.  Static terms (parameter, gradient and optimizer shards, FSDP all-gather /
+reduce-scatter buffers) follow from `ParallelDims` arithmetic:
+
+    params   Σ numel / shard(p) · store bytes          shard = fsdp·tp (dense), efsdp·ep·etp (experts), / pp
+    grads    same · grad bytes
+    optim    2 · 4 B · local params (AdamW fp32 moments); 0 on the device with Swap/Virtual optimizers
+    fsdp buf 2 · largest unit (unsharded over fsdp) · param bytes  +  reduce-scatter staging in reduce dtype
+    activ.   tracker peak / (tp · cp)  (sequence-parallel and context-parallel shard activations)
+
+The estimate is checked against the HBM budget (180 GB by default) and reports link traffic per
+step with the time it costs at NVLink bandwidth.  The fake-backend dry run (`--comm.mode
+fake_backend`) executes the real trainer for one step in one process and complements this static
+estimate.
+
+The reference has no simulator module; it documents estimation formulas and a snapshot analyser
+(.agents/skills/oom-analysis/references/memory-estimation-templates.md:7-107) and a fake-backend
+dry run (scripts/run_train.sh:23-27).  This module turns those into a first-class component.
+"""
+
+from __future__ import annotations
+
+import json
+import weakref
+from dataclasses import asdict, dataclass, field
+
+import torch
+from torch.utils._python_dispatch import TorchDispatchMode
+from torch.utils._pytree import tree_flatten
+
+__all__ = ["MetaMemoryTracker", "MemoryReport", "estimate", "run_from_config"]
+
+GIB = 1024 ** 3
+
+
+class MetaMemoryTracker(TorchDispatchMode):
+    """Tracks live bytes of storages created while the mode is active (works on meta tensors)."""
+
+    def __init__(self):
+        super().__init__()
+        self.current = 0
+        self.peak = 0
+        self._seen: dict[int, int] = {}
+
+    def _release(self, key: int) -> None:
+        self.current -= self._seen.pop(key, 0)
+
+    def _track(self, t: torch.Tensor) -> None:
+        try:
+            st = t.untyped_storage()
+        except Exception:
+            return
+        key = id(st)
+        if key in self._seen:
+            return
+        n = st.nbytes()
+        if n == 0:
+            n = t.numel() * t.element_size()
+        self._seen[key] = n
+        self.current += n
+        self.peak = max(self.peak, self.current)
+        weakref.finalize(st, self._release, key)
+
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        out = func(*args, **(kwargs or {}))
+        for leaf in tree_flatten(out)[0]:
+            if isinstance(leaf, torch.Tensor):
+                self._track(leaf)
+        return out
+
+
+@dataclass
+class MemoryReport:
+    world_size: int
+    parallelism: dict
+    params_total: int
+    params_local: int
+    bytes_params: int
+    bytes_grads: int
+    bytes_optimizer_device: int
+    bytes_optimizer_host: int
+    bytes_fsdp_buffers: int
+    bytes_activations: int
+    bytes_total: int
+    budget_bytes: int
+    fits: bool
+    comm_bytes_per_step: dict = field(default_factory=dict)
+    comm_seconds_per_step: float = 0.0
+    notes: list = field(default_factory=list)
+
+    def summary(self) -> str:
+        g = lambda b: f"{b / GIB:8.2f} GiB"  # noqa: E731
+        lines = [
+            f"memory estimate per rank ({self.world_size} ranks, {self.parallelism})",
+            f"  parameters        {g(self.bytes_params)}   ({self.params_local:,} of {self.params_total:,} params)",
+            f"  gradients         {g(self.bytes_grads)}",
+            f"  optimizer (HBM)   {g(self.bytes_optimizer_device)}   (+{g(self.bytes_optimizer_host)} pinned host)",
+            f"  FSDP buffers      {g(self.bytes_fsdp_buffers)}",
+            f"  activations       {g(self.bytes_activations)}",
+            f"  total             {g(self.bytes_total)}   budget {g(self.budget_bytes)}   "
+            f"{'FITS' if self.fits else 'DOES NOT FIT'}",
+            f"  link traffic/step {json.dumps({k: round(v / GIB, 3) for k, v in self.comm_bytes_per_step.items()})} GiB"
+            f" ≈ {self.comm_seconds_per_step * 1e3:.1f} ms at link rate",
+        ]
+        return "\n".join(lines + [f"  note: {n}" for n in self.notes])
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self))
+
+
+_DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+
+
+def _is_expert(name: str) -> bool:
+    return ".experts." in name and "shared_experts" not in name
+
+
+class _FlashStandIn(torch.autograd.Function):
+    """Memory-faithful stand-in for fused attention on meta tensors: keeps q, k, v, out and the
+    log-sum-exp row statistics alive for backward and never materialises the score matrix (the math
+    fallback that meta tensors would otherwise take allocates [B, H, S, S])."""
+
+    @staticmethod
+    def forward(ctx, q, k, v):
+        out = torch.empty(*q.shape[:-1], v.shape[-1], dtype=q.dtype, device=q.device)
+        lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
+        ctx.save_for_backward(q, k, v, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        q, k, v, _, _ = ctx.saved_tensors
+        return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _sdpa_stand_in(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, enable_gqa=False):
+    return _FlashStandIn.apply(q, k, v)
+
+
+def _measure_activations(model, model_config, training, loss_fn, num_mtp: int) -> int:
+    """Peak bytes of one forward+backward on meta tensors (parameters and their grads excluded)."""
+    import torch.nn.functional as F
+
+    b, s = training.local_batch_size, training.seq_len
+    tokens = torch.empty(b, s, dtype=torch.int64, device="meta")
+    labels = torch.empty(b, s + num_mtp, dtype=torch.int64, device="meta")
+    grads_bytes = sum(p.numel() * p.element_size() for p in model.parameters() if p.requires_grad)
+    real_sdpa = F.scaled_dot_product_attention
+    F.scaled_dot_product_attention = _sdpa_stand_in
+    try:
+        with MetaMemoryTracker() as tr:
+            out = model(tokens)
+            loss = loss_fn(out, labels)
+            del out
+            loss.backward()
+            peak = tr.peak
+    finally:
+        F.scaled_dot_product_attention = real_sdpa
+    # parameter gradients are created during backward and accounted separately
+    for p in model.parameters():
+        p.grad = None
+    return max(peak - grads_bytes, 0)
+
+
+def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> MemoryReport:
+    from titan_b200.parallel.parallel_dims import ParallelDims
+    from titan_b200.protocols.converter import ModelConvertersContainer
+    from titan_b200.protocols.model_spec import get_model_spec
+
+    cfg = trainer_config
+    par = cfg.parallelism
+    pd = ParallelDims(
+        dp_replicate=par.data_parallel_replicate_degree, dp_shard=par.data_parallel_shard_degree,
+        cp=par.context_parallel_degree, tp=par.tensor_parallel_degree, pp=par.pipeline_parallel_degree,
+        ep=par.expert_parallel_degree, etp=par.expert_tensor_parallel_degree, world_size=world_size)
+    spec = get_model_spec(cfg.model.name, cfg.model.flavor)
+    mc = spec.model
+    mc.update_from_config(trainer_config=cfg)
+    store_dt = _DT[cfg.training.dtype]
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(store_dt)
+    try:
+        with torch.device("meta"):
+            model = mc.build()
+    finally:
+        torch.set_default_dtype(old)
+    ModelConvertersContainer(cfg.model_converters.converters, model_spec=spec, trainer_config=cfg).convert(model)
+    notes = []
+
+    # ---- static shards
+    fsdp = pd.dp_shard * pd.cp
+    total = local = 0.0
+    largest_unit = 0.0
+    per_layer: dict[str, float] = {}
+    expert_local = 0.0
+    for name, p in model.named_parameters():
+        n = p.numel()
+        total += n
+        if _is_expert(name):
+            shard = pd.efsdp * pd.ep * (pd.etp if pd.etp_enabled else 1)
+            expert_local += n / shard / pd.pp
+        else:
+            tp_sharded = p.dim() >= 2 and pd.tp_enabled
+            shard = fsdp * (pd.tp if tp_sharded else 1)
+        local += n / shard / pd.pp
+        unit = name.split(".")[1] if name.startswith("layers.") else name.split(".")[0]
+        gathered = n / ((pd.ep * (pd.etp if pd.etp_enabled else 1)) if _is_expert(name)
+                        else (pd.tp if (p.dim() >= 2 and pd.tp_enabled) else 1))
+        per_layer[unit] = per_layer.get(unit, 0.0) + gathered
+    largest_unit = max(per_layer.values()) if per_layer else 0.0
+    sb = torch.empty((), dtype=store_dt).element_size()
+    param_dt = _DT[cfg.training.mixed_precision_param]
+    pb = torch.empty((), dtype=param_dt).element_size()
+    rb = torch.empty((), dtype=_DT[cfg.training.mixed_precision_reduce]).element_size()
+    bytes_params = int(local * sb)
+    bytes_grads = int(local * sb)
+    opt_bytes = int(local * 8)  # two fp32 moments
+    if cfg.optimizer.name == "Muon":
+        opt_bytes = int(local * 4)
+        notes.append("Muon keeps one momentum buffer for matrix params (AdamW moments for the rest are a few %)")
+    on_host = cfg.optimizer.swap_optimizer or cfg.optimizer.virtual_optimizer
+    bytes_opt_dev = 0 if on_host else opt_bytes
+    bytes_opt_host = opt_bytes if on_host else 0
+    if cfg.optimizer.swap_optimizer:
+        # one slice of the state is resident at a time while the step streams through
+        bytes_opt_dev = int(opt_bytes / max(cfg.optimizer.swap_optimizer_times, 1)) * 2
+    bytes_fsdp = 0
+    if fsdp > 1:
+        bytes_fsdp = int(2 * largest_unit * pb + largest_unit * rb * (1 + 1 / fsdp))
+        if sb != pb:
+            notes.append("parameters are stored in a wider dtype than they are gathered in")
+
+    # ---- activations from the meta run
+    loss_fn = spec.build_loss_fn(None, trainer_config=cfg) if spec.build_loss_fn else None
+    if cfg.activation_checkpoint.mode != "none":
+        from titan_b200.parallel.activation_checkpoint import apply_ac
+
+        apply_ac(model, cfg.activation_checkpoint)
+    try:
+        act = _measure_activations(model, mc, cfg.training, loss_fn, cfg.training.num_mtp_modules)
+    except Exception as e:  # an op without a meta kernel: fall back to a closed-form bound
+        L, d = mc.n_layers, mc.dim
+        tok = cfg.training.local_batch_size * cfg.training.seq_len
+        per_layer_act = {"full": 1, "selective": 10, "none": 24}[cfg.activation_checkpoint.mode]
+        act = int(tok * d * pb * per_layer_act * L + tok * mc.vocab_size * (pb + 4))
+        notes.append(f"activation term from the closed-form bound ({type(e).__name__}: {str(e)[:80]})")
+    act = int(act / (pd.tp * pd.cp) / pd.pp)
+
+    # ---- link traffic per step (bytes sent+received by one rank)
+    comm = {}
+    if fsdp > 1:
+        dense_total = (total - sum(p.numel() for n, p in model.named_parameters() if _is_expert(n))) / pd.pp
+        gathers = 2 if par.fsdp_reshard_after_forward != "never" else 1
+        comm["fsdp_all_gather"] = dense_total / (pd.tp if pd.tp_enabled else 1) * pb * gathers * (fsdp - 1) / fsdp
+        comm["fsdp_reduce_scatter"] = dense_total / (pd.tp if pd.tp_enabled else 1) * rb * (fsdp - 1) / fsdp
+    if pd.tp_enabled:
+        tok = cfg.training.local_batch_size * cfg.training.seq_len / pd.cp
+        per_layer_bytes = tok * mc.dim * pb * (pd.tp - 1) / pd.tp
+        comm["tp_sp_collectives"] = per_layer_bytes * 4 * 2 * mc.n_layers / pd.pp  # 2 AG + 2 RS, fwd + bwd
+    if pd.ep_enabled:
+        tok = cfg.training.local_batch_size * cfg.training.seq_len / pd.cp
+        topk = getattr(getattr(mc, "moe_args", None), "top_k", getattr(mc, "top_k", 1))
+        n_moe = getattr(mc, "n_layers", 0) - getattr(mc, "n_dense_layers", 0)
+        comm["ep_all_to_all"] = tok * topk * mc.dim * pb * (pd.ep - 1) / pd.ep * 4 * n_moe / pd.pp
+    seconds = sum(comm.values()) / (link_gbs * 1e9)
+
+    total_bytes = bytes_params + bytes_grads + bytes_opt_dev + bytes_fsdp + act
+    budget = int(cfg.memory_sim.hbm_budget_gib * 1e9)
+    return MemoryReport(
+        world_size=world_size,
+        parallelism={"dp_replicate": pd.dp_replicate, "dp_shard": pd.dp_shard, "cp": pd.cp, "tp": pd.tp, "pp": pd.pp,
+                     "ep": pd.ep, "etp": pd.etp},
+        params_total=int(total), params_local=int(local), bytes_params=bytes_params, bytes_grads=bytes_grads,
+        bytes_optimizer_device=bytes_opt_dev, bytes_optimizer_host=bytes_opt_host, bytes_fsdp_buffers=bytes_fsdp,
+        bytes_activations=act, bytes_total=total_bytes, budget_bytes=budget, fits=total_bytes <= budget,
+        comm_bytes_per_step={k: float(v) for k, v in comm.items()}, comm_seconds_per_step=seconds, notes=notes)
+
+
+def run_from_config(trainer_config) -> MemoryReport:
+    import os
+
+    world = int(os.environ.get("NGPU", os.environ.get("WORLD_SIZE", "1")))
+    rep = estimate(trainer_config, world)
+    path = trainer_config.memory_sim.report_path
+    if path:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(path, "w") as f:
+            f.write(rep.to_json())
+    return rep
