@@ -215,6 +215,12 @@ class ParallelDims:
             return None
         return self._meshes[name]
 
+    def mesh_even_if_trivial(self, name: str) -> DeviceMesh | None:
+        """Like `get_optional_mesh` but also returns meshes of degree 1 (None only if never built)."""
+        if self._dense is None:
+            self.build_mesh()
+        return self._meshes.get(name)
+
     def _hsdp_mesh(self, expert: bool = False) -> DeviceMesh:
         key = "hsdp_e" if expert else "hsdp"
         if key not in self._meshes:
