@@ -1,0 +1,258 @@
+// Compute fused with collectives over NVLink peer memory (plain P2P loads / stores; no multicast).
+//
+//   tb_ag_gemm            C = gather_rows(A_shards) · B      A tiles are TMA-loaded from the owner GPU
+//   tb_ag_b_gemm          C = A · gather_rows(B_shards)ᵀ     weight shards gathered inside the GEMM (FSDP)
+//   tb_gemm_rs            partial C tiles are stored into the owner's staging slot, flags released
+//   tb_rs_reduce          owner sums the nranks staged partials once every source's flag has arrived
+//   tb_castscale_rs       gradient bucket reduce-scatter: read chunk `rank` of every peer's bucket,
+//                         sum in fp32, scale, cast — one pass, no intermediate buffers
+//   tb_signal / tb_wait_flags / tb_barrier_all   flag plumbing with time-bounded waits
+//
+// Flags are 32-bit epoch counters in symmetric memory: a waiter compares `flag - epoch >= 0` so the
+// counters may wrap.  Peers' buffers are reached through pointers exchanged by the host (CUDA VMM
+// handles); every wait gives up after ~2 s and records TB_ERR_WAIT_PEER in the status word.
+//
+// Counterparts in the reference: `npu_all_gather_base_mm`, `npu_mm_reduce_scatter_base`
+// (patches/torch/micro_pipeline_tp.py:35-105) and the FSDP2 all-gather / reduce-scatter it inherits.
+#include "../gemm/gemm_kernel.cuh"
+
+using namespace tbg;
+
+namespace {
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__global__ void signal_kernel(PeerPtrs flags, int slot, unsigned int value, int nranks) {
+  const int r = threadIdx.x;
+  if (r < nranks) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned int*>(flags.p[r]) + slot, value);
+  }
+}
+
+__global__ void wait_flags_kernel(const unsigned int* flags, int first, int count, unsigned int value, int* status) {
+  const int i = threadIdx.x;
+  if (i < count) {
+    if (!wait_flag_ge(flags + first + i, value, nullptr) && status != nullptr) atomicExch(status, TB_ERR_WAIT_PEER);
+  }
+}
+
+// out[i] = scale * Σ_src in_src[rank_chunk + i]
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(512) castscale_rs_kernel(PeerPtrs in, TOut* __restrict__ out, long long chunk,
+                                                           long long chunk_offset, int nranks, int rank, float scale) {
+  constexpr int V = Vec16<TIn>::N;
+  const long long nvec = chunk / V;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc[k] = 0.f;
+    for (int s = 0; s < nranks; ++s) {
+      const int src = (rank + s) % nranks;  // start with the local bucket; peers in ring order
+      const Vec16<TIn> v = ld16(reinterpret_cast<const TIn*>(in.p[src]) + chunk_offset + i * V);
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[k] += to_f(v.v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) out[i * V + k] = from_f<TOut>(acc[k] * scale);
+  }
+  for (long long i = nvec * V + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunk;
+       i += (long long)gridDim.x * blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < nranks; ++s)
+      a += to_f(reinterpret_cast<const TIn*>(in.p[(rank + s) % nranks])[chunk_offset + i]);
+    out[i] = from_f<TOut>(a * scale);
+  }
+}
+
+// out[row, :] = Σ_src stage[src][row, :]; each block first makes sure all sources have published
+template <typename T>
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const T* __restrict__ stage, const unsigned int* flags,
+                                                        unsigned int epoch, T* __restrict__ out, long long numel,
+                                                        int nranks, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < nranks) {
+    if (!wait_flag_ge(flags + threadIdx.x, epoch, nullptr)) {
+      ok = 0;
+      if (status != nullptr) atomicExch(status, TB_ERR_WAIT_PEER);
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  constexpr int V = Vec16<T>::N;
+  const long long nvec = numel / V;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc[k] = 0.f;
+    for (int s = 0; s < nranks; ++s) {
+      const Vec16<T> v = ld16(stage + (long long)s * numel + i * V);
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[k] += to_f(v.v[k]);
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = from_f<T>(acc[k]);
+    st16(out + i * V, o);
+  }
+}
+
+}  // namespace
+
+// Write `value` into slot `slot` of the flag array of every rank (flag_ptrs[r] = that rank's array).
+TB_API int tb_signal(void* const* flag_ptrs, int nranks, int slot, unsigned int value, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS) return TB_ERR_ARG;
+  PeerPtrs f{};
+  for (int r = 0; r < nranks; ++r) f.p[r] = flag_ptrs[r];
+  signal_kernel<<<1, 32, 0, st>>>(f, slot, value, nranks);
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+// Wait until local flags[first .. first+count) have all reached `value` (bounded; reports through `status`).
+TB_API int tb_wait_flags(const unsigned int* flags, int first, int count, unsigned int value, int* status,
+                         cudaStream_t st) {
+  if (count < 1 || count > 32) return TB_ERR_ARG;
+  wait_flags_kernel<<<1, 32, 0, st>>>(flags, first, count, value, status);
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+// C[M,N] = concat_r(A_r)[M,K] · B[N,K]ᵀ where A_r = a_ptrs[r] is rank r's [m_shard, K] shard (K-major).
+// ready_flags: local array, slot r is set to >= epoch by rank r once its shard may be read.
+TB_API int tb_ag_gemm(void* const* a_ptrs, const void* B, void* C, int M, int N, int K, int m_shard, int b_mn,
+                      int dtype, int rank, int nranks, const unsigned int* ready_flags, unsigned int epoch,
+                      int* status, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || m_shard % BM || m_shard * nranks != M) return TB_ERR_ARG;
+  if ((K % 8) || (N % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  AMaps am;
+  CUtensorMap tb_;
+  for (int r = 0; r < nranks; ++r)
+    if (int rc = make_a_map(&am.m[r], a_ptrs[r], dtype, 0, (uint64_t)m_shard, (uint64_t)K, K)) return rc;
+  if (int rc = make_b_map(&tb_, B, dtype, b_mn, (uint64_t)N, (uint64_t)K, b_mn ? N : K)) return rc;
+  GemmParams p{};
+  p.mode = ALLGATHER; p.M = M; p.N = N; p.K = K; p.a_mn = 0; p.b_mn = b_mn; p.is_bf16 = dtype == 1;
+  p.ldc = N; p.C = C; p.status = status; p.rank = rank; p.nranks = nranks; p.m_shard = m_shard;
+  p.ready_flags = ready_flags; p.epoch = epoch;
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  return launch(am, tb_, p, tiles < sm_count() ? tiles : sm_count(), st);
+}
+
+// C[M,N] = A[M,K] · concat_r(B_r)[N,K]ᵀ where B_r = b_ptrs[r] is rank r's [n_shard, K] weight shard.
+TB_API int tb_ag_b_gemm(const void* A, void* const* b_ptrs, void* C, int M, int N, int K, int n_shard, int dtype,
+                        int rank, int nranks, const unsigned int* ready_flags, unsigned int epoch, int* status,
+                        cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || n_shard % BN || n_shard * nranks != N) return TB_ERR_ARG;
+  if ((K % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  AMaps am;
+  CUtensorMap ta;
+  for (int r = 0; r < nranks; ++r)
+    if (int rc = make_b_map(&am.m[r], b_ptrs[r], dtype, 0, (uint64_t)n_shard, (uint64_t)K, K)) return rc;
+  if (int rc = make_a_map(&ta, A, dtype, 0, (uint64_t)M, (uint64_t)K, K)) return rc;
+  GemmParams p{};
+  p.mode = ALLGATHER_B; p.M = M; p.N = N; p.K = K; p.is_bf16 = dtype == 1;
+  p.ldc = N; p.C = C; p.status = status; p.rank = rank; p.nranks = nranks; p.n_shard = n_shard;
+  p.ready_flags = ready_flags; p.epoch = epoch;
+  const int tiles = ((M + BM - 1) / BM) * (N / BN);
+  return launch(am, ta, p, tiles < sm_count() ? tiles : sm_count(), st);
+}
+
+// Partial product of this rank, scattered by rows: rows of owner d go to stage_ptrs[d] + [rank][m_shard][N].
+// peer_flags[d] + rank is released with `epoch` once all of this rank's tiles for d are stored.
+TB_API int tb_gemm_rs(const void* A, const void* B, void* const* stage_ptrs, void* const* peer_flags,
+                      unsigned int* tile_counters, int M, int N, int K, int m_shard, int b_mn, int dtype, int rank,
+                      int nranks, unsigned int epoch, int* status, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || m_shard % BM || m_shard * nranks != M) return TB_ERR_ARG;
+  if ((K % 8) || (N % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  AMaps am;
+  CUtensorMap tb_;
+  if (int rc = make_a_map(&am.m[0], A, dtype, 0, (uint64_t)M, (uint64_t)K, K)) return rc;
+  if (int rc = make_b_map(&tb_, B, dtype, b_mn, (uint64_t)N, (uint64_t)K, b_mn ? N : K)) return rc;
+  GemmParams p{};
+  p.mode = SCATTER; p.M = M; p.N = N; p.K = K; p.b_mn = b_mn; p.is_bf16 = dtype == 1;
+  p.ldc = N; p.C = nullptr; p.status = status; p.rank = rank; p.nranks = nranks; p.m_shard = m_shard;
+  p.epoch = epoch; p.tile_counters = tile_counters;
+  for (int r = 0; r < nranks; ++r) {
+    p.stage_ptrs[r] = stage_ptrs[r];
+    p.peer_flags[r] = reinterpret_cast<unsigned int*>(peer_flags[r]);
+  }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  return launch(am, tb_, p, tiles < sm_count() ? tiles : sm_count(), st);
+}
+
+// out[m_shard, N] = Σ_src stage[src]; waits (bounded) for flags[0..nranks) >= epoch first.
+TB_API int tb_rs_reduce(const void* stage, const unsigned int* flags, unsigned int epoch, void* out, long long numel,
+                        int nranks, int dtype, int* status, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || numel <= 0) return TB_ERR_ARG;
+  long long grid = (numel / 8 + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (grid < 1) grid = 1;
+  if (dtype == 1)
+    rs_reduce_kernel<__nv_bfloat16><<<(int)grid, 256, 0, st>>>((const __nv_bfloat16*)stage, flags, epoch,
+                                                               (__nv_bfloat16*)out, numel, nranks, status);
+  else if (dtype == 2)
+    rs_reduce_kernel<__half><<<(int)grid, 256, 0, st>>>((const __half*)stage, flags, epoch, (__half*)out, numel,
+                                                        nranks, status);
+  else
+    return TB_ERR_ARG;
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+// Gradient reduce-scatter with cast and scale.  in_ptrs[r]: rank r's full bucket (numel = chunk * nranks);
+// out: this rank's chunk.  in_dtype: 0 fp32 / 1 bf16; out_dtype: 0 fp32 / 1 bf16.  Callers order this after
+// a flag exchange that says every bucket is complete.
+TB_API int tb_castscale_rs(void* const* in_ptrs, void* out, long long chunk, int rank, int nranks, float scale,
+                           int in_dtype, int out_dtype, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || chunk <= 0) return TB_ERR_ARG;
+  PeerPtrs in{};
+  for (int r = 0; r < nranks; ++r) in.p[r] = in_ptrs[r];
+  long long grid = (chunk / 8 + 511) / 512;
+  if (grid > 148 * 4) grid = 148 * 4;
+  if (grid < 1) grid = 1;
+  const long long off = chunk * rank;
+  if ((off * (in_dtype == 0 ? 4 : 2)) % 16 != 0) return TB_ERR_ARG;
+#define TB_RS(TI, TO) castscale_rs_kernel<TI, TO><<<(int)grid, 512, 0, st>>>(in, (TO*)out, chunk, off, nranks, rank, scale)
+  if (in_dtype == 1 && out_dtype == 0) TB_RS(__nv_bfloat16, float);
+  else if (in_dtype == 1 && out_dtype == 1) TB_RS(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == 0 && out_dtype == 0) TB_RS(float, float);
+  else if (in_dtype == 0 && out_dtype == 1) TB_RS(float, __nv_bfloat16);
+  else return TB_ERR_ARG;
+#undef TB_RS
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+namespace {
+__global__ void put_kernel(PeerPtrs dst, const unsigned int* __restrict__ src, long long nwords, int nranks) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nwords;
+       i += (long long)gridDim.x * blockDim.x) {
+    const unsigned int v = src[i];
+    for (int r = 0; r < nranks; ++r) reinterpret_cast<unsigned int*>(dst.p[r])[i] = v;
+  }
+}
+}  // namespace
+
+// Copy `nbytes` (multiple of 4) from local `src` to dst_ptrs[r] on every rank (small control data: counts, sizes).
+TB_API int tb_put(void* const* dst_ptrs, int nranks, const void* src, long long nbytes, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || nbytes % 4) return TB_ERR_ARG;
+  if (nbytes == 0) return 0;
+  PeerPtrs d{};
+  for (int r = 0; r < nranks; ++r) d.p[r] = dst_ptrs[r];
+  long long grid = (nbytes / 4 + 255) / 256;
+  if (grid > 64) grid = 64;
+  put_kernel<<<(int)grid, 256, 0, st>>>(d, (const unsigned int*)src, nbytes / 4, nranks);
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}

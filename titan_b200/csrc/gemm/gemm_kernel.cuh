@@ -1,0 +1,236 @@
+// The kernel body shared by every GEMM entry point (see gemm_core.cuh for the design).
+#pragma once
+
+#include "gemm_core.cuh"
+
+namespace tbg {
+
+// The kernel is compiled once (in gemm_bf16.cu, which defines TBG_DEFINE_KERNEL); other files call launch().
+int launch(const AMaps& am, const CUtensorMap& tb_, const GemmParams& p, int grid, cudaStream_t st);
+
+#ifdef TBG_DEFINE_KERNEL
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint64_t* full_bar = bars;                     // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES]
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  int* s_offs = reinterpret_cast<int*>(bars) + 64;  // 256 B after the barrier block: [num_groups + 1]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (p.mode == GROUPED_M || p.mode == GROUPED_K) {
+    for (int i = threadIdx.x; i <= p.num_groups; i += NUM_THREADS) s_offs[i] = i == 0 ? 0 : p.offs[i - 1];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int num_tiles = total_tiles(p, s_offs);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      unsigned int src_ready = 1u << p.rank;  // ALLGATHER: sources whose flag has been seen
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const Tile tl = get_tile(p, s_offs, t);
+        if ((p.mode == ALLGATHER || p.mode == ALLGATHER_B) && !(src_ready & (1u << tl.src))) {
+          if (!wait_flag_ge(p.ready_flags + tl.src, p.epoch, abort_flag)) {
+            if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER); }
+            break;
+          }
+          src_ready |= 1u << tl.src;
+        }
+        // the gathered operand comes from the owner's map; the other operand from the single local map
+        const CUtensorMap* ta = p.mode == ALLGATHER_B ? &tmap_b : &amaps.m[tl.src];
+        const CUtensorMap* tbm = p.mode == ALLGATHER_B ? &amaps.m[tl.src] : &tmap_b;
+        for (int kb = 0; kb < tl.kblocks; ++kb) {
+          if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
+            ok = false; break;
+          }
+          mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* sa = smem_a + stage * A_STAGE_BYTES;
+          uint8_t* sb = smem_b + stage * B_STAGE_BYTES;
+          const int k0 = tl.k0 + kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(sa, ta, &full_bar[stage], k0, tl.a_row);  // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)  // box {64 m, 64 k}, 8 KB each
+              tma_load_2d(sa + j * 8192, ta, &full_bar[stage], tl.a_row + j * 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, tbm, &full_bar[stage], k0, (int)(tl.b_off + tl.n0));  // box {64 k, 256 n}
+          } else {
+            const int krow = p.mode == GROUPED_K ? k0 : (int)(tl.b_off + k0);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, tbm, &full_bar[stage], tl.n0 + j * 64, krow);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, BN, p.is_bf16 != 0, p.a_mn != 0, p.b_mn != 0);
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      int acc = 0; uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const Tile tl = get_tile(p, s_offs, t);
+        if (!wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_EMPTY); }
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < tl.kblocks; ++kb) {
+          if (!wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA); }
+            ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+          const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major : rows of 128 B, 8-row swizzle atoms 1024 B apart (SBO); a K step of 16 elements = +32 B
+            // MN-major: 64-element (128 B) runs along M/N, K rows 128 B apart, 8-row atoms 1024 B apart (SBO),
+            //           next 64-wide M/N block 8192 B further (LBO); a K step of 16 rows = +2048 B
+            const uint64_t da = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024, 2)
+                                       : make_smem_desc(sa + k * 32, 16, 1024, 2);
+            const uint64_t db = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024, 2)
+                                       : make_smem_desc(sb + k * 32, 16, 1024, 2);
+            umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full_bar[acc]);  // with no MMA issued (empty group) this arrives at once
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0; uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const Tile tl = get_tile(p, s_offs, t);
+      bool ok = wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0 && *abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL); }
+        break;
+      }
+      tc_fence_after();
+      const int row = tl.m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      // where this tile's rows go
+      void* cbase = p.C;
+      long long ld = p.ldc;
+      int out_row = row;
+      int dst_rank = -1;
+      if (p.mode == GROUPED_K) {
+        cbase = p.out_fp32 ? (void*)(reinterpret_cast<float*>(p.C) + (long long)tl.group * p.c_group_stride)
+                           : (void*)(reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)tl.group * p.c_group_stride);
+      } else if (p.mode == SCATTER) {
+        dst_rank = tl.m0 / p.m_shard;
+        cbase = p.stage_ptrs[dst_rank];
+        ld = p.N;
+        out_row = p.rank * p.m_shard + (row - dst_rank * p.m_shard);  // slot [src = this rank][local row]
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (tl.kblocks == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;  // empty group: nothing was accumulated
+        }
+        const int col = tl.n0 + c * 32;
+        if (row < tl.row_end && col < p.N) store_row32(p, cbase, ld, out_row, col, p.N, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+
+      if (p.mode == SCATTER) {
+        // count finished tiles per owner; whoever completes the last one publishes "my partial is there"
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+        if (warp == 2 && lane == 0) {
+          const int tiles_per_owner = (p.m_shard / BM) * ((p.N + BN - 1) / BN);
+          const unsigned int done = atomicAdd(p.tile_counters + dst_rank, 1u) + 1u;
+          if (done == (unsigned int)tiles_per_owner) {
+            p.tile_counters[dst_rank] = 0;  // ready for the next launch
+            __threadfence_system();
+            st_release_sys(p.peer_flags[dst_rank] + p.rank, p.epoch);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int launch(const AMaps& am, const CUtensorMap& tb_, const GemmParams& p, int grid, cudaStream_t st) {
+  TB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(am, tb_, p);
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+#endif  // TBG_DEFINE_KERNEL
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 148;
+  }
+  return n;
+}
+
+inline int make_a_map(CUtensorMap* out, const void* A, int dtype, int a_mn, uint64_t m, uint64_t k, long long lda) {
+  const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (!a_mn) return tbh::make_tmap_2d(out, A, dt, 2, m, k, (uint64_t)lda * 2, BM, BK, 3);
+  return tbh::make_tmap_2d(out, A, dt, 2, k, m, (uint64_t)lda * 2, 64, 64, 3);
+}
+inline int make_b_map(CUtensorMap* out, const void* B, int dtype, int b_mn, uint64_t n, uint64_t k, long long ldb) {
+  const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (!b_mn) return tbh::make_tmap_2d(out, B, dt, 2, n, k, (uint64_t)ldb * 2, BN, BK, 3);
+  return tbh::make_tmap_2d(out, B, dt, 2, k, n, (uint64_t)ldb * 2, 64, 64, 3);
+}
+
+}  // namespace tbg

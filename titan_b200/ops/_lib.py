@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
 
 import torch
 
@@ -49,6 +49,23 @@ def _declare(L) -> None:
         "tb_cross_entropy_fwd": [P, P, P, P, LL, I, LL, LL, I, P, P],
         "tb_cross_entropy_bwd": [P, P, P, P, P, LL, I, LL, LL, I, P],
         "tb_gemm_bf16": [P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P],
+        "tb_grouped_gemm_m": [P, P, P, P, I, I, I, I, I, I, P, P],
+        "tb_grouped_gemm_k": [P, P, P, P, I, I, I, I, I, I, P, P],
+        "tb_router_topk": [P, P, P, P, P, P, P, I, I, I, I, I, F, P, P],
+        "tb_moe_plan_blocks": [I],
+        "tb_moe_plan": [P, I, I, P, P, P, P, P, P, P, I, I, P, P],
+        "tb_moe_gather": [P, P, P, P, I, I, I, I, LL, I, P],
+        "tb_moe_zero_pad": [P, P, P, P, I, I, LL, I, P],
+        "tb_moe_combine": [P, I, P, P, P, P, I, I, I, LL, I, P],
+        "tb_moe_pair_dot": [P, I, P, P, P, I, I, I, LL, I, P],
+        "tb_signal": [P, I, I, c_uint, P],
+        "tb_wait_flags": [P, I, I, c_uint, P, P],
+        "tb_ag_gemm": [P, P, P, I, I, I, I, I, I, I, I, P, c_uint, P, P],
+        "tb_ag_b_gemm": [P, P, P, I, I, I, I, I, I, I, P, c_uint, P, P],
+        "tb_gemm_rs": [P, P, P, P, P, I, I, I, I, I, I, I, I, c_uint, P, P],
+        "tb_rs_reduce": [P, P, c_uint, P, LL, I, I, P, P],
+        "tb_castscale_rs": [P, P, LL, I, I, F, I, I, P],
+        "tb_put": [P, I, P, LL, P],
     }
     for name, args in sig.items():
         fn = getattr(L, name, None)

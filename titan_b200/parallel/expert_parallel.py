@@ -128,25 +128,18 @@ def _unpermute_autograd(x, idx):
 
 
 class FusedExpertParallel(ExpertParallel):
-    """Same sharding; tokens move through the peer-memory dispatch / combine kernels."""
+    """Same sharding as `ExpertParallel`; tokens move through the peer-memory dispatch / combine kernels.
 
-    def _token_dispatch(self, mod, inputs, device_mesh):
-        from titan_b200.ops import moe_comm
+    The fused MoE layer (`b200_moe_dispatch`) drives the exchange itself from its device-side routing plan, so
+    this style only shards the expert weights and records the mesh on the module.  Experts that were not
+    converted keep the NCCL hooks of the parent class."""
 
-        routed_input, num_tokens_per_expert = inputs
-        group = device_mesh.get_group()
-        if not routed_input.is_cuda or is_fake_process_group(group):
-            return super()._token_dispatch(mod, inputs, device_mesh)
-        out, counts_local, self._ticket = moe_comm.dispatch(routed_input, num_tokens_per_expert, group)
-        return out, counts_local
-
-    def _token_combine(self, mod, routed_output, device_mesh):
-        from titan_b200.ops import moe_comm
-
-        group = device_mesh.get_group()
-        if not routed_output.is_cuda or is_fake_process_group(group):
-            return super()._token_combine(mod, routed_output, device_mesh)
-        return moe_comm.combine(routed_output, self._ticket, group)
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        if not hasattr(module, "forward_padded"):
+            return super()._apply(module, device_mesh)
+        module = distribute_module(module, device_mesh, partition_fn=self._partition_fn)
+        module.ep_mesh = device_mesh
+        return module
 
 
 class TensorParallel(ParallelStyle):
