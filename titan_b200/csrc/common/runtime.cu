@@ -14,3 +14,11 @@ extern "C" __attribute__((visibility("default"))) void tb_note_launch(int n) { g
 TB_API long long tb_launch_count() { return g_launches.load(); }
 TB_API int tb_reset_launch_count() { g_launches.store(0); return 0; }
 TB_API int tb_version() { return 1; }
+
+// Make `device` current for the calling thread in this library's CUDA runtime (autograd worker threads
+// start without a context; multi-GPU processes must never fall back to device 0).
+TB_API int tb_bind_device(int device) {
+  TB_CUDA_CHECK(cudaSetDevice(device));
+  TB_CUDA_CHECK(cudaFree(nullptr));
+  return 0;
+}

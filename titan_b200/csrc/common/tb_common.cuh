@@ -304,16 +304,13 @@ inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   }
   return fn;
 }
-// Driver calls (tensor-map encoding) need a current context on the calling thread.  Threads that have
-// not made a runtime call yet (autograd worker threads) have none: bind the device that owns `ptr`.
-inline int ensure_context(const void* ptr) {
+// Driver calls (tensor-map encoding) need a current context on the calling thread.  The Python layer binds
+// every thread that enters the library to its device (`tb_bind_device`); this is the last-resort fallback for
+// foreign callers: it initialises the runtime's current device without ever switching to another device
+// (the address of an operand says nothing about the caller's device: it may live on a peer GPU).
+inline int ensure_context(const void*) {
   static thread_local bool bound = false;
   if (bound) return 0;
-  cudaPointerAttributes attr;
-  int dev = 0;
-  if (cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice) dev = attr.device;
-  else (void)cudaGetLastError();
-  TB_CUDA_CHECK(cudaSetDevice(dev));
   TB_CUDA_CHECK(cudaFree(nullptr));
   bound = true;
   return 0;

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
 
 import torch
@@ -119,7 +120,17 @@ def check(rc: int, what: str) -> None:
     raise KernelError(f"{what}: {_STATUS_TEXT.get(rc, f'error {rc}')}")
 
 
+_TLS = threading.local()
+
+
 def stream_ptr() -> int:
+    """Current stream handle; also binds the calling thread to the current device inside the library."""
+    dev = torch.cuda.current_device()
+    if getattr(_TLS, "device", None) != dev:
+        fn = lib().tb_bind_device
+        fn.argtypes, fn.restype = [c_int], c_int
+        check(fn(dev), "bind_device")
+        _TLS.device = dev
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -47,7 +47,11 @@ class SymmWorkspace:
         self.buf.zero_()
         torch.cuda.synchronize(self.device)
         self.handle = symm.rendezvous(self.buf, group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # buffer_ptrs are allocation bases; the tensor may sit at an offset inside the allocation
+        off = self.buf.data_ptr() - int(self.handle.buffer_ptrs[self.rank])
+        if off < 0 or off + self.nbytes > int(self.handle.buffer_size):
+            raise RuntimeError("symmetric buffer does not lie inside the rendezvoused allocation")
+        self.ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
         self.flags = self.buf[:FLAG_BYTES].view(torch.int32)
         self._epochs: dict[int, int] = {}
         dist.barrier(group=group)
