@@ -181,3 +181,75 @@ TB_API int tb_rmsnorm_bwd(const void* g, const void* x, const void* w, const flo
 #undef TB_BWD
   return TB_ERR_ARG;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant (declaration and contract: rmsnorm_noalloc.h).
+#include "rmsnorm_noalloc.h"
+
+#include <mutex>
+
+// Scratch for the per-CTA partial sums of dw.  In host code this name is only a handle for the symbol, not a
+// device address: the address is looked up per device with cudaGetSymbolAddress and handed to the kernel.
+static __device__ __align__(256) float g_rmsnorm_noalloc_scratch[TB_RMSNORM_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device; resolved on the first call per device.
+int noalloc_scratch_for_current_device(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TB_NOALLOC_ERR_SYMBOL;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_rmsnorm_noalloc_scratch) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return TB_NOALLOC_ERR_SYMBOL;
+    }
+    g_noalloc_scratch_ptr[dev] = p;
+  }
+  *out = g_noalloc_scratch_ptr[dev];
+  return 0;
+}
+
+template <typename T>
+int noalloc_launch(const void* g, const void* x, const void* w, const float* rstd, void* dx, void* dw, float* scratch,
+                   int rows, int dim, cudaStream_t st) {
+  if (dim % Vec16<T>::N != 0) return TB_NOALLOC_ERR_SHAPE;
+  int grid = (rows + 3) / 4;  // four warps (rows) per CTA
+  if (grid > TB_RMSNORM_NOALLOC_MAX_PARTIAL_ROWS) grid = TB_RMSNORM_NOALLOC_MAX_PARTIAL_ROWS;
+  // grid * dim <= MAX_PARTIAL_ROWS * MAX_DIM floats: the partial rows always fit the static array
+  return bwd_launch<T, 4>(g, x, w, rstd, dx, dw, scratch, grid, rows, dim, st);
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int tb_rmsnorm_bwd_noalloc(const void* g, const void* x,
+                                                                             const void* w, const float* rstd,
+                                                                             void* dx, void* dw, int rows, int dim,
+                                                                             int dtype, cudaStream_t stream) {
+  if (dim > TB_RMSNORM_NOALLOC_MAX_DIM) return TB_NOALLOC_ERR_TOO_LARGE;
+  if (rows < 1 || dim < 1 || dtype < 0 || dtype > 2) return TB_NOALLOC_ERR_SHAPE;
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch_for_current_device(&scratch)) return rc;
+  switch (dtype) {
+    case 0: return noalloc_launch<float>(g, x, w, rstd, dx, dw, scratch, rows, dim, stream);
+    case 1: return noalloc_launch<__nv_bfloat16>(g, x, w, rstd, dx, dw, scratch, rows, dim, stream);
+    default: return noalloc_launch<__half>(g, x, w, rstd, dx, dw, scratch, rows, dim, stream);
+  }
+}
+
+extern "C" __attribute__((visibility("default"))) const char* tb_rmsnorm_bwd_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case TB_NOALLOC_ERR_TOO_LARGE:
+      return "dim exceeds TB_RMSNORM_NOALLOC_MAX_DIM (8192): the built-in scratch array cannot hold the partial sums";
+    case TB_NOALLOC_ERR_SHAPE:
+      return "invalid shape or dtype: rows >= 1, dim a multiple of the 16-byte vector, dtype in {0, 1, 2}";
+    case TB_NOALLOC_ERR_SYMBOL:
+      return "could not obtain the device address of the built-in scratch array on the current device";
+    default:
+      return code >= 1000 ? "CUDA runtime error (code - 1000)" : "unknown error";
+  }
+}
