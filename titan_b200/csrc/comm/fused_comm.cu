@@ -128,41 +128,60 @@ TB_API int tb_wait_flags(const unsigned int* flags, int first, int count, unsign
 
 // C[M,N] = concat_r(A_r)[M,K] · B[N,K]ᵀ where A_r = a_ptrs[r] is rank r's [m_shard, K] shard (K-major).
 // ready_flags: local array, slot r is set to >= epoch by rank r once its shard may be read.
-TB_API int tb_ag_gemm(void* const* a_ptrs, const void* B, void* C, int M, int N, int K, int m_shard, int b_mn,
-                      int dtype, int rank, int nranks, const unsigned int* ready_flags, unsigned int epoch,
-                      int* status, cudaStream_t st) {
+// gathered: local [M, K] buffer that receives the remote shards (each crosses NVLink exactly once; the rows of
+// this rank's own shard are not written).  chunk_flags: local zero-initialised uint32 [M / 128], reused across
+// calls with increasing epochs.
+TB_API int tb_ag_gemm(void* const* a_ptrs, const void* B, void* C, void* gathered, unsigned int* chunk_flags, int M,
+                      int N, int K, int m_shard, int b_mn, int dtype, int rank, int nranks,
+                      const unsigned int* ready_flags, unsigned int epoch, int* status, cudaStream_t st) {
   if (nranks < 1 || nranks > MAX_RANKS || m_shard % BM || m_shard * nranks != M) return TB_ERR_ARG;
   if ((K % 8) || (N % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
   AMaps am;
   CUtensorMap tb_;
-  for (int r = 0; r < nranks; ++r)
-    if (int rc = make_a_map(&am.m[r], a_ptrs[r], dtype, 0, (uint64_t)m_shard, (uint64_t)K, K)) return rc;
+  CMaps cm;
+  if (int rc = make_a_map(&am.m[0], a_ptrs[rank], dtype, 0, (uint64_t)m_shard, (uint64_t)K, K)) return rc;
+  if (int rc = make_a_map(&am.m[1], gathered, dtype, 0, (uint64_t)M, (uint64_t)K, K)) return rc;
   if (int rc = make_b_map(&tb_, B, dtype, b_mn, (uint64_t)N, (uint64_t)K, b_mn ? N : K)) return rc;
+  if (int rc = make_c_map(&cm.m[0], C, dtype, (uint64_t)M, (uint64_t)N, N)) return rc;
   GemmParams p{};
   p.mode = ALLGATHER; p.M = M; p.N = N; p.K = K; p.a_mn = 0; p.b_mn = b_mn; p.is_bf16 = dtype == 1;
   p.ldc = N; p.C = C; p.status = status; p.rank = rank; p.nranks = nranks; p.m_shard = m_shard;
-  p.ready_flags = ready_flags; p.epoch = epoch;
+  p.ready_flags = ready_flags; p.epoch = epoch; p.tma_store = 1;
+  for (int r = 0; r < nranks; ++r) p.peer_src[r] = a_ptrs[r];
+  p.gather_dst = gathered; p.chunk_flags = chunk_flags;
+  p.num_copiers = nranks > 1 ? NUM_COPIERS : 0;
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
-  return launch(am, tb_, p, tiles < sm_count() ? tiles : sm_count(), st);
+  int workers = sm_count() - p.num_copiers;
+  if (tiles < workers) workers = tiles;
+  // copiers and GEMM CTAs wait on one another: all of them must be resident, i.e. the grid fits the SMs
+  return launch(am, tb_, cm, p, workers + p.num_copiers, st);
 }
 
 // C[M,N] = A[M,K] · concat_r(B_r)[N,K]ᵀ where B_r = b_ptrs[r] is rank r's [n_shard, K] weight shard.
-TB_API int tb_ag_b_gemm(const void* A, void* const* b_ptrs, void* C, int M, int N, int K, int n_shard, int dtype,
-                        int rank, int nranks, const unsigned int* ready_flags, unsigned int epoch, int* status,
-                        cudaStream_t st) {
+// gathered: local [N, K] buffer for the remote weight shards; chunk_flags: local uint32 [N / 256].
+TB_API int tb_ag_b_gemm(const void* A, void* const* b_ptrs, void* C, void* gathered, unsigned int* chunk_flags, int M,
+                        int N, int K, int n_shard, int dtype, int rank, int nranks,
+                        const unsigned int* ready_flags, unsigned int epoch, int* status, cudaStream_t st) {
   if (nranks < 1 || nranks > MAX_RANKS || n_shard % BN || n_shard * nranks != N) return TB_ERR_ARG;
   if ((K % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
   AMaps am;
   CUtensorMap ta;
-  for (int r = 0; r < nranks; ++r)
-    if (int rc = make_b_map(&am.m[r], b_ptrs[r], dtype, 0, (uint64_t)n_shard, (uint64_t)K, K)) return rc;
+  CMaps cm;
+  if (int rc = make_b_map(&am.m[0], b_ptrs[rank], dtype, 0, (uint64_t)n_shard, (uint64_t)K, K)) return rc;
+  if (int rc = make_b_map(&am.m[1], gathered, dtype, 0, (uint64_t)N, (uint64_t)K, K)) return rc;
   if (int rc = make_a_map(&ta, A, dtype, 0, (uint64_t)M, (uint64_t)K, K)) return rc;
+  if (int rc = make_c_map(&cm.m[0], C, dtype, (uint64_t)M, (uint64_t)N, N)) return rc;
   GemmParams p{};
   p.mode = ALLGATHER_B; p.M = M; p.N = N; p.K = K; p.is_bf16 = dtype == 1;
   p.ldc = N; p.C = C; p.status = status; p.rank = rank; p.nranks = nranks; p.n_shard = n_shard;
-  p.ready_flags = ready_flags; p.epoch = epoch;
+  p.ready_flags = ready_flags; p.epoch = epoch; p.tma_store = 1;
+  for (int r = 0; r < nranks; ++r) p.peer_src[r] = b_ptrs[r];
+  p.gather_dst = gathered; p.chunk_flags = chunk_flags;
+  p.num_copiers = nranks > 1 ? NUM_COPIERS : 0;
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
-  return launch(am, ta, p, tiles < sm_count() ? tiles : sm_count(), st);
+  int workers = sm_count() - p.num_copiers;
+  if (tiles < workers) workers = tiles;
+  return launch(am, ta, cm, p, workers + p.num_copiers, st);
 }
 
 // Partial product of this rank, scattered by rows: rows of owner d go to stage_ptrs[d] + [rank][m_shard][N].
@@ -180,12 +199,16 @@ TB_API int tb_gemm_rs(const void* A, const void* B, void* const* stage_ptrs, voi
   p.mode = SCATTER; p.M = M; p.N = N; p.K = K; p.b_mn = b_mn; p.is_bf16 = dtype == 1;
   p.ldc = N; p.C = nullptr; p.status = status; p.rank = rank; p.nranks = nranks; p.m_shard = m_shard;
   p.epoch = epoch; p.tile_counters = tile_counters;
+  CMaps cm;
   for (int r = 0; r < nranks; ++r) {
     p.stage_ptrs[r] = stage_ptrs[r];
     p.peer_flags[r] = reinterpret_cast<unsigned int*>(peer_flags[r]);
+    // every owner's staging area [nranks * m_shard, N]: whole tiles go there as bulk tensor stores
+    if (int rc = make_c_map(&cm.m[r], stage_ptrs[r], dtype, (uint64_t)nranks * m_shard, (uint64_t)N, N)) return rc;
   }
+  p.tma_store = 1;
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
-  return launch(am, tb_, p, tiles < sm_count() ? tiles : sm_count(), st);
+  return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
 }
 
 // out[m_shard, N] = Σ_src stage[src]; waits (bounded) for flags[0..nranks) >= epoch first.

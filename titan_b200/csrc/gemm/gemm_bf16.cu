@@ -41,10 +41,15 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   if (int rc = make_b_map(&tb_, B, dtype, b_mn, (uint64_t)N, (uint64_t)K, ldb)) return rc;
   GemmParams p;
   fill_common(p, PLAIN, M, N, K, a_mn, b_mn, dtype, out_fp32, accumulate, ldc, C, status);
+  CMaps cm;
+  if (!out_fp32 && !accumulate) {
+    if (int rc = make_c_map(&cm.m[0], C, dtype, (uint64_t)M, (uint64_t)N, ldc)) return rc;
+    p.tma_store = 1;
+  }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  return launch(am, tb_, p, grid, st);
+  return launch(am, tb_, cm, p, grid, st);
 }
 
 // A: [rows_cap, K] K-major.  B: b_mn = 0 → [G, N, K];  b_mn = 1 → [G, K, N].  C: [rows_cap, N].
@@ -66,7 +71,10 @@ TB_API int tb_grouped_gemm_m(const void* A, const void* B, void* C, const int* o
   GemmParams p;
   fill_common(p, GROUPED_M, rows_cap, N, K, 0, b_mn, dtype, 0, 0, N, C, status);
   p.num_groups = G; p.offs = offs; p.b_group_rows = b_mn ? K : N;
-  return launch(am, tb_, p, sm_count(), st);
+  CMaps cm;
+  if (int rc = make_c_map(&cm.m[0], C, dtype, (uint64_t)rows_cap, (uint64_t)N, N)) return rc;
+  p.tma_store = 1;  // segments are 128-row aligned: whole tiles always belong to one expert
+  return launch(am, tb_, cm, p, sm_count(), st);
 }
 
 // dW[g] [M, N] = A[rows of g, M]ᵀ · B[rows of g, N]   (A: [rows_cap, M], B: [rows_cap, N], both row-major)
@@ -83,6 +91,11 @@ TB_API int tb_grouped_gemm_k(const void* A, const void* B, void* C, const int* o
   GemmParams p;
   fill_common(p, GROUPED_K, M, N, rows_cap, 1, 1, dtype, out_fp32, 0, N, C, status);
   p.num_groups = G; p.offs = offs; p.c_group_stride = (long long)M * N;
+  CMaps cm;
+  if (!out_fp32 && M % BM == 0) {  // otherwise a tile's tail rows would land in the next group's matrix
+    if (int rc = make_c_map(&cm.m[0], C, dtype, (uint64_t)G * M, (uint64_t)N, N)) return rc;
+    p.tma_store = 1;
+  }
   const int tiles = G * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return launch(am, tb_, p, tiles < sm_count() ? tiles : sm_count(), st);
+  return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
 }

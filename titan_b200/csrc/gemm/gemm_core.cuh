@@ -36,8 +36,10 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int MAX_GROUPS = 256;
 constexpr int MAX_RANKS = 8;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/ +
-                           (MAX_GROUPS + 1) * 4;
+constexpr int C_STAGE_BYTES = 32 * 1024;    // epilogue staging: half an output tile (128 x 128 x 2 B)
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + C_STAGE_BYTES + 1024 /*align*/ +
+                           256 /*barriers*/ + (MAX_GROUPS + 1) * 4;
+constexpr int NUM_COPIERS = 16;             // CTAs that pull remote shards into local memory (gather modes)
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;
@@ -67,6 +69,16 @@ struct GemmParams {
   void* stage_ptrs[MAX_RANKS];          // SCATTER: staging buffer base on every rank: [src][m_shard][N]
   unsigned int* peer_flags[MAX_RANKS];  // SCATTER: flag array [nranks] on every rank (slot = source rank)
   unsigned int* tile_counters;          // SCATTER: [nranks] local counters of finished tiles per owner
+  int tma_store;                        // epilogue stores whole tiles with TMA (16-bit output, no accumulate)
+  // gather modes: copier CTAs bring every remote shard into `gather_dst` exactly once
+  const void* peer_src[MAX_RANKS];      // shard base on every rank (peer-mapped)
+  void* gather_dst;                     // local [nranks * shard_rows, K] buffer
+  unsigned int* chunk_flags;            // local [num chunks]; chunk c holds `epoch` once it has been copied
+  int num_copiers;
+};
+
+struct CMaps {
+  CUtensorMap m[MAX_RANKS];
 };
 
 struct AMaps {
@@ -82,6 +94,7 @@ struct Tile {
   int k0, kblocks;   // contraction start (elements) and number of 64-wide blocks
   int row_end;       // stores are masked to rows < row_end
   int group;
+  int chunk;         // gather modes: index of the gathered operand's tile row (copier hand-off flag)
 };
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
@@ -125,6 +138,29 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
   }
 }
 
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded spin on a flag written by another CTA of this GPU
+__device__ __forceinline__ bool wait_local_flag_ge(const unsigned int* flag, unsigned int want,
+                                                   volatile int* abort_flag) {
+  if ((int)(ld_acquire_gpu(flag) - want) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    if ((int)(ld_acquire_gpu(flag) - want) >= 0) return true;
+    if ((++it & 15u) == 0u) {
+      if (abort_flag != nullptr && *abort_flag != 0) return false;
+      if (globaltimer_ns() - t0 > WAIT_NS) return false;
+    }
+  }
+}
+
 __device__ __forceinline__ int total_tiles(const GemmParams& p, const int* s_offs) {
   const int num_n = (p.N + BN - 1) / BN;
   if (p.mode == GROUPED_M) return (s_offs[p.num_groups] / BM) * num_n;
@@ -135,7 +171,7 @@ __device__ __forceinline__ int total_tiles(const GemmParams& p, const int* s_off
 // s_offs: [num_groups + 1] with s_offs[0] = 0 (shared memory copy of the cumulative offsets)
 __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int* s_offs, int t) {
   Tile tl;
-  tl.valid = 1; tl.src = 0; tl.b_off = 0; tl.k0 = 0; tl.kblocks = (p.K + BK - 1) / BK; tl.group = 0;
+  tl.valid = 1; tl.src = 0; tl.chunk = 0; tl.b_off = 0; tl.k0 = 0; tl.kblocks = (p.K + BK - 1) / BK; tl.group = 0;
   const int num_n = (p.N + BN - 1) / BN;
   if (p.mode == GROUPED_M) {
     const int mt = t / num_n, nt = t - mt * num_n;
@@ -168,13 +204,16 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int* s_offs,
     const int per = p.m_shard / BM;
     mt = (mt + p.rank * per) % num_m;
     tl.src = (mt * BM) / p.m_shard;
-    tl.a_row = mt * BM - tl.src * p.m_shard;
+    // own shard: read in place (map 0); remote shards: read the local gathered copy (map 1, global rows)
+    tl.a_row = tl.src == p.rank ? mt * BM - tl.src * p.m_shard : mt * BM;
+    tl.chunk = mt;
   } else if (p.mode == ALLGATHER_B) {
     const int per = p.n_shard / BN;
     const int num_nt = (p.N + BN - 1) / BN;
     nt = (nt + p.rank * per) % num_nt;
     tl.src = (nt * BN) / p.n_shard;
-    tl.b_off = -(long long)tl.src * p.n_shard;  // row inside the owner's shard = n0 + b_off
+    tl.b_off = tl.src == p.rank ? -(long long)tl.src * p.n_shard : 0;  // own shard in place, else gathered copy
+    tl.chunk = nt;
     tl.a_row = mt * BM;
   } else if (p.mode == SCATTER) {
     // tiles owned by this rank come last (they need no transfer)

@@ -6,17 +6,52 @@
 namespace tbg {
 
 // The kernel is compiled once (in gemm_bf16.cu, which defines TBG_DEFINE_KERNEL); other files call launch().
-int launch(const AMaps& am, const CUtensorMap& tb_, const GemmParams& p, int grid, cudaStream_t st);
+int launch(const AMaps& am, const CUtensorMap& tb_, const CMaps& cm, const GemmParams& p, int grid, cudaStream_t st);
 
 #ifdef TBG_DEFINE_KERNEL
+
+// Copier role of the gather modes: pull remote shards into local memory once, chunk by chunk, and hand each
+// chunk to the GEMM CTAs through a local flag.  Chunks are visited in ring order starting at the next rank.
+__device__ __forceinline__ void copier_role(const GemmParams& p, volatile int* abort_flag) {
+  const int chunk_rows = p.mode == ALLGATHER ? BM : BN;
+  const int shard_rows = p.mode == ALLGATHER ? p.m_shard : p.n_shard;
+  const int per = shard_rows / chunk_rows;
+  const int remote_chunks = (p.nranks - 1) * per;
+  const long long chunk_vec = (long long)chunk_rows * p.K * 2 / 16;  // 16-byte vectors per chunk
+  __shared__ int s_ok;
+  for (int idx = blockIdx.x; idx < remote_chunks; idx += p.num_copiers) {
+    const int d = idx / per + 1, within = idx - (d - 1) * per;
+    const int src = (p.rank + d) % p.nranks;
+    if (threadIdx.x == 0) {
+      s_ok = wait_flag_ge(p.ready_flags + src, p.epoch, abort_flag) ? 1 : 0;
+      if (!s_ok && p.status) atomicExch(p.status, TB_ERR_WAIT_PEER);
+    }
+    __syncthreads();
+    if (!s_ok) return;  // GEMM CTAs time out on the chunk flag and report as well
+    const uint4* from = reinterpret_cast<const uint4*>(p.peer_src[src]) + (long long)within * chunk_vec;
+    uint4* to = reinterpret_cast<uint4*>(p.gather_dst) + ((long long)src * per + within) * chunk_vec;
+    long long i = threadIdx.x;
+    for (; i + 3LL * NUM_THREADS < chunk_vec; i += 4LL * NUM_THREADS) {  // four loads in flight per thread
+      const uint4 v0 = from[i], v1 = from[i + NUM_THREADS], v2 = from[i + 2 * NUM_THREADS],
+                  v3 = from[i + 3 * NUM_THREADS];
+      to[i] = v0; to[i + NUM_THREADS] = v1; to[i + 2 * NUM_THREADS] = v2; to[i + 3 * NUM_THREADS] = v3;
+    }
+    for (; i < chunk_vec; i += NUM_THREADS) to[i] = from[i];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu(p.chunk_flags + src * per + within, p.epoch);
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ GemmParams p) {
+                    const __grid_constant__ CMaps cmaps, const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* smem_c = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);  // 32 KB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_c + C_STAGE_BYTES);
   uint64_t* full_bar = bars;                     // [STAGES]
   uint64_t* empty_bar = bars + STAGES;           // [STAGES]
   uint64_t* tmem_full_bar = bars + 2 * STAGES;   // [2]
@@ -26,6 +61,16 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
   int* s_offs = reinterpret_cast<int*>(bars) + 64;  // 256 B after the barrier block: [num_groups + 1]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool gather = p.mode == ALLGATHER || p.mode == ALLGATHER_B;
+
+  if (gather && (int)blockIdx.x < p.num_copiers) {
+    if (threadIdx.x == 0) *abort_flag = 0;
+    __syncthreads();
+    copier_role(p, abort_flag);
+    return;
+  }
+  const int cta = gather ? (int)blockIdx.x - p.num_copiers : (int)blockIdx.x;
+  const int ncta = gather ? (int)gridDim.x - p.num_copiers : (int)gridDim.x;
 
   if (p.mode == GROUPED_M || p.mode == GROUPED_K) {
     for (int i = threadIdx.x; i <= p.num_groups; i += NUM_THREADS) s_offs[i] = i == 0 ? 0 : p.offs[i - 1];
@@ -51,19 +96,20 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      unsigned int src_ready = 1u << p.rank;  // ALLGATHER: sources whose flag has been seen
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += ncta) {
         const Tile tl = get_tile(p, s_offs, t);
-        if ((p.mode == ALLGATHER || p.mode == ALLGATHER_B) && !(src_ready & (1u << tl.src))) {
-          if (!wait_flag_ge(p.ready_flags + tl.src, p.epoch, abort_flag)) {
+        int gmap = 0;  // which map of the gathered operand: 0 = own shard in place, 1 = local gathered copy
+        if (gather && tl.src != p.rank) {
+          if (!wait_local_flag_ge(p.chunk_flags + tl.chunk, p.epoch, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER); }
             break;
           }
-          src_ready |= 1u << tl.src;
+          // the chunk was written with ordinary stores by a copier CTA; TMA reads through the async proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          gmap = 1;
         }
-        // the gathered operand comes from the owner's map; the other operand from the single local map
-        const CUtensorMap* ta = p.mode == ALLGATHER_B ? &tmap_b : &amaps.m[tl.src];
-        const CUtensorMap* tbm = p.mode == ALLGATHER_B ? &amaps.m[tl.src] : &tmap_b;
+        const CUtensorMap* ta = p.mode == ALLGATHER_B ? &tmap_b : &amaps.m[p.mode == ALLGATHER ? gmap : 0];
+        const CUtensorMap* tbm = p.mode == ALLGATHER_B ? &amaps.m[gmap] : &tmap_b;
         for (int kb = 0; kb < tl.kblocks; ++kb) {
           if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
@@ -98,7 +144,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
       const uint32_t idesc = make_idesc_f16(BM, BN, p.is_bf16 != 0, p.a_mn != 0, p.b_mn != 0);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t acc_phase = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += ncta) {
         const Tile tl = get_tile(p, s_offs, t);
         if (!wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_EMPTY); }
@@ -135,54 +181,130 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const bool issuer = warp == 2 && lane == 0;
     int acc = 0; uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int t = cta; t < num_tiles; t += ncta) {
       const Tile tl = get_tile(p, s_offs, t);
       bool ok = wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        if (lane == 0 && *abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL); }
-        break;
+      if (!ok && lane == 0 && *abort_flag == 0) {
+        *abort_flag = 1;
+        if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL);
+      }
+      {
+        // one decision for all four epilogue warps: they share named barriers further down
+        uint32_t all_ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred pin, pout;\n"
+            "setp.ne.u32 pin, %1, 0;\n"
+            "barrier.red.and.pred pout, 1, 128, pin;\n"
+            "selp.u32 %0, 1, 0, pout;\n"
+            "}\n"
+            : "=r"(all_ok)
+            : "r"(ok ? 1u : 0u)
+            : "memory");
+        if (!all_ok) break;
       }
       tc_fence_after();
-      const int row = tl.m0 + q * 32 + lane;
+      const int row_in_tile = q * 32 + lane;
+      const int row = tl.m0 + row_in_tile;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      // where this tile's rows go
-      void* cbase = p.C;
-      long long ld = p.ldc;
-      int out_row = row;
-      int dst_rank = -1;
-      if (p.mode == GROUPED_K) {
-        cbase = p.out_fp32 ? (void*)(reinterpret_cast<float*>(p.C) + (long long)tl.group * p.c_group_stride)
-                           : (void*)(reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)tl.group * p.c_group_stride);
-      } else if (p.mode == SCATTER) {
-        dst_rank = tl.m0 / p.m_shard;
-        cbase = p.stage_ptrs[dst_rank];
-        ld = p.N;
-        out_row = p.rank * p.m_shard + (row - dst_rank * p.m_shard);  // slot [src = this rank][local row]
-      }
+      int dst_rank = 0;
+      if (p.mode == SCATTER) dst_rank = tl.m0 / p.m_shard;
+
+      if (p.tma_store) {
+        // tile → swizzled shared staging (two halves of 128 columns) → TMA store (coalesced, clipped at edges)
+        const CUtensorMap* cm = &cmaps.m[p.mode == SCATTER ? dst_rank : 0];
+        int y = tl.m0;
+        if (p.mode == GROUPED_K) y = tl.group * p.M + tl.m0;
+        else if (p.mode == SCATTER) y = p.rank * p.m_shard + (tl.m0 - dst_rank * p.m_shard);
+        const uint32_t srow = smem_u32(smem_c) + row_in_tile * 128;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (tl.kblocks == 0) {
+        for (int half = 0; half < 2; ++half) {
+          if (issuer) tma_store_wait_read<0>();  // previous stores have finished reading the staging buffer
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + (half * 4 + cc) * 32, r);
+            tmem_ld_wait();
+            uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;  // empty group: nothing was accumulated
+            for (int i = 0; i < 16; ++i) {
+              float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
+              if (tl.kblocks == 0) { lo = 0.f; hi = 0.f; }  // empty group: nothing was accumulated
+              if (p.is_bf16) {
+                pk[i] = pack_bf16x2(lo, hi);
+              } else {
+                __half2 h = __floats2half2_rn(lo, hi);
+                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+              }
+            }
+            const uint32_t box = srow + (cc >> 1) * 16384;  // 64-column box inside the half
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t chunk = (uint32_t)((cc & 1) * 4 + i) ^ (uint32_t)(row_in_tile & 7);  // 128B swizzle
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box + chunk * 16), "r"(pk[4 * i]),
+                           "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                           : "memory");
+            }
+          }
+          if (half == 1) {  // all TMEM reads of this accumulator are done
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+          }
+          fence_proxy_async();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (issuer) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              const int x = tl.n0 + half * 128 + b * 64;
+              if (x < p.N) tma_store_2d(cm, smem_c + b * 16384, x, y);
+            }
+            tma_store_commit();
+          }
         }
-        const int col = tl.n0 + c * 32;
-        if (row < tl.row_end && col < p.N) store_row32(p, cbase, ld, out_row, col, p.N, r);
+      } else {
+        void* cbase = p.C;
+        long long ld = p.ldc;
+        int out_row = row;
+        if (p.mode == GROUPED_K) {
+          cbase = p.out_fp32 ? (void*)(reinterpret_cast<float*>(p.C) + (long long)tl.group * p.c_group_stride)
+                             : (void*)(reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)tl.group * p.c_group_stride);
+        } else if (p.mode == SCATTER) {
+          cbase = p.stage_ptrs[dst_rank];
+          ld = p.N;
+          out_row = p.rank * p.m_shard + (row - dst_rank * p.m_shard);  // slot [src = this rank][local row]
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (tl.kblocks == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          const int col = tl.n0 + c * 32;
+          if (row < tl.row_end && col < p.N) store_row32(p, cbase, ld, out_row, col, p.N, r);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
 
       if (p.mode == SCATTER) {
         // count finished tiles per owner; whoever completes the last one publishes "my partial is there"
-        __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
-        if (warp == 2 && lane == 0) {
+        if (p.tma_store) {
+          if (issuer) tma_store_wait_all<0>();  // the bulk stores of this tile are complete
+        } else {
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (issuer) {
+          __threadfence_system();
           const int tiles_per_owner = (p.m_shard / BM) * ((p.N + BN - 1) / BN);
           const unsigned int done = atomicAdd(p.tile_counters + dst_rank, 1u) + 1u;
           if (done == (unsigned int)tiles_per_owner) {
@@ -193,6 +315,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
         }
       }
     }
+    if (issuer && p.tma_store) tma_store_wait_all<0>();  // nothing in flight when the CTA exits
   }
 
   tc_fence_before();
@@ -203,9 +326,9 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
   }
 }
 
-int launch(const AMaps& am, const CUtensorMap& tb_, const GemmParams& p, int grid, cudaStream_t st) {
+int launch(const AMaps& am, const CUtensorMap& tb_, const CMaps& cm, const GemmParams& p, int grid, cudaStream_t st) {
   TB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(am, tb_, p);
+  gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(am, tb_, cm, p);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;
@@ -222,15 +345,20 @@ inline int sm_count() {
   return n;
 }
 
+inline CUtensorMapDataType tm_dtype(int dtype) {
+  return dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
 inline int make_a_map(CUtensorMap* out, const void* A, int dtype, int a_mn, uint64_t m, uint64_t k, long long lda) {
-  const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  if (!a_mn) return tbh::make_tmap_2d(out, A, dt, 2, m, k, (uint64_t)lda * 2, BM, BK, 3);
-  return tbh::make_tmap_2d(out, A, dt, 2, k, m, (uint64_t)lda * 2, 64, 64, 3);
+  if (!a_mn) return tbh::make_tmap_2d(out, A, tm_dtype(dtype), 2, m, k, (uint64_t)lda * 2, BM, BK, 3);
+  return tbh::make_tmap_2d(out, A, tm_dtype(dtype), 2, k, m, (uint64_t)lda * 2, 64, 64, 3);
 }
 inline int make_b_map(CUtensorMap* out, const void* B, int dtype, int b_mn, uint64_t n, uint64_t k, long long ldb) {
-  const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  if (!b_mn) return tbh::make_tmap_2d(out, B, dt, 2, n, k, (uint64_t)ldb * 2, BN, BK, 3);
-  return tbh::make_tmap_2d(out, B, dt, 2, k, n, (uint64_t)ldb * 2, 64, 64, 3);
+  if (!b_mn) return tbh::make_tmap_2d(out, B, tm_dtype(dtype), 2, n, k, (uint64_t)ldb * 2, BN, BK, 3);
+  return tbh::make_tmap_2d(out, B, tm_dtype(dtype), 2, k, n, (uint64_t)ldb * 2, 64, 64, 3);
+}
+// output map: [rows, cols] 16-bit row-major, box {64 cols, 128 rows}, 128B swizzle (matches the staging layout)
+inline int make_c_map(CUtensorMap* out, void* C, int dtype, uint64_t rows, uint64_t cols, long long ldc) {
+  return tbh::make_tmap_2d(out, C, tm_dtype(dtype), 2, rows, cols, (uint64_t)ldc * 2, BM, 64, 3);
 }
 
 }  // namespace tbg

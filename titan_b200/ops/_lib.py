@@ -61,8 +61,8 @@ def _declare(L) -> None:
         "tb_moe_pair_dot": [P, I, P, P, P, I, I, I, LL, I, P],
         "tb_signal": [P, I, I, c_uint, P],
         "tb_wait_flags": [P, I, I, c_uint, P, P],
-        "tb_ag_gemm": [P, P, P, I, I, I, I, I, I, I, I, P, c_uint, P, P],
-        "tb_ag_b_gemm": [P, P, P, I, I, I, I, I, I, I, P, c_uint, P, P],
+        "tb_ag_gemm": [P, P, P, P, P, I, I, I, I, I, I, I, I, P, c_uint, P, P],
+        "tb_ag_b_gemm": [P, P, P, P, P, I, I, I, I, I, I, I, P, c_uint, P, P],
         "tb_gemm_rs": [P, P, P, P, P, I, I, I, I, I, I, I, I, c_uint, P, P],
         "tb_rs_reduce": [P, P, c_uint, P, LL, I, I, P, P],
         "tb_castscale_rs": [P, P, LL, I, I, F, I, I, P],

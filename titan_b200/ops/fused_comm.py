@@ -77,6 +77,19 @@ def _slots(group, tag: str, slot_bytes: int, ready_ch: int, done_ch: int) -> _Sl
     return s
 
 
+_CHUNK_FLAGS: dict = {}
+
+
+def _chunk_flags(ws: SymmWorkspace, tag: str, n: int) -> torch.Tensor:
+    """Local hand-off flags between copier CTAs and GEMM CTAs (zeroed once; epochs only grow)."""
+    key = (id(ws), tag)
+    t = _CHUNK_FLAGS.get(key)
+    if t is None or t.numel() < n:
+        t = torch.zeros(max(n, 1024), dtype=torch.int32, device=ws.device)
+        _CHUNK_FLAGS[key] = t
+    return t
+
+
 # ------------------------------------------------------------------------------ all-gather → GEMM
 def all_gather_matmul_baseline(a_shard, b, group):
     world = dist.get_world_size(group)
@@ -101,10 +114,12 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None) -> tor
     epoch = ws.next_epoch(CH_AG_READY)
     ws.signal(CH_AG_READY, epoch)
     out = torch.empty(world * m_shard, N, dtype=a_shard.dtype, device=a_shard.device)
+    gathered = torch.empty(world * m_shard, K, dtype=a_shard.dtype, device=a_shard.device)
     b = b.contiguous()
-    rc = _lib.lib().tb_ag_gemm(ws.ptr_array(off), b.data_ptr(), out.data_ptr(), world * m_shard, N, K, m_shard, 0,
-                               _lib.dtype_code(a_shard.dtype), rank, world, ws.channel_flags_ptr(CH_AG_READY), epoch,
-                               _lib.shared_status().ptr, _lib.stream_ptr())
+    rc = _lib.lib().tb_ag_gemm(ws.ptr_array(off), b.data_ptr(), out.data_ptr(), gathered.data_ptr(),
+                               _chunk_flags(ws, "ag", world * m_shard // 128).data_ptr(), world * m_shard, N, K,
+                               m_shard, 0, _lib.dtype_code(a_shard.dtype), rank, world,
+                               ws.channel_flags_ptr(CH_AG_READY), epoch, _lib.shared_status().ptr, _lib.stream_ptr())
     _lib.check(rc, "ag_gemm")
     s.release(slot)
     return out
@@ -128,10 +143,12 @@ def all_gather_weight_matmul(x: torch.Tensor, w_shard: torch.Tensor, group=None)
     epoch = ws.next_epoch(CH_AGB_READY)
     ws.signal(CH_AGB_READY, epoch)
     out = torch.empty(M, world * n_shard, dtype=x.dtype, device=x.device)
+    gathered = torch.empty(world * n_shard, K, dtype=x.dtype, device=x.device)
     x = x.contiguous()
-    rc = _lib.lib().tb_ag_b_gemm(x.data_ptr(), ws.ptr_array(off), out.data_ptr(), M, world * n_shard, K, n_shard,
-                                 _lib.dtype_code(x.dtype), rank, world, ws.channel_flags_ptr(CH_AGB_READY), epoch,
-                                 _lib.shared_status().ptr, _lib.stream_ptr())
+    rc = _lib.lib().tb_ag_b_gemm(x.data_ptr(), ws.ptr_array(off), out.data_ptr(), gathered.data_ptr(),
+                                 _chunk_flags(ws, "agb", world * n_shard // 256).data_ptr(), M, world * n_shard, K,
+                                 n_shard, _lib.dtype_code(x.dtype), rank, world, ws.channel_flags_ptr(CH_AGB_READY),
+                                 epoch, _lib.shared_status().ptr, _lib.stream_ptr())
     _lib.check(rc, "ag_b_gemm")
     s.release(slot)
     return out
