@@ -12,35 +12,85 @@ int launch(const AMaps& am, const CUtensorMap& tb_, const CMaps& cm, const GemmP
 
 // Copier role of the gather modes: pull remote shards into local memory once, chunk by chunk, and hand each
 // chunk to the GEMM CTAs through a local flag.  Chunks are visited in ring order starting at the next rank.
-__device__ __forceinline__ void copier_role(const GemmParams& p, volatile int* abort_flag) {
+// One thread drives bulk asynchronous copies (peer global -> shared -> local global) through a ring of
+// COPY_BUFS shared buffers, so a CTA keeps ~190 KB in flight on the link without spending registers or
+// issue slots; no multicast is involved.
+constexpr int COPY_PIECE = 32 * 1024;
+constexpr int COPY_BUFS = 6;
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void copier_role(const GemmParams& p, uint8_t* bufs, uint64_t* bars,
+                                            volatile int* abort_flag) {
+  if (threadIdx.x != 0) return;
+  for (int b = 0; b < COPY_BUFS; ++b) mbar_init(&bars[b], 1);
+  fence_barrier_init();
   const int chunk_rows = p.mode == ALLGATHER ? BM : BN;
   const int shard_rows = p.mode == ALLGATHER ? p.m_shard : p.n_shard;
   const int per = shard_rows / chunk_rows;
   const int remote_chunks = (p.nranks - 1) * per;
-  const long long chunk_vec = (long long)chunk_rows * p.K * 2 / 16;  // 16-byte vectors per chunk
-  __shared__ int s_ok;
-  for (int idx = blockIdx.x; idx < remote_chunks; idx += p.num_copiers) {
-    const int d = idx / per + 1, within = idx - (d - 1) * per;
-    const int src = (p.rank + d) % p.nranks;
-    if (threadIdx.x == 0) {
-      s_ok = wait_flag_ge(p.ready_flags + src, p.epoch, abort_flag) ? 1 : 0;
-      if (!s_ok && p.status) atomicExch(p.status, TB_ERR_WAIT_PEER);
+  const long long chunk_bytes = (long long)chunk_rows * p.K * 2;
+  const int pieces = (int)((chunk_bytes + COPY_PIECE - 1) / COPY_PIECE);
+  int my_chunks = 0;
+  for (int idx = blockIdx.x; idx < remote_chunks; idx += p.num_copiers) ++my_chunks;
+  const long long total = (long long)my_chunks * pieces;
+  unsigned int seen = 1u << p.rank;
+  const int D = COPY_BUFS - 1;  // loads run this many pieces ahead of the stores
+  for (long long i = 0; i < total + D; ++i) {
+    if (i < total) {
+      const int ci = (int)(i / pieces), pi = (int)(i - (long long)ci * pieces);
+      const int idx = blockIdx.x + ci * p.num_copiers;
+      const int d = idx / per + 1, within = idx - (d - 1) * per;
+      const int src = (p.rank + d) % p.nranks;
+      if (!(seen & (1u << src))) {
+        if (!wait_flag_ge(p.ready_flags + src, p.epoch, abort_flag)) {
+          if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER);
+          return;  // GEMM CTAs time out on the chunk flag and report as well
+        }
+        seen |= 1u << src;
+      }
+      const int b = (int)(i % COPY_BUFS);
+      if (i >= COPY_BUFS) tma_store_wait_read<0>();  // the store that used this buffer has read it
+      const long long off = (long long)pi * COPY_PIECE;
+      const uint32_t bytes = (uint32_t)((chunk_bytes - off) < COPY_PIECE ? (chunk_bytes - off) : COPY_PIECE);
+      const uint8_t* from = reinterpret_cast<const uint8_t*>(p.peer_src[src]) + (long long)within * chunk_bytes + off;
+      mbar_expect_tx(&bars[b], bytes);
+      bulk_load(bufs + b * COPY_PIECE, from, bytes, &bars[b]);
     }
-    __syncthreads();
-    if (!s_ok) return;  // GEMM CTAs time out on the chunk flag and report as well
-    const uint4* from = reinterpret_cast<const uint4*>(p.peer_src[src]) + (long long)within * chunk_vec;
-    uint4* to = reinterpret_cast<uint4*>(p.gather_dst) + ((long long)src * per + within) * chunk_vec;
-    long long i = threadIdx.x;
-    for (; i + 3LL * NUM_THREADS < chunk_vec; i += 4LL * NUM_THREADS) {  // four loads in flight per thread
-      const uint4 v0 = from[i], v1 = from[i + NUM_THREADS], v2 = from[i + 2 * NUM_THREADS],
-                  v3 = from[i + 3 * NUM_THREADS];
-      to[i] = v0; to[i + NUM_THREADS] = v1; to[i + 2 * NUM_THREADS] = v2; to[i + 3 * NUM_THREADS] = v3;
+    const long long j = i - D;
+    if (j >= 0 && j < total) {
+      const int ci = (int)(j / pieces), pi = (int)(j - (long long)ci * pieces);
+      const int idx = blockIdx.x + ci * p.num_copiers;
+      const int d = idx / per + 1, within = idx - (d - 1) * per;
+      const int src = (p.rank + d) % p.nranks;
+      const int b = (int)(j % COPY_BUFS);
+      if (!wait_bounded(&bars[b], (uint32_t)((j / COPY_BUFS) & 1), abort_flag)) {
+        if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA);
+        return;
+      }
+      const long long off = (long long)pi * COPY_PIECE;
+      const uint32_t bytes = (uint32_t)((chunk_bytes - off) < COPY_PIECE ? (chunk_bytes - off) : COPY_PIECE);
+      uint8_t* to = reinterpret_cast<uint8_t*>(p.gather_dst) + ((long long)src * per + within) * chunk_bytes + off;
+      bulk_store(to, bufs + b * COPY_PIECE, bytes);
+      tma_store_commit();
+      if (pi == pieces - 1) {  // chunk complete: make it visible, then hand it to the GEMM CTAs
+        tma_store_wait_all<0>();
+        __threadfence();
+        st_release_gpu(p.chunk_flags + src * per + within, p.epoch);
+      }
     }
-    for (; i < chunk_vec; i += NUM_THREADS) to[i] = from[i];
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu(p.chunk_flags + src * per + within, p.epoch);
   }
+  tma_store_wait_all<0>();
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -66,7 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
   if (gather && (int)blockIdx.x < p.num_copiers) {
     if (threadIdx.x == 0) *abort_flag = 0;
     __syncthreads();
-    copier_role(p, abort_flag);
+    copier_role(p, smem_a, bars, abort_flag);  // the operand stages double as copy buffers here
     return;
   }
   const int cta = gather ? (int)blockIdx.x - p.num_copiers : (int)blockIdx.x;

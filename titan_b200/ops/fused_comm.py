@@ -1,9 +1,11 @@
 """GEMMs fused with their collective over NVLink peer memory (Python side of `csrc/comm/fused_comm.cu`).
 
-* `all_gather_matmul(a_shard, b)`      – ``concat_ranks(a_shard) @ b.T``: every M tile is TMA-loaded from the
-  GPU that owns it, the moment that owner's ready flag arrives; no gathered copy of A is ever written.
+* `all_gather_matmul(a_shard, b)`      – ``concat_ranks(a_shard) @ b.T`` in ONE kernel: a few copier CTAs pull
+  every remote shard across NVLink exactly once (bulk async copies, ring order) into a local buffer and hand
+  128-row chunks to the GEMM CTAs through flags; the GEMM starts on the local shard at once and consumes
+  remote chunks as they land.
 * `all_gather_weight_matmul(x, w_shard)` – ``x @ concat_ranks(w_shard).T``: FSDP weight shards are gathered
-  inside the first GEMM that consumes them.
+  inside the first GEMM that consumes them (same mechanism on the B operand, 256-row chunks).
 * `matmul_reduce_scatter(a, b)`        – partial ``a @ b.T`` tiles are stored into the owner's staging slot as
   they leave tensor memory; the owner sums the `world` partials once all flags have arrived.
 * `castscale_reduce_scatter(bucket, scale)` – gradient bucket reduce-scatter reading peers' buckets directly,
