@@ -99,3 +99,23 @@ TB_API int tb_grouped_gemm_k(const void* A, const void* B, void* C, const int* o
   const int tiles = G * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
 }
+
+// Lightning-indexer scores.  q: [S*H, D] (row = query*H + head), k: [T, D], w: [S*H] fp32 head weights,
+// scores: [S, ld] fp32 with scores[s, t] = Σ_h w[s,h]·relu(q[s,h]·k[t]) for every t <= pos_offset + s (entries in
+// the causal future of a query are left unwritten where a whole tile is skipped: consumers must not read them).
+TB_API int tb_indexer_scores(const void* q, const void* k, const float* w, float* scores, int S, int H, int T, int D,
+                             long long ld, int pos_offset, int dtype, int* status, cudaStream_t st) {
+  if (S <= 0 || T <= 0) return 0;
+  if (H < 1 || BM % H != 0 || D % 8 || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  AMaps am;
+  CUtensorMap tb_;
+  CMaps cm;
+  const int M = S * H;
+  if (int rc = make_a_map(&am.m[0], q, dtype, 0, (uint64_t)M, (uint64_t)D, D)) return rc;
+  if (int rc = make_b_map(&tb_, k, dtype, 0, (uint64_t)T, (uint64_t)D, D)) return rc;
+  GemmParams p;
+  fill_common(p, INDEXER, M, T, D, 0, 0, dtype, 0, 0, T, nullptr, status);
+  p.idx_weights = w; p.idx_heads = H; p.idx_scores = scores; p.idx_ld = ld; p.idx_pos_offset = pos_offset;
+  const int tiles = ((M + BM - 1) / BM) * ((T + BN - 1) / BN);
+  return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
+}

@@ -16,6 +16,9 @@
 //              owner's memory (no multicast) once that owner's ready flag has arrived
 //   ALLGATHER_B same for a B operand sharded by rows of N (FSDP weight shards gathered inside the GEMM);
 //              `n_shard` rows per rank, a multiple of 256
+//   INDEXER    lightning-indexer scores: rows of A are (query, head) pairs, B holds index keys; the epilogue
+//              computes Σ_head w[q,head]·relu(acc) per (query, key) and writes fp32 scores; tiles that lie
+//              entirely in the causal future of their queries are skipped by every role
 //   SCATTER    C is reduce-scattered by rows: each tile is stored into the owner rank's staging slot
 //              for this rank; the last tile for an owner releases a flag on that owner
 //
@@ -45,7 +48,7 @@ constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;
 constexpr unsigned long long WAIT_NS = 2000000000ull;
 
-enum Mode : int { PLAIN = 0, GROUPED_M = 1, GROUPED_K = 2, ALLGATHER = 3, SCATTER = 4, ALLGATHER_B = 5 };
+enum Mode : int { PLAIN = 0, GROUPED_M = 1, GROUPED_K = 2, ALLGATHER = 3, SCATTER = 4, ALLGATHER_B = 5, INDEXER = 6 };
 
 struct GemmParams {
   int mode;
@@ -75,6 +78,12 @@ struct GemmParams {
   void* gather_dst;                     // local [nranks * shard_rows, K] buffer
   unsigned int* chunk_flags;            // local [num chunks]; chunk c holds `epoch` once it has been copied
   int num_copiers;
+  // INDEXER
+  const float* idx_weights;  // [M] = [queries * heads] head weights (already scaled)
+  int idx_heads;             // heads per query (divides 128)
+  float* idx_scores;         // [queries, idx_ld] fp32 out
+  long long idx_ld;
+  int idx_pos_offset;        // key t is visible to local query s iff t <= idx_pos_offset + s
 };
 
 struct CMaps {
@@ -159,6 +168,13 @@ __device__ __forceinline__ bool wait_local_flag_ge(const unsigned int* flag, uns
       if (globaltimer_ns() - t0 > WAIT_NS) return false;
     }
   }
+}
+
+// INDEXER: the whole tile is in the causal future of all of its queries (nothing to compute or store)
+__device__ __forceinline__ bool tile_is_future(const GemmParams& p, int m0, int n0) {
+  if (p.mode != INDEXER) return false;
+  const int last_query = min(m0 + BM, p.M) / p.idx_heads - (min(m0 + BM, p.M) % p.idx_heads == 0 ? 1 : 0);
+  return n0 > p.idx_pos_offset + last_query;
 }
 
 __device__ __forceinline__ int total_tiles(const GemmParams& p, const int* s_offs) {

@@ -148,6 +148,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (int t = cta; t < num_tiles && ok; t += ncta) {
         const Tile tl = get_tile(p, s_offs, t);
+        if (tile_is_future(p, tl.m0, tl.n0)) continue;
         int gmap = 0;  // which map of the gathered operand: 0 = own shard in place, 1 = local gathered copy
         if (gather && tl.src != p.rank) {
           if (!wait_local_flag_ge(p.chunk_flags + tl.chunk, p.epoch, abort_flag)) {
@@ -196,6 +197,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
       int acc = 0; uint32_t acc_phase = 0;
       for (int t = cta; t < num_tiles && ok; t += ncta) {
         const Tile tl = get_tile(p, s_offs, t);
+        if (tile_is_future(p, tl.m0, tl.n0)) continue;
         if (!wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_EMPTY); }
           break;
@@ -235,6 +237,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
     int acc = 0; uint32_t acc_phase = 0;
     for (int t = cta; t < num_tiles; t += ncta) {
       const Tile tl = get_tile(p, s_offs, t);
+      if (tile_is_future(p, tl.m0, tl.n0)) continue;
       bool ok = wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
       if (!ok && lane == 0 && *abort_flag == 0) {
         *abort_flag = 1;
@@ -262,7 +265,33 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
       int dst_rank = 0;
       if (p.mode == SCATTER) dst_rank = tl.m0 / p.m_shard;
 
-      if (p.tma_store) {
+      if (p.mode == INDEXER) {
+        // score[q, t] = Σ_h w[q, h] · relu(acc[(q, h), t]); rows of the tile are (query, head) pairs
+        float* stage = reinterpret_cast<float*>(smem_c);  // [128 rows][33] fp32 (padded against bank conflicts)
+        const int heads = p.idx_heads, qpt = BM / heads;
+        const float wrow = row < p.M ? p.idx_weights[row] : 0.f;
+        const int et = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stage[row_in_tile * 33 + i] = fmaxf(__uint_as_float(r[i]), 0.f) * wrow;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int o = et; o < qpt * 32; o += 128) {
+            const int ql = o >> 5, col = o & 31;
+            float sum = 0.f;
+            for (int h = 0; h < heads; ++h) sum += stage[(ql * heads + h) * 33 + col];
+            const int query = tl.m0 / heads + ql, key = tl.n0 + c * 32 + col;
+            if (query * heads < p.M && key < p.N) p.idx_scores[(long long)query * p.idx_ld + key] = sum;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      } else if (p.tma_store) {
         // tile → swizzled shared staging (two halves of 128 columns) → TMA store (coalesced, clipped at edges)
         const CUtensorMap* cm = &cmaps.m[p.mode == SCATTER ? dst_rank : 0];
         int y = tl.m0;

@@ -1,0 +1,133 @@
+"""DeepSeek sparse attention (DSA) operators.
+
+* `lightning_indexer_topk` – index scores ``Σ_h w[s,h]·relu(q_idx[s,h]·k_idx[t])`` for every visible key and
+  the top-k keys per query.  On CUDA the S×T scoring runs on the tcgen05 GEMM with a fused
+  relu·weight·head-sum epilogue (`tb_indexer_scores`; tiles in the causal future are skipped) and selection
+  is an exact radix select (`tb_topk_select`); nothing of size ``[S, T]`` per head is ever materialised.
+  Selection carries no gradient.
+* `sparse_mla_attention`   – attention of every query over its selected keys of the shared one-head KV latent
+  (MLA absorb layout), in query chunks: gather ``[chunk, k, D]`` rows → scores → softmax (+ log-sum-exp) →
+  values.  Also returns the head-summed probability mass on the selected keys (the indexer's teacher).
+* `indexer_scores_selected` – differentiable re-evaluation of the index scores at the selected keys only
+  (``O(S·k)``): this is where the indexer's parameters get their gradient.
+* `dsa_attention`           – the three together + the KL indexer loss; the drop-in for the eager oracle.
+
+Parity: `npu_lightning_indexer`, `npu_sparse_flash_attention`, `npu_sparse_lightning_indexer_grad_kl_loss`
+(torchtitan_npu/converters/kernels/dsa.py:22-309) with the eager model code as oracle
+(models/deepseek_v32/model.py:224-236, 363-420).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from titan_b200.models.common.dsa_indexer_loss import dsa_indexer_loss
+from titan_b200.ops import _lib
+
+__all__ = ["lightning_indexer_topk", "lightning_indexer_topk_ref", "sparse_mla_attention",
+           "indexer_scores_selected", "dsa_attention"]
+
+
+def lightning_indexer_topk_ref(q_idx, weights, k_idx, topk: int, pos_offset: int = 0):
+    """Oracle: dense scores, causal mask, `torch.topk`; invalid slots → index -1 / value -inf."""
+    B, S, H, D = q_idx.shape
+    T = k_idx.shape[1]
+    p = torch.matmul(q_idx.float().transpose(1, 2), k_idx.float().permute(0, 2, 3, 1))
+    score = (F.relu(p) * weights.float().permute(0, 2, 1).unsqueeze(-1)).sum(1)  # [B, S, T]
+    pos = torch.arange(S, device=score.device).unsqueeze(-1) + pos_offset
+    future = torch.arange(T, device=score.device).unsqueeze(0) > pos
+    score = score.masked_fill(future, float("-inf"))
+    kk = min(topk, T)
+    vals, idx = score.topk(kk, dim=-1)
+    valid = torch.isfinite(vals)
+    idx = torch.where(valid, idx, torch.full_like(idx, -1))
+    if kk < topk:
+        idx = F.pad(idx, (0, topk - kk), value=-1)
+        vals = F.pad(vals, (0, topk - kk), value=float("-inf"))
+    return idx.to(torch.int32), vals
+
+
+@torch.no_grad()
+def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0):
+    """q_idx [B,S,H,D], weights [B,S,H], k_idx [B,T,1,D] → (idx [B,S,topk] int32 with -1 padding, vals fp32)."""
+    if not q_idx.is_cuda or q_idx.dtype not in (torch.bfloat16, torch.float16) or 128 % q_idx.shape[2] != 0:
+        return lightning_indexer_topk_ref(q_idx, weights, k_idx, topk, pos_offset)
+    B, S, H, D = q_idx.shape
+    T = k_idx.shape[1]
+    L = _lib.lib()
+    import ctypes
+
+    P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    _lib.declare("tb_indexer_scores", [P, P, P, P, I, I, I, I, LL, I, I, P, P])
+    _lib.declare("tb_topk_select", [P, LL, I, I, I, I, P, P, P])
+    ld = (T + 3) // 4 * 4
+    scores = torch.empty(S, ld, dtype=torch.float32, device=q_idx.device)
+    idx = torch.empty(B, S, topk, dtype=torch.int32, device=q_idx.device)
+    vals = torch.empty(B, S, topk, dtype=torch.float32, device=q_idx.device)
+    for b in range(B):
+        q2 = q_idx[b].reshape(S * H, D).contiguous()
+        k2 = k_idx[b].reshape(T, D).contiguous().to(q2.dtype)
+        w2 = weights[b].reshape(S * H).float().contiguous()
+        rc = L.tb_indexer_scores(q2.data_ptr(), k2.data_ptr(), w2.data_ptr(), scores.data_ptr(), S, H, T, D, ld,
+                                 pos_offset, _lib.dtype_code(q2.dtype), _lib.shared_status().ptr, _lib.stream_ptr())
+        _lib.check(rc, "indexer_scores")
+        rc = L.tb_topk_select(scores.data_ptr(), ld, S, T, topk, pos_offset, idx[b].data_ptr(), vals[b].data_ptr(),
+                              _lib.stream_ptr())
+        _lib.check(rc, "topk_select")
+    return idx, vals
+
+
+def indexer_scores_selected(q_idx, weights, k_idx, idx):
+    """Differentiable index scores at the selected keys: [B,S,k]; padded slots (-1) → -inf."""
+    B, S, H, D = q_idx.shape
+    safe = idx.clamp_min(0).long()
+    ksel = k_idx[:, :, 0][torch.arange(B, device=idx.device).view(B, 1, 1), safe]  # [B,S,k,D]
+    s = torch.einsum("bshd,bskd->bshk", q_idx.float(), ksel.float())
+    s = (F.relu(s) * weights.float().unsqueeze(-1)).sum(2)
+    return s.masked_fill(idx < 0, float("-inf"))
+
+
+def _sparse_chunk(q, kv, v, idx, scale):
+    """q [H,Sc,Dq], kv [T,Dq], v [T,Dv], idx [Sc,k] → (out [H,Sc,Dv], teacher [Sc,k], lse [H,Sc])."""
+    safe = idx.clamp_min(0).long()
+    ksel, vsel = kv[safe], v[safe]  # [Sc,k,D]
+    s = torch.einsum("hsd,skd->hsk", q.float(), ksel.float()) * scale
+    s = s.masked_fill((idx < 0).unsqueeze(0), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    p = torch.nan_to_num(p)  # a row without any visible key
+    out = torch.einsum("hsk,skd->hsd", p, vsel.float()).to(q.dtype)
+    return out, p.detach().sum(0), lse
+
+
+def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256):
+    """q [B,H,S,Dq], k [B,1,T,Dq], v [B,1,T,Dv], idx [B,S,topk] → (out [B,H,S,Dv], teacher [B,S,topk], lse [B,H,S])."""
+    B, H, S, _ = q.shape
+    outs, teach, lses = [], [], []
+    for b in range(B):
+        ob, tb, lb = [], [], []
+        for s0 in range(0, S, chunk):
+            s1 = min(s0 + chunk, S)
+            args = (q[b, :, s0:s1], k[b, 0], v[b, 0], idx[b, s0:s1], scale)
+            if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad):
+                o, t, l = checkpoint(_sparse_chunk, *args, use_reentrant=False)  # gathered rows are not kept
+            else:
+                o, t, l = _sparse_chunk(*args)
+            ob.append(o); tb.append(t); lb.append(l)
+        outs.append(torch.cat(ob, dim=1)); teach.append(torch.cat(tb, dim=0)); lses.append(torch.cat(lb, dim=1))
+    return torch.stack(outs), torch.stack(teach), torch.stack(lses)
+
+
+def dsa_attention(q, k, v, *, scale, q_indexer, k_indexer, weights, index_topk: int, loss_scale: float = 1.0):
+    """Fused-path equivalent of the eager sparse-attention oracle → (indexer loss, out [B,H,S,Dv])."""
+    S, T = q.shape[2], k.shape[2]
+    pos_offset = T - S  # with context parallelism the local queries are the tail of the gathered key range
+    topk = min(index_topk, T)
+    idx, _ = lightning_indexer_topk(q_indexer, weights, k_indexer, topk, pos_offset)
+    out, teacher, _ = sparse_mla_attention(q, k, v, idx, scale)
+    student = indexer_scores_selected(q_indexer, weights, k_indexer, idx)
+    student = torch.where(idx < 0, torch.full_like(student, -1e30), student)  # finite: masked slots get zero mass
+    loss = dsa_indexer_loss(teacher.masked_fill(idx < 0, 0.0), student, loss_scale)
+    return loss, out
