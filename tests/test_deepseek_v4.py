@@ -1,0 +1,224 @@
+"""DeepSeek-V4 on CPU: index sets, compressor, hyper-connections, fused sparse path vs the dense oracle, MoE routing,
+state-dict mapping, and a two-step trainer run.
+
+Models what the reference covers in tests/unit_tests/models/test_deepseek_v4_{moe,rope_cache,state_dict_adapter,
+parallelize_static,pp_static}.py and tests/unit_tests/converters/test_mhc*.py.
+"""
+
+import pytest
+import torch
+
+from titan_b200.models.deepseek_v4 import DeepSeekV4Model, deepseekv4_configs
+from titan_b200.models.deepseek_v4.layers import (
+    Compressor,
+    compress_visible_idxs,
+    li_compute,
+    sparse_attention_dense,
+    window_topk_idxs,
+)
+from titan_b200.ops import mhc
+from titan_b200.ops.smla import li_select, smla_attention
+
+
+def _cfg(**kw):
+    cfg = deepseekv4_configs["smoketest"]()
+    cfg.max_seq_len = 256
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    return cfg
+
+
+def test_window_and_compress_index_sets():
+    w = window_topk_idxs(4, 6)
+    assert w.shape == (6, 4)
+    assert w[0].tolist() == [0, -1, -1, -1]
+    assert w[5].tolist() == [2, 3, 4, 5]
+    c = compress_visible_idxs(4, 8, offset=8)
+    assert c.shape == (8, 2)
+    assert c[2].tolist() == [-1, -1]  # block 0 closes at token 3
+    assert c[3].tolist() == [8, -1]
+    assert c[7].tolist() == [8, 9]
+
+
+def test_sinkhorn_is_doubly_stochastic_and_hc_roundtrip_shapes():
+    torch.manual_seed(0)
+    mixes = torch.randn(5, 24)
+    pre, post, comb = mhc.hc_split_sinkhorn(mixes, torch.tensor([1.0, 1.0, 1.0]), torch.zeros(24), 4, 20, 1e-6)
+    assert pre.shape == (5, 4) and post.shape == (5, 4) and comb.shape == (5, 4, 4)
+    assert torch.allclose(comb.sum(-1), torch.ones(5, 4), atol=1e-3)
+    assert torch.allclose(comb.sum(-2), torch.ones(5, 4), atol=1e-3)
+    assert (post > 0).all() and (post < 2).all()
+    x = torch.randn(2, 3, 4, 16)
+    fn = torch.randn(24, 64) * 0.1
+    y, post, comb = mhc.hc_pre(x, fn, torch.ones(3), torch.zeros(24))
+    assert y.shape == (2, 3, 16)
+    out = mhc.hc_post(y, x, post, comb)
+    assert out.shape == x.shape
+    # out[n] = post[n]·y + Σ_m comb[m, n]·x[m]
+    ref = post[..., None] * y[..., None, :] + torch.einsum("bsmn,bsmd->bsnd", comb, x)
+    assert torch.allclose(out, ref, atol=1e-5)
+
+
+def test_compressor_overlap_pools_previous_block():
+    cfg = _cfg()
+    comp = Compressor(cfg, 4, 32)
+    comp.init_states()
+    # first compressed key only sees block 0's second-half projections: the slots of the (missing) previous block
+    # carry -inf gates and must get zero weight
+    kv = torch.randn(1, 8, 64)
+    score = torch.zeros(1, 8, 64)
+    with torch.no_grad():
+        comp.ape.zero_()
+    pooled = comp.pool(kv, score)
+    assert pooled.shape == (1, 2, 32)
+    assert torch.allclose(pooled[0, 0], kv[0, :4, 32:].mean(0), atol=1e-6)
+    expect = torch.cat([kv[0, :4, :32], kv[0, 4:, 32:]], 0).mean(0)
+    assert torch.allclose(pooled[0, 1], expect, atol=1e-6)
+
+
+@pytest.mark.parametrize("ratio", [1, 4, 16])
+def test_fused_sparse_attention_matches_dense_oracle(ratio):
+    torch.manual_seed(1)
+    B, S, H, hd, window = 2, 64, 4, 32, 8
+    q = torch.randn(B, S, H, hd, requires_grad=True)
+    kv = torch.randn(B, S, hd, requires_grad=True)
+    sink = torch.randn(H, requires_grad=True)
+    kvc = torch.randn(B, S // ratio, hd, requires_grad=True) if ratio > 1 else None
+    idx = None
+    if ratio == 4:
+        qi, ki, w = torch.randn(B, S, 2, 16), torch.randn(B, S // 4, 16), torch.rand(B, S, 2)
+        idx, _ = li_compute(qi, ki, w, 4, 5, S)
+    out_ref, probs = sparse_attention_dense(q, kv, sink, kvc, idx, window, ratio, hd ** -0.5)
+    g = torch.randn_like(out_ref)
+    grads_ref = torch.autograd.grad(out_ref, [t for t in (q, kv, sink, kvc) if t is not None], g)
+    out, dist = smla_attention(q, kv, sink, kvc, idx, window, ratio, hd ** -0.5, want_dist=True, chunk=16)
+    grads = torch.autograd.grad(out, [t for t in (q, kv, sink, kvc) if t is not None], g)
+    assert torch.allclose(out, out_ref, atol=1e-5)
+    for a, b in zip(grads, grads_ref):
+        assert torch.allclose(a, b, atol=1e-4)
+    if ratio == 4:
+        cmp = probs[..., S:].sum(1) / H
+        ref_dist = torch.gather(cmp, -1, (idx - S).clamp(min=0)).masked_fill(idx < 0, 0.0)
+        assert torch.allclose(dist, ref_dist, atol=1e-6)
+
+
+def test_li_select_matches_eager_selection():
+    torch.manual_seed(2)
+    B, S, Hi, Di = 2, 64, 4, 16
+    qi, ki, w = torch.randn(B, S, Hi, Di), torch.randn(B, S // 4, Di), torch.rand(B, S, Hi)
+    idx_ref, val_ref = li_compute(qi, ki, w, 4, 6, S)
+    idx, val = li_select(qi, ki, w, 4, 6, S)
+    assert torch.equal(idx.sort(-1).values, idx_ref.sort(-1).values)
+    ok = idx_ref >= 0
+    assert torch.allclose(val.sort(-1).values[ok.sort(-1).values], val_ref.sort(-1).values[ok.sort(-1).values],
+                          atol=1e-5)
+
+
+def test_model_forward_backward_with_and_without_fused_core():
+    torch.manual_seed(0)
+    cfg = _cfg(num_mtp_modules=1)
+    model = DeepSeekV4Model(cfg)
+    model.init_states()
+    tok = torch.randint(0, cfg.vocab_size, (2, 129))
+    cfg.max_seq_len = 128
+    outs = model(tok)
+    assert [tuple(o.shape) for o in outs] == [(2, 128, cfg.vocab_size)] * 2
+    from titan_b200.converters.smla import SMLAConverter
+
+    SMLAConverter().convert(model)
+    outs_f = model(tok)
+    for a, b in zip(outs, outs_f):
+        assert torch.allclose(a, b, atol=2e-4), (a - b).abs().max()
+    sum(o.float().logsumexp(-1).mean() for o in outs_f).backward()
+    missing = [n for n, p in model.named_parameters() if p.grad is None]
+    assert missing == []
+    # the indexer is trained by its KL loss only
+    g = model.layers["2"].attention.pre_attention.indexer.wq_b.weight.grad
+    assert g.abs().sum() > 0
+
+
+def test_hash_layers_route_by_token_id_and_have_no_bias():
+    cfg = _cfg()
+    model = DeepSeekV4Model(cfg)
+    model.init_states()
+    moe0, moe1 = model.layers["0"].moe, model.layers["1"].moe
+    assert moe0.router.hash and moe0.expert_bias is None
+    assert not moe1.router.hash and moe1.expert_bias is not None
+    x = torch.randn(6, cfg.dim)
+    ids = torch.tensor([5, 9, 5, 9, 5, 9])
+    _, sel, _ = moe0.router(x, None, ids)
+    assert torch.equal(sel[0], sel[2]) and torch.equal(sel[1], sel[3])
+
+
+def test_state_dict_adapter_roundtrip():
+    from titan_b200.models.deepseek_v4.state_dict_adapter import DeepSeekV4StateDictAdapter
+
+    cfg = _cfg(num_mtp_modules=1)
+    model = DeepSeekV4Model(cfg)
+    model.init_states()
+    sd = {k: v for k, v in model.state_dict().items()}
+    ad = DeepSeekV4StateDictAdapter(cfg)
+    hf = ad.to_hf(sd)
+    assert "embed.weight" in hf and "head.weight" in hf and "hc_head_fn" in hf
+    assert "layers.2.attn.compressor.ape" in hf and "layers.3.attn.compressor.wkv.weight" in hf
+    assert "layers.2.attn.indexer.compressor.ape" in hf
+    assert "layers.0.ffn.gate.tid2eid" in hf and hf["layers.0.ffn.gate.tid2eid"].dtype == torch.float32
+    assert "layers.1.ffn.gate.bias" in hf and "layers.0.ffn.gate.bias" not in hf
+    assert "layers.1.ffn.experts.7.w2.weight" in hf
+    assert "mtp.0.e_proj.weight" in hf and "mtp.0.norm.weight" in hf and "mtp.0.hc_head_scale" in hf
+    back = ad.from_hf(hf)
+    assert set(back) == set(sd)
+    for k in sd:
+        assert torch.equal(back[k].to(sd[k].dtype), sd[k]), k
+
+
+def _launch(args, nproc, port, timeout=900):
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "titan_b200.entry", *args]
+    res = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=timeout)
+    log = res.stdout + res.stderr
+    assert res.returncode == 0, log[-4000:]
+    return log
+
+
+def _losses(log):
+    import re
+
+    return [float(m) for m in re.findall(r"r0\] .*? step:\s+\d+\s+loss:\s+([0-9.]+|nan|inf)", log)]
+
+
+_BASE = ["--module", "deepseek_v4", "--config", "deepseek_v4_smoketest", "--training.seq_len", "128",
+         "--comm.backend", "gloo", "--training.local_batch_size", "2"]
+
+
+def _step_line(log, step):
+    import re
+
+    m = re.search(rf"r0\] .*? step:\s+{step}\s+loss:\s+([0-9.]+)\s+grad_norm:\s+([0-9.]+)", log)
+    assert m, log[-3000:]
+    return float(m.group(1)), float(m.group(2))
+
+
+def test_trainer_tp2_and_fsdp2_reproduce_the_single_rank_step(tmp_path):
+    """One rank trains 2 steps and checkpoints after step 1.  A tensor-parallel pair resumes from that checkpoint
+    (resharded load) and must reproduce step 2: same loss and same gradient norm."""
+    folder = str(tmp_path / "run")
+    common = [*_BASE, "--job.dump_folder", folder, "--checkpoint.enable", "--checkpoint.interval", "1",
+              "--training.steps", "2"]
+    ref = _step_line(_launch(common, 1, 29560), 2)
+    tp = _step_line(_launch([*common, "--checkpoint.load_step", "1", "--parallelism.data_parallel_shard_degree", "1",
+                             "--parallelism.tensor_parallel_degree", "2"], 2, 29561), 2)
+    assert abs(tp[0] - ref[0]) < 2e-3 and abs(tp[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (tp, ref)
+
+
+def test_trainer_fsdp2_three_steps(tmp_path):
+    log = _launch([*_BASE, "--job.dump_folder", str(tmp_path / "fsdp"), "--training.local_batch_size", "1",
+                   "--parallelism.data_parallel_shard_degree", "2", "--training.steps", "3"], 2, 29562)
+    fsdp = _losses(log)
+    assert len(fsdp) == 3 and all(x == x and x < 20 for x in fsdp), log[-2000:]

@@ -1,7 +1,7 @@
 // Row-wise top-k selection over long score rows (lightning indexer: up to 131072 keys, k up to 2048).
 //
-// One CTA per query row.  Row r may only look at keys t <= pos_offset + r (causal prefix), so masked entries are
-// never read and need not exist in memory.  Selection is an exact radix select on the order-preserving integer
+// One CTA per query row.  Row r may only look at its first (pos_offset + r + 1) / ratio keys (causal prefix; ratio > 1
+// for compressed keys that stand for `ratio` tokens each), so masked entries are never read and need not exist.  Selection is an exact radix select on the order-preserving integer
 // image of the fp32 scores: four 8-bit histogram rounds find the k-th largest key, a last pass emits every
 // element above it plus as many ties as still fit.  The emitted SET is exact; the order inside a row is
 // arbitrary (consumers gather by index).  Rows with fewer than k visible keys are padded with index -1 and
@@ -23,7 +23,7 @@ __device__ __forceinline__ uint32_t ordered_key(float x) {
 
 __global__ void __launch_bounds__(TK_THREADS) topk_select_kernel(const float* __restrict__ scores, long long ld,
                                                                  int rows, int T, int k, int pos_offset,
-                                                                 int* __restrict__ out_idx,
+                                                                 int ratio, int* __restrict__ out_idx,
                                                                  float* __restrict__ out_val) {
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(TK_THREADS) topk_select_kernel(const float* __
   const int r = blockIdx.x;
   if (r >= rows) return;
   const float* row = scores + (long long)r * ld;
-  long long vis = (long long)pos_offset + r + 1;
+  long long vis = ((long long)pos_offset + r + 1) / ratio;
   const int n = (int)(vis < 0 ? 0 : (vis > T ? T : vis));
   int* oi = out_idx + (long long)r * k;
   float* ov = out_val != nullptr ? out_val + (long long)r * k : nullptr;
@@ -89,11 +89,11 @@ __global__ void __launch_bounds__(TK_THREADS) topk_select_kernel(const float* __
 }  // namespace
 
 // scores: [rows, ld] fp32; out_idx: [rows, k] int32; out_val: [rows, k] fp32 or nullptr.
-TB_API int tb_topk_select(const float* scores, long long ld, int rows, int T, int k, int pos_offset, int* out_idx,
-                          float* out_val, cudaStream_t st) {
+TB_API int tb_topk_select(const float* scores, long long ld, int rows, int T, int k, int pos_offset, int ratio,
+                          int* out_idx, float* out_val, cudaStream_t st) {
   if (rows <= 0) return 0;
-  if (k < 1 || T < 1) return TB_ERR_ARG;
-  topk_select_kernel<<<rows, TK_THREADS, 0, st>>>(scores, ld, rows, T, k, pos_offset, out_idx, out_val);
+  if (k < 1 || T < 1 || ratio < 1) return TB_ERR_ARG;
+  topk_select_kernel<<<rows, TK_THREADS, 0, st>>>(scores, ld, rows, T, k, pos_offset, ratio, out_idx, out_val);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

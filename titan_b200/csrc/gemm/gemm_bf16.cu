@@ -101,11 +101,14 @@ TB_API int tb_grouped_gemm_k(const void* A, const void* B, void* C, const int* o
 }
 
 // Lightning-indexer scores.  q: [S*H, D] (row = query*H + head), k: [T, D], w: [S*H] fp32 head weights,
-// scores: [S, ld] fp32 with scores[s, t] = Σ_h w[s,h]·relu(q[s,h]·k[t]) for every t <= pos_offset + s (entries in
-// the causal future of a query are left unwritten where a whole tile is skipped: consumers must not read them).
+// scores: [S, ld] fp32 with scores[s, t] = Σ_h w[s,h]·relu(q[s,h]·k[t]) for every visible key
+// t < (pos_offset + s + 1) / ratio (ratio 1: causal tokens; ratio r: compressed keys, one per r tokens, visible once
+// their block is complete).  Entries in the causal future of a query are left unwritten where a whole tile is
+// skipped: consumers must not read them.
 TB_API int tb_indexer_scores(const void* q, const void* k, const float* w, float* scores, int S, int H, int T, int D,
-                             long long ld, int pos_offset, int dtype, int* status, cudaStream_t st) {
+                             long long ld, int pos_offset, int ratio, int dtype, int* status, cudaStream_t st) {
   if (S <= 0 || T <= 0) return 0;
+  if (ratio < 1) return TB_ERR_ARG;
   if (H < 1 || BM % H != 0 || D % 8 || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
   AMaps am;
   CUtensorMap tb_;
@@ -116,6 +119,7 @@ TB_API int tb_indexer_scores(const void* q, const void* k, const float* w, float
   GemmParams p;
   fill_common(p, INDEXER, M, T, D, 0, 0, dtype, 0, 0, T, nullptr, status);
   p.idx_weights = w; p.idx_heads = H; p.idx_scores = scores; p.idx_ld = ld; p.idx_pos_offset = pos_offset;
+  p.idx_ratio = ratio;
   const int tiles = ((M + BM - 1) / BM) * ((T + BN - 1) / BN);
   return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
 }

@@ -83,7 +83,8 @@ struct GemmParams {
   int idx_heads;             // heads per query (divides 128)
   float* idx_scores;         // [queries, idx_ld] fp32 out
   long long idx_ld;
-  int idx_pos_offset;        // key t is visible to local query s iff t <= idx_pos_offset + s
+  int idx_pos_offset;        // key t is visible to local query s iff t < (idx_pos_offset + s + 1) / idx_ratio
+  int idx_ratio;             // 1 = plain causal keys; r > 1 = keys are blocks of r tokens, visible once closed
 };
 
 struct CMaps {
@@ -174,7 +175,7 @@ __device__ __forceinline__ bool wait_local_flag_ge(const unsigned int* flag, uns
 __device__ __forceinline__ bool tile_is_future(const GemmParams& p, int m0, int n0) {
   if (p.mode != INDEXER) return false;
   const int last_query = min(m0 + BM, p.M) / p.idx_heads - (min(m0 + BM, p.M) % p.idx_heads == 0 ? 1 : 0);
-  return n0 > p.idx_pos_offset + last_query;
+  return n0 >= (p.idx_pos_offset + last_query + 1) / p.idx_ratio;
 }
 
 __device__ __forceinline__ int total_tiles(const GemmParams& p, const int* s_offs) {

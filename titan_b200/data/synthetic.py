@@ -38,7 +38,8 @@ class SyntheticDataLoader(Stateful):
         g.manual_seed((self.seed * 1_000_003 + self.dp_rank) * 1_000_003 + step)
         n = self.seq_len + 1 + self.extra_tokens
         tok = torch.randint(0, self.vocab_size, (self.batch_size, n), generator=g, dtype=torch.int64)
-        inputs = tok[:, : self.seq_len].contiguous()
+        # with MTP the model gets the look-ahead tokens too: depth k embeds inputs[:, k : k + seq_len]
+        inputs = tok[:, : self.seq_len + self.extra_tokens].contiguous()
         labels = tok[:, 1:].contiguous()
         if self.pin_memory:
             inputs, labels = inputs.pin_memory(), labels.pin_memory()

@@ -94,6 +94,9 @@ class FeedForward(Module):
         self.w3 = Linear(dim, hidden_dim, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        limit = float(getattr(self, "swiglu_limit", 0.0) or 0.0)
+        if limit > 0:  # DeepSeek-V4 clamps gate and up before the activation (models/deepseek_v4/moe.py:183-203)
+            return self.w2(F.silu(self.w1(x).clamp(max=limit)) * self.w3(x).clamp(min=-limit, max=limit))
         return self.w2(F.silu(self.w1(x)) * self.w3(x))
 
     def init_states(self, *, init_std: float = 0.02, **kwargs) -> None:

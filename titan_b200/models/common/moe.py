@@ -96,7 +96,9 @@ class TokenChoiceTopKRouter(Module):
 
     def forward(self, x: torch.Tensor, expert_bias: torch.Tensor | None = None, input_ids: torch.Tensor | None = None):
         """x [T, dim] → (top_scores [T, k] fp32, selected [T, k] int64, tokens_per_expert [E] fp32)."""
-        logits = F.linear(x.float(), self.gate.weight.float())  # routing in fp32
+        w = self.gate.weight
+        w = w.to_local() if hasattr(w, "to_local") else w  # replicated under tensor parallelism
+        logits = F.linear(x.float(), w.float())  # routing in fp32
         scores = self._scores(logits)
         if self.hash:
             if input_ids is None:

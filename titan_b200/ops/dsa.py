@@ -30,14 +30,14 @@ __all__ = ["lightning_indexer_topk", "lightning_indexer_topk_ref", "sparse_mla_a
            "indexer_scores_selected", "dsa_attention"]
 
 
-def lightning_indexer_topk_ref(q_idx, weights, k_idx, topk: int, pos_offset: int = 0):
+def lightning_indexer_topk_ref(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, ratio: int = 1):
     """Oracle: dense scores, causal mask, `torch.topk`; invalid slots → index -1 / value -inf."""
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]
     p = torch.matmul(q_idx.float().transpose(1, 2), k_idx.float().permute(0, 2, 3, 1))
     score = (F.relu(p) * weights.float().permute(0, 2, 1).unsqueeze(-1)).sum(1)  # [B, S, T]
-    pos = torch.arange(S, device=score.device).unsqueeze(-1) + pos_offset
-    future = torch.arange(T, device=score.device).unsqueeze(0) > pos
+    visible = (torch.arange(S, device=score.device).unsqueeze(-1) + pos_offset + 1) // ratio
+    future = torch.arange(T, device=score.device).unsqueeze(0) >= visible
     score = score.masked_fill(future, float("-inf"))
     kk = min(topk, T)
     vals, idx = score.topk(kk, dim=-1)
@@ -50,18 +50,21 @@ def lightning_indexer_topk_ref(q_idx, weights, k_idx, topk: int, pos_offset: int
 
 
 @torch.no_grad()
-def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0):
-    """q_idx [B,S,H,D], weights [B,S,H], k_idx [B,T,1,D] → (idx [B,S,topk] int32 with -1 padding, vals fp32)."""
+def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, ratio: int = 1):
+    """q_idx [B,S,H,D], weights [B,S,H], k_idx [B,T,1,D] → (idx [B,S,topk] int32 with -1 padding, vals fp32).
+
+    ``ratio`` > 1: the keys are compressed blocks of ``ratio`` tokens; query ``s`` sees the first
+    ``(pos_offset + s + 1) // ratio`` of them."""
     if not q_idx.is_cuda or q_idx.dtype not in (torch.bfloat16, torch.float16) or 128 % q_idx.shape[2] != 0:
-        return lightning_indexer_topk_ref(q_idx, weights, k_idx, topk, pos_offset)
+        return lightning_indexer_topk_ref(q_idx, weights, k_idx, topk, pos_offset, ratio)
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]
     L = _lib.lib()
     import ctypes
 
     P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-    _lib.declare("tb_indexer_scores", [P, P, P, P, I, I, I, I, LL, I, I, P, P])
-    _lib.declare("tb_topk_select", [P, LL, I, I, I, I, P, P, P])
+    _lib.declare("tb_indexer_scores", [P, P, P, P, I, I, I, I, LL, I, I, I, P, P])
+    _lib.declare("tb_topk_select", [P, LL, I, I, I, I, I, P, P, P])
     ld = (T + 3) // 4 * 4
     scores = torch.empty(S, ld, dtype=torch.float32, device=q_idx.device)
     idx = torch.empty(B, S, topk, dtype=torch.int32, device=q_idx.device)
@@ -71,10 +74,11 @@ def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0
         k2 = k_idx[b].reshape(T, D).contiguous().to(q2.dtype)
         w2 = weights[b].reshape(S * H).float().contiguous()
         rc = L.tb_indexer_scores(q2.data_ptr(), k2.data_ptr(), w2.data_ptr(), scores.data_ptr(), S, H, T, D, ld,
-                                 pos_offset, _lib.dtype_code(q2.dtype), _lib.shared_status().ptr, _lib.stream_ptr())
+                                 pos_offset, ratio, _lib.dtype_code(q2.dtype), _lib.shared_status().ptr,
+                                 _lib.stream_ptr())
         _lib.check(rc, "indexer_scores")
-        rc = L.tb_topk_select(scores.data_ptr(), ld, S, T, topk, pos_offset, idx[b].data_ptr(), vals[b].data_ptr(),
-                              _lib.stream_ptr())
+        rc = L.tb_topk_select(scores.data_ptr(), ld, S, T, topk, pos_offset, ratio, idx[b].data_ptr(),
+                              vals[b].data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "topk_select")
     return idx, vals
 

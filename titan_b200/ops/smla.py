@@ -1,0 +1,121 @@
+"""Sparse multi-query latent attention for DeepSeek-V4: sliding window ∪ compressed keys ∪ sink.
+
+Every query attends to
+* its causal window of ``window`` raw keys of the one shared KV latent (values = keys),
+* compressed keys: either the ``k`` picked by the lightning indexer (``compress_idx``, ratio 4) or every compressed
+  key whose block is complete (other ratios),
+* a learned per-head sink logit that takes probability mass and contributes no value.
+
+`smla_attention` never builds anything of size ``S × T``: queries are processed in chunks; a chunk touches the
+``chunk + window`` raw keys it can see (dense band) and gathers its selected compressed keys.  Chunks are
+recomputed in backward, so what stays alive is O(S·H·hd).  It also returns the head-mean probability on the selected
+compressed keys – the teacher of the indexer's KL loss – so the loss needs no second attention pass.
+
+`li_select` is the matching selection step: tcgen05 index scoring + radix top-k over the compressed keys, then a
+differentiable re-evaluation of the scores at the selected keys only (that is where the indexer gets its gradient).
+
+Parity: `SparseAttention`, `LiCompute`, `LiLoss._current_selected_attn_dist`
+(torchtitan_npu/models/deepseek_v4/model.py:421-457, 553-657) and the fused `npu_smla` path
+(converters/kernels/npu_smla.py).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+__all__ = ["smla_attention", "li_select"]
+
+
+def _chunk(q, kv, sink, kvc, cidx, s0: int, window: int, ratio: int, scale: float, n_heads_total: int,
+           want_dist: bool):
+    """q [Sc,H,hd], kv [S,hd], kvc [Tc,hd] | None, cidx [Sc,k] local compressed ids (-1 empty) | None."""
+    Sc, H, hd = q.shape
+    s1 = s0 + Sc
+    t0 = max(0, s0 - window + 1)
+    kwin = kv[t0:s1]  # [W, hd]
+    qh = q.transpose(0, 1)  # [H, Sc, hd]
+    logit_w = torch.matmul(qh, kwin.t()).float() * scale  # [H, Sc, W]
+    spos = torch.arange(s0, s1, device=q.device).unsqueeze(1)
+    tpos = torch.arange(t0, s1, device=q.device).unsqueeze(0)
+    logit_w = logit_w.masked_fill(((tpos > spos) | (tpos <= spos - window)).unsqueeze(0), float("-inf"))
+    parts = [logit_w]
+    ksel = None
+    if kvc is not None and ratio > 1:
+        if cidx is not None:
+            ksel = kvc[cidx.clamp(min=0).long()]  # [Sc, k, hd]
+            logit_c = torch.einsum("hsd,skd->hsk", qh, ksel).float() * scale
+            logit_c = logit_c.masked_fill((cidx < 0).unsqueeze(0), float("-inf"))
+        else:
+            c_end = s1 // ratio
+            kc = kvc[:c_end]
+            logit_c = torch.matmul(qh, kc.t()).float() * scale  # [H, Sc, c_end]
+            hidden = torch.arange(c_end, device=q.device).unsqueeze(0) >= (spos + 1) // ratio
+            logit_c = logit_c.masked_fill(hidden.unsqueeze(0), float("-inf"))
+        parts.append(logit_c)
+    parts.append(sink.float().view(H, 1, 1).expand(H, Sc, 1))
+    p = torch.softmax(torch.cat(parts, dim=-1), dim=-1)
+    W = logit_w.shape[-1]
+    out = torch.matmul(p[..., :W].to(kv.dtype), kwin)  # [H, Sc, hd]
+    dist = None
+    if len(parts) == 3:
+        pc = p[..., W:-1]
+        if ksel is not None:
+            out = out + torch.einsum("hsk,skd->hsd", pc.to(kv.dtype), ksel)
+            if want_dist:
+                dist = pc.detach().sum(0) / n_heads_total
+        else:
+            out = out + torch.matmul(pc.to(kv.dtype), kvc[: pc.shape[-1]])
+    out = out.transpose(0, 1)
+    return (out, dist) if dist is not None else (out,)
+
+
+def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: int, scale: float,
+                   want_dist: bool = False, *, n_heads_total: int | None = None, chunk: int = 256):
+    """q [B,S,H,hd], kv [B,S,hd], sink [H], kv_compress [B,Tc,hd] | None, compress_idx [B,S,k] | None (ids offset by
+    S as in the dense layout; -1 = empty) → (out [B,S,H,hd], dist [B,S,k] | None)."""
+    B, S, H, _ = q.shape
+    n_heads_total = n_heads_total or H
+    local_idx = None
+    if compress_idx is not None:
+        local_idx = torch.where(compress_idx < 0, compress_idx, compress_idx - S)
+    outs, dists = [], []
+    need_grad = torch.is_grad_enabled() and (q.requires_grad or kv.requires_grad)
+    for b in range(B):
+        ob, db = [], []
+        for s0 in range(0, S, chunk):
+            s1 = min(s0 + chunk, S)
+            args = (q[b, s0:s1], kv[b], sink, None if kv_compress is None else kv_compress[b],
+                    None if local_idx is None else local_idx[b, s0:s1], s0, window, ratio, scale, n_heads_total,
+                    want_dist)
+            res = checkpoint(_chunk, *args, use_reentrant=False) if need_grad else _chunk(*args)
+            ob.append(res[0])
+            if len(res) > 1:
+                db.append(res[1])
+        outs.append(torch.cat(ob, dim=0))
+        if db:
+            dists.append(torch.cat(db, dim=0))
+    out = torch.stack(outs)
+    dist = torch.stack(dists).masked_fill(compress_idx < 0, 0.0) if dists else None
+    return out, dist
+
+
+def li_select(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset: int = 0):
+    """Fused counterpart of the eager selection: (idx [B,S,k] with ``offset`` added, -1 = empty; scores [B,S,k]).
+
+    Selection (no gradient) runs on the scoring GEMM + radix-select kernels; the returned scores are recomputed at
+    the selected keys only and carry the gradient to the indexer."""
+    from titan_b200.ops.dsa import lightning_indexer_topk
+
+    B, S = q_indexer.shape[:2]
+    T = k_indexer.shape[1]
+    k = min(index_topk, S // ratio)
+    idx, _ = lightning_indexer_topk(q_indexer.detach(), weights.detach(), k_indexer.detach().unsqueeze(2), k, 0, ratio)
+    idx = idx.long()
+    safe = idx.clamp(min=0)
+    ksel = k_indexer[torch.arange(B, device=idx.device).view(B, 1, 1), safe]  # [B,S,k,D]
+    s = torch.einsum("bshd,bskd->bshk", q_indexer, ksel)
+    s = (F.relu(s) * weights.unsqueeze(-1)).sum(2)
+    s = s.masked_fill(idx < 0, torch.finfo(q_indexer.dtype).min)
+    return torch.where(idx < 0, idx, idx + offset), s

@@ -38,7 +38,10 @@ def expert_style_for(*, tp: bool, ep: bool, etp: bool, comm_backend: str = "stan
 
 
 def apply_moe_ep_tp(model: nn.Module, *, tp_mesh=None, ep_mesh=None, etp_mesh=None, ep_etp_mesh=None,
-                    comm_backend: str = "standard", layers_attr: str = "layers") -> None:
+                    comm_backend: str = "standard", layers_attr: str = "layers", extra_moe_inputs: int = 0) -> None:
+    """``extra_moe_inputs``: positional inputs after the tokens that pass through untouched (DeepSeek-V4 hands the
+    token ids to the MoE block for hash routing)."""
+    none = (None,) * extra_moe_inputs
     for block in getattr(model, layers_attr).values():
         if block is None or not getattr(block, "moe_enabled", False):
             continue
@@ -48,7 +51,7 @@ def apply_moe_ep_tp(model: nn.Module, *, tp_mesh=None, ep_mesh=None, etp_mesh=No
                 # tokens enter sequence-sharded, are gathered for routing, and leave as partial sums that are
                 # reduce-scattered back to the sequence shard
                 "moe": PrepareModuleInputOutput(
-                    input_layouts=(Shard(1),), desired_input_layouts=(Replicate(),), use_local_input=True,
+                    input_layouts=(Shard(1), *none), desired_input_layouts=(Replicate(), *none), use_local_input=True,
                     output_layouts=(Partial(),), desired_output_layouts=(Shard(1),)),
                 "moe.router.gate": NoParallel(),
             }

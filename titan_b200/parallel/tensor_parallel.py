@@ -37,6 +37,7 @@ __all__ = [
     "NoParallel",
     "AwaitRowwiseParallel",
     "PrepareModuleInputOutputWithBwdAllReduce",
+    "SequenceShardedLinear",
     "maybe_enable_async_tp",
     "async_tp_enabled",
 ]
@@ -107,17 +108,26 @@ class _AllReduceBwd(torch.autograd.Function):
         return g, None
 
 
-class PrepareModuleInputOutputWithBwdAllReduce(PrepareModuleInputOutput):
-    """Like `PrepareModuleInputOutput`, and sums the grads of the inputs listed in
-    ``bwd_allreduce_input_idx`` over the mesh: each TP rank attends with its own
-    heads to the same replicated K/V latent, so dK/dV are partial sums."""
+class PrepareModuleInputOutputWithBwdAllReduce(ParallelStyle):
+    """Sums the grads of the inputs listed in ``bwd_allreduce_input_idx`` over the mesh: each TP rank attends
+    with its own heads to the same replicated K/V latent, so dK/dV are partial sums.
 
-    def __init__(self, *, bwd_allreduce_input_idx: tuple[int, ...] = (), **kwargs):
-        super().__init__(**kwargs)
+    With layouts given it also behaves like `PrepareModuleInputOutput`; with ``input_layouts=None`` the module's
+    inputs and outputs are plain local tensors and are left alone."""
+
+    def __init__(self, *, bwd_allreduce_input_idx: tuple[int, ...] = (), input_layouts=None,
+                 desired_input_layouts=None, output_layouts=None, desired_output_layouts=None, **kwargs):
+        super().__init__()
         self.bwd_allreduce_input_idx = tuple(bwd_allreduce_input_idx)
+        self.inner = None
+        if input_layouts is not None or output_layouts is not None:
+            self.inner = PrepareModuleInputOutput(
+                input_layouts=input_layouts, desired_input_layouts=desired_input_layouts,
+                output_layouts=output_layouts, desired_output_layouts=desired_output_layouts, **kwargs)
 
     def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
-        module = super()._apply(module, device_mesh)
+        if self.inner is not None:
+            module = self.inner._apply(module, device_mesh)
         group = device_mesh.get_group()
         idxs = self.bwd_allreduce_input_idx
 
@@ -129,6 +139,37 @@ class PrepareModuleInputOutputWithBwdAllReduce(PrepareModuleInputOutput):
             return tuple(args)
 
         module.register_forward_pre_hook(pre_hook)
+        return module
+
+
+def replicated_param_local(p, *, partial_grad: bool):
+    """Local tensor of a parameter that is replicated over its mesh.  ``partial_grad``: the parameter is applied to
+    activations that differ per rank (sequence-sharded), so its gradient is summed over the mesh in backward."""
+    if not isinstance(p, DTensor):
+        return p
+    local = p.to_local()
+    if partial_grad:
+        local = _AllReduceBwd.apply(local, p.device_mesh.get_group())
+    return local
+
+
+class SequenceShardedLinear(ParallelStyle):
+    """A full (unsplit) linear applied to sequence-sharded local activations: the weight is replicated, every rank
+    multiplies its own tokens, and the weight gradient is a partial sum that is reduced over the mesh."""
+
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        from torch.distributed.tensor import Partial
+
+        for name, p in list(module.named_parameters(recurse=False)):
+            module.register_parameter(name, nn.Parameter(distribute_tensor(p.data, device_mesh, [Replicate()]),
+                                                         requires_grad=p.requires_grad))
+
+        def forward(x, _m=module):
+            w = replicated_param_local(_m.weight, partial_grad=True)
+            b = replicated_param_local(_m.bias, partial_grad=True) if _m.bias is not None else None
+            return torch.nn.functional.linear(x, w, b)
+
+        module.forward = forward
         return module
 
 

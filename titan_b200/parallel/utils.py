@@ -22,7 +22,7 @@ from datetime import timedelta
 import torch
 import torch.distributed as dist
 from torch.distributed.device_mesh import DeviceMesh
-from torch.distributed.tensor import DTensor, Partial, Shard
+from torch.distributed.tensor import DTensor, Partial, Replicate, Shard
 
 from titan_b200.utils.logging import logger
 
@@ -119,6 +119,20 @@ def set_determinism(seed: int | None, deterministic: bool, *, parallel_dims=None
 
 
 # ----------------------------------------------------------------------- gradient clipping
+@torch.no_grad()
+def reduce_partial_grads(parameters) -> int:
+    """Replicated parameters applied to sequence-sharded activations (sequence-parallel norms) end backward with a
+    `Partial` DTensor gradient: one pending sum over the mesh.  Reduce those now, so that clipping and optimizers
+    that read local shards see the complete gradient.  Returns how many gradients were reduced."""
+    n = 0
+    for p in parameters:
+        g = p.grad
+        if isinstance(g, DTensor) and any(isinstance(pl, Partial) for pl in g.placements):
+            p.grad = g.redistribute(placements=[Replicate() if isinstance(pl, Partial) else pl for pl in g.placements])
+            n += 1
+    return n
+
+
 def _pow_sum(grads: list[torch.Tensor], p: float) -> torch.Tensor:
     local = [g.to_local() if isinstance(g, DTensor) else g for g in grads]
     if p == math.inf:

@@ -329,6 +329,8 @@ class Trainer:
         losses = [self.forward_backward_step(inp, lab, global_valid) for inp, lab in micro]
 
         params = [p for m in self.model_parts for p in m.parameters()]
+        if pd.tp_enabled:
+            dist_utils.reduce_partial_grads(params)
         grad_norm = dist_utils.clip_grad_norm_(
             params, self.config.training.max_norm, foreach=True,
             pp_mesh=pd.get_optional_mesh("pp") if dist.is_initialized() else None, ep_enabled=pd.ep_enabled,
