@@ -154,11 +154,57 @@ def bench_elementwise(iters):
          frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
 
 
+def profile_case(name: str, launches: int = 3) -> None:
+    """One small workload (inputs larger than L2, well under 1 GB on the device), launched a few times: the
+    target of a profiler capture.  Prints nothing but the case name; timings come from the bench modes."""
+    dev, bf = "cuda", torch.bfloat16
+    if name == "gemm":
+        from titan_b200.ops.gemm import gemm
+
+        a, b = torch.randn(8192, 4096, device=dev, dtype=bf), torch.randn(4096, 4096, device=dev, dtype=bf)
+        out = torch.empty(8192, 4096, device=dev, dtype=bf)
+        fn = lambda: gemm(a, b, out=out)  # noqa: E731
+    elif name == "gemm_wgrad":
+        from titan_b200.ops.gemm import gemm
+
+        a, b = torch.randn(8192, 14336, device=dev, dtype=bf), torch.randn(8192, 4096, device=dev, dtype=bf)
+        out = torch.empty(14336, 4096, device=dev, dtype=bf)
+        fn = lambda: gemm(a, b, a_mn=True, b_mn=True, out=out)  # noqa: E731
+    elif name == "rmsnorm_bwd":
+        from titan_b200.ops.norm import rms_norm
+
+        x = torch.randn(16384, 4096, device=dev, dtype=bf, requires_grad=True)
+        w = torch.ones(4096, device=dev, dtype=bf, requires_grad=True)
+        g = torch.randn(16384, 4096, device=dev, dtype=bf)
+
+        def fn():
+            x.grad = w.grad = None
+            rms_norm(x, w, 1e-6).backward(g)
+    elif name == "indexer_topk":
+        from titan_b200.ops.dsa import lightning_indexer_topk
+
+        q = torch.randn(1, 4096, 64, 128, device=dev, dtype=bf)
+        k = torch.randn(1, 16384, 1, 128, device=dev, dtype=bf)
+        w = torch.rand(1, 4096, 64, device=dev)
+        fn = lambda: lightning_indexer_topk(q, w, k, 2048, 16384 - 4096)  # noqa: E731
+    else:
+        raise SystemExit(f"unknown profile case {name!r}")
+    for _ in range(launches):
+        fn()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "launches": launches}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="gemm,elementwise")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--profile-case", default=None,
+                    help="run one small case a few times and exit (gemm | gemm_wgrad | rmsnorm_bwd | indexer_topk)")
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case)
+        return
     which = set(args.only.split(","))
     if "gemm" in which:
         bench_gemm(args.iters)

@@ -327,6 +327,8 @@ class ModelConfigRef:
     flavor: str = "debugmodel"
     hf_assets_path: str = "./assets/hf"
     tokenizer_path: str | None = None
+    overrides: dict[str, Any] = field(default_factory=dict)
+    """Fields of the flavor's model config to replace (e.g. ``{"mask_type": "varlen"}``)."""
 
 
 @dataclass(kw_only=True, slots=True)

@@ -19,7 +19,9 @@ class FusedRMSNorm(RMSNorm):
         eps = self.eps if self.eps is not None else torch.finfo(x.dtype).eps
         w = self.weight
         if hasattr(w, "to_local"):  # sequence-parallel norm: weight is a replicated DTensor
-            w = w.to_local()
+            from titan_b200.parallel.tensor_parallel import norm_weight_local
+
+            w = norm_weight_local(w, x)
         if hasattr(x, "to_local"):
             from torch.distributed.tensor import DTensor
 

@@ -61,7 +61,13 @@ class RMSNorm(Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         eps = self.eps if self.eps is not None else torch.finfo(x.dtype).eps
-        return F.rms_norm(x, (self.dim,), self.weight, eps)
+        w = self.weight
+        if hasattr(w, "to_local") and not hasattr(x, "to_local"):
+            # replicated weight on per-rank activations (local heads / sequence slice)
+            from titan_b200.parallel.tensor_parallel import norm_weight_local
+
+            w = norm_weight_local(w, x)
+        return F.rms_norm(x, (self.dim,), w, eps)
 
     def init_states(self, **kwargs) -> None:
         nn.init.ones_(self.weight)

@@ -38,6 +38,9 @@ __all__ = [
     "AwaitRowwiseParallel",
     "PrepareModuleInputOutputWithBwdAllReduce",
     "SequenceShardedLinear",
+    "ReplicateParams",
+    "norm_weight_local",
+    "replicated_param_local",
     "maybe_enable_async_tp",
     "async_tp_enabled",
 ]
@@ -151,6 +154,27 @@ def replicated_param_local(p, *, partial_grad: bool):
     if partial_grad:
         local = _AllReduceBwd.apply(local, p.device_mesh.get_group())
     return local
+
+
+def norm_weight_local(w, x):
+    """Local weight of a norm whose parameter is replicated over a mesh.  The gradient is complete on every rank only
+    if the activations are replicated too (a `Replicate` DTensor); sharded DTensors and plain local tensors (per-rank
+    heads or sequence slices) leave a partial sum that is reduced in backward."""
+    if not isinstance(w, DTensor):
+        return w
+    replicated = isinstance(x, DTensor) and all(isinstance(pl, Replicate) for pl in x.placements)
+    return replicated_param_local(w, partial_grad=not replicated)
+
+
+class ReplicateParams(ParallelStyle):
+    """Only turns the module's parameters into replicated DTensors (uniform layout for clipping / checkpoints); the
+    module itself keeps working on local tensors."""
+
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        for name, p in list(module.named_parameters(recurse=False)):
+            module.register_parameter(name, nn.Parameter(distribute_tensor(p.data, device_mesh, [Replicate()]),
+                                                         requires_grad=p.requires_grad))
+        return module
 
 
 class SequenceShardedLinear(ParallelStyle):

@@ -114,6 +114,10 @@ class Trainer:
         # ---- model spec, dataloader
         self.model_spec = get_model_spec(cfg.model.name, cfg.model.flavor)
         model_config = self.model_spec.model
+        for key, value in cfg.model.overrides.items():
+            if not hasattr(model_config, key):
+                raise AttributeError(f"model config of {cfg.model.name}/{cfg.model.flavor} has no field {key!r}")
+            setattr(model_config, key, value)
         model_config.update_from_config(trainer_config=cfg)
         self.model_config = model_config
         self.tokenizer = self._build_tokenizer()
@@ -272,6 +276,13 @@ class Trainer:
         extra_kwargs: dict[str, Any] = {}
         for hook in stash.post_dataloading_hooks():
             inputs, labels, extra_inputs, extra_kwargs = hook(self, inputs, labels, extra_inputs, extra_kwargs)
+        if getattr(self.model_config, "mask_type", None) == "varlen" and "positions" in extra_inputs:
+            # document boundaries of the FULL sequence: built before any context-parallel slicing
+            from titan_b200.models.common.varlen_attention import build_varlen_metadata
+
+            extra_kwargs["attention_masks"] = build_varlen_metadata(extra_inputs["positions"])
+        if "positions" in extra_inputs:  # sliced together with the tokens under context parallelism
+            extra_kwargs["positions"] = extra_inputs.pop("positions")
         if self.parallel_dims.cp_enabled:
             from titan_b200.parallel.context_parallel.sharding import prepare_context_parallel_input
 
