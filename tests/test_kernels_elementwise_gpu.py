@@ -14,7 +14,8 @@ def _need_cuda(cuda_device):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,dim", [(37, 256), (512, 4096), (5, 1536)])
+@pytest.mark.parametrize("rows,dim", [(37, 256), (512, 4096), (5, 1536), (1000, 128), (333, 512), (129, 1024),
+                                      (64, 2048), (77, 8192), (9, 16384), (4099, 4096)])
 def test_rmsnorm_fwd_bwd(dtype, rows, dim):
     from titan_b200.ops.norm import rms_norm
 

@@ -38,6 +38,7 @@ __all__ = [
     "DSV4EncoderConfig",
     "ChatDataLoaderConfig",
     "SyntheticDataLoaderConfig",
+    "MultiModalDataLoaderConfig",
     "TrainerConfig",
     "trainer_base_config",
     "debug_single_node_eq_pruned_config",
@@ -290,6 +291,22 @@ class SyntheticDataLoaderConfig:
 
 
 @dataclass(kw_only=True, slots=True)
+class MultiModalDataLoaderConfig:
+    """Image + text batches.  ``dataset="synthetic"`` draws random patches and tokens from a fixed seed; any other name
+    is looked up in the multimodal dataset registry (needs the `datasets` package and local files)."""
+
+    dataset: str = "synthetic"
+    dataset_path: str | None = None
+    max_patches_per_image: int = 256
+    max_images_per_batch: int = 64
+    patch_size: int = 16
+    n_channels: int = 3
+    seed: int = 0
+    pin_memory: bool = True
+    infinite: bool = True
+
+
+@dataclass(kw_only=True, slots=True)
 class ChatEncoderConfig:
     name: str = "chatml"
 
@@ -300,6 +317,9 @@ class DSV4EncoderConfig(ChatEncoderConfig):
     encoding_path: str = ""
     """Path of the external `encoding_dsv4.py` implementation."""
     mode: Literal["chat", "thinking"] = "chat"
+    drop_thinking: bool = True
+    """Drop thinking blocks of earlier assistant turns (kept anyway when the conversation defines tools)."""
+    reasoning_effort: Literal["max", "high"] | None = None
 
 
 @dataclass(kw_only=True, slots=True)
@@ -348,7 +368,7 @@ class TrainerConfig:
     comm: CommConfig = field(default_factory=CommConfig)
     debug: DebugConfig = field(default_factory=DebugConfig)
     memory_sim: MemorySimConfig = field(default_factory=MemorySimConfig)
-    dataloader: TextDataLoaderConfig | ChatDataLoaderConfig | SyntheticDataLoaderConfig = field(
+    dataloader: TextDataLoaderConfig | ChatDataLoaderConfig | SyntheticDataLoaderConfig | MultiModalDataLoaderConfig = field(
         default_factory=SyntheticDataLoaderConfig
     )
 

@@ -11,6 +11,7 @@
 // Semantics follow the reference's fused norm op (converters/kernels/rms_norm.py:39-44:
 // `npu_rms_norm(x, w, eps)` returning (y, rstd)).
 #include "../common/tb_common.cuh"
+#include "rmsnorm_fast.cuh"
 
 namespace {
 
@@ -117,6 +118,12 @@ int fwd_impl(const void* x, const void* w, void* y, float* rstd, int rows, int d
   if (dim % Vec16<T>::N != 0) return TB_ERR_ARG;
   const int grid = (rows + 3) / 4;
   if (grid == 0) return 0;
+  if (tb_rms::fwd_fast<T>((const T*)x, (const T*)w, (T*)y, rstd, rows, dim, eps, st)) {
+    TB_CUDA_CHECK(cudaGetLastError());
+    tb_note_launch(1);
+    return 0;
+  }
+  // rows too long for registers: two passes, the second one from L1/L2
   rmsnorm_fwd_kernel<T><<<grid, 128, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, rows, dim, eps);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
@@ -142,13 +149,30 @@ int bwd_launch(const void* g, const void* x, const void* w, const float* rstd, v
 
 }  // namespace
 
-// Number of partial rows the backward writes (= its grid size); scratch must hold grid*dim floats.
-TB_API int tb_rmsnorm_bwd_grid(int rows, int dim) {
+namespace {
+int legacy_bwd_grid(int rows, int dim) {
   const int warps = dim <= 8192 ? 4 : 2;
   int grid = (rows + warps - 1) / warps;
   const int cap = 148 * 2;
   if (grid > cap) grid = cap;
   return grid < 1 ? 1 : grid;
+}
+
+constexpr int kBwdGridCap = 148 * 8;
+
+// 16-bit types take the register-resident kernels for every supported dim; fp32 rows beyond 8192 elements do not
+// fit and keep the shared-memory kernel.
+bool bwd_uses_fast(int dim, int vec) { return dim % vec == 0 && (dim / vec + 511) / 512 <= 4; }
+}  // namespace
+
+// Number of partial rows the backward writes (= its grid size); scratch must hold grid*dim floats.  The vector
+// width only matters for fp32 rows longer than 8192 elements, which report the (larger) bound of both layouts.
+TB_API int tb_rmsnorm_bwd_grid(int rows, int dim) {
+  const int fast = tb_rms::bwd_plan(rows, dim, 8, kBwdGridCap).grid;
+  const int fast32 = tb_rms::bwd_plan(rows, dim, 4, kBwdGridCap).grid;
+  const int legacy = legacy_bwd_grid(rows, dim);
+  int m = fast > fast32 ? fast : fast32;
+  return m > legacy ? m : legacy;
 }
 
 // dtype: 0 = fp32, 1 = bf16, 2 = fp16
@@ -166,10 +190,21 @@ TB_API int tb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, in
 TB_API int tb_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, void* dx, void* dw,
                           float* scratch, int rows, int dim, int dtype, cudaStream_t st) {
   if (dim > 16384 || rows < 1) return TB_ERR_ARG;
-  const int grid = tb_rmsnorm_bwd_grid(rows, dim);
+  const int grid = legacy_bwd_grid(rows, dim);
 #define TB_BWD(T)                                                                              \
   do {                                                                                         \
     if (dim % Vec16<T>::N != 0) return TB_ERR_ARG;                                             \
+    if (bwd_uses_fast(dim, Vec16<T>::N)) {                                                     \
+      const tb_rms::BwdPlan plan = tb_rms::bwd_plan(rows, dim, Vec16<T>::N, kBwdGridCap);      \
+      if (tb_rms::bwd_fast<T>(plan, (const T*)g, (const T*)x, (const T*)w, rstd, (T*)dx, scratch, rows, dim, st)) { \
+        TB_CUDA_CHECK(cudaGetLastError());                                                     \
+        tb_note_launch(1);                                                                     \
+        rmsnorm_dw_reduce_kernel<T><<<(dim + 255) / 256, 256, 0, st>>>(scratch, (T*)dw, plan.grid, dim); \
+        TB_CUDA_CHECK(cudaGetLastError());                                                     \
+        tb_note_launch(1);                                                                     \
+        return 0;                                                                              \
+      }                                                                                        \
+    }                                                                                          \
     if (dim <= 8192) return bwd_launch<T, 4>(g, x, w, rstd, dx, dw, scratch, grid, rows, dim, st); \
     return bwd_launch<T, 2>(g, x, w, rstd, dx, dw, scratch, grid, rows, dim, st);              \
   } while (0)

@@ -100,7 +100,7 @@ TB_API int tb_grouped_gemm_k(const void* A, const void* B, void* C, const int* o
   return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
 }
 
-// Lightning-indexer scores.  q: [S*H, D] (row = query*H + head), k: [T, D], w: [S*H] fp32 head weights,
+// Lightning-indexer scores.  q: [S*H, D] (row = query*H + head; H a power of two), k: [T, D], w: [S*H] fp32 weights,
 // scores: [S, ld] fp32 with scores[s, t] = Σ_h w[s,h]·relu(q[s,h]·k[t]) for every visible key
 // t < (pos_offset + s + 1) / ratio (ratio 1: causal tokens; ratio r: compressed keys, one per r tokens, visible once
 // their block is complete).  Entries in the causal future of a query are left unwritten where a whole tile is
@@ -109,17 +109,17 @@ TB_API int tb_indexer_scores(const void* q, const void* k, const float* w, float
                              long long ld, int pos_offset, int ratio, int dtype, int* status, cudaStream_t st) {
   if (S <= 0 || T <= 0) return 0;
   if (ratio < 1) return TB_ERR_ARG;
-  if (H < 1 || BM % H != 0 || D % 8 || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  if (H < 1 || H > BN || (H & (H - 1)) != 0 || D % 8 || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
   AMaps am;
   CUtensorMap tb_;
   CMaps cm;
-  const int M = S * H;
-  if (int rc = make_a_map(&am.m[0], q, dtype, 0, (uint64_t)M, (uint64_t)D, D)) return rc;
-  if (int rc = make_b_map(&tb_, k, dtype, 0, (uint64_t)T, (uint64_t)D, D)) return rc;
+  const int N = S * H;  // columns: (query, head) pairs; rows: keys
+  if (int rc = make_a_map(&am.m[0], k, dtype, 0, (uint64_t)T, (uint64_t)D, D)) return rc;
+  if (int rc = make_b_map(&tb_, q, dtype, 0, (uint64_t)N, (uint64_t)D, D)) return rc;
   GemmParams p;
-  fill_common(p, INDEXER, M, T, D, 0, 0, dtype, 0, 0, T, nullptr, status);
+  fill_common(p, INDEXER, T, N, D, 0, 0, dtype, 0, 0, N, nullptr, status);
   p.idx_weights = w; p.idx_heads = H; p.idx_scores = scores; p.idx_ld = ld; p.idx_pos_offset = pos_offset;
   p.idx_ratio = ratio;
-  const int tiles = ((M + BM - 1) / BM) * ((T + BN - 1) / BN);
+  const int tiles = ((T + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
 }

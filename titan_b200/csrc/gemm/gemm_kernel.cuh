@@ -266,27 +266,61 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
       if (p.mode == SCATTER) dst_rank = tl.m0 / p.m_shard;
 
       if (p.mode == INDEXER) {
-        // score[q, t] = Σ_h w[q, h] · relu(acc[(q, h), t]); rows of the tile are (query, head) pairs
-        float* stage = reinterpret_cast<float*>(smem_c);  // [128 rows][33] fp32 (padded against bank conflicts)
-        const int heads = p.idx_heads, qpt = BM / heads;
-        const float wrow = row < p.M ? p.idx_weights[row] : 0.f;
-        const int et = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
+        // score[q, t] = Σ_h w[q, h] · relu(acc[t, (q, h)]): rows of the tile are KEYS (one per TMEM lane = per
+        // thread), columns are (query, head) pairs, so the head sum runs inside a thread with no exchange at all;
+        // for a fixed query the 128 threads store 128 consecutive keys (coalesced).
+        float* wst = reinterpret_cast<float*>(smem_c);  // weights of this tile's 256 columns (broadcast reads)
+        const int hmask = p.idx_heads - 1;              // heads is a power of two
+        const int hshift = 31 - __clz(p.idx_heads);
+        const int et = (warp - 2) * 32 + lane;          // 0..127 among the epilogue threads
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's readers are done with wst
+        for (int i = et; i < BN; i += 128) wst[i] = (tl.n0 + i) < p.N ? p.idx_weights[tl.n0 + i] : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int queries = p.N >> hshift;
+        if (p.idx_heads >= 32) {
+          // A query's heads end on 32-column chunk boundaries.  One epilogue warp runs alone on its scheduler, so
+          // the loop is written for latency: four independent accumulators, weights as 128-bit shared loads, the
+          // next chunk's tcgen05.ld in flight while this one is summed, one boundary test per chunk.
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+          uint32_t r[2][32];
+          tmem_ld_32x32(taddr, r[0]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) stage[row_in_tile * 33 + i] = fmaxf(__uint_as_float(r[i]), 0.f) * wrow;
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          for (int o = et; o < qpt * 32; o += 128) {
-            const int ql = o >> 5, col = o & 31;
-            float sum = 0.f;
-            for (int h = 0; h < heads; ++h) sum += stage[(ql * heads + h) * 33 + col];
-            const int query = tl.m0 / heads + ql, key = tl.n0 + c * 32 + col;
-            if (query * heads < p.M && key < p.N) p.idx_scores[(long long)query * p.idx_ld + key] = sum;
+          for (int c = 0; c < BN / 32; ++c) {
+            tmem_ld_wait();
+            if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, r[(c + 1) & 1]);
+            const float4* w4 = reinterpret_cast<const float4*>(wst + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 w = w4[i];
+              s0 = fmaf(fmaxf(__uint_as_float(r[c & 1][4 * i + 0]), 0.f), w.x, s0);
+              s1 = fmaf(fmaxf(__uint_as_float(r[c & 1][4 * i + 1]), 0.f), w.y, s1);
+              s2 = fmaf(fmaxf(__uint_as_float(r[c & 1][4 * i + 2]), 0.f), w.z, s2);
+              s3 = fmaf(fmaxf(__uint_as_float(r[c & 1][4 * i + 3]), 0.f), w.w, s3);
+            }
+            if ((((c + 1) * 32) & hmask) == 0) {  // last head of a query
+              const int query = (tl.n0 + c * 32) >> hshift;
+              if (row < p.M && query < queries)
+                p.idx_scores[(long long)query * p.idx_ld + row] = (s0 + s1) + (s2 + s3);
+              s0 = s1 = s2 = s3 = 0.f;
+            }
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+        } else {
+          float sum = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              sum = fmaf(fmaxf(__uint_as_float(r[i]), 0.f), wst[c * 32 + i], sum);
+              if (((c * 32 + i + 1) & hmask) == 0) {  // last head of a query
+                const int query = (tl.n0 + c * 32 + i) >> hshift;
+                if (row < p.M && query < queries) p.idx_scores[(long long)query * p.idx_ld + row] = sum;
+                sum = 0.f;
+              }
+            }
+          }
         }
         tc_fence_before();
         __syncwarp();

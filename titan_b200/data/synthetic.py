@@ -83,4 +83,11 @@ def build_dataloader(cfg, *, model_config, training, dp_rank: int, dp_world_size
 
         return build_chat_dataloader(cfg, tokenizer=tokenizer, training=training, dp_rank=dp_rank,
                                      dp_world_size=dp_world_size)
+    from titan_b200.config.configs import MultiModalDataLoaderConfig
+
+    if isinstance(cfg, MultiModalDataLoaderConfig):
+        from titan_b200.data.mm_synthetic import build_mm_dataloader
+
+        return build_mm_dataloader(cfg, model_config=model_config, training=training, dp_rank=dp_rank,
+                                   dp_world_size=dp_world_size, tokenizer=tokenizer)
     raise TypeError(f"unknown dataloader config {type(cfg).__name__}")

@@ -50,10 +50,10 @@ def softplus_stable(x: torch.Tensor) -> torch.Tensor:
 
 def build_hash_routing_table(vocab_size: int, num_experts: int, top_k: int, device=None, seed: int = 0):
     """Fixed token-id → expert-ids table ``[vocab, top_k]`` (distinct experts per token, deterministic)."""
-    g = torch.Generator().manual_seed(seed)
-    base = torch.randint(0, num_experts, (vocab_size, 1), generator=g)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    base = torch.randint(0, num_experts, (vocab_size, 1), generator=g, device="cpu")
     step = max(num_experts // max(top_k, 1), 1)
-    table = (base + torch.arange(top_k).view(1, -1) * step) % num_experts
+    table = (base + torch.arange(top_k, device="cpu").view(1, -1) * step) % num_experts
     return table.to(device=device, dtype=torch.int64)
 
 

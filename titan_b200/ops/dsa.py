@@ -55,7 +55,9 @@ def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0
 
     ``ratio`` > 1: the keys are compressed blocks of ``ratio`` tokens; query ``s`` sees the first
     ``(pos_offset + s + 1) // ratio`` of them."""
-    if not q_idx.is_cuda or q_idx.dtype not in (torch.bfloat16, torch.float16) or 128 % q_idx.shape[2] != 0:
+    heads = q_idx.shape[2]
+    if (not q_idx.is_cuda or q_idx.dtype not in (torch.bfloat16, torch.float16) or heads > 256
+            or heads & (heads - 1) != 0 or q_idx.shape[3] % 8 != 0):
         return lightning_indexer_topk_ref(q_idx, weights, k_idx, topk, pos_offset, ratio)
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]

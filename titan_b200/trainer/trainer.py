@@ -232,6 +232,8 @@ class Trainer:
 
         if isinstance(self.config.dataloader, SyntheticDataLoaderConfig):
             return None
+        if getattr(self.config.dataloader, "dataset", None) == "synthetic":  # synthetic multimodal batches
+            return None
         from titan_b200.data.tokenizer import build_tokenizer
 
         return build_tokenizer(self.config.model.tokenizer_path or self.config.model.hf_assets_path)
