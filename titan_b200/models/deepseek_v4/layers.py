@@ -91,19 +91,20 @@ def compress_visible_idxs(ratio: int, seqlen: int, offset: int = 0, device=None)
     return torch.where(hidden, -1, m + offset)
 
 
-def li_compute(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset: int = 0):
+def li_compute(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset: int = 0, pos_offset: int = 0):
     """Lightning-indexer selection over compressed keys.
 
-    q_indexer [B,S,Hi,Di], k_indexer [B,S/ratio,Di], weights [B,S,Hi] → (idx [B,S,k] with ``offset`` added and -1
-    for hidden keys, scores [B,S,k] – the selected logits, differentiable)."""
-    B, S = q_indexer.shape[:2]
+    q_indexer [B,S,Hi,Di], k_indexer [B,Tc,Di], weights [B,S,Hi] → (idx [B,S,k] with ``offset`` added and -1
+    for hidden keys, scores [B,S,k] – the selected logits, differentiable).  Local query ``s`` stands at global
+    position ``pos_offset + s`` and sees the compressed keys whose block of ``ratio`` tokens is complete."""
+    S, T = q_indexer.shape[1], k_indexer.shape[1]
     score = torch.einsum("bshd,btd->bsht", q_indexer, k_indexer)
     score = (F.relu(score) * weights.unsqueeze(-1)).sum(dim=2)
-    base = torch.arange(S, device=score.device).unsqueeze(1)
+    base = torch.arange(S, device=score.device).unsqueeze(1) + pos_offset
     visible_end = (base + 1) // ratio
-    hidden = torch.arange(S // ratio, device=score.device).unsqueeze(0) >= visible_end
+    hidden = torch.arange(T, device=score.device).unsqueeze(0) >= visible_end
     score = score + torch.where(hidden, torch.finfo(q_indexer.dtype).min, 0.0)
-    vals, idx = score.topk(min(index_topk, S // ratio), dim=-1)
+    vals, idx = score.topk(min(index_topk, T), dim=-1)
     return torch.where(idx >= visible_end, -1, idx + offset), vals
 
 

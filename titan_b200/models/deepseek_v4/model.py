@@ -111,19 +111,23 @@ class InnerAttention(Module):
             dist = torch.gather(cmp, -1, local).masked_fill(compress_idx < 0, 0.0)
         return out, dist
 
-    def forward(self, q, kv, kv_compress, q_idx, k_idx, weights):
-        S = kv.shape[1]
+    def forward(self, q, kv, kv_compress, q_idx, k_idx, weights, q_pos0: int = 0, kv_pos0: int = 0):
+        """``q_pos0`` / ``kv_pos0``: global positions of the first local query / raw key (context parallelism hands in
+        a slice of the queries with the previous rank's window prepended to the keys; compressed keys are global)."""
+        offset = kv.shape[1]
         sink = self.attn_sink.to_local() if hasattr(self.attn_sink, "to_local") else self.attn_sink
         compress_idx = scores = None
         has_li = q_idx is not None
         if has_li:
             sel = self.select or li_compute
-            compress_idx, scores = sel(q_idx, k_idx, weights, self.compress_ratio, self.index_topk, S)
+            compress_idx, scores = sel(q_idx, k_idx, weights, self.compress_ratio, self.index_topk, offset, q_pos0)
         want = has_li and self.enable_indexer_loss and torch.is_grad_enabled()
         if self.core is not None:
             out, dist = self.core(q, kv, sink, kv_compress, compress_idx, self.window, self.compress_ratio,
-                                  self.scale, want)
+                                  self.scale, want, q_pos0=q_pos0, kv_pos0=kv_pos0)
         else:
+            if q_pos0 or kv_pos0:
+                raise NotImplementedError("the dense attention oracle has no context-parallel form")
             out, dist = self._dense_core(q, kv, sink, kv_compress, compress_idx, want)
         if want:
             if self.tp_group is not None:  # every rank holds the probability mass of its own heads only
@@ -172,6 +176,8 @@ class V4Attention(Module):
         self.post_attention = PostAttention(cfg)
 
     def forward(self, x, freqs_cis, attention_masks=None, positions=None):
+        if getattr(self, "cp", None) is not None:  # context parallelism: set by its strategy
+            return self.cp.forward(self, x, freqs_cis)
         q, kv, kv_c, q_idx, k_idx, w = self.pre_attention(x, freqs_cis, positions)
         o = self.inner_attention(q, kv, kv_c, q_idx, k_idx, w)
         return self.post_attention(o, freqs_cis, positions)

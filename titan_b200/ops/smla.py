@@ -28,18 +28,21 @@ from torch.utils.checkpoint import checkpoint
 __all__ = ["smla_attention", "li_select"]
 
 
-def _chunk(q, kv, sink, kvc, cidx, s0: int, window: int, ratio: int, scale: float, n_heads_total: int,
-           want_dist: bool):
-    """q [Sc,H,hd], kv [S,hd], kvc [Tc,hd] | None, cidx [Sc,k] local compressed ids (-1 empty) | None."""
+def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, ratio: int, scale: float,
+           n_heads_total: int, want_dist: bool):
+    """q [Sc,H,hd] (local queries s0..s0+Sc), kv [Tk,hd] raw keys where local query s sits at key index s + koff,
+    kvc [Tc,hd] | None compressed keys (global ids), cidx [Sc,k] compressed ids (-1 empty) | None; ``qpos0`` is the
+    global position of local query 0."""
     Sc, H, hd = q.shape
     s1 = s0 + Sc
-    t0 = max(0, s0 - window + 1)
-    kwin = kv[t0:s1]  # [W, hd]
+    t0 = max(0, s0 + koff - window + 1)
+    kwin = kv[t0: s1 + koff]  # [W, hd]
     qh = q.transpose(0, 1)  # [H, Sc, hd]
     logit_w = torch.matmul(qh, kwin.t()).float() * scale  # [H, Sc, W]
     spos = torch.arange(s0, s1, device=q.device).unsqueeze(1)
-    tpos = torch.arange(t0, s1, device=q.device).unsqueeze(0)
-    logit_w = logit_w.masked_fill(((tpos > spos) | (tpos <= spos - window)).unsqueeze(0), float("-inf"))
+    kpos = spos + koff
+    tpos = torch.arange(t0, s1 + koff, device=q.device).unsqueeze(0)
+    logit_w = logit_w.masked_fill(((tpos > kpos) | (tpos <= kpos - window)).unsqueeze(0), float("-inf"))
     parts = [logit_w]
     ksel = None
     if kvc is not None and ratio > 1:
@@ -48,10 +51,10 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, window: int, ratio: int, scale: floa
             logit_c = torch.einsum("hsd,skd->hsk", qh, ksel).float() * scale
             logit_c = logit_c.masked_fill((cidx < 0).unsqueeze(0), float("-inf"))
         else:
-            c_end = s1 // ratio
+            c_end = min((qpos0 + s1) // ratio, kvc.shape[0])
             kc = kvc[:c_end]
             logit_c = torch.matmul(qh, kc.t()).float() * scale  # [H, Sc, c_end]
-            hidden = torch.arange(c_end, device=q.device).unsqueeze(0) >= (spos + 1) // ratio
+            hidden = torch.arange(c_end, device=q.device).unsqueeze(0) >= (qpos0 + spos + 1) // ratio
             logit_c = logit_c.masked_fill(hidden.unsqueeze(0), float("-inf"))
         parts.append(logit_c)
     parts.append(sink.float().view(H, 1, 1).expand(H, Sc, 1))
@@ -72,14 +75,23 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, window: int, ratio: int, scale: floa
 
 
 def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: int, scale: float,
-                   want_dist: bool = False, *, n_heads_total: int | None = None, chunk: int = 256):
-    """q [B,S,H,hd], kv [B,S,hd], sink [H], kv_compress [B,Tc,hd] | None, compress_idx [B,S,k] | None (ids offset by
-    S as in the dense layout; -1 = empty) → (out [B,S,H,hd], dist [B,S,k] | None)."""
+                   want_dist: bool = False, *, n_heads_total: int | None = None, chunk: int = 256, q_pos0: int = 0,
+                   kv_pos0: int = 0, idx_offset: int | None = None):
+    """q [B,S,H,hd], kv [B,Tk,hd], sink [H], kv_compress [B,Tc,hd] | None, compress_idx [B,S,k] | None (compressed ids
+    + ``idx_offset``, default ``Tk`` as in the dense layout; -1 = empty) → (out [B,S,H,hd], dist [B,S,k] | None).
+
+    Without context parallelism ``Tk == S``.  With it the local queries start at global position ``q_pos0`` and the raw
+    keys at ``kv_pos0 <= q_pos0`` (the previous rank's window is prepended): ``Tk == S + q_pos0 - kv_pos0``; the
+    compressed keys are global."""
     B, S, H, _ = q.shape
     n_heads_total = n_heads_total or H
+    koff = q_pos0 - kv_pos0
+    if kv.shape[1] != S + koff:
+        raise ValueError(f"raw keys must cover the local queries and their window: {kv.shape[1]} != {S} + {koff}")
+    idx_offset = kv.shape[1] if idx_offset is None else idx_offset
     local_idx = None
     if compress_idx is not None:
-        local_idx = torch.where(compress_idx < 0, compress_idx, compress_idx - S)
+        local_idx = torch.where(compress_idx < 0, compress_idx, compress_idx - idx_offset)
     outs, dists = [], []
     need_grad = torch.is_grad_enabled() and (q.requires_grad or kv.requires_grad)
     for b in range(B):
@@ -87,8 +99,8 @@ def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: i
         for s0 in range(0, S, chunk):
             s1 = min(s0 + chunk, S)
             args = (q[b, s0:s1], kv[b], sink, None if kv_compress is None else kv_compress[b],
-                    None if local_idx is None else local_idx[b, s0:s1], s0, window, ratio, scale, n_heads_total,
-                    want_dist)
+                    None if local_idx is None else local_idx[b, s0:s1], s0, koff, q_pos0, window, ratio, scale,
+                    n_heads_total, want_dist)
             res = checkpoint(_chunk, *args, use_reentrant=False) if need_grad else _chunk(*args)
             ob.append(res[0])
             if len(res) > 1:
@@ -101,17 +113,18 @@ def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: i
     return out, dist
 
 
-def li_select(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset: int = 0):
+def li_select(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset: int = 0, pos_offset: int = 0):
     """Fused counterpart of the eager selection: (idx [B,S,k] with ``offset`` added, -1 = empty; scores [B,S,k]).
 
     Selection (no gradient) runs on the scoring GEMM + radix-select kernels; the returned scores are recomputed at
-    the selected keys only and carry the gradient to the indexer."""
+    the selected keys only and carry the gradient to the indexer.  ``pos_offset`` is the global position of local
+    query 0 (context parallelism: the keys are global, the queries a slice)."""
     from titan_b200.ops.dsa import lightning_indexer_topk
 
-    B, S = q_indexer.shape[:2]
-    T = k_indexer.shape[1]
-    k = min(index_topk, S // ratio)
-    idx, _ = lightning_indexer_topk(q_indexer.detach(), weights.detach(), k_indexer.detach().unsqueeze(2), k, 0, ratio)
+    B = q_indexer.shape[0]
+    k = min(index_topk, k_indexer.shape[1])
+    idx, _ = lightning_indexer_topk(q_indexer.detach(), weights.detach(), k_indexer.detach().unsqueeze(2), k,
+                                    pos_offset, ratio)
     idx = idx.long()
     safe = idx.clamp(min=0)
     ksel = k_indexer[torch.arange(B, device=idx.device).view(B, 1, 1), safe]  # [B,S,k,D]
