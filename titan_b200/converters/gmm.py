@@ -47,6 +47,11 @@ class FusedGroupedExperts(Module):
     def forward_padded(self, xp: torch.Tensor, offs: torch.Tensor, scores: torch.Tensor | None = None):
         """xp: padded expert-major rows [cap, D]; offs: cumulative padded ends of the LOCAL experts."""
         w13, w2 = self._local(self.w13), self._local(self.w2)
+        mx = getattr(self, "mx_round_mode", None)
+        if mx is not None:  # MXFP8 experts: both GEMMs block-quantised along their contraction dims
+            h13 = self.mx_grouped_mm(xp, w13.to(xp.dtype), offs, mx)
+            h = swiglu_fused(h13, scores, self.swiglu_limit)
+            return self.mx_grouped_mm(h, w2.to(xp.dtype), offs, mx)
         h13 = grouped_linear(xp, w13.to(xp.dtype), offs)
         h = swiglu_fused(h13, scores, self.swiglu_limit)
         return grouped_linear(h, w2.to(xp.dtype), offs)
@@ -55,6 +60,10 @@ class FusedGroupedExperts(Module):
         """Unpadded expert-sorted rows (the layout of the NCCL expert-parallel path)."""
         w13, w2 = self._local(self.w13), self._local(self.w2)
         offs = torch.cumsum(num_tokens_per_expert, 0, dtype=torch.int32)
+        mx = getattr(self, "mx_round_mode", None)
+        if mx is not None:
+            h13 = self.mx_grouped_mm(x, w13.to(x.dtype), offs, mx)
+            return self.mx_grouped_mm(swiglu_fused(h13, None, self.swiglu_limit), w2.to(x.dtype), offs, mx)
         if x.is_cuda:
             h13 = torch._grouped_mm(x.bfloat16(), w13.bfloat16().transpose(-2, -1), offs=offs)
             h = swiglu_fused(h13, None, self.swiglu_limit)

@@ -130,4 +130,17 @@ class ScaledDotProductAttention(Module):
         enable_gqa = q.shape[1] != k.shape[1]
         if attn_mask is not None:
             return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, scale=scale, enable_gqa=enable_gqa)
+        if q.is_cuda:
+            # backend order of the upstream attention wrapper: the cuDNN kernel first (on B200 it runs the Llama-3 8B
+            # shape at 1.38 PFLOP/s forward against 0.35 for the sm_80-style flash kernel), then flash, then the rest
+            with _sdpa_backends():
+                return F.scaled_dot_product_attention(q, k, v, is_causal=self.causal, scale=scale,
+                                                      enable_gqa=enable_gqa)
         return F.scaled_dot_product_attention(q, k, v, is_causal=self.causal, scale=scale, enable_gqa=enable_gqa)
+
+
+def _sdpa_backends():
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    return sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION,
+                        SDPBackend.MATH], set_priority=True)

@@ -185,6 +185,13 @@ class GroupedExperts(Module):
     def forward(self, x: torch.Tensor, num_tokens_per_expert: torch.Tensor) -> torch.Tensor:
         w1, w2, w3 = self._local(self.w1), self._local(self.w2), self._local(self.w3)
         counts = num_tokens_per_expert
+        mx = getattr(self, "mx_round_mode", None)
+        if mx is not None:  # MXFP8 experts (set by the MXFP8 converter)
+            offs = torch.cumsum(counts, 0, dtype=torch.int32)
+            g, u = self.mx_grouped_mm(x, w1.to(x.dtype), offs, mx), self.mx_grouped_mm(x, w3.to(x.dtype), offs, mx)
+            if self.swiglu_limit > 0:
+                g, u = g.clamp(max=self.swiglu_limit), u.clamp(min=-self.swiglu_limit, max=self.swiglu_limit)
+            return self.mx_grouped_mm(F.silu(g) * u, w2.to(x.dtype), offs, mx)
         if self.use_grouped_mm and x.is_cuda:
             return run_experts_grouped_mm(w1, w2, w3, x, counts.to(torch.int32), self.swiglu_limit)
         return run_experts_for_loop(w1, w2, w3, x, counts.long(), self.swiglu_limit)
