@@ -1,0 +1,42 @@
+"""Fused sequence-parallel linears: autograd identities on one rank, and a two-rank run through the library fallbacks
+of the fused ops (same dataflow as on GPUs) that must reproduce the single-rank step."""
+
+import torch
+import torch.distributed as dist
+
+from _launch import launch, step_line
+
+
+def test_ag_multi_linear_and_linear_rs_gradients_single_rank():
+    from titan_b200.parallel.async_tp import ag_multi_linear, linear_rs
+
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29653", rank=0, world_size=1)
+    try:
+        g = dist.group.WORLD
+        torch.manual_seed(0)
+        x = torch.randn(16, 32, requires_grad=True)
+        wa, wb = torch.randn(24, 32, requires_grad=True), torch.randn(8, 32, requires_grad=True)
+        wo = torch.randn(32, 24, requires_grad=True)
+        a, b = ag_multi_linear(x, [wa, wb], g)
+        y = linear_rs(torch.tanh(a), wo, g) + b.sum(dim=1, keepdim=True)
+        y.pow(2).sum().backward()
+        xr, war, wbr, wor = (t.detach().clone().requires_grad_() for t in (x, wa, wb, wo))
+        yr = torch.tanh(xr @ war.t()) @ wor.t() + (xr @ wbr.t()).sum(dim=1, keepdim=True)
+        yr.pow(2).sum().backward()
+        for got, ref in ((x, xr), (wa, war), (wb, wbr), (wo, wor)):
+            assert torch.allclose(got.grad, ref.grad, atol=1e-4, rtol=1e-4)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_async_tp2_reproduces_single_rank_step(tmp_path):
+    folder = str(tmp_path / "run")
+    common = ["--module", "llama3", "--config", "llama3_debugmodel", "--training.seq_len", "256", "--comm.backend",
+              "gloo", "--training.local_batch_size", "1", "--job.dump_folder", folder, "--checkpoint.enable",
+              "--checkpoint.interval", "1", "--training.steps", "2"]
+    ref = step_line(launch(common, 1, 29650), 2)
+    got = step_line(launch([*common, "--checkpoint.load_step", "1", "--parallelism.data_parallel_shard_degree", "1",
+                            "--parallelism.tensor_parallel_degree", "2",
+                            "--parallelism.enable_async_tensor_parallel"], 2, 29651), 2)
+    assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)

@@ -38,6 +38,23 @@ def apply_tp(model: nn.Module, tp_mesh, *, loss_parallel: bool, async_tp: bool =
             ),
         },
     )
+    if async_tp:
+        # fused sequence-parallel linears: weights keep the column / row shards, but no module-level gather or
+        # scatter hooks; the sub-layers exchange plain sequence-sharded tensors and the collectives run inside the
+        # all-gather→GEMM / GEMM→reduce-scatter kernels
+        from titan_b200.parallel.async_tp import enable_for_llama
+        from titan_b200.parallel.tensor_parallel import ShardOnly
+
+        for block in model.layers.values():
+            parallelize_module(block, tp_mesh, {
+                "attention_norm": SequenceParallel(use_local_output=True),
+                "attention.wq": ShardOnly(0), "attention.wk": ShardOnly(0), "attention.wv": ShardOnly(0),
+                "attention.wo": ShardOnly(1),
+                "ffn_norm": SequenceParallel(use_local_output=True),
+                "feed_forward.w1": ShardOnly(0), "feed_forward.w3": ShardOnly(0), "feed_forward.w2": ShardOnly(1),
+            })
+        enable_for_llama(model, tp_mesh)
+        return
     for block in model.layers.values():
         plan = {
             "attention_norm": SequenceParallel(),

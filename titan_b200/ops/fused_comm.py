@@ -100,14 +100,20 @@ def all_gather_matmul_baseline(a_shard, b, group):
     return full @ b.t()
 
 
-def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
-    """``concat_ranks(a_shard) @ b.T`` → [world·m_shard, N].  a_shard [m_shard, K], b [N, K]; m_shard % 128 == 0."""
+def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None, return_gathered: bool = False):
+    """``concat_ranks(a_shard) @ b.T`` → [world·m_shard, N].  a_shard [m_shard, K], b [N, K]; m_shard % 128 == 0.
+
+    ``return_gathered``: also return the gathered operand [world·m_shard, K] (the kernel's copier CTAs build it
+    anyway; sequence-parallel linears reuse it for their other projections and for the weight gradient)."""
     group = group or _STATE["group"]
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     m_shard, K = a_shard.shape
     N = b.shape[0]
     if m_shard % 128 or K % 8 or N % 8 or a_shard.dtype not in (torch.bfloat16, torch.float16):
-        return all_gather_matmul_baseline(a_shard, b, group)
+        full = torch.empty(world * m_shard, K, dtype=a_shard.dtype, device=a_shard.device)
+        dist.all_gather_into_tensor(full, a_shard.contiguous(), group=group)
+        out = full @ b.t()
+        return (out, full) if return_gathered else out
     nbytes = m_shard * K * a_shard.element_size()
     s = _slots(group, "ag", nbytes, CH_AG_READY, CH_AG_DONE)
     ws = s.ws
@@ -124,6 +130,10 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None) -> tor
                                ws.channel_flags_ptr(CH_AG_READY), epoch, _lib.shared_status().ptr, _lib.stream_ptr())
     _lib.check(rc, "ag_gemm")
     s.release(slot)
+    if return_gathered:
+        # the kernel copies the REMOTE shards; the own shard is read in place
+        gathered[rank * m_shard: (rank + 1) * m_shard].copy_(a_shard)
+        return out, gathered
     return out
 
 

@@ -177,6 +177,23 @@ class ReplicateParams(ParallelStyle):
         return module
 
 
+class ShardOnly(ParallelStyle):
+    """Shard a linear's weight along ``dim`` (0 = column-parallel / output features, 1 = row-parallel / input
+    features) and nothing else: no input or output hooks.  The module's forward is provided by the fused
+    sequence-parallel path, which reads the local shard itself."""
+
+    def __init__(self, dim: int):
+        super().__init__()
+        self.dim = dim
+
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        for name, p in list(module.named_parameters(recurse=False)):
+            placement = Shard(self.dim) if p.dim() > self.dim else Replicate()
+            module.register_parameter(name, nn.Parameter(distribute_tensor(p.data, device_mesh, [placement]),
+                                                         requires_grad=p.requires_grad))
+        return module
+
+
 class SequenceShardedLinear(ParallelStyle):
     """A full (unsplit) linear applied to sequence-sharded local activations: the weight is replicated, every rank
     multiplies its own tokens, and the weight gradient is a partial sum that is reduced over the mesh."""
@@ -202,9 +219,13 @@ def maybe_enable_async_tp(parallelism_config, tp_mesh: DeviceMesh | None) -> boo
     if tp_mesh is None or not getattr(parallelism_config, "enable_async_tensor_parallel", False):
         _ASYNC_TP["enabled"] = False
         return False
-    if not torch.cuda.is_available():
-        raise RuntimeError("enable_async_tensor_parallel needs CUDA: the fused SP kernels are sm_100a code")
     from titan_b200.ops import fused_comm
+
+    if not torch.cuda.is_available():
+        # same dataflow through the library fallbacks of the fused ops (fp32 on CPU): used to test the autograd logic
+        import warnings
+
+        warnings.warn("enable_async_tensor_parallel without CUDA: the fused kernels fall back to library collectives")
 
     fused_comm.enable_for_group(tp_mesh.get_group())
     _ASYNC_TP["enabled"] = True
