@@ -256,7 +256,8 @@ def main() -> int:
             "config": {
                 "model": f"{cfg.model.name}-{cfg.model.flavor}", "recipe": recipe,
                 "global_batch": cfg.training.local_batch_size * dp, "seq_len": cfg.training.seq_len,
-                "parallelism": par, "activation_checkpoint": cfg.activation_checkpoint.mode,
+                "parallelism": par, "activation_checkpoint": (cfg.activation_checkpoint.mode if cfg.activation_checkpoint.mode != "selective"
+                                          else f"selective/{cfg.activation_checkpoint.selective_ac_option}"),
                 "optimizer": f"{cfg.optimizer.name}/{cfg.optimizer.implementation}",
                 "converters": [getattr(c, "name", str(c)) for c in cfg.model_converters.converters],
                 "l2": "inputs larger than L2 (weights + activations >> 126 MB); no explicit flush",
