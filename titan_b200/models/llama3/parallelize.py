@@ -109,9 +109,17 @@ def parallelize_llama(
     if parallel_dims.fsdp_enabled:
         names = ("dp_replicate", "fsdp") if parallel_dims.dp_replicate_enabled else None
         dp_mesh = parallel_dims.get_mesh(names) if names else parallel_dims.get_mesh("fsdp")
+        ignored = None
+        if getattr(parallelism, "fsdp_fused_collectives", False):
+            if parallel_dims.tp_enabled or parallel_dims.dp_replicate_enabled:
+                raise NotImplementedError("fsdp_fused_collectives composes with plain FSDP only (no TP / HSDP)")
+            from titan_b200.parallel.fused_fsdp import shard_linears
+
+            ignored = set(shard_linears(model, dp_mesh))
         apply_fsdp(
             model,
             dp_mesh,
+            ignored_params=ignored,
             param_dtype=DTYPE_MAP[training.mixed_precision_param],
             reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce],
             pp_enabled=parallel_dims.pp_enabled,

@@ -109,7 +109,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None, return
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     m_shard, K = a_shard.shape
     N = b.shape[0]
-    if m_shard % 128 or K % 8 or N % 8 or a_shard.dtype not in (torch.bfloat16, torch.float16):
+    if not a_shard.is_cuda or m_shard % 128 or K % 8 or N % 8 or a_shard.dtype not in (torch.bfloat16, torch.float16):
         full = torch.empty(world * m_shard, K, dtype=a_shard.dtype, device=a_shard.device)
         dist.all_gather_into_tensor(full, a_shard.contiguous(), group=group)
         out = full @ b.t()
@@ -143,7 +143,7 @@ def all_gather_weight_matmul(x: torch.Tensor, w_shard: torch.Tensor, group=None)
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     n_shard, K = w_shard.shape
     M = x.shape[0]
-    if n_shard % 256 or K % 8 or x.dtype not in (torch.bfloat16, torch.float16):
+    if not x.is_cuda or n_shard % 256 or K % 8 or x.dtype not in (torch.bfloat16, torch.float16):
         full = torch.empty(world * n_shard, K, dtype=w_shard.dtype, device=w_shard.device)
         dist.all_gather_into_tensor(full, w_shard.contiguous(), group=group)
         return x @ full.t()
@@ -184,7 +184,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, group=None) -> torch
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     M, K = a.shape
     N = b.shape[0]
-    if M % (128 * world) or K % 8 or N % 8 or a.dtype not in (torch.bfloat16, torch.float16):
+    if not a.is_cuda or M % (128 * world) or K % 8 or N % 8 or a.dtype not in (torch.bfloat16, torch.float16):
         return matmul_reduce_scatter_baseline(a, b, group)
     m_shard = M // world
     nbytes = world * m_shard * N * a.element_size()
@@ -227,7 +227,8 @@ def castscale_reduce_scatter(bucket: torch.Tensor, scale: float, out_dtype: torc
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     n = bucket.numel()
     esz = bucket.element_size()
-    if n % world or (n // world * esz) % 16 or bucket.dtype not in (torch.bfloat16, torch.float32) \
+    if not bucket.is_cuda or n % world or (n // world * esz) % 16 \
+            or bucket.dtype not in (torch.bfloat16, torch.float32) \
             or out_dtype not in (torch.bfloat16, torch.float32):
         return castscale_reduce_scatter_baseline(bucket, scale, out_dtype, group)
     s = _slots(group, "grad", n * esz, CH_GRAD_READY, CH_GRAD_DONE)

@@ -69,10 +69,14 @@ def apply_fsdp(
     gradient_divide_factor: int | None = None,
     layers_attr: str = "layers",
     extra_modules: tuple[str, ...] = (),
+    ignored_params: set | None = None,
 ) -> nn.Module:
-    """Shard `model` block by block over `dp_mesh` (1-D = FSDP, 2-D = HSDP)."""
+    """Shard `model` block by block over `dp_mesh` (1-D = FSDP, 2-D = HSDP).  ``ignored_params``: parameters that
+    another mechanism already shards (the fused-collective linears) and FSDP2 must leave alone."""
     mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
     cfg = {"mesh": dp_mesh, "mp_policy": mp}
+    if ignored_params:
+        cfg["ignored_params"] = set(ignored_params)
     if cpu_offload:
         cfg["offload_policy"] = CPUOffloadPolicy()
     reshard = reshard_policy(reshard_after_forward_policy, pp_enabled)
