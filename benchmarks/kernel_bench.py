@@ -156,6 +156,32 @@ def bench_elementwise(iters):
          frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
 
 
+def bench_attention(iters):
+    """Causal GQA attention forward, Llama-3 8B shape: the tcgen05 kernel against the library backends."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    from titan_b200.ops.flash_attention import _FlashFn
+
+    tf_peak, _, tag = peaks()
+    B, S, H, HK, D = 1, 8192, 32, 8, 128
+    q = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+    k = torch.randn(B, S, HK, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+    v = torch.randn(B, S, HK, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+    fl = 4.0 * B * H * S * S * D / 2
+    ours = timeit(lambda: _FlashFn.apply(q, k, v, D ** -0.5), iters)
+    rec = dict(kernel="flash_fwd_tcgen05", shape=[B, H, HK, S, D], ms=ours, tflops=fl / ours / 1e9,
+               frac_of_peak=fl / ours / 1e9 / tf_peak, peak=tag)
+    for name, be in (("cudnn", SDPBackend.CUDNN_ATTENTION), ("flash2", SDPBackend.FLASH_ATTENTION)):
+        try:
+            with sdpa_kernel(be):
+                ms = timeit(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True), iters)
+            rec[f"{name}_ms"], rec[f"{name}_tflops"] = ms, fl / ms / 1e9
+        except RuntimeError as e:  # backend not available for this shape
+            rec[f"{name}_error"] = str(e)[:80]
+    emit(**rec)
+
+
 def profile_case(name: str, launches: int = 3) -> None:
     """One small workload (inputs larger than L2, well under 1 GB on the device), launched a few times: the
     target of a profiler capture.  Prints nothing but the case name; timings come from the bench modes."""
@@ -189,6 +215,13 @@ def profile_case(name: str, launches: int = 3) -> None:
         k = torch.randn(1, 16384, 1, 128, device=dev, dtype=bf)
         w = torch.rand(1, 4096, 64, device=dev)
         fn = lambda: lightning_indexer_topk(q, w, k, 2048, 16384 - 4096)  # noqa: E731
+    elif name == "flash_fwd":
+        from titan_b200.ops.flash_attention import _FlashFn
+
+        q = torch.randn(1, 8192, 32, 128, device=dev, dtype=bf).transpose(1, 2)
+        k = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).transpose(1, 2)
+        v = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).transpose(1, 2)
+        fn = lambda: _FlashFn.apply(q, k, v, 128 ** -0.5)  # noqa: E731
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     for _ in range(launches):
@@ -212,6 +245,8 @@ def main():
         bench_gemm(args.iters)
     if "elementwise" in which:
         bench_elementwise(args.iters)
+    if "attention" in which:
+        bench_attention(args.iters)
 
 
 if __name__ == "__main__":

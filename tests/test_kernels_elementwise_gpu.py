@@ -179,3 +179,20 @@ def test_fused_adamw_grad_scale():
     opt.step()
     ref.step()
     torch.testing.assert_close(p.detach(), r.detach(), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("n", [64, 128, 256, 512])
+def test_hadamard_matches_matrix_product(n):
+    import scipy.linalg
+
+    from titan_b200.ops.hadamard import hadamard, hadamard_ref
+
+    x = torch.randn(3, 37, n, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    H = torch.tensor(scipy.linalg.hadamard(n), dtype=torch.float32, device="cuda")
+    y = hadamard(x)
+    ref = (x.detach().float() @ H) * n ** -0.5
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(hadamard_ref(x.detach(), n ** -0.5).float(), ref, rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    torch.testing.assert_close(x.grad.float(), (g.float() @ H) * n ** -0.5, rtol=2e-2, atol=2e-2)
