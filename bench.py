@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--flavor", default=None, help="override the model flavor (smoke runs only)")
     ap.add_argument("--converters", default=None, help="comma-separated converter names overriding the recipe")
     ap.add_argument("--ac", default=None, choices=["none", "selective", "full"])
+    ap.add_argument("--set", action="append", default=[], metavar="SECTION.FIELD=VALUE",
+                    help="extra recipe overrides, e.g. --set parallelism.expert_parallel_degree=2 (repeatable)")
     return ap.parse_args()
 
 
@@ -137,6 +139,10 @@ def build_config(args):
         cfg.model_converters.converters = [get_model_converter_config(n) for n in args.converters.split(",") if n]
     if args.ac:
         cfg.activation_checkpoint.mode = args.ac
+    if args.set:
+        from titan_b200.config.manager import apply_overrides
+
+        cfg = apply_overrides(cfg, [f"--{kv}" for kv in args.set])
     cfg.training.steps = 10 ** 9  # the bench drives steps itself; keeps the LR schedule in warm-up
     cfg.metrics.log_freq = 10 ** 9
     cfg.checkpoint.enable = False
