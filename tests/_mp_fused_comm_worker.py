@@ -89,6 +89,35 @@ def main():
     torch.testing.assert_close(local.w2.grad.float(), gw[rank * e_local:(rank + 1) * e_local], rtol=5e-2, atol=0.3)
     torch.cuda.synchronize()
     _lib.shared_status().raise_if_set("moe ep")
+
+    # Ulysses: projection fused with the head->sequence exchange and the way back, forward and backward,
+    # against all_to_all_single + matmul
+    from titan_b200.ops import ulysses_fused as uf
+
+    for rep in range(3):
+        batch, s_loc, dim, heads, hd = 2, 256, 512, 4 * world, 64
+        nq = heads * hd
+        torch.manual_seed(99)
+        wq = (torch.randn(nq, dim, device=dev) * 0.05).to(torch.bfloat16)
+        wo = (torch.randn(dim, nq, device=dev) * 0.05).to(torch.bfloat16)
+        torch.manual_seed(4321 + rank + rep)
+        x = torch.randn(batch * s_loc, dim, device=dev, dtype=torch.bfloat16)
+        xa, wqa, woa = (t.clone().requires_grad_(True) for t in (x, wq, wo))
+        xb, wqb, wob = (t.clone().requires_grad_(True) for t in (x, wq, wo))
+        q = uf.proj_all_to_all(xa, wqa, s_loc, group)           # [batch * s_full, nq / world]
+        y = uf.all_to_all_proj(torch.tanh(q), woa, s_loc, group)  # [batch * s_loc, dim]
+        qr = uf.proj_all_to_all_baseline(xb, wqb, s_loc, group)
+        yr, _ = uf.all_to_all_proj_baseline(torch.tanh(qr), wob, s_loc, group)
+        torch.testing.assert_close(q.float(), qr.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(y.float(), yr.float(), rtol=3e-2, atol=3e-2)
+        gy = torch.randn_like(y)
+        y.backward(gy)
+        yr.backward(gy)
+        torch.testing.assert_close(xa.grad.float(), xb.grad.float(), rtol=5e-2, atol=5e-2)
+        torch.testing.assert_close(wqa.grad.float(), wqb.grad.float(), rtol=5e-2, atol=0.3)
+        torch.testing.assert_close(woa.grad.float(), wob.grad.float(), rtol=5e-2, atol=0.3)
+    torch.cuda.synchronize()
+    _lib.shared_status().raise_if_set("ulysses fused")
     dist.barrier()
     if rank == 0:
         print("FUSED_COMM_WORKER_OK")

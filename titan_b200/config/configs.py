@@ -183,6 +183,8 @@ class ParallelismConfig:
     context_parallel_load_balancer: str | None = None
     """None = contiguous shards (required by Ulysses / DSA / compressor CP)."""
     context_parallel_rotate_method: str = "allgather"
+    context_parallel_fused_projections: bool = False
+    """Ulysses only: fold the head <-> sequence exchanges into the q/k/v and output projections (peer-memory GEMMs)."""
     expert_parallel_degree: int = 1
     expert_tensor_parallel_degree: int = 1
     expert_parallel_comm_backend: Literal["standard", "fused_p2p", "deepep", "hybridep", "torchao"] = "standard"

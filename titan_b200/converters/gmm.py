@@ -56,8 +56,13 @@ class FusedGroupedExperts(Module):
         h = swiglu_fused(h13, scores, self.swiglu_limit)
         return grouped_linear(h, w2.to(xp.dtype), offs)
 
-    def forward(self, x: torch.Tensor, num_tokens_per_expert: torch.Tensor) -> torch.Tensor:
-        """Unpadded expert-sorted rows (the layout of the NCCL expert-parallel path)."""
+    def forward(self, x: torch.Tensor, num_tokens_per_expert: torch.Tensor, scores: torch.Tensor | None = None,
+                padded: bool = False) -> torch.Tensor:
+        """Unpadded expert-sorted rows (the layout of the NCCL expert-parallel path); ``padded=True`` takes the
+        128-row-padded layout with cumulative ends instead.  The fused MoE layer calls the module (not
+        `forward_padded` directly) so that FSDP's unshard / gradient-reduction hooks run around the experts."""
+        if padded:
+            return self.forward_padded(x, num_tokens_per_expert, scores)
         w13, w2 = self._local(self.w13), self._local(self.w2)
         offs = torch.cumsum(num_tokens_per_expert, 0, dtype=torch.int32)
         mx = getattr(self, "mx_round_mode", None)

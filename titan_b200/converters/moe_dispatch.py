@@ -60,11 +60,11 @@ class FusedMoE(MoE):
         plan = moe_ops.make_plan(idx, r.num_experts)
         if self.score_before_experts:
             xp = moe_ops.permute(x2, plan, scale=gate)
-            yp = experts.forward_padded(xp, plan.offs)
+            yp = experts(xp, plan.offs, padded=True)
             out = moe_ops.combine(yp, plan, T, weights=None, base=base)
         else:
             xp = moe_ops.permute(x2, plan)
-            yp = experts.forward_padded(xp, plan.offs)
+            yp = experts(xp, plan.offs, padded=True)
             out = moe_ops.combine(yp, plan, T, weights=gate, base=base)
         return out.reshape(bs, slen, dim)
 

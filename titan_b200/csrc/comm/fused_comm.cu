@@ -279,3 +279,67 @@ TB_API int tb_put(void* const* dst_ptrs, int nranks, const void* src, long long 
   tb_note_launch(1);
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Ulysses context parallelism: the head <-> sequence all-to-all fused into the projections on either side of it
+// (reference: distributed/context_parallel/ulysses_cp.py:28-64 does chunk -> all_to_all -> cat around the attention).
+//
+// tb_gemm_a2a_scatter: C = A[M,K] · B[N,K]ᵀ (or B[K,N] with b_mn) where M = batch * seq_local rows of this rank's
+// sequence slice and the N columns are heads; columns [r*n_shard, (r+1)*n_shard) are stored into rank r's receive
+// buffer recv_ptrs[r] = [batch * seq_local * nranks, n_shard] at rows b*seq_full + rank*seq_local + s.
+// peer_flags[r] + rank is released with `epoch` when all of this rank's boxes for r have landed.
+TB_API int tb_gemm_a2a_scatter(const void* A, const void* B, void* const* recv_ptrs, void* const* peer_flags,
+                               unsigned int* tile_counters, int M, int N, int K, int n_shard, int seq_local, int b_mn,
+                               int dtype, int rank, int nranks, unsigned int epoch, int* status, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || n_shard % 64 || n_shard * nranks != N) return TB_ERR_ARG;
+  if (seq_local <= 0 || seq_local % BM || M % seq_local || (K % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  AMaps am;
+  CUtensorMap tb_;
+  CMaps cm;
+  if (int rc = make_a_map(&am.m[0], A, dtype, 0, (uint64_t)M, (uint64_t)K, K)) return rc;
+  if (int rc = make_b_map(&tb_, B, dtype, b_mn, (uint64_t)N, (uint64_t)K, b_mn ? N : K)) return rc;
+  GemmParams p{};
+  p.mode = SCATTER_N; p.M = M; p.N = N; p.K = K; p.b_mn = b_mn; p.is_bf16 = dtype == 1;
+  p.ldc = N; p.C = nullptr; p.status = status; p.rank = rank; p.nranks = nranks; p.n_shard = n_shard;
+  p.seq_local = seq_local; p.seq_full = seq_local * nranks;
+  p.epoch = epoch; p.tile_counters = tile_counters; p.tma_store = 1;
+  for (int r = 0; r < nranks; ++r) {
+    p.peer_flags[r] = reinterpret_cast<unsigned int*>(peer_flags[r]);
+    if (int rc = make_c_map(&cm.m[r], recv_ptrs[r], dtype, (uint64_t)M * nranks, (uint64_t)n_shard, n_shard))
+      return rc;
+  }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  return launch(am, tb_, cm, p, tiles < sm_count() ? tiles : sm_count(), st);
+}
+
+// tb_a2a_gather_gemm: C[M,N] = gather_k(A)[M, nranks*k_shard] · B[N,K]ᵀ (or B[K,N] with b_mn).  Rank r holds the
+// k_shard columns [r*k_shard, ...) of every rank's rows in a_ptrs[r] = [batch * seq_full, k_shard]; this rank's rows
+// are b*seq_full + rank*seq_local + s.  gathered: local [nranks, M, k_shard] buffer (the remote slices land there,
+// each crossing NVLink once); chunk_flags: local uint32 [nranks * M / 128].
+TB_API int tb_a2a_gather_gemm(void* const* a_ptrs, const void* B, void* C, void* gathered, unsigned int* chunk_flags,
+                              int M, int N, int k_shard, int seq_local, int b_mn, int dtype, int rank, int nranks,
+                              const unsigned int* ready_flags, unsigned int epoch, int* status, cudaStream_t st) {
+  if (nranks < 1 || nranks > MAX_RANKS || k_shard <= 0 || k_shard % BK) return TB_ERR_ARG;
+  if (seq_local <= 0 || seq_local % BM || M % seq_local || (N % 8) || (dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  const int K = k_shard * nranks;
+  AMaps am;
+  CUtensorMap tb_;
+  CMaps cm;
+  if (int rc = make_a_map(&am.m[0], a_ptrs[rank], dtype, 0, (uint64_t)M * nranks, (uint64_t)k_shard, k_shard))
+    return rc;
+  if (int rc = make_a_map(&am.m[1], gathered, dtype, 0, (uint64_t)M * nranks, (uint64_t)k_shard, k_shard)) return rc;
+  if (int rc = make_b_map(&tb_, B, dtype, b_mn, (uint64_t)N, (uint64_t)K, b_mn ? N : K)) return rc;
+  if (int rc = make_c_map(&cm.m[0], C, dtype, (uint64_t)M, (uint64_t)N, N)) return rc;
+  GemmParams p{};
+  p.mode = GATHER_K; p.M = M; p.N = N; p.K = K; p.b_mn = b_mn; p.is_bf16 = dtype == 1;
+  p.ldc = N; p.C = C; p.status = status; p.rank = rank; p.nranks = nranks; p.k_shard = k_shard;
+  p.seq_local = seq_local; p.seq_full = seq_local * nranks;
+  p.ready_flags = ready_flags; p.epoch = epoch; p.tma_store = 1;
+  for (int r = 0; r < nranks; ++r) p.peer_src[r] = a_ptrs[r];
+  p.gather_dst = gathered; p.chunk_flags = chunk_flags;
+  p.num_copiers = nranks > 1 ? NUM_COPIERS : 0;
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  int workers = sm_count() - p.num_copiers;
+  if (tiles < workers) workers = tiles;
+  return launch(am, tb_, cm, p, workers + p.num_copiers, st);
+}

@@ -22,6 +22,12 @@
 //              entirely in the causal future of their queries are skipped by every role
 //   SCATTER    C is reduce-scattered by rows: each tile is stored into the owner rank's staging slot
 //              for this rank; the last tile for an owner releases a flag on that owner
+//   SCATTER_N  projection fused with a head -> sequence all-to-all (Ulysses): columns of C belong to the rank that
+//              owns those heads; every 64-column box is stored into that rank's receive buffer
+//              [batch * seq_full, n_shard] at the rows of this rank's sequence slice
+//   GATHER_K   the reverse exchange fused into the consuming GEMM: the contraction dimension of A is sliced by
+//              owner rank (k_shard columns each, rows laid out [batch * seq_full] on the owner); copier CTAs bring
+//              the remote slices of this rank's rows into a local [nranks][M][k_shard] buffer once
 //
 // Operand storage: a_mn/b_mn = 0 → K-major ([M,K] / [N,K] row-major), 1 → MN-major ([K,M] / [K,N]).
 // Every wait is time-bounded; on expiry the kernel records a status code, raises a CTA-wide abort flag,
@@ -49,7 +55,10 @@ constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;
 constexpr unsigned long long WAIT_NS = 2000000000ull;
 
-enum Mode : int { PLAIN = 0, GROUPED_M = 1, GROUPED_K = 2, ALLGATHER = 3, SCATTER = 4, ALLGATHER_B = 5, INDEXER = 6 };
+enum Mode : int {
+  PLAIN = 0, GROUPED_M = 1, GROUPED_K = 2, ALLGATHER = 3, SCATTER = 4, ALLGATHER_B = 5, INDEXER = 6, SCATTER_N = 7,
+  GATHER_K = 8
+};
 
 struct GemmParams {
   int mode;
@@ -67,7 +76,9 @@ struct GemmParams {
   // collectives
   int rank, nranks;
   int m_shard;              // rows per rank (multiple of 128)
-  int n_shard;              // ALLGATHER_B: rows of B per rank (multiple of 256)
+  int n_shard;              // ALLGATHER_B: rows of B per rank (multiple of 256); SCATTER_N: columns of C per owner
+  int k_shard;              // GATHER_K: contraction columns per owner (multiple of 64)
+  int seq_local, seq_full;  // SCATTER_N / GATHER_K: local row b*seq_local+s is row b*seq_full+rank*seq_local+s there
   const unsigned int* ready_flags;  // ALLGATHER: [nranks] in local memory, written by peers
   unsigned int epoch;
   void* stage_ptrs[MAX_RANKS];          // SCATTER: staging buffer base on every rank: [src][m_shard][N]
@@ -247,11 +258,21 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int* s_offs,
     const int per = p.m_shard / BM;
     mt = (mt + ((p.rank + 1) % p.nranks) * per) % num_m;
     tl.a_row = mt * BM;
+  } else if (p.mode == SCATTER_N) {
+    // start at the next rank's columns, finish with the local ones
+    nt = (nt + (((p.rank + 1) % p.nranks) * p.n_shard) / BN) % num_n;
+    tl.a_row = mt * BM;
   } else {
     tl.a_row = mt * BM;
   }
   tl.m0 = mt * BM; tl.n0 = nt * BN; tl.row_end = p.M;
   return tl;
+}
+
+// SCATTER_N / GATHER_K: row of the full-sequence layout that holds local row `m` of rank `rank`
+__device__ __forceinline__ int seq_row(const GemmParams& p, int m, int rank) {
+  const int b = m / p.seq_local;
+  return b * p.seq_full + rank * p.seq_local + (m - b * p.seq_local);
 }
 
 // store 32 consecutive fp32 accumulator values of one row

@@ -35,23 +35,33 @@ __device__ __forceinline__ void copier_role(const GemmParams& p, uint8_t* bufs, 
   if (threadIdx.x != 0) return;
   for (int b = 0; b < COPY_BUFS; ++b) mbar_init(&bars[b], 1);
   fence_barrier_init();
-  const int chunk_rows = p.mode == ALLGATHER ? BM : BN;
-  const int shard_rows = p.mode == ALLGATHER ? p.m_shard : p.n_shard;
+  // GATHER_K: a chunk is 128 rows of one owner's k_shard-wide slice (contiguous on the owner); chunks are visited
+  // row-block by row-block, since every output tile needs the slices of all owners for its rows.
+  const bool gk = p.mode == GATHER_K;
+  const int chunk_rows = p.mode == ALLGATHER_B ? BN : BM;
+  const int shard_rows = gk ? p.M : (p.mode == ALLGATHER ? p.m_shard : p.n_shard);
   const int per = shard_rows / chunk_rows;
   const int remote_chunks = (p.nranks - 1) * per;
-  const long long chunk_bytes = (long long)chunk_rows * p.K * 2;
+  const long long row_bytes = (long long)(gk ? p.k_shard : p.K) * 2;
+  const long long chunk_bytes = (long long)chunk_rows * row_bytes;
   const int pieces = (int)((chunk_bytes + COPY_PIECE - 1) / COPY_PIECE);
   int my_chunks = 0;
   for (int idx = blockIdx.x; idx < remote_chunks; idx += p.num_copiers) ++my_chunks;
   const long long total = (long long)my_chunks * pieces;
   unsigned int seen = 1u << p.rank;
   const int D = COPY_BUFS - 1;  // loads run this many pieces ahead of the stores
+  auto locate = [&](int idx, int& src, int& within, long long& src_off) {
+    int d;
+    if (gk) { within = idx / (p.nranks - 1); d = idx - within * (p.nranks - 1) + 1; }
+    else { d = idx / per + 1; within = idx - (d - 1) * per; }
+    src = (p.rank + d) % p.nranks;
+    src_off = gk ? (long long)seq_row(p, within * BM, p.rank) * row_bytes : (long long)within * chunk_bytes;
+  };
   for (long long i = 0; i < total + D; ++i) {
     if (i < total) {
       const int ci = (int)(i / pieces), pi = (int)(i - (long long)ci * pieces);
-      const int idx = blockIdx.x + ci * p.num_copiers;
-      const int d = idx / per + 1, within = idx - (d - 1) * per;
-      const int src = (p.rank + d) % p.nranks;
+      int src, within; long long src_off;
+      locate(blockIdx.x + ci * p.num_copiers, src, within, src_off);
       if (!(seen & (1u << src))) {
         if (!wait_flag_ge(p.ready_flags + src, p.epoch, abort_flag)) {
           if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER);
@@ -63,16 +73,15 @@ __device__ __forceinline__ void copier_role(const GemmParams& p, uint8_t* bufs, 
       if (i >= COPY_BUFS) tma_store_wait_read<0>();  // the store that used this buffer has read it
       const long long off = (long long)pi * COPY_PIECE;
       const uint32_t bytes = (uint32_t)((chunk_bytes - off) < COPY_PIECE ? (chunk_bytes - off) : COPY_PIECE);
-      const uint8_t* from = reinterpret_cast<const uint8_t*>(p.peer_src[src]) + (long long)within * chunk_bytes + off;
+      const uint8_t* from = reinterpret_cast<const uint8_t*>(p.peer_src[src]) + src_off + off;
       mbar_expect_tx(&bars[b], bytes);
       bulk_load(bufs + b * COPY_PIECE, from, bytes, &bars[b]);
     }
     const long long j = i - D;
     if (j >= 0 && j < total) {
       const int ci = (int)(j / pieces), pi = (int)(j - (long long)ci * pieces);
-      const int idx = blockIdx.x + ci * p.num_copiers;
-      const int d = idx / per + 1, within = idx - (d - 1) * per;
-      const int src = (p.rank + d) % p.nranks;
+      int src, within; long long src_off;
+      locate(blockIdx.x + ci * p.num_copiers, src, within, src_off);
       const int b = (int)(j % COPY_BUFS);
       if (!wait_bounded(&bars[b], (uint32_t)((j / COPY_BUFS) & 1), abort_flag)) {
         if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA);
@@ -111,7 +120,9 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
   int* s_offs = reinterpret_cast<int*>(bars) + 64;  // 256 B after the barrier block: [num_groups + 1]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool gather = p.mode == ALLGATHER || p.mode == ALLGATHER_B;
+  const bool gather_mn = p.mode == ALLGATHER || p.mode == ALLGATHER_B;  // whole tiles of A / B come from one owner
+  const bool gather_k = p.mode == GATHER_K;                              // the owner changes along the contraction
+  const bool gather = gather_mn || gather_k;
 
   if (gather && (int)blockIdx.x < p.num_copiers) {
     if (threadIdx.x == 0) *abort_flag = 0;
@@ -150,7 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
         const Tile tl = get_tile(p, s_offs, t);
         if (tile_is_future(p, tl.m0, tl.n0)) continue;
         int gmap = 0;  // which map of the gathered operand: 0 = own shard in place, 1 = local gathered copy
-        if (gather && tl.src != p.rank) {
+        if (gather_mn && tl.src != p.rank) {
           if (!wait_local_flag_ge(p.chunk_flags + tl.chunk, p.epoch, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER); }
             break;
@@ -161,7 +172,30 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
         }
         const CUtensorMap* ta = p.mode == ALLGATHER_B ? &tmap_b : &amaps.m[p.mode == ALLGATHER ? gmap : 0];
         const CUtensorMap* tbm = p.mode == ALLGATHER_B ? &amaps.m[gmap] : &tmap_b;
+        const int kps = gather_k ? p.k_shard / BK : 1;  // 64-wide blocks per owner slice
         for (int kb = 0; kb < tl.kblocks; ++kb) {
+          int k0 = tl.k0 + kb * BK;  // contraction coordinate (the B operand always uses it)
+          int ax = k0, ay = tl.a_row;
+          if (gather_k) {
+            // own slice first, then the owners in ring order (the order in which the copiers fetch them)
+            const int s = (p.rank + kb / kps) % p.nranks, kk = kb - (kb / kps) * kps;
+            k0 = s * p.k_shard + kk * BK;
+            ax = kk * BK;
+            if (s == p.rank) {
+              ta = &amaps.m[0];  // own slice in place: rows of the full-sequence layout
+              ay = seq_row(p, tl.m0, p.rank);
+            } else {
+              if (kk == 0) {
+                if (!wait_local_flag_ge(p.chunk_flags + s * (p.M / BM) + tl.m0 / BM, p.epoch, abort_flag)) {
+                  if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER); }
+                  ok = false; break;
+                }
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+              }
+              ta = &amaps.m[1];  // local copy [owner][M][k_shard]
+              ay = s * p.M + tl.m0;
+            }
+          }
           if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
             ok = false; break;
@@ -169,9 +203,8 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
           mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
           uint8_t* sa = smem_a + stage * A_STAGE_BYTES;
           uint8_t* sb = smem_b + stage * B_STAGE_BYTES;
-          const int k0 = tl.k0 + kb * BK;
           if (!p.a_mn) {
-            tma_load_2d(sa, ta, &full_bar[stage], k0, tl.a_row);  // box {64 k, 128 m}
+            tma_load_2d(sa, ta, &full_bar[stage], ax, ay);  // box {64 k, 128 m}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)  // box {64 m, 64 k}, 8 KB each
@@ -331,6 +364,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
         int y = tl.m0;
         if (p.mode == GROUPED_K) y = tl.group * p.M + tl.m0;
         else if (p.mode == SCATTER) y = p.rank * p.m_shard + (tl.m0 - dst_rank * p.m_shard);
+        else if (p.mode == SCATTER_N) y = seq_row(p, tl.m0, p.rank);  // this rank's sequence slice on the owner
         const uint32_t srow = smem_u32(smem_c) + row_in_tile * 128;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
@@ -373,7 +407,13 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
               const int x = tl.n0 + half * 128 + b * 64;
-              if (x < p.N) tma_store_2d(cm, smem_c + b * 16384, x, y);
+              if (x >= p.N) continue;
+              if (p.mode == SCATTER_N) {  // the 64-column box goes to the rank that owns those heads
+                const int owner = x / p.n_shard;
+                tma_store_2d(&cmaps.m[owner], smem_c + b * 16384, x - owner * p.n_shard, y);
+              } else {
+                tma_store_2d(cm, smem_c + b * 16384, x, y);
+              }
             }
             tma_store_commit();
           }
@@ -425,6 +465,25 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
             __threadfence_system();
             st_release_sys(p.peer_flags[dst_rank] + p.rank, p.epoch);
           }
+        }
+      }
+      if (p.mode == SCATTER_N && issuer) {
+        // count the delivered 64-column boxes per owner; the last one publishes "this rank's slice is complete"
+        tma_store_wait_all<0>();
+        __threadfence_system();
+        const unsigned int expected = (unsigned int)((p.M / BM) * (p.n_shard / 64));
+        const int x_end = min(tl.n0 + BN, p.N);
+        for (int x = tl.n0; x < x_end;) {
+          const int owner = x / p.n_shard;
+          const int stop = min((owner + 1) * p.n_shard, x_end);
+          const unsigned int boxes = (unsigned int)((stop - x) / 64);
+          const unsigned int done = atomicAdd(p.tile_counters + owner, boxes) + boxes;
+          if (done == expected) {
+            p.tile_counters[owner] = 0;  // ready for the next launch
+            __threadfence_system();
+            st_release_sys(p.peer_flags[owner] + p.rank, p.epoch);
+          }
+          x = stop;
         }
       }
     }

@@ -115,7 +115,10 @@ class TokenChoiceTopKRouter(Module):
         if self.route_norm:
             top_scores = top_scores / (top_scores.sum(-1, keepdim=True) + 1e-20)
         top_scores = top_scores * self.route_scale
-        counts = torch.histc(selected.reshape(-1).float(), bins=self.num_experts, min=0, max=self.num_experts)
+        # integer counts: FSDP's mixed-precision policy casts floating-point forward inputs of the experts module to
+        # bf16, which cannot hold counts above 256 exactly (the all-to-all split sizes would no longer add up)
+        counts = torch.histc(selected.reshape(-1).float(), bins=self.num_experts, min=0,
+                             max=self.num_experts).to(torch.int64)
         return top_scores, selected, counts
 
     def init_states(self, *, init_std: float = 0.02, **kw):

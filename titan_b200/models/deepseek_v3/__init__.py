@@ -43,6 +43,12 @@ deepseekv3_configs = {
                          moe_args=_moe(num_experts=64, num_shared_experts=2, top_k=6, score_func="softmax"),
                          q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
                          mscale=0.70),
+    # the 16B_mla layer shapes with 5 of the 27 layers: fits two GPUs with fp32 AdamW state (expert-parallel benchmarks)
+    "16B_mla_5l": lambda: C(vocab_size=102400, dim=2048, inter_dim=10944, moe_inter_dim=1408, n_layers=5,
+                            n_dense_layers=1, n_heads=16,
+                            moe_args=_moe(num_experts=64, num_shared_experts=2, top_k=6, score_func="softmax"),
+                            q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                            mscale=0.70),
     "236B": lambda: C(vocab_size=102400, dim=5120, inter_dim=12288, moe_inter_dim=1536, n_layers=60, n_dense_layers=1,
                       n_heads=128, moe_args=_moe(num_experts=160, num_shared_experts=2, top_k=6, route_norm=False,
                                                  route_scale=16.0, num_expert_groups=8, num_limited_groups=3),

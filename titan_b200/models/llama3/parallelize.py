@@ -75,6 +75,33 @@ def apply_tp(model: nn.Module, tp_mesh, *, loss_parallel: bool, async_tp: bool =
         parallelize_module(block, tp_mesh, plan)
 
 
+def apply_ulysses_cp(model: nn.Module, parallel_dims, parallelism, *, rope: str) -> None:
+    """Ulysses context parallelism on every block's attention: hooks around the attention core, or (with
+    ``parallelism.context_parallel_fused_projections``) the exchanges folded into the projections."""
+    from titan_b200.parallel.context_parallel import apply_cp_to_attention_module
+
+    cp_mesh = parallel_dims.get_mesh("cp")
+    blocks = [b for b in model.layers.values() if b is not None]
+    for b in blocks:
+        a = b.attention
+        tp = parallel_dims.tp if parallel_dims.tp_enabled else 1
+        for what, n in (("n_heads", a.n_heads), ("n_kv_heads", a.n_kv_heads)):
+            if (n // tp) % parallel_dims.cp != 0:
+                raise ValueError(f"[Ulysses CP] {what}={n} (per TP rank {n // tp}) must be divisible by "
+                                 f"context_parallel_degree={parallel_dims.cp}.")
+    if getattr(parallelism, "context_parallel_fused_projections", False):
+        if parallel_dims.tp_enabled:
+            raise NotImplementedError("context_parallel_fused_projections does not compose with tensor parallelism")
+        from titan_b200.models.common.rope import apply_rotary_emb_complex, apply_rotary_emb_cos_sin
+        from titan_b200.parallel.context_parallel.ulysses import apply_fused_ulysses
+
+        rope_fn = apply_rotary_emb_complex if rope == "complex" else apply_rotary_emb_cos_sin
+        for b in blocks:
+            apply_fused_ulysses(b.attention, cp_mesh, rope_fn)
+    else:
+        apply_cp_to_attention_module([b.attention.inner_attention for b in blocks], cp_mesh)
+
+
 def apply_compile(model: nn.Module, compile_config) -> None:
     for name, block in list(model.layers.named_children()):
         model.layers.register_module(name, torch.compile(block, backend=compile_config.backend, fullgraph=True))
@@ -99,6 +126,9 @@ def parallelize_llama(
         tp_mesh = parallel_dims.get_mesh("tp")
         async_tp = maybe_enable_async_tp(parallelism, tp_mesh)
         apply_tp(model, tp_mesh, loss_parallel=not parallelism.disable_loss_parallel, async_tp=async_tp)
+
+    if parallel_dims.cp_enabled:
+        apply_ulysses_cp(model, parallel_dims, parallelism, rope="complex")
 
     if ac_config is not None and ac_config.mode != "none":
         apply_ac(model, ac_config)

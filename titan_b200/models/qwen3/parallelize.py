@@ -84,7 +84,18 @@ def parallelize_qwen3(model: nn.Module, *, parallel_dims, training, model_conver
         from titan_b200.parallel.context_parallel import apply_cp_to_attention_module
 
         validate_ulysses(model, pd.cp)
-        apply_cp_to_attention_module([b.attention.inner_attention for b in model.layers.values()], pd.get_mesh("cp"))
+        if getattr(parallelism, "context_parallel_fused_projections", False):
+            if tp_mesh is not None:
+                raise NotImplementedError("context_parallel_fused_projections does not compose with tensor "
+                                          "parallelism")
+            from titan_b200.models.common.rope import apply_rotary_emb_cos_sin
+            from titan_b200.parallel.context_parallel.ulysses import apply_fused_ulysses
+
+            for b in model.layers.values():
+                apply_fused_ulysses(b.attention, pd.get_mesh("cp"), apply_rotary_emb_cos_sin)
+        else:
+            apply_cp_to_attention_module([b.attention.inner_attention for b in model.layers.values()],
+                                         pd.get_mesh("cp"))
     if model.config.moe_enabled and (tp_mesh is not None or pd.ep_enabled):
         ep_etp = pd._sparse["ep", "etp"] if (pd.ep_enabled and pd.etp_enabled) else None
         apply_moe_ep_tp(model, tp_mesh=tp_mesh, ep_mesh=pd.get_optional_mesh("ep"),

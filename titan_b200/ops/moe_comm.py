@@ -205,10 +205,10 @@ def moe_forward_ep(x2, gate, idx, experts, group, *, base=None, score_before_exp
     ep.plan(idx, counts)
     if score_before_experts:
         xp = _EPDispatch.apply(x2, gate, ep)
-        yp = experts.forward_padded(xp, ep.offs_local)
+        yp = experts(xp, ep.offs_local, padded=True)
         return _EPCombine.apply(yp, None, base, ep)
     xp = _EPDispatch.apply(x2, None, ep)
-    yp = experts.forward_padded(xp, ep.offs_local)
+    yp = experts(xp, ep.offs_local, padded=True)
     return _EPCombine.apply(yp, gate, base, ep)
 
 

@@ -94,3 +94,56 @@ def _is_sdpa_core(mod: nn.Module) -> bool:
 
 
 register_cp_strategy("ulysses", _is_sdpa_core, lambda m, mesh: UlyssesCP(mesh).apply(m))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Fused form: the two exchanges disappear into the projections next to them.  `wq / wk / wv` become GEMMs whose
+# epilogue stores each head slice into the owner's receive buffer; `wo` becomes a GEMM that pulls the head slices of
+# its rows from the peers while it runs (ops/ulysses_fused.py).  RoPE and the per-head q/k norms act per position and
+# per head, so they commute with the exchange and run afterwards on (all positions, local heads).
+def _gather_positions(positions: torch.Tensor | None, group, cp: int):
+    if positions is None or cp == 1:
+        return positions
+    local = positions.contiguous().view(-1, positions.shape[-1])  # [rows, S_local]
+    out = torch.empty((cp * local.shape[0], local.shape[1]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local, group=group)
+    full = out.view(cp, local.shape[0], local.shape[1]).transpose(0, 1).reshape(local.shape[0], -1)
+    return full.view(*positions.shape[:-1], cp * positions.shape[-1])
+
+
+def apply_fused_ulysses(attn: nn.Module, cp_mesh: DeviceMesh, rope_fn) -> nn.Module:
+    """Replace ``attn.forward`` (an attention block with bias-free ``wq, wk, wv, wo`` projections, ``head_dim``, an
+    optional ``q_norm / k_norm`` pair and an ``inner_attention`` core taking ``[B, H, S, D]``) by the fused form.
+    ``rope_fn(xq, xk, rope_cache, positions)`` is the model's rotary embedding on ``[B, S, H, D]``."""
+    from titan_b200.ops.ulysses_fused import all_to_all_proj, proj_all_to_all
+
+    group, cp = cp_mesh.get_group(), cp_mesh.size()
+    for name in ("wq", "wk", "wv", "wo"):
+        lin = getattr(attn, name)
+        if getattr(lin, "bias", None) is not None:
+            raise NotImplementedError(f"fused Ulysses projections need bias-free linears ({name} has a bias)")
+    hd = attn.head_dim
+
+    def forward(x, rope_cache, attention_masks=None, positions=None):
+        bs, s_loc, dim = x.shape
+        x2 = x.reshape(bs * s_loc, dim)
+
+        def w(lin):
+            t = lin.weight
+            if hasattr(t, "to_local"):
+                raise NotImplementedError("fused Ulysses projections do not compose with tensor parallelism")
+            return t.to(x2.dtype)
+
+        q = proj_all_to_all(x2, w(attn.wq), s_loc, group).view(bs, cp * s_loc, -1, hd)
+        k = proj_all_to_all(x2, w(attn.wk), s_loc, group).view(bs, cp * s_loc, -1, hd)
+        v = proj_all_to_all(x2, w(attn.wv), s_loc, group).view(bs, cp * s_loc, -1, hd)
+        if getattr(attn, "q_norm", None) is not None:
+            q, k = attn.q_norm(q), attn.k_norm(k)
+        q, k = rope_fn(q, k, rope_cache, _gather_positions(positions, group, cp))
+        out = attn.inner_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=attention_masks)
+        o = out.transpose(1, 2).reshape(bs * cp * s_loc, -1)
+        return all_to_all_proj(o, w(attn.wo), s_loc, group).view(bs, s_loc, dim)
+
+    attn.forward = forward
+    attn._cp_strategy = "ulysses_fused"
+    return attn

@@ -150,6 +150,11 @@ class TensorParallel(ParallelStyle):
         for pname, p in list(mod.named_parameters(recurse=False)):
             if p is None:
                 continue
+            if pname == "w13":
+                # the fused [E, 2H, D] weight holds w1 above w3: a split on dim 1 would hand w1 to one rank and w3 to
+                # the other instead of halving both
+                raise NotImplementedError("tensor-parallel experts need separate w1 / w3 weights: remove the "
+                                          "b200_gmm converter or use expert parallelism without expert TP")
             dim = 2 if pname == "w2" else 1
             mod.register_parameter(pname, nn.Parameter(distribute_tensor(p, device_mesh, [Shard(dim)])))
 
@@ -189,6 +194,11 @@ class ExpertTensorParallel(ExpertParallel):
         for pname, p in list(mod.named_parameters(recurse=False)):
             if p is None:
                 continue
+            if pname == "w13":
+                # the fused [E, 2H, D] weight holds w1 above w3: a split on dim 1 would hand w1 to one rank and w3 to
+                # the other instead of halving both
+                raise NotImplementedError("tensor-parallel experts need separate w1 / w3 weights: remove the "
+                                          "b200_gmm converter or use expert parallelism without expert TP")
             dim = 2 if pname == "w2" else 1
             mod.register_parameter(pname, nn.Parameter(distribute_tensor(p, device_mesh, [Shard(0), Shard(dim)])))
 
