@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--flavor", default=None, help="override the model flavor (smoke runs only)")
     ap.add_argument("--converters", default=None, help="comma-separated converter names overriding the recipe")
     ap.add_argument("--ac", default=None, choices=["none", "selective", "full"])
+    ap.add_argument("--breakdown", type=int, default=0, metavar="ROWS",
+                    help="after timing, profile one more step and write the top ROWS kernels by device time")
+    ap.add_argument("--breakdown-out", default="kernel_breakdown.txt")
     ap.add_argument("--set", action="append", default=[], metavar="SECTION.FIELD=VALUE",
                     help="extra recipe overrides, e.g. --set parallelism.expert_parallel_degree=2 (repeatable)")
     return ap.parse_args()
@@ -244,6 +247,21 @@ def main() -> int:
     h2d = 2 * tokens_per_step_rank * 8  # int64 inputs + labels per rank and step
     d2h = 4 if cfg.training.dtype == "float32" else trainer._last_loss.element_size()
 
+    if args.breakdown:
+        # one extra step under the profiler, after (never inside) the timed regions: shares of device time per kernel
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            trainer.step += 1
+            trainer.train_step(sit)
+            torch.cuda.synchronize()
+        if rank == 0:
+            table = prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.breakdown,
+                                              max_name_column_width=90)
+            with open(args.breakdown_out, "w") as f:
+                f.write(table)
+            print(f"kernel breakdown of one step written to {args.breakdown_out}", file=sys.stderr)
+
     _lib.shared_status().raise_if_set("bench")  # any kernel-reported failure invalidates the run
     mem_gib = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
@@ -253,7 +271,9 @@ def main() -> int:
         from titan_b200.utils.device import get_peak_flops
 
         mfu = 100.0 * trainer.flops_per_token * (value / args.gpus) / get_peak_flops()
-        par = "fsdp%d" % args.gpus if args.gpus > 1 else "single"
+        pd = trainer.parallel_dims
+        par = "+".join(f"{n}{v}" for n, v in (("fsdp", pd.dp_shard), ("hsdp", pd.dp_replicate), ("tp", pd.tp),
+                                               ("cp", pd.cp), ("pp", pd.pp), ("ep", pd.ep)) if v > 1) or "single"
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

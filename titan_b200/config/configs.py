@@ -290,6 +290,8 @@ class SyntheticDataLoaderConfig:
     """None = the model's vocab size."""
     pin_memory: bool = True
     infinite: bool = True
+    documents_per_row: int = 0
+    """> 0: every row holds about this many packed documents and the batch carries their `positions`."""
 
 
 @dataclass(kw_only=True, slots=True)

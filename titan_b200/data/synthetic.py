@@ -22,7 +22,8 @@ __all__ = ["SyntheticDataLoader", "build_dataloader"]
 
 class SyntheticDataLoader(Stateful):
     def __init__(self, *, vocab_size: int, seq_len: int, batch_size: int, dp_rank: int = 0, dp_world_size: int = 1,
-                 seed: int = 0, pin_memory: bool = True, extra_tokens: int = 0, infinite: bool = True):
+                 seed: int = 0, pin_memory: bool = True, extra_tokens: int = 0, infinite: bool = True,
+                 documents_per_row: int = 0):
         self.vocab_size = vocab_size
         self.seq_len = seq_len
         self.batch_size = batch_size
@@ -31,6 +32,7 @@ class SyntheticDataLoader(Stateful):
         self.seed = seed
         self.extra_tokens = extra_tokens  # MTP needs `num_mtp` more label tokens
         self.pin_memory = pin_memory and torch.cuda.is_available()
+        self.documents_per_row = documents_per_row  # > 0: rows are packed documents and carry `positions`
         self._step = 0
 
     def _batch(self, step: int):
@@ -41,9 +43,19 @@ class SyntheticDataLoader(Stateful):
         # with MTP the model gets the look-ahead tokens too: depth k embeds inputs[:, k : k + seq_len]
         inputs = tok[:, : self.seq_len + self.extra_tokens].contiguous()
         labels = tok[:, 1:].contiguous()
+        batch = {"input": inputs}
+        if self.documents_per_row > 0:
+            # random document boundaries: position inside the document for each of the seq_len main tokens
+            width = self.seq_len
+            cuts = torch.rand(self.batch_size, width, generator=g) < (self.documents_per_row - 1) / max(width, 1)
+            cuts[:, 0] = True
+            idx = torch.arange(width).expand(self.batch_size, width)
+            start = torch.where(cuts, idx, torch.zeros_like(idx)).cummax(dim=1).values
+            batch["positions"] = (idx - start).contiguous()
         if self.pin_memory:
-            inputs, labels = inputs.pin_memory(), labels.pin_memory()
-        return {"input": inputs}, labels
+            batch = {k: v.pin_memory() for k, v in batch.items()}
+            labels = labels.pin_memory()
+        return batch, labels
 
     def __iter__(self):
         while True:
@@ -72,6 +84,7 @@ def build_dataloader(cfg, *, model_config, training, dp_rank: int, dp_world_size
             vocab_size=cfg.vocab_size or model_config.vocab_size, seq_len=training.seq_len,
             batch_size=training.local_batch_size, dp_rank=dp_rank, dp_world_size=dp_world_size, seed=cfg.seed,
             pin_memory=cfg.pin_memory, extra_tokens=extra, infinite=cfg.infinite,
+            documents_per_row=cfg.documents_per_row,
         )
     if isinstance(cfg, TextDataLoaderConfig):
         from titan_b200.data.text_datasets import build_text_dataloader

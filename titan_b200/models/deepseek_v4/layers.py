@@ -156,28 +156,24 @@ class Compressor(Module):
         self.wgate = Linear(cfg.dim, width, bias=False).to(torch.float32)
         self.norm = RMSNorm(head_dim, eps=cfg.norm_eps)
 
-    def _overlap(self, t: torch.Tensor, fill: float) -> torch.Tensor:
-        """[B, C, r, 2d] → [B, C, 2r, d]: slots r.. = this block's second half, slots ..r = previous block's first."""
-        B, C, r, _ = t.shape
-        d = self.head_dim
-        out = t.new_full((B, C, 2 * r, d), fill)
-        out[:, :, r:] = t[..., d:]
-        out[:, 1:, :r] = t[:, :-1, :, :d]
-        return out
-
     def pool(self, kv: torch.Tensor, score: torch.Tensor) -> torch.Tensor:
-        """kv, score [B, S, width] fp32 → pooled [B, S/ratio, head_dim] fp32."""
-        r = self.ratio
-        kv = kv.unflatten(1, (-1, r))
-        score = score.unflatten(1, (-1, r)) + _w(self.ape).float()
-        if self.overlap:
-            kv, score = self._overlap(kv, 0.0), self._overlap(score, float("-inf"))
-        return (kv * score.softmax(dim=2)).sum(dim=2)
+        """kv, score [B, S, width] fp32 → pooled [B, S/ratio, head_dim] fp32 (one kernel on CUDA)."""
+        from titan_b200.ops.compressor_pool import compressor_pool
 
-    def forward(self, x: torch.Tensor, freqs_cis: torch.Tensor, positions=None) -> torch.Tensor:
+        return compressor_pool(kv, score, _w(self.ape), self.ratio, self.head_dim, self.overlap)
+
+    def forward(self, x: torch.Tensor, freqs_cis: torch.Tensor, positions=None,
+                allow_residual: bool = False) -> torch.Tensor:
         B, S, _ = x.shape
         if S % self.ratio != 0:
-            raise ValueError(f"sequence length {S} must be a multiple of the compression ratio {self.ratio}")
+            if not allow_residual:
+                raise ValueError(f"sequence length {S} must be a multiple of the compression ratio {self.ratio}")
+            # packed documents: the tokens after the last complete block stay uncompressed
+            S = S // self.ratio * self.ratio
+            x = x[:, :S]
+            positions = positions[..., :S] if positions is not None else None
+            if S == 0:
+                return x.new_zeros(B, 0, self.head_dim)
         xf = x.float()
         kv = F.linear(xf, _w(self.wkv.weight).float())
         score = F.linear(xf, _w(self.wgate.weight).float())
@@ -205,11 +201,11 @@ class Indexer(Module):
         self.compressor = Compressor(cfg, ratio, self.head_dim)
         self.scale = self.head_dim ** -0.5 * self.n_heads ** -0.5
 
-    def forward(self, x, qr, freqs_cis, positions=None):
+    def forward(self, x, qr, freqs_cis, positions=None, allow_residual: bool = False):
         B, S, _ = x.shape
         q = self.wq_b(qr).view(B, S, self.n_heads, self.head_dim)
         q = rotate_activation(rope_tail(q, freqs_cis, self.rd, positions))
-        k = rotate_activation(self.compressor(x, freqs_cis, positions))
+        k = rotate_activation(self.compressor(x, freqs_cis, positions, allow_residual))
         return q, k, self.weights_proj(x) * self.scale
 
     def init_states(self, *, init_std=0.02, **kw):

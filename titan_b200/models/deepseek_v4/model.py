@@ -54,7 +54,9 @@ class PreAttention(Module):
         elif self.compress_ratio > 1:
             self.compressor_128 = Compressor(cfg, self.compress_ratio, cfg.head_dim)
 
-    def forward(self, x, freqs_cis, positions=None):
+    def forward(self, x, freqs_cis, positions=None, allow_residual: bool = False):
+        """``allow_residual``: packed documents whose length is no multiple of the compression ratio keep their tail
+        uncompressed instead of raising."""
         B, S, _ = x.shape
         qr = self.q_norm(self.wq_a(x))
         q = self.wq_b(qr).unflatten(-1, (-1, self.head_dim))  # local heads under tensor parallelism
@@ -64,10 +66,10 @@ class PreAttention(Module):
         kv_compress = q_idx = k_idx = weights = None
         if self.compress_ratio == 4:
             # the indexer learns from its own KL loss only: its inputs are cut from the main graph
-            q_idx, k_idx, weights = self.indexer(x.detach(), qr.detach(), freqs_cis, positions)
-            kv_compress = self.compressor(x, freqs_cis, positions)
+            q_idx, k_idx, weights = self.indexer(x.detach(), qr.detach(), freqs_cis, positions, allow_residual)
+            kv_compress = self.compressor(x, freqs_cis, positions, allow_residual)
         elif self.compress_ratio > 1:
-            kv_compress = self.compressor_128(x, freqs_cis, positions)
+            kv_compress = self.compressor_128(x, freqs_cis, positions, allow_residual)
         return q, kv, kv_compress, q_idx, k_idx, weights
 
     def init_states(self, *, init_std=0.02, **kw):
@@ -178,7 +180,19 @@ class V4Attention(Module):
     def forward(self, x, freqs_cis, attention_masks=None, positions=None):
         if getattr(self, "cp", None) is not None:  # context parallelism: set by its strategy
             return self.cp.forward(self, x, freqs_cis)
-        q, kv, kv_c, q_idx, k_idx, w = self.pre_attention(x, freqs_cis, positions)
+        ranges = getattr(attention_masks, "doc_ranges", None)
+        if ranges is not None:
+            # packed stream [1, T, D]: window, compressor, indexer and attention see one document at a time (its
+            # positions restart at 0, so no explicit positions are needed inside a document)
+            if x.shape[0] != 1:
+                raise ValueError("a packed DeepSeek-V4 stream has batch size 1")
+            return torch.cat([self._one_sequence(x[:, a:b], freqs_cis, None, True) for a, b in ranges], dim=1)
+        return self._one_sequence(x, freqs_cis, positions, False)
+
+    def _one_sequence(self, x, freqs_cis, positions, allow_residual: bool):
+        q, kv, kv_c, q_idx, k_idx, w = self.pre_attention(x, freqs_cis, positions, allow_residual)
+        if kv_c is not None and kv_c.shape[1] == 0:  # shorter than one block: window attention only
+            kv_c = q_idx = k_idx = w = None
         o = self.inner_attention(q, kv, kv_c, q_idx, k_idx, w)
         return self.post_attention(o, freqs_cis, positions)
 

@@ -141,6 +141,8 @@ class DeepSeekV4Model(Module):
         use_smla: bool = False
         num_mtp_modules: int = 0
         mtp_layer_compress_ratio: int = 1
+        use_global_tnd: bool = False
+        """Pack every valid token of a batch of documents into one [1, T] stream (needs dataloader positions)."""
 
         def update_from_config(self, *, trainer_config, **kw) -> None:
             from titan_b200.protocols.converter import has_converter
@@ -211,14 +213,15 @@ class DeepSeekV4Model(Module):
     def _freqs_for(self, layer_id: int):
         return self.freqs_cis if _ratio_of(self.config, layer_id) > 1 else self.freqs_cis_wo_compressor
 
-    def forward(self, tokens, input_ids=None, attention_masks=None, positions=None):
+    def forward(self, tokens, input_ids=None, attention_masks=None, positions=None, mtp_inputs=None):
         """tokens [B, S + num_mtp] ids (first stage) or hidden streams [B, S, hc, D] (later pipeline stages, which
-        get the token ids as ``input_ids`` for hash routing)."""
+        get the token ids as ``input_ids`` for hash routing).  A packed stream (``attention_masks`` = the packed
+        layout) is [1, T] without an MTP tail; its MTP depths read ``mtp_inputs`` [num_mtp, 1, T] instead."""
         cfg = self.config
         raw = None
         if self.tok_embeddings is not None:
             raw = tokens
-            s = tokens.shape[1] - cfg.num_mtp_modules
+            s = tokens.shape[1] - (cfg.num_mtp_modules if mtp_inputs is None else 0)
             input_ids = tokens[:, :s].detach().long()
             h = self.tok_embeddings(tokens[:, :s]).unsqueeze(2).repeat(1, 1, self.hc_mult, 1)
         else:
@@ -239,7 +242,7 @@ class DeepSeekV4Model(Module):
             raise RuntimeError("DeepSeek-V4 MTP needs the token ids on the stage that owns the output head")
         outs = [out]
         for k in range(cfg.num_mtp_modules):
-            emb = self.tok_embeddings(raw[:, k + 1: k + 1 + s])
+            emb = self.tok_embeddings(raw[:, k + 1: k + 1 + s] if mtp_inputs is None else mtp_inputs[k])
             layer_id = cfg.n_layers + k
             prev, hn = self.layers[str(layer_id)](emb, prev, input_ids, self.freqs_cis_wo_compressor, attention_masks,
                                                   positions)

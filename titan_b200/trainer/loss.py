@@ -46,7 +46,9 @@ def multi_token_cross_entropy_loss(preds, labels: torch.Tensor, *, num_mtp: int,
     """
     if not isinstance(preds, (list, tuple)):
         return _one(preds, labels)
-    if labels.dim() == 2:
+    if labels.dim() == 3:  # packed stream: one row of labels per head, already aligned ([1 + num_mtp, 1, T])
+        parts = list(labels.unbind(0))
+    elif labels.dim() == 2:
         s = labels.shape[1] - num_mtp
         parts = [labels[:, k: k + s] for k in range(num_mtp + 1)]
     else:

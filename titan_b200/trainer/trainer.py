@@ -283,6 +283,19 @@ class Trainer:
             from titan_b200.models.common.varlen_attention import build_varlen_metadata
 
             extra_kwargs["attention_masks"] = build_varlen_metadata(extra_inputs["positions"])
+        if getattr(self.model_config, "use_global_tnd", False) and "positions" in extra_inputs:
+            # DeepSeek-V4 packed stream: every valid token of the batch in one [1, T] sequence
+            if self.parallel_dims.pp_enabled or self.parallel_dims.cp_enabled:
+                raise NotImplementedError("use_global_tnd excludes pipeline and context parallelism")
+            from titan_b200.models.deepseek_v4.tnd import pack_global_tnd
+
+            rows = tuple(inputs.shape)
+            inputs, labels, packed = pack_global_tnd(inputs, labels, extra_inputs.pop("positions"), self.model_config)
+            extra_kwargs.update(packed)
+            if not getattr(self, "_tnd_logged", False):
+                self._tnd_logged = True
+                logger.info("global TND: batch %s packed into one stream of %d tokens, %d documents", rows,
+                            inputs.shape[1], packed["attention_masks"].batch_size)
         if "positions" in extra_inputs:  # sliced together with the tokens under context parallelism
             extra_kwargs["positions"] = extra_inputs.pop("positions")
         if self.parallel_dims.cp_enabled:
