@@ -16,7 +16,9 @@
 #include "../common/tb_common.cuh"
 
 #define TB_ADAM_MAX_TENSORS 24
-#define TB_ADAM_MAX_BLOCKS 480
+// 592 = 148 SMs x 4 resident blocks of 512 threads: one balanced wave per launch (480 blocks left 3 or 4 per SM,
+// i.e. a fifth of the machine idle while the fuller SMs finished)
+#define TB_ADAM_MAX_BLOCKS 592
 #define TB_ADAM_CHUNK 65536
 
 struct TbAdamArgs {
@@ -26,8 +28,9 @@ struct TbAdamArgs {
   void* v[TB_ADAM_MAX_TENSORS];
   void* vmax[TB_ADAM_MAX_TENSORS];  // amsgrad only
   long long n[TB_ADAM_MAX_TENSORS];
-  int block_chunk[TB_ADAM_MAX_BLOCKS];
+  unsigned short block_chunk[TB_ADAM_MAX_BLOCKS];  // chunk index inside the slot's window (see `base`)
   unsigned char block_tensor[TB_ADAM_MAX_BLOCKS];
+  long long base[TB_ADAM_MAX_TENSORS];             // first element of the slot's window inside its tensor
 };
 
 namespace {
@@ -66,7 +69,7 @@ __global__ void __launch_bounds__(512) adamw_kernel(const __grid_constant__ TbAd
                                                     const float* __restrict__ grad_scale, int decoupled,
                                                     int amsgrad, int maximize) {
   const int t = a.block_tensor[blockIdx.x];
-  const long long start = (long long)a.block_chunk[blockIdx.x] * TB_ADAM_CHUNK;
+  const long long start = a.base[t] + (long long)a.block_chunk[blockIdx.x] * TB_ADAM_CHUNK;
   const long long n = a.n[t];
   PT* p = (PT*)a.p[t];
   const GT* g = (const GT*)a.g[t];
@@ -179,9 +182,11 @@ TB_API int tb_adamw_multi(void* const* p, const void* const* g, void* const* m, 
       a.p[slot] = p[i]; a.g[slot] = g[i]; a.m[slot] = m[i]; a.v[slot] = v[i];
       a.vmax[slot] = (amsgrad && vmax != nullptr) ? vmax[i] : nullptr;
       a.n[slot] = n;
+      a.base[slot] = done * TB_ADAM_CHUNK;  // a tensor that spans several launches continues where it stopped
+      unsigned short local = 0;
       while (done < chunks && nb < TB_ADAM_MAX_BLOCKS) {
         a.block_tensor[nb] = (unsigned char)slot;
-        a.block_chunk[nb] = (int)done;
+        a.block_chunk[nb] = local++;
         ++nb; ++done;
       }
     }

@@ -1,0 +1,306 @@
+// Block-scaled MXFP8 GEMM on the 5th-generation tensor cores:
+//
+//   C[M,N] (bf16) = Σ_k  (A_q[m,k] · 2^(SA[m,k/32]-127)) · (B_q[n,k] · 2^(SB[n,k/32]-127))
+//
+// A_q [M,K], B_q [N,K]: e4m3 bytes, K contiguous.  SA / SB: e8m0 bytes, one per 32 elements of K, handed over in
+// "atom" order (see below).  The scaling happens INSIDE the MMA (`tcgen05.mma.kind::mxf8f6f4.block_scale`): the
+// scale bytes travel global -> shared (bulk copy) -> tensor memory (`tcgen05.cp`) next to the operand tiles, so the
+// GEMM reads one byte per element and runs at the fp8 rate.
+//
+// Roles (192 threads, persistent, one CTA per SM): warp 0 lane 0 = TMA producer, warp 1 lane 0 = MMA issuer (also
+// issues the scale copies into tensor memory), warps 2..5 = epilogue (tcgen05.ld -> bf16 -> swizzled staging -> TMA
+// store).  Stage = 128 K-elements: A 128x128 B, B 256x128 B (128B-swizzled), 3 scale atoms of 512 B.
+//
+// Scale atom: the scales of 128 rows x 4 consecutive K-blocks (= one stage), 512 bytes, byte offset of
+// (row = 32*m1 + m0, block kb) is  m0*16 + m1*4 + kb.  `tcgen05.cp.32x128b.warpx4` copies the 32 rows x 16 bytes of an
+// atom into 4 tensor-memory columns of every lane quarter; the MMA of K-step kb selects byte kb of each column
+// through the scale-factor id fields of its instruction descriptor.  Atoms are stored [row block][stage] in global
+// memory so one 512-byte bulk copy fetches one.
+//
+// Tensor memory: columns 0..255 accumulator (one 128x256 fp32 tile), 256.. scale slots (16 columns per stage: 4 for A,
+// 8 for B).  With a single accumulator the next tile's MMAs wait for the epilogue to drain the previous one.
+//
+// Every wait is bounded (gemm_core.cuh `wait_bounded`); on expiry: status word, CTA abort flag, drain, free TMEM.
+//
+// Reference counterpart: the MXFP8 linear / grouped GEMM of torchtitan_npu/converters/lowp (mx_linear.py:26-100,
+// mxfp8_grouped_mm.py:22-109), which call `npu_quant_matmul` / `npu_grouped_matmul` with e8m0 block scales.
+#include "../gemm/gemm_core.cuh"
+
+using namespace tbg;
+
+namespace {
+
+constexpr int XBK = 128;                       // K elements (= bytes) per stage
+constexpr int XA_STAGE = BM * XBK;             // 16 KB
+constexpr int XB_STAGE = BN * XBK;             // 32 KB
+constexpr int SF_ATOM = 512;
+constexpr int XSF_STAGE = 3 * SF_ATOM;         // A atom, two B atoms
+constexpr int XSTAGES = 4;
+constexpr int XC_STAGE = 16 * 1024;            // epilogue staging: one 128 x 64 bf16 box
+constexpr int XSMEM = XSTAGES * (XA_STAGE + XB_STAGE + XSF_STAGE) + XC_STAGE + 1024 + 256;
+static_assert(XSMEM <= 227 * 1024, "shared memory budget");
+constexpr int SF_TMEM_BASE = 256;              // first scale column
+constexpr int SF_TMEM_PER_STAGE = 16;
+
+struct XParams {
+  int M, N, K;
+  const uint8_t* sfa;  // [M/128][K/128][512]
+  const uint8_t* sfb;  // [N/128][K/128][512]
+  int* status;
+};
+
+// instruction descriptor of kind::mxf8f6f4 with block scaling: [4,6) B scale id | [7,10) A format (0 = e4m3) |
+// [10,13) B format | 15/16 A/B major (0 = K) | [17,23) N >> 3 | 23 scale format (1 = ue8m0) | [24,29) M >> 4 |
+// [29,31) A scale id
+__device__ __forceinline__ uint32_t idesc_mxf8(int m, int n, uint32_t sf_id) {
+  return (sf_id << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) | (sf_id << 29);
+}
+
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t sfa,
+                                          uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+// 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, replicated into the four lane quarters
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint32_t smem_addr) {
+  const uint64_t desc = make_smem_desc(smem_addr, 16, 128, 0);  // no swizzle; 8-row groups 128 B apart
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ XParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem_a + XSTAGES * XA_STAGE;
+  uint8_t* smem_c = smem_b + XSTAGES * XB_STAGE;  // 16 KB staging, 1024-byte aligned
+  uint8_t* smem_sf = smem_c + XC_STAGE;           // [XSTAGES][3][512]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sf + XSTAGES * XSF_STAGE);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + XSTAGES;
+  uint64_t* tmem_full_bar = bars + 2 * XSTAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 1;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < XSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_empty_bar, 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int num_m = p.M / BM, num_n = (p.N + BN - 1) / BN, kstages = p.K / XBK;
+  const int num_tiles = num_m * num_n;
+
+  auto tile_of = [&](int t, int& m0, int& n0) {  // grouped raster: GROUP_M row tiles share their B columns in L2
+    const int per_group = GROUP_M * num_n;
+    const int group = t / per_group, first_m = group * GROUP_M;
+    const int gsize = min(num_m - first_m, GROUP_M);
+    const int in_group = t - group * per_group;
+    m0 = (first_m + in_group % gsize) * BM;
+    n0 = (in_group / gsize) * BN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m0, n0;
+        tile_of(t, m0, n0);
+        const bool second_b = n0 + 128 < p.N;  // the tile's upper 128 columns exist
+        for (int ks = 0; ks < kstages; ++ks) {
+          if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
+            ok = false; break;
+          }
+          mbar_expect_tx(&full_bar[stage], XA_STAGE + XB_STAGE + (second_b ? 3 : 2) * SF_ATOM);
+          tma_load_2d(smem_a + stage * XA_STAGE, &tmap_a, &full_bar[stage], ks * XBK, m0);
+          tma_load_2d(smem_b + stage * XB_STAGE, &tmap_b, &full_bar[stage], ks * XBK, n0);
+          uint8_t* sf = smem_sf + stage * XSF_STAGE;
+          bulk_g2s(sf, p.sfa + ((long long)(m0 / 128) * kstages + ks) * SF_ATOM, SF_ATOM, &full_bar[stage]);
+          bulk_g2s(sf + SF_ATOM, p.sfb + ((long long)(n0 / 128) * kstages + ks) * SF_ATOM, SF_ATOM, &full_bar[stage]);
+          if (second_b)
+            bulk_g2s(sf + 2 * SF_ATOM, p.sfb + ((long long)(n0 / 128 + 1) * kstages + ks) * SF_ATOM, SF_ATOM,
+                     &full_bar[stage]);
+          if (++stage == XSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!wait_bounded(tmem_empty_bar, acc_phase ^ 1, abort_flag)) {
+          if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_EMPTY); }
+          break;
+        }
+        tc_fence_after();
+        for (int ks = 0; ks < kstages; ++ks) {
+          if (!wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA); }
+            ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem_a + stage * XA_STAGE);
+          const uint32_t sb = smem_u32(smem_b + stage * XB_STAGE);
+          const uint32_t sf = smem_u32(smem_sf + stage * XSF_STAGE);
+          const uint32_t sfa_t = tmem_base + SF_TMEM_BASE + stage * SF_TMEM_PER_STAGE;
+          const uint32_t sfb_t = sfa_t + 4;
+          tmem_cp_sf(sfa_t, sf);
+          tmem_cp_sf(sfb_t, sf + SF_ATOM);
+          tmem_cp_sf(sfb_t + 4, sf + 2 * SF_ATOM);
+#pragma unroll
+          for (int k = 0; k < XBK / 32; ++k) {
+            // K-major, 128-byte swizzled rows (128 fp8 each), 8-row atoms 1024 B apart; a K step of 32 elements = +32 B
+            const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, 2);
+            const uint64_t db = make_smem_desc(sb + k * 32, 16, 1024, 2);
+            umma_mxf8(tmem_base, da, db, idesc_mxf8(BM, BN, (uint32_t)k), sfa_t, sfb_t, (ks > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == XSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(tmem_full_bar);
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const bool issuer = warp == 2 && lane == 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int m0, n0;
+      tile_of(t, m0, n0);
+      bool ok = wait_bounded(tmem_full_bar, acc_phase, abort_flag);
+      if (!ok && lane == 0 && *abort_flag == 0) {
+        *abort_flag = 1;
+        if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL);
+      }
+      {
+        uint32_t all_ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred pin, pout;\n"
+            "setp.ne.u32 pin, %1, 0;\n"
+            "barrier.red.and.pred pout, 1, 128, pin;\n"
+            "selp.u32 %0, 1, 0, pout;\n"
+            "}\n"
+            : "=r"(all_ok)
+            : "r"(ok ? 1u : 0u)
+            : "memory");
+        if (!all_ok) break;
+      }
+      tc_fence_after();
+      const int row_in_tile = q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+      const uint32_t srow = smem_u32(smem_c) + row_in_tile * 128;
+#pragma unroll 1
+      for (int box = 0; box < 4; ++box) {  // four 64-column boxes through one staging buffer
+        if (issuer) tma_store_wait_read<0>();  // the previous store has finished reading the buffer
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + (box * 2 + cc) * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t chunk = (uint32_t)(cc * 4 + i) ^ (uint32_t)(row_in_tile & 7);  // 128B swizzle
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + chunk * 16), "r"(pk[4 * i]),
+                         "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                         : "memory");
+          }
+        }
+        if (box == 3) {  // all reads of the accumulator are done
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty_bar);
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          const int x = n0 + box * 64;
+          if (x < p.N) tma_store_2d(&tmap_c, smem_c, x, m0);
+          tma_store_commit();
+        }
+      }
+      acc_phase ^= 1;
+    }
+    if (issuer) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int sm_count_x() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+// A_q [M,K], B_q [N,K] e4m3 (K contiguous); sfa [M/128][K/128][512], sfb [ceil(N/128)][K/128][512] e8m0 atoms;
+// C [M,N] bf16.  M % 128 == 0, N % 8 == 0, K % 128 == 0.
+TB_API int tb_mxfp8_gemm(const void* A, const void* B, const void* sfa, const void* sfb, void* C, int M, int N, int K,
+                         int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % 8 || K % XBK) return TB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return TB_ERR_ARG;
+  CUtensorMap ta, tb_, tc;
+  if (int rc = tbh::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM,
+                                 XBK, 3))
+    return rc;
+  if (int rc = tbh::make_tmap_2d(&tb_, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN,
+                                 XBK, 3))
+    return rc;
+  if (int rc = tbh::make_tmap_2d(&tc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N,
+                                 (uint64_t)N * 2, BM, 64, 3))
+    return rc;
+  XParams p{M, N, K, reinterpret_cast<const uint8_t*>(sfa), reinterpret_cast<const uint8_t*>(sfb), status};
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count_x() ? tiles : sm_count_x();
+  TB_CUDA_CHECK(cudaFuncSetAttribute(mxfp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XSMEM));
+  mxfp8_gemm_kernel<<<grid, NUM_THREADS, XSMEM, st>>>(ta, tb_, tc, p);
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}

@@ -1,0 +1,70 @@
+"""Block-scaled MXFP8 GEMM (`csrc/lowp/mxfp8_gemm.cu`): ``C = dequant(A_q, S_a) · dequant(B_q, S_b)ᵀ`` computed by
+`tcgen05.mma.kind::mxf8f6f4.block_scale` with the e8m0 scales applied inside the tensor core.
+
+`pack_scale_atoms` lays the ``[rows, K/32]`` scale bytes out the way the kernel's `tcgen05.cp` wants them: atoms of
+128 rows × 4 K-blocks (512 bytes, byte ``(row % 32)·16 + (row // 32 % 4)·4 + block % 4``), stored ``[row block][K/128]``.
+
+Parity: `npu_quant_matmul` with MX scales as used by torchtitan_npu/patches/torchao_npu/mx_linear.py:26-100.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from titan_b200.ops import _lib
+
+__all__ = ["pack_scale_atoms", "mxfp8_gemm", "mxfp8_gemm_supported", "mxfp8_gemm_ref"]
+
+_DECLARED = False
+
+
+def pack_scale_atoms(scales: torch.Tensor, order: str = "m0,m1,kb") -> torch.Tensor:
+    """[R, K/32] uint8 → [ceil(R/128), K/128, 512] uint8.  Rows are padded with 127 (scale 1.0).  ``order`` names the
+    byte order inside an atom from slowest to fastest index (kept as a parameter so a test can pin the layout)."""
+    R, kb = scales.shape
+    if kb % 4:
+        raise ValueError("K must be a multiple of 128 (4 scale blocks per stage)")
+    pad = (-R) % 128
+    if pad:
+        scales = torch.cat([scales, scales.new_full((pad, kb), 127)], dim=0)
+    rb = scales.shape[0] // 128
+    v = scales.view(rb, 4, 32, kb // 4, 4)  # [row block, m1, m0, stage, block in stage]
+    names = {"m1": 1, "m0": 2, "kb": 4}
+    dims = [names[n] for n in order.split(",")]
+    return v.permute(0, 3, *dims).contiguous().view(rb, kb // 4, 512)
+
+
+def mxfp8_gemm_supported(M: int, N: int, K: int) -> bool:
+    return M > 0 and N > 0 and M % 128 == 0 and N % 8 == 0 and K % 128 == 0
+
+
+def mxfp8_gemm_ref(aq, sa, bq, sb) -> torch.Tensor:
+    """fp32 reference: dequantise both operands (1×32 blocks along K) and multiply."""
+    a = aq.float() * torch.exp2(sa.float() - 127.0).repeat_interleave(32, dim=1)
+    b = bq.float() * torch.exp2(sb.float() - 127.0).repeat_interleave(32, dim=1)
+    return a @ b.t()
+
+
+def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor, *, packed: bool = False,
+               order: str = "m0,m1,kb") -> torch.Tensor:
+    """aq [M, K], bq [N, K] float8_e4m3fn (or uint8 bit patterns); sa [M, K/32], sb [N, K/32] uint8 e8m0 (or, with
+    ``packed``, already in atom order) → bf16 [M, N]."""
+    global _DECLARED
+    M, K = aq.shape
+    N = bq.shape[0]
+    if not (aq.is_cuda and mxfp8_gemm_supported(M, N, K)):
+        raise ValueError(f"mxfp8_gemm: unsupported problem M={M} N={N} K={K} on {aq.device}")
+    if not _DECLARED:
+        P, I = ctypes.c_void_p, ctypes.c_int
+        _lib.declare("tb_mxfp8_gemm", [P, P, P, P, P, I, I, I, P, P])
+        _DECLARED = True
+    if not packed:
+        sa, sb = pack_scale_atoms(sa, order), pack_scale_atoms(sb, order)
+    aq, bq = aq.contiguous(), bq.contiguous()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+    rc = _lib.lib().tb_mxfp8_gemm(aq.data_ptr(), bq.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), M, N, K,
+                                  _lib.shared_status().ptr, _lib.stream_ptr())
+    _lib.check(rc, "mxfp8_gemm")
+    return out

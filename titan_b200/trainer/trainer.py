@@ -357,9 +357,12 @@ class Trainer:
         params = [p for m in self.model_parts for p in m.parameters()]
         if pd.tp_enabled:
             dist_utils.reduce_partial_grads(params)
+        opts = list(self.optimizers)
+        fused_clip = opts if opts and all(hasattr(o, "grad_scale") for o in opts) else None
         grad_norm = dist_utils.clip_grad_norm_(
             params, self.config.training.max_norm, foreach=True,
             pp_mesh=pd.get_optional_mesh("pp") if dist.is_initialized() else None, ep_enabled=pd.ep_enabled,
+            defer_scale_to=fused_clip,  # optimizers that apply the clip coefficient inside their update kernel
         )
         self.optimizers.step()
         self.lr_schedulers.step()
