@@ -182,6 +182,34 @@ def bench_attention(iters):
     emit(**rec)
 
 
+def bench_lowp(iters):
+    """Block-scaled MXFP8 GEMM (operands already quantised) against the library bf16 GEMM of the same shape, and the
+    whole quantise + GEMM product against it."""
+    from titan_b200.lowp.mx import mx_quantize
+    from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, pack_scale_atoms
+
+    tf_peak, _, tag = peaks()
+    for M, N, K in [(8192, 4096, 4096), (8192, 14336, 4096), (8192, 4096, 14336), (16384, 8192, 8192)]:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        aq, sa = mx_quantize(a, -1)
+        bq, sb = mx_quantize(b, -1)
+        pa, pb = pack_scale_atoms(sa), pack_scale_atoms(sb)
+        fl = 2.0 * M * N * K
+        gemm_ms = timeit(lambda: mxfp8_gemm(aq, pa, bq, pb, packed=True), iters)
+
+        def whole():
+            q1, s1 = mx_quantize(a, -1)
+            q2, s2 = mx_quantize(b, -1)
+            return mxfp8_gemm(q1, s1, q2, s2)
+
+        whole_ms = timeit(whole, iters)
+        lib_ms = timeit(lambda: a @ b.t(), iters)
+        emit(kernel="mxfp8_gemm_block_scaled", shape=[M, N, K], ms=gemm_ms, tflops=fl / gemm_ms / 1e9,
+             with_quantise_ms=whole_ms, with_quantise_tflops=fl / whole_ms / 1e9, cublas_bf16_ms=lib_ms,
+             cublas_bf16_tflops=fl / lib_ms / 1e9, vs_bf16_peak=fl / gemm_ms / 1e9 / tf_peak, peak=tag)
+
+
 def profile_case(name: str, launches: int = 3) -> None:
     """One small workload (inputs larger than L2, well under 1 GB on the device), launched a few times: the
     target of a profiler capture.  Prints nothing but the case name; timings come from the bench modes."""
@@ -222,6 +250,14 @@ def profile_case(name: str, launches: int = 3) -> None:
         k = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).transpose(1, 2)
         v = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).transpose(1, 2)
         fn = lambda: _FlashFn.apply(q, k, v, 128 ** -0.5)  # noqa: E731
+    elif name == "mxfp8_gemm":
+        from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, pack_scale_atoms
+
+        aq = torch.randn(8192, 4096, device=dev).to(torch.float8_e4m3fn)
+        bq = torch.randn(4096, 4096, device=dev).to(torch.float8_e4m3fn)
+        pa = pack_scale_atoms(torch.randint(120, 134, (8192, 128), dtype=torch.uint8, device=dev))
+        pb = pack_scale_atoms(torch.randint(120, 134, (4096, 128), dtype=torch.uint8, device=dev))
+        fn = lambda: mxfp8_gemm(aq, pa, bq, pb, packed=True)  # noqa: E731
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     for _ in range(launches):
@@ -235,7 +271,7 @@ def main():
     ap.add_argument("--only", default="gemm,elementwise")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--profile-case", default=None,
-                    help="run one small case a few times and exit (gemm | gemm_wgrad | rmsnorm_bwd | indexer_topk)")
+                    help="run one small case a few times and exit (gemm | gemm_wgrad | rmsnorm_bwd | indexer_topk | flash_fwd | mxfp8_gemm)")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)
@@ -247,6 +283,8 @@ def main():
         bench_elementwise(args.iters)
     if "attention" in which:
         bench_attention(args.iters)
+    if "lowp" in which:
+        bench_lowp(args.iters)
 
 
 if __name__ == "__main__":

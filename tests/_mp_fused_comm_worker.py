@@ -106,8 +106,12 @@ def main():
         xb, wqb, wob = (t.clone().requires_grad_(True) for t in (x, wq, wo))
         q = uf.proj_all_to_all(xa, wqa, s_loc, group)           # [batch * s_full, nq / world]
         y = uf.all_to_all_proj(torch.tanh(q), woa, s_loc, group)  # [batch * s_loc, dim]
-        qr = uf.proj_all_to_all_baseline(xb, wqb, s_loc, group)
-        yr, _ = uf.all_to_all_proj_baseline(torch.tanh(qr), wob, s_loc, group)
+        # differentiable reference: matmul + the autograd all-to-all of the hook-based Ulysses path
+        from titan_b200.parallel.context_parallel.ulysses import all_to_all_4d
+
+        qr = all_to_all_4d((xb @ wqb.t()).view(batch, s_loc, world, -1), 2, 1, group).reshape(batch * s_loc * world, -1)
+        o4 = torch.tanh(qr).view(batch, s_loc * world, 1, -1)
+        yr = all_to_all_4d(o4, 1, 2, group).reshape(batch * s_loc, -1) @ wob.t()
         torch.testing.assert_close(q.float(), qr.float(), rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(y.float(), yr.float(), rtol=3e-2, atol=3e-2)
         gy = torch.randn_like(y)

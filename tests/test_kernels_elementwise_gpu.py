@@ -196,3 +196,18 @@ def test_hadamard_matches_matrix_product(n):
     g = torch.randn_like(y)
     y.backward(g)
     torch.testing.assert_close(x.grad.float(), (g.float() @ H) * n ** -0.5, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_multi_tensor_sum_of_squares(dtype):
+    from titan_b200.ops.multi_tensor import sum_of_squares
+
+    torch.manual_seed(0)
+    # sizes around the 65536-element chunk, a ragged tail, a tensor spanning several launches, an unaligned view
+    big = torch.randn(70_000_000, device="cuda").to(dtype)
+    ts = [torch.randn(n, device="cuda").to(dtype) for n in (1, 7, 65535, 65536, 65537, 1_000_003)] + [big]
+    ts.append(torch.randn(4099, device="cuda").to(dtype)[3:])
+    got = sum_of_squares(ts)
+    ref = sum(t.double().pow(2).sum() for t in ts)
+    assert abs(float(got) - float(ref)) / float(ref) < 1e-4

@@ -262,6 +262,8 @@ class DebugConfig:
     deterministic_warn_only: bool = False
     print_config: bool = False
     moe_force_load_balance: bool = False
+    grad_norm_breakdown: bool = False
+    """Log the gradient norm of the routed-expert weights and of everything else separately at every logged step."""
 
 
 @dataclass(kw_only=True, slots=True)
@@ -292,6 +294,9 @@ class SyntheticDataLoaderConfig:
     infinite: bool = True
     documents_per_row: int = 0
     """> 0: every row holds about this many packed documents and the batch carries their `positions`."""
+    global_stream: bool = False
+    """Draw the global batch from one stream and give each data-parallel rank its rows (N ranks x batch b then see the
+    rows of 1 rank x batch N*b)."""
 
 
 @dataclass(kw_only=True, slots=True)

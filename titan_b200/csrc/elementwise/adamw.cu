@@ -95,22 +95,37 @@ __global__ void __launch_bounds__(512) adamw_kernel(const __grid_constant__ TbAd
     pf -= step_size * mf / (sqrtf(denom_v) * rsqrt_bc2 + eps);
   };
   if (vec_ok) {
-    for (long long i = start + (long long)threadIdx.x * 4; i < end; i += 512 * 4) {
-      if (i + 4 <= end) {
-        float pf[4], gf[4], mf[4], vf[4], xf[4] = {0, 0, 0, 0};
-        load4(p + i, pf); load4(g + i, gf); load4(m + i, mf); load4(v + i, vf);
-        if (amsgrad) load4(vm + i, xf);
+    auto tail = [&](long long i) {  // fewer than 4 elements left for this thread
+      for (long long j = i; j < end; ++j) {
+        float pf = to_f(p[j]), mf = to_f(m[j]), vf = to_f(v[j]), xf = amsgrad ? to_f(vm[j]) : 0.f;
+        update(pf, to_f(g[j]), mf, vf, xf);
+        p[j] = from_f<PT>(pf); m[j] = from_f<ST>(mf); v[j] = from_f<ST>(vf);
+        if (amsgrad) vm[j] = from_f<ST>(xf);
+      }
+    };
+    // two groups of 4 elements per thread and iteration: all eight loads are issued before the first update
+    for (long long i = start + (long long)threadIdx.x * 4; i < end; i += 512 * 8) {
+      const long long j = i + 512 * 4;
+      const bool has_a = i + 4 <= end, has_b = j + 4 <= end;
+      float pa[4], ga[4], ma[4], va[4], xa[4] = {0, 0, 0, 0};
+      float pb[4], gb[4], mb[4], vb[4], xb[4] = {0, 0, 0, 0};
+      if (has_a) { load4(p + i, pa); load4(g + i, ga); load4(m + i, ma); load4(v + i, va); if (amsgrad) load4(vm + i, xa); }
+      if (has_b) { load4(p + j, pb); load4(g + j, gb); load4(m + j, mb); load4(v + j, vb); if (amsgrad) load4(vm + j, xb); }
+      if (has_a) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) update(pf[k], gf[k], mf[k], vf[k], xf[k]);
-        store4(p + i, pf); store4(m + i, mf); store4(v + i, vf);
-        if (amsgrad) store4(vm + i, xf);
+        for (int k = 0; k < 4; ++k) update(pa[k], ga[k], ma[k], va[k], xa[k]);
+        store4(p + i, pa); store4(m + i, ma); store4(v + i, va);
+        if (amsgrad) store4(vm + i, xa);
       } else {
-        for (long long j = i; j < end; ++j) {
-          float pf = to_f(p[j]), mf = to_f(m[j]), vf = to_f(v[j]), xf = amsgrad ? to_f(vm[j]) : 0.f;
-          update(pf, to_f(g[j]), mf, vf, xf);
-          p[j] = from_f<PT>(pf); m[j] = from_f<ST>(mf); v[j] = from_f<ST>(vf);
-          if (amsgrad) vm[j] = from_f<ST>(xf);
-        }
+        tail(i);
+      }
+      if (has_b) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) update(pb[k], gb[k], mb[k], vb[k], xb[k]);
+        store4(p + j, pb); store4(m + j, mb); store4(v + j, vb);
+        if (amsgrad) store4(vm + j, xb);
+      } else if (j < end) {
+        tail(j);
       }
     }
   } else {
@@ -192,4 +207,95 @@ TB_API int tb_adamw_multi(void* const* p, const void* const* g, void* const* m, 
     }
   }
   return flush();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Multi-tensor sum of squares (the gradient norm before clipping): block b reduces one chunk of one tensor and writes
+// ONE partial; the caller sums the partials (a fixed order, so the norm is reproducible).  Same chunk table as AdamW.
+struct TbSumSqArgs {
+  const void* g[TB_ADAM_MAX_TENSORS];
+  long long n[TB_ADAM_MAX_TENSORS];
+  long long base[TB_ADAM_MAX_TENSORS];
+  unsigned short block_chunk[TB_ADAM_MAX_BLOCKS];
+  unsigned char block_tensor[TB_ADAM_MAX_BLOCKS];
+};
+
+namespace {
+template <typename GT>
+__global__ void __launch_bounds__(512) sumsq_kernel(const __grid_constant__ TbSumSqArgs a, float* __restrict__ out) {
+  const int t = a.block_tensor[blockIdx.x];
+  const long long start = a.base[t] + (long long)a.block_chunk[blockIdx.x] * TB_ADAM_CHUNK;
+  const long long n = a.n[t];
+  const GT* g = (const GT*)a.g[t];
+  const long long end = (start + TB_ADAM_CHUNK < n) ? start + TB_ADAM_CHUNK : n;
+  float acc0 = 0.f, acc1 = 0.f;
+  if ((reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+    constexpr int V = tb::Vec16<GT>::N;
+    long long i = start + (long long)threadIdx.x * V;
+    for (; i + V <= end; i += 512LL * V) {
+      const tb::Vec16<GT> v = tb::ld16(g + i);
+#pragma unroll
+      for (int k = 0; k < V; k += 2) {
+        const float x = tb::to_f(v.v[k]), y = tb::to_f(v.v[k + 1]);
+        acc0 = fmaf(x, x, acc0); acc1 = fmaf(y, y, acc1);
+      }
+    }
+    if (i < end) {  // at most one thread holds the ragged tail of the chunk
+      for (long long j = i; j < end && j < i + V; ++j) { const float x = tb::to_f(g[j]); acc0 = fmaf(x, x, acc0); }
+    }
+  } else {
+    for (long long j = start + threadIdx.x; j < end; j += 512) { const float x = tb::to_f(g[j]); acc0 = fmaf(x, x, acc0); }
+  }
+  float s = tb::warp_sum(acc0 + acc1);
+  __shared__ float part[16];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < 16 ? part[threadIdx.x] : 0.f;
+    s = tb::warp_sum(s);
+    if (threadIdx.x == 0) out[blockIdx.x] = s;
+  }
+}
+}  // namespace
+
+// partials: float[capacity]; on return *written partials hold Σ g² of consecutive chunks.  dtype: 0 fp32, 1 bf16, 2 fp16.
+TB_API int tb_multi_sumsq(const void* const* g, const long long* numel, int count, int dtype, float* partials,
+                          long long capacity, long long* written, cudaStream_t st) {
+  if (count < 0 || (dtype != 0 && dtype != 1 && dtype != 2)) return TB_ERR_ARG;
+  TbSumSqArgs a;
+  int nt = 0, nb = 0;
+  long long out_pos = 0;
+  auto flush = [&]() -> int {
+    if (nb == 0) { nt = 0; return 0; }
+    if (out_pos + nb > capacity) return TB_ERR_ARG;
+    float* out = partials + out_pos;
+    if (dtype == 0) sumsq_kernel<float><<<nb, 512, 0, st>>>(a, out);
+    else if (dtype == 1) sumsq_kernel<__nv_bfloat16><<<nb, 512, 0, st>>>(a, out);
+    else sumsq_kernel<__half><<<nb, 512, 0, st>>>(a, out);
+    TB_CUDA_CHECK(cudaGetLastError());
+    tb_note_launch(1);
+    out_pos += nb;
+    nt = 0; nb = 0;
+    return 0;
+  };
+  for (int i = 0; i < count; ++i) {
+    const long long n = numel[i];
+    if (n <= 0) continue;
+    const long long chunks = (n + TB_ADAM_CHUNK - 1) / TB_ADAM_CHUNK;
+    long long done = 0;
+    while (done < chunks) {
+      if (nt == TB_ADAM_MAX_TENSORS || nb == TB_ADAM_MAX_BLOCKS) { if (int rc = flush()) return rc; }
+      const int slot = nt++;
+      a.g[slot] = g[i]; a.n[slot] = n; a.base[slot] = done * TB_ADAM_CHUNK;
+      unsigned short local = 0;
+      while (done < chunks && nb < TB_ADAM_MAX_BLOCKS) {
+        a.block_tensor[nb] = (unsigned char)slot;
+        a.block_chunk[nb] = local++;
+        ++nb; ++done;
+      }
+    }
+  }
+  if (int rc = flush()) return rc;
+  *written = out_pos;
+  return 0;
 }

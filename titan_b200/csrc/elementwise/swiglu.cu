@@ -16,7 +16,7 @@
 namespace {
 using namespace tb;
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restrict__ up,
@@ -24,14 +24,8 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ g
                                                          long long rows, int H, long long in_pitch,
                                                          long long out_pitch, float limit) {
   constexpr int V = Vec16<T>::N;
-  const int vec_per_row = H / V;
-  const long long total = rows * vec_per_row;
-  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total;
-       it += (long long)gridDim.x * blockDim.x) {
-    const long long r = it / vec_per_row;
-    const int c = (int)(it % vec_per_row) * V;
-    Vec16<T> gv = ld16(gate + r * in_pitch + c), uv = ld16(up + r * in_pitch + c);
-    const float sc = score != nullptr ? score[r] : 1.f;
+  // a block walks whole rows (no index division); two vectors per thread are in flight per iteration
+  auto act = [&](const Vec16<T>& gv, const Vec16<T>& uv, float sc) {
     Vec16<T> o;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
@@ -42,7 +36,21 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ g
       }
       o.v[i] = from_f<T>(g * sigmoidf_(g) * u * sc);
     }
-    st16(out + r * out_pitch + c, o);
+    return o;
+  };
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* gp = gate + r * in_pitch;
+    const T* upp = up + r * in_pitch;
+    T* op = out + r * out_pitch;
+    const float sc = score != nullptr ? score[r] : 1.f;
+    int c = threadIdx.x * V;
+    for (; c + (int)blockDim.x * V < H; c += 2 * blockDim.x * V) {
+      const int c2 = c + blockDim.x * V;
+      const Vec16<T> g1 = ld16(gp + c), u1 = ld16(upp + c), g2 = ld16(gp + c2), u2 = ld16(upp + c2);
+      st16(op + c, act(g1, u1, sc));
+      st16(op + c2, act(g2, u2, sc));
+    }
+    if (c < H) st16(op + c, act(ld16(gp + c), ld16(upp + c), sc));
   }
 }
 
@@ -113,8 +121,13 @@ TB_API int tb_swiglu_fwd(const void* gate, const void* up, void* out, const floa
   TB_DISPATCH_DTYPE(dtype, {
     constexpr int V = Vec16<T>::N;
     if (H % V != 0 || in_pitch % V != 0 || out_pitch % V != 0) return TB_ERR_ARG;
-    swiglu_fwd_kernel<T><<<grid_for(rows * (H / V), 256), 256, 0, st>>>((const T*)gate, (const T*)up, (T*)out, score,
-                                                                       rows, H, in_pitch, out_pitch, limit);
+    // a block per row (grid-stride): as many threads as half the row's vectors, between one warp and 256
+    int block = ((H / V + 1) / 2 + 31) / 32 * 32;
+    block = block < 32 ? 32 : (block > 256 ? 256 : block);
+    const long long cap = 148LL * 16 * (256 / block);
+    const int grid = (int)(rows < cap ? rows : cap);
+    swiglu_fwd_kernel<T><<<grid, block, 0, st>>>((const T*)gate, (const T*)up, (T*)out, score, rows, H, in_pitch,
+                                                 out_pitch, limit);
   });
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);

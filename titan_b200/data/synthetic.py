@@ -23,7 +23,7 @@ __all__ = ["SyntheticDataLoader", "build_dataloader"]
 class SyntheticDataLoader(Stateful):
     def __init__(self, *, vocab_size: int, seq_len: int, batch_size: int, dp_rank: int = 0, dp_world_size: int = 1,
                  seed: int = 0, pin_memory: bool = True, extra_tokens: int = 0, infinite: bool = True,
-                 documents_per_row: int = 0):
+                 documents_per_row: int = 0, global_stream: bool = False):
         self.vocab_size = vocab_size
         self.seq_len = seq_len
         self.batch_size = batch_size
@@ -33,13 +33,22 @@ class SyntheticDataLoader(Stateful):
         self.extra_tokens = extra_tokens  # MTP needs `num_mtp` more label tokens
         self.pin_memory = pin_memory and torch.cuda.is_available()
         self.documents_per_row = documents_per_row  # > 0: rows are packed documents and carry `positions`
+        # one stream for the whole job: every step draws the GLOBAL batch and each data-parallel rank keeps its rows,
+        # so N ranks x batch b see exactly the rows of 1 rank x batch N*b (parallel runs become comparable)
+        self.global_stream = global_stream
         self._step = 0
 
     def _batch(self, step: int):
         g = torch.Generator()
-        g.manual_seed((self.seed * 1_000_003 + self.dp_rank) * 1_000_003 + step)
         n = self.seq_len + 1 + self.extra_tokens
-        tok = torch.randint(0, self.vocab_size, (self.batch_size, n), generator=g, dtype=torch.int64)
+        if self.global_stream:
+            g.manual_seed(self.seed * 1_000_003 * 1_000_003 + step)
+            tok = torch.randint(0, self.vocab_size, (self.batch_size * self.dp_world_size, n), generator=g,
+                                dtype=torch.int64)
+            tok = tok[self.dp_rank * self.batch_size: (self.dp_rank + 1) * self.batch_size]
+        else:
+            g.manual_seed((self.seed * 1_000_003 + self.dp_rank) * 1_000_003 + step)
+            tok = torch.randint(0, self.vocab_size, (self.batch_size, n), generator=g, dtype=torch.int64)
         # with MTP the model gets the look-ahead tokens too: depth k embeds inputs[:, k : k + seq_len]
         inputs = tok[:, : self.seq_len + self.extra_tokens].contiguous()
         labels = tok[:, 1:].contiguous()
@@ -84,7 +93,7 @@ def build_dataloader(cfg, *, model_config, training, dp_rank: int, dp_world_size
             vocab_size=cfg.vocab_size or model_config.vocab_size, seq_len=training.seq_len,
             batch_size=training.local_batch_size, dp_rank=dp_rank, dp_world_size=dp_world_size, seed=cfg.seed,
             pin_memory=cfg.pin_memory, extra_tokens=extra, infinite=cfg.infinite,
-            documents_per_row=cfg.documents_per_row,
+            documents_per_row=cfg.documents_per_row, global_stream=cfg.global_stream,
         )
     if isinstance(cfg, TextDataLoaderConfig):
         from titan_b200.data.text_datasets import build_text_dataloader

@@ -357,6 +357,14 @@ class Trainer:
         params = [p for m in self.model_parts for p in m.parameters()]
         if pd.tp_enabled:
             dist_utils.reduce_partial_grads(params)
+        if self.config.debug.grad_norm_breakdown:
+            named = [(n, p) for m in self.model_parts for n, p in m.named_parameters() if p.grad is not None]
+            pp_mesh = pd.get_optional_mesh("pp") if dist.is_initialized() else None
+            for label, pick in (("experts", True), ("other", False)):
+                gs = [p.grad for n, p in named if (".experts." in n) == pick]
+                if gs:
+                    logger.info("step %d grad norm of %s: %.4f", self.step, label,
+                                float(dist_utils.get_total_norm_local(gs, 2.0, pp_mesh=pp_mesh)))
         opts = list(self.optimizers)
         fused_clip = opts if opts and all(hasattr(o, "grad_scale") for o in opts) else None
         grad_norm = dist_utils.clip_grad_norm_(
