@@ -197,6 +197,8 @@ def bench_lowp(iters):
         pa, pb = pack_scale_atoms(sa), pack_scale_atoms(sb)
         fl = 2.0 * M * N * K
         gemm_ms = timeit(lambda: mxfp8_gemm(aq, pa, bq, pb, packed=True), iters)
+        t128 = timeit(lambda: mxfp8_gemm(aq, pa, bq, pb, packed=True, tile_n=128), iters)
+        t256 = timeit(lambda: mxfp8_gemm(aq, pa, bq, pb, packed=True, tile_n=256), iters)
 
         def whole():
             q1, s1 = mx_quantize(a, -1)
@@ -206,6 +208,7 @@ def bench_lowp(iters):
         whole_ms = timeit(whole, iters)
         lib_ms = timeit(lambda: a @ b.t(), iters)
         emit(kernel="mxfp8_gemm_block_scaled", shape=[M, N, K], ms=gemm_ms, tflops=fl / gemm_ms / 1e9,
+             tile128_ms=t128, tile256_ms=t256,
              with_quantise_ms=whole_ms, with_quantise_tflops=fl / whole_ms / 1e9, cublas_bf16_ms=lib_ms,
              cublas_bf16_tflops=fl / lib_ms / 1e9, vs_bf16_peak=fl / gemm_ms / 1e9 / tf_peak, peak=tag)
 

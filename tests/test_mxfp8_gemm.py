@@ -19,8 +19,9 @@ def test_scale_atoms_layout():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tile_n", [128, 256])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 384, 512), (1024, 1032, 1024)])
-def test_kernel_matches_dequantised_reference(M, N, K):
+def test_kernel_matches_dequantised_reference(M, N, K, tile_n):
     from titan_b200.lowp.mx import mx_quantize
     from titan_b200.ops import _lib
 
@@ -29,7 +30,7 @@ def test_kernel_matches_dequantised_reference(M, N, K):
     b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
     aq, sa = mx_quantize(a, -1)
     bq, sb = mx_quantize(b, -1)
-    out = mxfp8_gemm(aq, sa, bq, sb)
+    out = mxfp8_gemm(aq, sa, bq, sb, tile_n=tile_n)
     ref = mxfp8_gemm_ref(aq, sa, bq, sb)
     torch.cuda.synchronize()
     _lib.shared_status().raise_if_set("mxfp8 gemm")

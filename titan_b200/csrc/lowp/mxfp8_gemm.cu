@@ -9,7 +9,7 @@
 //
 // Roles (192 threads, persistent, one CTA per SM): warp 0 lane 0 = TMA producer, warp 1 lane 0 = MMA issuer (also
 // issues the scale copies into tensor memory), warps 2..5 = epilogue (tcgen05.ld -> bf16 -> swizzled staging -> TMA
-// store).  Stage = 128 K-elements: A 128x128 B, B 256x128 B (128B-swizzled), 3 scale atoms of 512 B.
+// store).  Stage = 128 K-elements: A 128x128 B, B XBNx128 B (128B-swizzled), one scale atom of 512 B per 128 rows.
 //
 // Scale atom: the scales of 128 rows x 4 consecutive K-blocks (= one stage), 512 bytes, byte offset of
 // (row = 32*m1 + m0, block kb) is  m0*16 + m1*4 + kb.  `tcgen05.cp.32x128b.warpx4` copies the 32 rows x 16 bytes of an
@@ -17,8 +17,10 @@
 // through the scale-factor id fields of its instruction descriptor.  Atoms are stored [row block][stage] in global
 // memory so one 512-byte bulk copy fetches one.
 //
-// Tensor memory: columns 0..255 accumulator (one 128x256 fp32 tile), 256.. scale slots (16 columns per stage: 4 for A,
-// 8 for B).  With a single accumulator the next tile's MMAs wait for the epilogue to drain the previous one.
+// Two tile shapes (template parameter XBN): 128x256 with ONE accumulator (the next tile's MMAs wait for the epilogue to
+// drain it; least operand traffic per flop) and 128x128 with TWO accumulators and six stages (the epilogue of a tile
+// overlaps the MMAs of the next).  Tensor memory: columns 0..255 accumulators, 256.. scale slots (16 columns per
+// stage: 4 for A, up to 8 for B).
 //
 // Every wait is bounded (gemm_core.cuh `wait_bounded`); on expiry: status word, CTA abort flag, drain, free TMEM.
 //
@@ -32,15 +34,22 @@ namespace {
 
 constexpr int XBK = 128;                       // K elements (= bytes) per stage
 constexpr int XA_STAGE = BM * XBK;             // 16 KB
-constexpr int XB_STAGE = BN * XBK;             // 32 KB
 constexpr int SF_ATOM = 512;
-constexpr int XSF_STAGE = 3 * SF_ATOM;         // A atom, two B atoms
-constexpr int XSTAGES = 4;
 constexpr int XC_STAGE = 16 * 1024;            // epilogue staging: one 128 x 64 bf16 box
-constexpr int XSMEM = XSTAGES * (XA_STAGE + XB_STAGE + XSF_STAGE) + XC_STAGE + 1024 + 256;
-static_assert(XSMEM <= 227 * 1024, "shared memory budget");
 constexpr int SF_TMEM_BASE = 256;              // first scale column
 constexpr int SF_TMEM_PER_STAGE = 16;
+
+template <int XBN>
+struct Cfg {
+  static constexpr int STAGES = XBN == 128 ? 6 : 4;
+  static constexpr int NACC = XBN == 128 ? 2 : 1;
+  static constexpr int B_STAGE = XBN * XBK;
+  static constexpr int B_ATOMS = XBN / 128;
+  static constexpr int SF_STAGE = (1 + B_ATOMS) * SF_ATOM;
+  static constexpr int SMEM = STAGES * (XA_STAGE + B_STAGE + SF_STAGE) + XC_STAGE + 1024 + 256;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+  static_assert(SF_TMEM_BASE + STAGES * SF_TMEM_PER_STAGE <= TMEM_COLS && NACC * XBN <= SF_TMEM_BASE, "TMEM budget");
+};
 
 struct XParams {
   int M, N, K;
@@ -81,28 +90,30 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                : "memory");
 }
 
+template <int XBN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ XParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using C = Cfg<XBN>;
+  constexpr int XSTAGES = C::STAGES, XB_STAGE = C::B_STAGE, XSF_STAGE = C::SF_STAGE, NACC = C::NACC;
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem_a + XSTAGES * XA_STAGE;
   uint8_t* smem_c = smem_b + XSTAGES * XB_STAGE;  // 16 KB staging, 1024-byte aligned
-  uint8_t* smem_sf = smem_c + XC_STAGE;           // [XSTAGES][3][512]
+  uint8_t* smem_sf = smem_c + XC_STAGE;           // [XSTAGES][1 + B_ATOMS][512]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sf + XSTAGES * XSF_STAGE);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + XSTAGES;
-  uint64_t* tmem_full_bar = bars + 2 * XSTAGES;
-  uint64_t* tmem_empty_bar = tmem_full_bar + 1;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 1);
+  uint64_t* tmem_full_bar = bars + 2 * XSTAGES;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;   // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < XSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(tmem_full_bar, 1);
-    mbar_init(tmem_empty_bar, 4);
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 4); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -116,7 +127,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
-  const int num_m = p.M / BM, num_n = (p.N + BN - 1) / BN, kstages = p.K / XBK;
+  const int num_m = p.M / BM, num_n = (p.N + XBN - 1) / XBN, kstages = p.K / XBK;
   const int num_tiles = num_m * num_n;
 
   auto tile_of = [&](int t, int& m0, int& n0) {  // grouped raster: GROUP_M row tiles share their B columns in L2
@@ -125,7 +136,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int gsize = min(num_m - first_m, GROUP_M);
     const int in_group = t - group * per_group;
     m0 = (first_m + in_group % gsize) * BM;
-    n0 = (in_group / gsize) * BN;
+    n0 = (in_group / gsize) * XBN;
   };
 
   if (warp == 0) {
@@ -134,7 +145,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m0, n0;
         tile_of(t, m0, n0);
-        const bool second_b = n0 + 128 < p.N;  // the tile's upper 128 columns exist
+        const bool second_b = C::B_ATOMS == 2 && n0 + 128 < p.N;  // the tile's upper 128 columns exist
         for (int ks = 0; ks < kstages; ++ks) {
           if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
@@ -156,9 +167,9 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      uint32_t acc_phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!wait_bounded(tmem_empty_bar, acc_phase ^ 1, abort_flag)) {
+        if (!wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_EMPTY); }
           break;
         }
@@ -176,29 +187,30 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sfb_t = sfa_t + 4;
           tmem_cp_sf(sfa_t, sf);
           tmem_cp_sf(sfb_t, sf + SF_ATOM);
-          tmem_cp_sf(sfb_t + 4, sf + 2 * SF_ATOM);
+          if (C::B_ATOMS == 2) tmem_cp_sf(sfb_t + 4, sf + 2 * SF_ATOM);
 #pragma unroll
           for (int k = 0; k < XBK / 32; ++k) {
             // K-major, 128-byte swizzled rows (128 fp8 each), 8-row atoms 1024 B apart; a K step of 32 elements = +32 B
             const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, 2);
             const uint64_t db = make_smem_desc(sb + k * 32, 16, 1024, 2);
-            umma_mxf8(tmem_base, da, db, idesc_mxf8(BM, BN, (uint32_t)k), sfa_t, sfb_t, (ks > 0 || k > 0) ? 1u : 0u);
+            umma_mxf8(tmem_base + acc * XBN, da, db, idesc_mxf8(BM, XBN, (uint32_t)k), sfa_t, sfb_t,
+                      (ks > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == XSTAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(tmem_full_bar);
-        acc_phase ^= 1;
+        if (ok) umma_commit(&tmem_full_bar[acc]);
+        if (++acc == NACC) { acc = 0; acc_phase ^= 1; }
       }
     }
   } else {
     const int q = warp & 3;
     const bool issuer = warp == 2 && lane == 0;
-    uint32_t acc_phase = 0;
+    int acc = 0; uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int m0, n0;
       tile_of(t, m0, n0);
-      bool ok = wait_bounded(tmem_full_bar, acc_phase, abort_flag);
+      bool ok = wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
       if (!ok && lane == 0 && *abort_flag == 0) {
         *abort_flag = 1;
         if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL);
@@ -219,10 +231,10 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       tc_fence_after();
       const int row_in_tile = q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * XBN + ((uint32_t)(q * 32) << 16);
       const uint32_t srow = smem_u32(smem_c) + row_in_tile * 128;
 #pragma unroll 1
-      for (int box = 0; box < 4; ++box) {  // four 64-column boxes through one staging buffer
+      for (int box = 0; box < XBN / 64; ++box) {  // 64-column boxes through one staging buffer
         if (issuer) tma_store_wait_read<0>();  // the previous store has finished reading the buffer
         asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
@@ -241,10 +253,10 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                          : "memory");
           }
         }
-        if (box == 3) {  // all reads of the accumulator are done
+        if (box == XBN / 64 - 1) {  // all reads of the accumulator are done
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tmem_empty_bar);
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
         }
         fence_proxy_async();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -254,7 +266,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tma_store_commit();
         }
       }
-      acc_phase ^= 1;
+      if (++acc == NACC) { acc = 0; acc_phase ^= 1; }
     }
     if (issuer) tma_store_wait_all<0>();
   }
@@ -277,30 +289,38 @@ int sm_count_x() {
   return n;
 }
 
-}  // namespace
-
-// A_q [M,K], B_q [N,K] e4m3 (K contiguous); sfa [M/128][K/128][512], sfb [ceil(N/128)][K/128][512] e8m0 atoms;
-// C [M,N] bf16.  M % 128 == 0, N % 8 == 0, K % 128 == 0.
-TB_API int tb_mxfp8_gemm(const void* A, const void* B, const void* sfa, const void* sfb, void* C, int M, int N, int K,
-                         int* status, cudaStream_t st) {
-  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % 8 || K % XBK) return TB_ERR_ARG;
-  if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return TB_ERR_ARG;
+template <int XBN>
+int launch_x(const void* A, const void* B, void* C, const XParams& p, cudaStream_t st) {
   CUtensorMap ta, tb_, tc;
-  if (int rc = tbh::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM,
-                                 XBK, 3))
+  if (int rc = tbh::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.K,
+                                 BM, XBK, 3))
     return rc;
-  if (int rc = tbh::make_tmap_2d(&tb_, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN,
-                                 XBK, 3))
+  if (int rc = tbh::make_tmap_2d(&tb_, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.N, (uint64_t)p.K,
+                                 (uint64_t)p.K, XBN, XBK, 3))
     return rc;
-  if (int rc = tbh::make_tmap_2d(&tc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N,
-                                 (uint64_t)N * 2, BM, 64, 3))
+  if (int rc = tbh::make_tmap_2d(&tc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.M, (uint64_t)p.N,
+                                 (uint64_t)p.N * 2, BM, 64, 3))
     return rc;
-  XParams p{M, N, K, reinterpret_cast<const uint8_t*>(sfa), reinterpret_cast<const uint8_t*>(sfb), status};
-  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int tiles = (p.M / BM) * ((p.N + XBN - 1) / XBN);
   const int grid = tiles < sm_count_x() ? tiles : sm_count_x();
-  TB_CUDA_CHECK(cudaFuncSetAttribute(mxfp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XSMEM));
-  mxfp8_gemm_kernel<<<grid, NUM_THREADS, XSMEM, st>>>(ta, tb_, tc, p);
+  TB_CUDA_CHECK(cudaFuncSetAttribute(mxfp8_gemm_kernel<XBN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg<XBN>::SMEM));
+  mxfp8_gemm_kernel<XBN><<<grid, NUM_THREADS, Cfg<XBN>::SMEM, st>>>(ta, tb_, tc, p);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;
+}
+
+}  // namespace
+
+// A_q [M,K], B_q [N,K] e4m3 (K contiguous); sfa [M/128][K/128][512], sfb [ceil(N/128)][K/128][512] e8m0 atoms;
+// C [M,N] bf16.  M % 128 == 0, N % 8 == 0, K % 128 == 0.  tile_n: 128, 256, or 0 = the library's choice.
+TB_API int tb_mxfp8_gemm(const void* A, const void* B, const void* sfa, const void* sfb, void* C, int M, int N, int K,
+                         int tile_n, int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % 8 || K % XBK) return TB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return TB_ERR_ARG;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return TB_ERR_ARG;
+  XParams p{M, N, K, reinterpret_cast<const uint8_t*>(sfa), reinterpret_cast<const uint8_t*>(sfb), status};
+  if (tile_n == 0) tile_n = 256;
+  return tile_n == 128 ? launch_x<128>(A, B, C, p, st) : launch_x<256>(A, B, C, p, st);
 }

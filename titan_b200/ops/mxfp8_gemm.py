@@ -48,9 +48,10 @@ def mxfp8_gemm_ref(aq, sa, bq, sb) -> torch.Tensor:
 
 
 def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor, *, packed: bool = False,
-               order: str = "m0,m1,kb") -> torch.Tensor:
+               order: str = "m0,m1,kb", tile_n: int = 0) -> torch.Tensor:
     """aq [M, K], bq [N, K] float8_e4m3fn (or uint8 bit patterns); sa [M, K/32], sb [N, K/32] uint8 e8m0 (or, with
-    ``packed``, already in atom order) → bf16 [M, N]."""
+    ``packed``, already in atom order) → bf16 [M, N].  ``tile_n``: 128 (two accumulators, epilogue overlapped), 256
+    (one accumulator, least operand traffic) or 0 for the library's choice."""
     global _DECLARED
     M, K = aq.shape
     N = bq.shape[0]
@@ -58,13 +59,13 @@ def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.T
         raise ValueError(f"mxfp8_gemm: unsupported problem M={M} N={N} K={K} on {aq.device}")
     if not _DECLARED:
         P, I = ctypes.c_void_p, ctypes.c_int
-        _lib.declare("tb_mxfp8_gemm", [P, P, P, P, P, I, I, I, P, P])
+        _lib.declare("tb_mxfp8_gemm", [P, P, P, P, P, I, I, I, I, P, P])
         _DECLARED = True
     if not packed:
         sa, sb = pack_scale_atoms(sa, order), pack_scale_atoms(sb, order)
     aq, bq = aq.contiguous(), bq.contiguous()
     out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
     rc = _lib.lib().tb_mxfp8_gemm(aq.data_ptr(), bq.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), M, N, K,
-                                  _lib.shared_status().ptr, _lib.stream_ptr())
+                                  int(tile_n), _lib.shared_status().ptr, _lib.stream_ptr())
     _lib.check(rc, "mxfp8_gemm")
     return out
