@@ -24,6 +24,16 @@ struct PeerPtrs {
   void* p[MAX_RANKS];
 };
 
+// How many CTAs copy instead of multiply: a copier keeps about 190 KB in flight, i.e. roughly 40 GB/s of a link with a
+// few microseconds of latency, so a link-bound problem wants dozens of them and a compute-bound one few.  The share of
+// SMs follows the share of the link in (link time + GEMM time), between 8 and 40.
+int pick_copiers(double flops, double link_bytes, int nranks) {
+  if (nranks <= 1) return 0;
+  const double t_gemm = flops / 1.4e15, t_link = link_bytes / 7.0e11;
+  int c = (int)(148.0 * t_link / (t_link + t_gemm) * 0.6);
+  return c < 8 ? 8 : (c > 40 ? 40 : c);
+}
+
 __global__ void signal_kernel(PeerPtrs flags, int slot, unsigned int value, int nranks) {
   const int r = threadIdx.x;
   if (r < nranks) {
@@ -129,7 +139,7 @@ TB_API int tb_wait_flags(const unsigned int* flags, int first, int count, unsign
 // C[M,N] = concat_r(A_r)[M,K] · B[N,K]ᵀ where A_r = a_ptrs[r] is rank r's [m_shard, K] shard (K-major).
 // ready_flags: local array, slot r is set to >= epoch by rank r once its shard may be read.
 // gathered: local [M, K] buffer that receives the remote shards (each crosses NVLink exactly once; the rows of
-// this rank's own shard are not written).  chunk_flags: local zero-initialised uint32 [M / 128], reused across
+// this rank's own shard are not written).  chunk_flags: local zero-initialised uint32 [2 * M / 128] (flags, then piece counters), reused across
 // calls with increasing epochs.
 TB_API int tb_ag_gemm(void* const* a_ptrs, const void* B, void* C, void* gathered, unsigned int* chunk_flags, int M,
                       int N, int K, int m_shard, int b_mn, int dtype, int rank, int nranks,
@@ -149,7 +159,7 @@ TB_API int tb_ag_gemm(void* const* a_ptrs, const void* B, void* C, void* gathere
   p.ready_flags = ready_flags; p.epoch = epoch; p.tma_store = 1;
   for (int r = 0; r < nranks; ++r) p.peer_src[r] = a_ptrs[r];
   p.gather_dst = gathered; p.chunk_flags = chunk_flags;
-  p.num_copiers = nranks > 1 ? NUM_COPIERS : 0;
+  p.num_copiers = pick_copiers(2.0 * M * N * K, (double)(nranks - 1) * m_shard * K * 2, nranks);
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   int workers = sm_count() - p.num_copiers;
   if (tiles < workers) workers = tiles;
@@ -158,7 +168,7 @@ TB_API int tb_ag_gemm(void* const* a_ptrs, const void* B, void* C, void* gathere
 }
 
 // C[M,N] = A[M,K] · concat_r(B_r)[N,K]ᵀ where B_r = b_ptrs[r] is rank r's [n_shard, K] weight shard.
-// gathered: local [N, K] buffer for the remote weight shards; chunk_flags: local uint32 [N / 256].
+// gathered: local [N, K] buffer for the remote weight shards; chunk_flags: local uint32 [2 * N / 256] (flags, then piece counters).
 TB_API int tb_ag_b_gemm(const void* A, void* const* b_ptrs, void* C, void* gathered, unsigned int* chunk_flags, int M,
                         int N, int K, int n_shard, int dtype, int rank, int nranks,
                         const unsigned int* ready_flags, unsigned int epoch, int* status, cudaStream_t st) {
@@ -177,7 +187,7 @@ TB_API int tb_ag_b_gemm(const void* A, void* const* b_ptrs, void* C, void* gathe
   p.ready_flags = ready_flags; p.epoch = epoch; p.tma_store = 1;
   for (int r = 0; r < nranks; ++r) p.peer_src[r] = b_ptrs[r];
   p.gather_dst = gathered; p.chunk_flags = chunk_flags;
-  p.num_copiers = nranks > 1 ? NUM_COPIERS : 0;
+  p.num_copiers = pick_copiers(2.0 * M * N * K, (double)(nranks - 1) * n_shard * K * 2, nranks);
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   int workers = sm_count() - p.num_copiers;
   if (tiles < workers) workers = tiles;
@@ -315,7 +325,7 @@ TB_API int tb_gemm_a2a_scatter(const void* A, const void* B, void* const* recv_p
 // tb_a2a_gather_gemm: C[M,N] = gather_k(A)[M, nranks*k_shard] · B[N,K]ᵀ (or B[K,N] with b_mn).  Rank r holds the
 // k_shard columns [r*k_shard, ...) of every rank's rows in a_ptrs[r] = [batch * seq_full, k_shard]; this rank's rows
 // are b*seq_full + rank*seq_local + s.  gathered: local [nranks, M, k_shard] buffer (the remote slices land there,
-// each crossing NVLink once); chunk_flags: local uint32 [nranks * M / 128].
+// each crossing NVLink once); chunk_flags: local uint32 [2 * nranks * M / 128] (flags, then piece counters).
 TB_API int tb_a2a_gather_gemm(void* const* a_ptrs, const void* B, void* C, void* gathered, unsigned int* chunk_flags,
                               int M, int N, int k_shard, int seq_local, int b_mn, int dtype, int rank, int nranks,
                               const unsigned int* ready_flags, unsigned int epoch, int* status, cudaStream_t st) {
@@ -337,7 +347,7 @@ TB_API int tb_a2a_gather_gemm(void* const* a_ptrs, const void* B, void* C, void*
   p.ready_flags = ready_flags; p.epoch = epoch; p.tma_store = 1;
   for (int r = 0; r < nranks; ++r) p.peer_src[r] = a_ptrs[r];
   p.gather_dst = gathered; p.chunk_flags = chunk_flags;
-  p.num_copiers = nranks > 1 ? NUM_COPIERS : 0;
+  p.num_copiers = pick_copiers(2.0 * M * N * K, (double)(nranks - 1) * M * k_shard * 2, nranks);
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   int workers = sm_count() - p.num_copiers;
   if (tiles < workers) workers = tiles;

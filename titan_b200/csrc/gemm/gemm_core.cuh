@@ -49,7 +49,6 @@ constexpr int MAX_RANKS = 8;
 constexpr int C_STAGE_BYTES = 32 * 1024;    // epilogue staging: half an output tile (128 x 128 x 2 B)
 constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + C_STAGE_BYTES + 1024 /*align*/ +
                            256 /*barriers*/ + (MAX_GROUPS + 1) * 4;
-constexpr int NUM_COPIERS = 8;              // CTAs that pull remote shards into local memory (gather modes)
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;

@@ -83,11 +83,12 @@ _CHUNK_FLAGS: dict = {}
 
 
 def _chunk_flags(ws: SymmWorkspace, tag: str, n: int) -> torch.Tensor:
-    """Local hand-off flags between copier CTAs and GEMM CTAs (zeroed once; epochs only grow)."""
-    key = (id(ws), tag)
+    """Local hand-off state between copier CTAs and GEMM CTAs: ``n`` chunk flags (zeroed once; epochs only grow)
+    followed by ``n`` piece counters (the copier that delivers a chunk's last piece resets its counter)."""
+    key = (id(ws), tag, n)
     t = _CHUNK_FLAGS.get(key)
-    if t is None or t.numel() < n:
-        t = torch.zeros(max(n, 1024), dtype=torch.int32, device=ws.device)
+    if t is None:
+        t = torch.zeros(2 * n, dtype=torch.int32, device=ws.device)
         _CHUNK_FLAGS[key] = t
     return t
 
