@@ -7,11 +7,13 @@
 //   warp 1      MMA issuer (one thread): S_j = Q K_j^T  (M128 N128 K128, both operands K-major)
 //                                        PV_j = P_j V_j (A = P_j from shared memory, B = V_j MN-major)
 //               S_{j+1} is issued before PV_j so the tensor cores work while the softmax warps handle block j
-//   warps 2..5  softmax, one query row per thread (TMEM lane = row): two passes over S_j in tensor memory (row
-//               maximum, then exp2 / row sum / bf16 P_j into the swizzled A-operand layout), then fold PV_{j-1}
-//               into the running output kept in REGISTERS (128 fp32 per thread):  O <- (O + PV_{j-1}) * 2^(m_{j-1}-m_j)
+//   warps 2..9  softmax, TWO threads per query row (TMEM lane = row; warps w and w+4 share a lane quarter and take
+//               64 of the 128 columns each): one read of S_j from tensor memory into registers, row maximum
+//               (halves exchanged through shared memory), exp2 / row sum / bf16 P_j into the swizzled A-operand
+//               layout, then fold PV_{j-1} into the running output kept in REGISTERS (64 fp32 per thread):
+//               O <- (O + PV_{j-1}) * 2^(m_{j-1}-m_j)
 // Tensor memory: S double-buffered (2 x 128 columns) + PV double-buffered (2 x 128 columns) = all 512 columns.
-// Shared memory: Q 32 KB + K 2 x 32 KB + V 2 x 32 KB + P 2 x 32 KB = 224 KB.
+// Shared memory: Q 32 KB + K 2 x 32 KB + V 2 x 32 KB + P 2 x 32 KB = 224 KB, + 2 KB exchange area and barriers.
 //
 // Every wait is bounded (mbar_wait gives up after 2^22 polls): on expiry the role records a status code, raises the
 // CTA-wide abort flag, and all roles drain to the common exit where the tensor memory is freed.
@@ -27,7 +29,7 @@ constexpr int D = 128;        // head dim
 constexpr int BQ = 128;       // query rows per CTA
 constexpr int BK = 128;       // keys per block
 constexpr int TILE = 32768;   // bytes of a [128 x 128] bf16 tile (two 16 KB boxes of 64 columns)
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 softmax warps
 constexpr uint32_t TMEM_COLS = 512;
 
 struct FaParams {
@@ -44,6 +46,7 @@ struct __align__(8) Bars {
   uint64_t s_full[2], s_empty[2], p_ready[2], o_full[2], o_empty[2];
   uint32_t tmem_slot;
   int abort_flag;
+  float xchg[2][2][BQ];  // [parity][column half][row]: row maxima (and, at the end, row sums) of the two halves
 };
 
 __device__ __forceinline__ void fail(Bars* b, int* status, int code) {
@@ -58,7 +61,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
                                                                 const __grid_constant__ CUtensorMap tm_v,
                                                                 const FaParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The tiles need 1024-byte alignment and there is no room for alignment slack (224 KB of tiles + barriers +
+  // exchange area): the dynamic window of a kernel without static shared memory starts aligned; otherwise refuse.
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, TB_ERR_ARG);
+    return;
+  }
+  uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sK = smem + TILE;          // 2 stages
   uint8_t* sV = smem + 3 * TILE;      // 2 stages
@@ -79,9 +88,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1);
       mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 4);
-      mbar_init(&bars->p_ready[i], 4);
-      mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 8);
+      mbar_init(&bars->p_ready[i], 8);
+      mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 8);
     }
     bars->abort_flag = 0;
     fence_barrier_init();
@@ -169,62 +178,68 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax + output (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    // ---------------------------------------------------------------- softmax + output (warps 2..9)
+    constexpr int HC = BK / 2;            // columns per thread
+    const int quarter = warp & 3;         // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;     // which 64 columns of S / PV / O
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const int pair_bar = 2 + quarter;     // named barrier of the two warps that share this lane quarter
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    auto ex2 = [](float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; };
     float m_run = -INFINITY, l_run = 0.f;
-    float o[D];
+    float o[HC];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < HC; ++i) o[i] = 0.f;
+    // A thread that gives up (a bounded wait ran out) must not leave its partner alone at the pair barrier: it keeps
+    // walking to the next exchange, publishes NaN there, and both leave together right after that barrier.
     bool ok = true;
-    for (int j = 0; j < nblk && ok; ++j) {
+    for (int j = 0; j < nblk; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&bars->s_full[st], ph, abort_flag)) { fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL); ok = false; break; }
+      if (ok && !mbar_wait(&bars->s_full[st], ph, abort_flag)) { fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL); ok = false; }
       tc_fence_after();
-      const uint32_t s_addr = lane_base + st * BK;
+      const uint32_t s_addr = lane_base + st * BK + half * HC;
       const bool diag = j == nblk - 1;
-      // pass 1: row maximum
+      uint32_t r[2][32];
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BK / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
+      if (ok) {
+        tmem_ld_32x32(s_addr, r[0]);
+        tmem_ld_32x32(s_addr + 32, r[1]);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]);
-          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, s);
-        }
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!diag || half * HC + c * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[c][i]));
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float alpha = exp2f(m_run - m_new);
-      // pass 2: P = 2^(s' - m), row sum, bf16 into the swizzled K-major A-operand layout
+      bars->xchg[st][half][row] = ok ? mx : NAN;
+      pair_sync();
+      const float other = bars->xchg[st][half ^ 1][row];
+      if (!ok || other != other) { ok = false; break; }
+      const float m_new = fmaxf(m_run, fmaxf(mx, other) * p.scale_log2);
+      const float alpha = ex2(m_run - m_new);
+      // P = 2^(s' - m), row sum, bf16 into the swizzled K-major A-operand layout (this thread's 64 keys = one box)
       float sum = 0.f;
-      const uint32_t prow = smem_u32(sP + st * TILE) + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < BK / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      const uint32_t prow = smem_u32(sP + st * TILE) + row * 128 + half * 16384;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_new);
-          float p1 = exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_new);
+          float p0 = ex2(fmaf(__uint_as_float(r[c][2 * i]), p.scale_log2, -m_new));
+          float p1 = ex2(fmaf(__uint_as_float(r[c][2 * i + 1]), p.scale_log2, -m_new));
           if (diag) {
-            if (c * 32 + 2 * i > row) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+            if (half * HC + c * 32 + 2 * i > row) p0 = 0.f;
+            if (half * HC + c * 32 + 2 * i + 1 > row) p1 = 0.f;
           }
           sum += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        const uint32_t box = prow + (c >> 1) * 16384;  // keys 0..63 | 64..127
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const uint32_t chunk = (uint32_t)((c & 1) * 4 + i) ^ (uint32_t)(row & 7);  // 128B swizzle
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box + chunk * 16), "r"(pk[4 * i]),
+          const uint32_t chunk = (uint32_t)(c * 4 + i) ^ (uint32_t)(row & 7);  // 128B swizzle
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16), "r"(pk[4 * i]),
                        "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
                        : "memory");
         }
@@ -237,33 +252,51 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       if (lane == 0) { mbar_arrive(&bars->s_empty[st]); mbar_arrive(&bars->p_ready[st]); }
       if (j >= 1) {
         const int ps = (j - 1) & 1;
-        if (!mbar_wait(&bars->o_full[ps], ((j - 1) >> 1) & 1, abort_flag)) { fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL); ok = false; break; }
+        if (!mbar_wait(&bars->o_full[ps], ((j - 1) >> 1) & 1, abort_flag)) {
+          fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL);
+          ok = false;
+          continue;  // to the next exchange (or the final one), where the pair leaves together
+        }
         tc_fence_after();
-        const uint32_t o_addr = lane_base + 2 * BK + ps * D;
+        const uint32_t o_addr = lane_base + 2 * BK + ps * D + half * HC;
+        const bool rescale = alpha != 1.f;  // the running maximum moved
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(o_addr + c * 32, r);
+        for (int c = 0; c < HC / 32; ++c) {
+          uint32_t pv[32];
+          tmem_ld_32x32(o_addr + c * 32, pv);
           tmem_ld_wait();
+          if (rescale) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * alpha;
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(pv[i])) * alpha;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(pv[i]);
+          }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->o_empty[ps]);
       }
     }
-    if (ok) {
+    {
+      // final exchange: partial row sums (NaN = this half gave up)
+      const int xs = nblk & 1;
       const int ps = (nblk - 1) & 1;
-      if (!mbar_wait(&bars->o_full[ps], ((nblk - 1) >> 1) & 1, abort_flag)) {
+      if (ok && !mbar_wait(&bars->o_full[ps], ((nblk - 1) >> 1) & 1, abort_flag)) {
         fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL);
-      } else {
+        ok = false;
+      }
+      bars->xchg[xs][half][row] = ok ? l_run : NAN;
+      pair_sync();
+      const float l_other = bars->xchg[xs][half ^ 1][row];
+      if (ok && l_other == l_other) {
         tc_fence_after();
-        const uint32_t o_addr = lane_base + 2 * BK + ps * D;
-        const float inv = 1.f / l_run;
-        __nv_bfloat16* dst = p.O + ((size_t)(q_row0 + row) * p.H + h) * D;
+        const float l_tot = l_run + l_other;
+        const uint32_t o_addr = lane_base + 2 * BK + ps * D + half * HC;
+        const float inv = 1.f / l_tot;
+        __nv_bfloat16* dst = p.O + ((size_t)(q_row0 + row) * p.H + h) * D + half * HC;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < HC / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(o_addr + c * 32, r);
           tmem_ld_wait();
@@ -280,8 +313,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
             *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = v;
           }
         }
-        if (p.LSE != nullptr)
-          p.LSE[((size_t)b * p.H + h) * p.S + qb * BQ + row] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+        if (p.LSE != nullptr && half == 0)
+          p.LSE[((size_t)b * p.H + h) * p.S + qb * BQ + row] = (m_run + log2f(l_tot)) * 0.6931471805599453f;
         tc_fence_before();
       }
     }
@@ -309,7 +342,7 @@ TB_API int tb_flash_attn_fwd(const void* q, const void* k, const void* v, void* 
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.O = (__nv_bfloat16*)out; p.LSE = lse; p.status = status;
-  const size_t smem = 7 * TILE + sizeof(Bars) + 1024;
+  const size_t smem = 7 * TILE + sizeof(Bars);
   TB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(S / BQ, H, B);
   flash_fwd_kernel<<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);

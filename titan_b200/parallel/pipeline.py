@@ -148,6 +148,8 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, trainer_config, device, mod
     has_first = any(s.is_first for s in stages)
     has_last = any(s.is_last for s in stages)
     _force_reshard_per_microbatch(parts)
+    for stage in stages:
+        _sync_every_microbatch(stage)
     return schedule, parts, has_first, has_last
 
 
@@ -161,3 +163,34 @@ def _force_reshard_per_microbatch(parts: list[nn.Module]) -> None:
                 m.set_reshard_after_backward(True)
                 m.set_requires_gradient_sync(True)
                 m.set_is_last_backward(True)
+
+
+def _sync_every_microbatch(stage: PipelineStage) -> None:
+    """Replace the stage's `backward_maybe_with_nosync`: the stock version switches FSDP's reshard / gradient sync OFF
+    for every microbatch and reduces once at the end of the step, which keeps a stage's unsharded parameters and
+    full-size gradients alive across all microbatches.  Here every microbatch backward reduce-scatters into the
+    sharded gradient and reshards the parameters (parity: torchtitan_npu/patches/torch/pipelining.py:100-162,
+    "always reshard + sync")."""
+    from torch.distributed.fsdp import FSDPModule
+    from torch.distributed.pipelining._backward import stage_backward, stage_backward_input, stage_backward_weight
+
+    stock = stage.backward_maybe_with_nosync
+
+    def backward(backward_type, bwd_kwargs: dict, last_backward: bool = False):
+        sub = stage.submod
+        if not isinstance(sub, FSDPModule):
+            return stock(backward_type, bwd_kwargs, last_backward=last_backward)
+        sub.set_is_last_backward(True)
+        sub.set_reshard_after_backward(True)
+        sub.set_requires_gradient_sync(True)
+        if backward_type == "full":
+            return stage_backward(bwd_kwargs["stage_output"], bwd_kwargs["output_grads"],
+                                  bwd_kwargs["input_values"]), None
+        if backward_type == "input":
+            return stage_backward_input(bwd_kwargs["stage_output"], bwd_kwargs["output_grads"],
+                                        bwd_kwargs["input_values"], sub.parameters())
+        if backward_type == "weight":
+            return stage_backward_weight(sub.parameters(), bwd_kwargs["param_groups"]), None
+        raise RuntimeError(f"unknown backward type {backward_type!r}")
+
+    stage.backward_maybe_with_nosync = backward
