@@ -14,7 +14,10 @@ int launch(const AMaps& am, const CUtensorMap& tb_, const CMaps& cm, const GemmP
 // chunk to the GEMM CTAs through a local flag.  Chunks are visited in ring order starting at the next rank.
 // One thread drives bulk asynchronous copies (peer global -> shared -> local global) through a ring of
 // COPY_BUFS shared buffers, so a CTA keeps ~190 KB in flight on the link without spending registers or
-// issue slots; no multicast is involved.
+// issue slots; no multicast is involved.  A copier owns whole chunks.  Dealing the 32 KB pieces of one chunk to all
+// copiers (so that chunks complete one by one) was measured on 2 GPUs and gained nothing (fsdp weight gather
+// 8192x28672x4096: 1.80 ms either way), and a completion counter per PIECE (an atomic round trip per 32 KB) cost
+// a third of the copy rate (2.40 ms).
 constexpr int COPY_PIECE = 32 * 1024;
 constexpr int COPY_BUFS = 6;
 
@@ -45,40 +48,23 @@ __device__ __forceinline__ void copier_role(const GemmParams& p, uint8_t* bufs, 
   const long long row_bytes = (long long)(gk ? p.k_shard : p.K) * 2;
   const long long chunk_bytes = (long long)chunk_rows * row_bytes;
   const int pieces = (int)((chunk_bytes + COPY_PIECE - 1) / COPY_PIECE);
-  // ALL copiers work on the same chunk at the same time (pieces are dealt round-robin), so chunks complete one after
-  // the other at the full rate of the link instead of all together at the end; a per-chunk counter finds the copier
-  // that delivered the last piece, and that one hands the chunk to the GEMM CTAs.
-  const long long all_pieces = (long long)remote_chunks * pieces;
-  long long total = 0;
-  for (long long g = blockIdx.x; g < all_pieces; g += p.num_copiers) ++total;
-  unsigned int* counters = p.chunk_flags + (long long)p.nranks * per;  // second half of the flag buffer
+  int my_chunks = 0;
+  for (int idx = blockIdx.x; idx < remote_chunks; idx += p.num_copiers) ++my_chunks;
+  const long long total = (long long)my_chunks * pieces;
   unsigned int seen = 1u << p.rank;
   const int D = COPY_BUFS - 1;  // loads run this many pieces ahead of the stores
-  auto locate = [&](long long i, int& src, int& within, int& pi, long long& src_off) {
-    const long long g = blockIdx.x + i * p.num_copiers;
-    const int idx = (int)(g / pieces);
-    pi = (int)(g - (long long)idx * pieces);
+  auto locate = [&](int idx, int& src, int& within, long long& src_off) {
     int d;
     if (gk) { within = idx / (p.nranks - 1); d = idx - within * (p.nranks - 1) + 1; }
     else { d = idx / per + 1; within = idx - (d - 1) * per; }
     src = (p.rank + d) % p.nranks;
     src_off = gk ? (long long)seq_row(p, within * BM, p.rank) * row_bytes : (long long)within * chunk_bytes;
   };
-  auto delivered = [&](long long i) {  // piece i of this copier is complete in local memory
-    int src, within, pi; long long src_off;
-    locate(i, src, within, pi, src_off);
-    __threadfence();
-    const int c = src * per + within;
-    if (atomicAdd(counters + c, 1u) + 1u == (unsigned int)pieces) {
-      counters[c] = 0;  // ready for the next launch
-      __threadfence();
-      st_release_gpu(p.chunk_flags + c, p.epoch);
-    }
-  };
   for (long long i = 0; i < total + D; ++i) {
     if (i < total) {
-      int src, within, pi; long long src_off;
-      locate(i, src, within, pi, src_off);
+      const int ci = (int)(i / pieces), pi = (int)(i - (long long)ci * pieces);
+      int src, within; long long src_off;
+      locate(blockIdx.x + ci * p.num_copiers, src, within, src_off);
       if (!(seen & (1u << src))) {
         if (!wait_flag_ge(p.ready_flags + src, p.epoch, abort_flag)) {
           if (p.status) atomicExch(p.status, TB_ERR_WAIT_PEER);
@@ -96,8 +82,9 @@ __device__ __forceinline__ void copier_role(const GemmParams& p, uint8_t* bufs, 
     }
     const long long j = i - D;
     if (j >= 0 && j < total) {
-      int src, within, pi; long long src_off;
-      locate(j, src, within, pi, src_off);
+      const int ci = (int)(j / pieces), pi = (int)(j - (long long)ci * pieces);
+      int src, within; long long src_off;
+      locate(blockIdx.x + ci * p.num_copiers, src, within, src_off);
       const int b = (int)(j % COPY_BUFS);
       if (!wait_bounded(&bars[b], (uint32_t)((j / COPY_BUFS) & 1), abort_flag)) {
         if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA);
@@ -108,14 +95,14 @@ __device__ __forceinline__ void copier_role(const GemmParams& p, uint8_t* bufs, 
       uint8_t* to = reinterpret_cast<uint8_t*>(p.gather_dst) + ((long long)src * per + within) * chunk_bytes + off;
       bulk_store(to, bufs + b * COPY_PIECE, bytes);
       tma_store_commit();
-      if (j >= 2) {  // all but the two newest stores are complete: piece j-2 has landed
-        tma_store_wait_all<2>();
-        delivered(j - 2);
+      if (pi == pieces - 1) {  // chunk complete: make it visible, then hand it to the GEMM CTAs
+        tma_store_wait_all<0>();
+        __threadfence();
+        st_release_gpu(p.chunk_flags + src * per + within, p.epoch);
       }
     }
   }
   tma_store_wait_all<0>();
-  for (long long k = (total >= 2 ? total - 2 : 0); k < total; ++k) delivered(k);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
