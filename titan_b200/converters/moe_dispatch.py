@@ -51,7 +51,10 @@ class FusedMoE(MoE):
             self.tokens_per_expert.add_(counts.to(self.tokens_per_expert.dtype))
         base = self.shared_experts(x2) if self.shared_experts is not None else None
         ep_mesh = getattr(experts, "ep_mesh", None)
-        if ep_mesh is not None and ep_mesh.size() > 1 and x.is_cuda:
+        if ep_mesh is not None and ep_mesh.size() > 1:
+            if not x.is_cuda:
+                raise RuntimeError("the fused expert-parallel MoE exchanges tokens through GPU peer memory; on CPU run "
+                                   "expert parallelism without the b200_moe_dispatch / b200_gmm converters")
             from titan_b200.ops import moe_comm
 
             out = moe_comm.moe_forward_ep(x2, gate, idx, experts, ep_mesh.get_group(), base=base,
