@@ -272,3 +272,37 @@ def test_v4_model_bf16_step_on_gpu_with_fused_paths():
     loss.backward()
     assert torch.isfinite(loss)
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+def test_sparse_attention_dense_mask_and_gather_paths_agree():
+    """The selected compressed keys are attended either through one masked GEMM (short streams) or through a row gather
+    whose backward is a scatter-add (long streams): same output, same gradients."""
+    from titan_b200.ops import smla
+
+    torch.manual_seed(3)
+    B, S, H, hd, ratio, k = 1, 64, 2, 16, 4, 6
+    Tc = S // ratio
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64)
+    q, kv, kvc, sink = mk(B, S, H, hd), mk(B, S, hd), mk(B, Tc, hd), mk(H)
+    # per query: k distinct visible compressed keys (or -1 where fewer are visible)
+    idx = torch.full((B, S, k), -1, dtype=torch.long)
+    for s in range(S):
+        vis = (s + 1) // ratio
+        pick = torch.randperm(vis)[:k] if vis else torch.empty(0, dtype=torch.long)
+        idx[0, s, : pick.numel()] = pick + S
+    results = []
+    for dense_ratio in (4, 0):
+        smla.DENSE_RATIO = dense_ratio
+        try:
+            leaves = [t.clone().requires_grad_(True) for t in (q, kv, kvc)]
+            out, dist = smla.smla_attention(leaves[0], leaves[1], sink, leaves[2], idx, 8, ratio, hd ** -0.5,
+                                            want_dist=True, chunk=16)
+            out.square().sum().backward()
+            results.append((out.detach(), dist, [t.grad for t in leaves]))
+        finally:
+            smla.DENSE_RATIO = 4
+    (o1, d1, g1), (o2, d2, g2) = results
+    torch.testing.assert_close(o1, o2)
+    torch.testing.assert_close(d1, d2)
+    for a, b in zip(g1, g2):  # the gather path accumulates its scatter-add in fp32
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)

@@ -28,6 +28,32 @@ from torch.utils.checkpoint import checkpoint
 __all__ = ["smla_attention", "li_select"]
 
 
+DENSE_RATIO = 4  # a compressed stream at most this many times longer than k is attended densely with a mask
+
+
+class _GatherRows(torch.autograd.Function):
+    """``src[idx]`` for ``src [T, D]`` and integer ``idx [...]``; the backward is ONE scatter-add with fp32 atomics
+    (the stock advanced-indexing backward sorts the indices first: 68 % of a DeepSeek-V4 step when it was used here)."""
+
+    @staticmethod
+    def forward(ctx, src, idx):
+        ctx.save_for_backward(idx)
+        ctx.rows, ctx.dtype = src.shape[0], src.dtype
+        return src[idx]
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        d = g.shape[-1]
+        acc = torch.zeros(ctx.rows, d, dtype=torch.float32, device=g.device)
+        acc.index_add_(0, idx.reshape(-1), g.reshape(-1, d).float())
+        return acc.to(ctx.dtype), None
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    return _GatherRows.apply(src, idx)
+
+
 def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, ratio: int, scale: float,
            n_heads_total: int, want_dist: bool):
     """q [Sc,H,hd] (local queries s0..s0+Sc), kv [Tk,hd] raw keys where local query s sits at key index s + koff,
@@ -45,9 +71,19 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, 
     logit_w = logit_w.masked_fill(((tpos > kpos) | (tpos <= kpos - window)).unsqueeze(0), float("-inf"))
     parts = [logit_w]
     ksel = None
+    dense_sel = False
     if kvc is not None and ratio > 1:
-        if cidx is not None:
-            ksel = kvc[cidx.clamp(min=0).long()]  # [Sc, k, hd]
+        if cidx is not None and kvc.shape[0] <= DENSE_RATIO * cidx.shape[1]:
+            # short compressed stream: all keys through one GEMM, the selection as a mask (no gather, no scatter-add)
+            dense_sel = True
+            c_end = kvc.shape[0]
+            kc = kvc
+            logit_c = torch.matmul(qh, kc.t()).float() * scale  # [H, Sc, Tc]
+            slot = torch.where(cidx < 0, c_end, cidx).long()     # empty slots point at a scratch column
+            allowed = torch.zeros(Sc, c_end + 1, dtype=torch.bool, device=q.device).scatter_(1, slot, True)[:, :c_end]
+            logit_c = logit_c.masked_fill(~allowed.unsqueeze(0), float("-inf"))
+        elif cidx is not None:
+            ksel = gather_rows(kvc, cidx.clamp(min=0).long())  # [Sc, k, hd]
             logit_c = torch.einsum("hsd,skd->hsk", qh, ksel).float() * scale
             logit_c = logit_c.masked_fill((cidx < 0).unsqueeze(0), float("-inf"))
         else:
@@ -68,6 +104,11 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, 
             out = out + torch.einsum("hsk,skd->hsd", pc.to(kv.dtype), ksel)
             if want_dist:
                 dist = pc.detach().sum(0) / n_heads_total
+        elif dense_sel:
+            out = out + torch.matmul(pc.to(kv.dtype), kvc)
+            if want_dist:  # head-mean probability at the selected keys, in the order of `cidx`
+                mass = pc.detach().sum(0) / n_heads_total  # [Sc, Tc]
+                dist = torch.gather(mass, 1, cidx.clamp(min=0).long())
         else:
             out = out + torch.matmul(pc.to(kv.dtype), kvc[: pc.shape[-1]])
     out = out.transpose(0, 1)
@@ -75,8 +116,8 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, 
 
 
 def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: int, scale: float,
-                   want_dist: bool = False, *, n_heads_total: int | None = None, chunk: int = 256, q_pos0: int = 0,
-                   kv_pos0: int = 0, idx_offset: int | None = None):
+                   want_dist: bool = False, *, n_heads_total: int | None = None, chunk: int | None = None,
+                   q_pos0: int = 0, kv_pos0: int = 0, idx_offset: int | None = None):
     """q [B,S,H,hd], kv [B,Tk,hd], sink [H], kv_compress [B,Tc,hd] | None, compress_idx [B,S,k] | None (compressed ids
     + ``idx_offset``, default ``Tk`` as in the dense layout; -1 = empty) → (out [B,S,H,hd], dist [B,S,k] | None).
 
@@ -85,6 +126,13 @@ def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: i
     compressed keys are global."""
     B, S, H, _ = q.shape
     n_heads_total = n_heads_total or H
+    if chunk is None:
+        # queries per chunk: as many as keep the fp32 logits of a chunk ([H, chunk, chunk + window + Tc]) near
+        # 512 MB; few large chunks matter because this path is launch-bound on short sequences
+        width = window + (kv_compress.shape[1] if kv_compress is not None else 0)
+        chunk = 256
+        while chunk < S and 4 * H * (2 * chunk) * (2 * chunk + width) <= (512 << 20):
+            chunk *= 2
     koff = q_pos0 - kv_pos0
     if kv.shape[1] != S + koff:
         raise ValueError(f"raw keys must cover the local queries and their window: {kv.shape[1]} != {S} + {koff}")
@@ -127,8 +175,16 @@ def li_select(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset
                                     pos_offset, ratio)
     idx = idx.long()
     safe = idx.clamp(min=0)
-    ksel = k_indexer[torch.arange(B, device=idx.device).view(B, 1, 1), safe]  # [B,S,k,D]
-    s = torch.einsum("bshd,bskd->bshk", q_indexer, ksel)
-    s = (F.relu(s) * weights.unsqueeze(-1)).sum(2)
+    T = k_indexer.shape[1]
+    if T <= DENSE_RATIO * k:
+        # short key stream: score all keys with one GEMM per batch row and pick the selected ones (the gradient of a
+        # gather along the key axis is a cheap scatter; no [B,S,k,D] tensor is built)
+        dense = torch.einsum("bshd,btd->bsht", q_indexer, k_indexer)
+        dense = (F.relu(dense) * weights.unsqueeze(-1)).sum(2)  # [B,S,T]
+        s = torch.gather(dense, 2, safe)
+    else:
+        ksel = torch.stack([gather_rows(k_indexer[b], safe[b]) for b in range(B)])  # [B,S,k,D]
+        s = torch.einsum("bshd,bskd->bshk", q_indexer, ksel)
+        s = (F.relu(s) * weights.unsqueeze(-1)).sum(2)
     s = s.masked_fill(idx < 0, torch.finfo(q_indexer.dtype).min)
     return torch.where(idx < 0, idx, idx + offset), s
