@@ -81,3 +81,35 @@ def test_indexer_kernels_match_reference(cuda_device, S, H, T, k, off):
         a, b = set(idx[0, s].tolist()) - {-1}, set(idx_r[0, s].tolist()) - {-1}
         overlap.append(len(a & b) / max(len(b), 1))
     assert min(overlap) > 0.9  # bf16 rounding may swap a few keys at the threshold
+
+
+def test_sparse_mla_dense_mask_and_gather_paths_agree():
+    """Selected keys through one masked GEMM (short key streams) or through a row gather with a scatter-add backward
+    (long ones): same outputs, same gradients; the same for the differentiable index scores."""
+    from titan_b200.ops import dsa
+
+    torch.manual_seed(5)
+    B, H, S, Dq, Dv, k = 1, 2, 24, 8, 6, 5
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64)
+    q, kk, v = mk(B, H, S, Dq), mk(B, 1, S, Dq), mk(B, 1, S, Dv)
+    qi, ki, w = mk(B, S, 3, 4), mk(B, S, 1, 4), torch.rand(B, S, 3, dtype=torch.float64)
+    idx = torch.full((B, S, k), -1, dtype=torch.long)
+    for s in range(S):
+        pick = torch.randperm(s + 1)[:k]
+        idx[0, s, : pick.numel()] = pick
+    results = []
+    for ratio in (4, 0):
+        dsa.DENSE_RATIO = ratio
+        try:
+            leaves = [t.clone().requires_grad_(True) for t in (q, kk, v, qi, ki, w)]
+            out, teacher, lse = dsa.sparse_mla_attention(leaves[0], leaves[1], leaves[2], idx, Dq ** -0.5, chunk=8)
+            sc = dsa.indexer_scores_selected(leaves[3], leaves[5], leaves[4], idx, chunk=8)
+            (out.square().sum() + sc.masked_fill(idx < 0, 0.0).sum()).backward()
+            results.append((out.detach(), teacher, lse.detach(), sc.detach(), [t.grad for t in leaves]))
+        finally:
+            dsa.DENSE_RATIO = 4
+    a, b = results
+    for x, y in zip(a[:4], b[:4]):
+        torch.testing.assert_close(x, y)
+    for x, y in zip(a[4], b[4]):  # the gather path accumulates its scatter-add in fp32
+        torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-5)

@@ -189,6 +189,9 @@ class ParallelismConfig:
     expert_tensor_parallel_degree: int = 1
     expert_parallel_comm_backend: Literal["standard", "fused_p2p", "deepep", "hybridep", "torchao"] = "standard"
     """`fused_p2p` = in-kernel peer-memory dispatch/combine; `standard` = NCCL all-to-all."""
+    expert_parallel_capacity_factor: float = 4.0
+    """`fused_p2p` only: rows an owner rank's receive buffer holds, in multiples of the balanced load; the number of
+    EP ranks makes it dropless.  A routing beyond it stops the step with a kernel status (nothing is dropped)."""
     fsdp_fused_collectives: bool = False
     """Fuse FSDP all-gather into the consuming GEMM and cast/scale into reduce-scatter."""
     dedicated_ep_group: bool = True

@@ -85,20 +85,80 @@ def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0
     return idx, vals
 
 
-def indexer_scores_selected(q_idx, weights, k_idx, idx):
-    """Differentiable index scores at the selected keys: [B,S,k]; padded slots (-1) → -inf."""
+DENSE_RATIO = 4  # a key stream at most this many times longer than top-k is scored densely with a selection mask
+
+
+class _GatherRows(torch.autograd.Function):
+    """``src[idx]`` for ``src [T, D]`` and integer ``idx [...]``; the backward is ONE scatter-add with fp32 atomics
+    (the stock advanced-indexing backward sorts the indices first: 68 % of a DeepSeek-V4 step when it was used here)."""
+
+    @staticmethod
+    def forward(ctx, src, idx):
+        ctx.save_for_backward(idx)
+        ctx.rows, ctx.dtype = src.shape[0], src.dtype
+        return src[idx]
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        d = g.shape[-1]
+        acc = torch.zeros(ctx.rows, d, dtype=torch.float32, device=g.device)
+        acc.index_add_(0, idx.reshape(-1), g.reshape(-1, d).float())
+        return acc.to(ctx.dtype), None
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    return _GatherRows.apply(src, idx)
+
+
+def _dense_index_scores(q, w, k, safe):
+    """q [Sc,H,D], w [Sc,H], k [T,D], safe [Sc,kk] → scores of the selected keys [Sc,kk] through one GEMM."""
+    s = torch.einsum("shd,td->sht", q.float(), k.float())
+    s = (F.relu(s) * w.float().unsqueeze(-1)).sum(1)  # [Sc,T]
+    return torch.gather(s, 1, safe)
+
+
+def indexer_scores_selected(q_idx, weights, k_idx, idx, chunk: int = 512):
+    """Differentiable index scores at the selected keys: [B,S,k]; padded slots (-1) → -inf.  A short key stream is
+    scored densely in query chunks (one GEMM, then a gather along the key axis); a long one gathers the selected key
+    rows (scatter-add backward)."""
     B, S, H, D = q_idx.shape
+    T, kk = k_idx.shape[1], idx.shape[-1]
     safe = idx.clamp_min(0).long()
-    ksel = k_idx[:, :, 0][torch.arange(B, device=idx.device).view(B, 1, 1), safe]  # [B,S,k,D]
-    s = torch.einsum("bshd,bskd->bshk", q_idx.float(), ksel.float())
-    s = (F.relu(s) * weights.float().unsqueeze(-1)).sum(2)
+    if T <= DENSE_RATIO * kk:
+        need_grad = torch.is_grad_enabled() and (q_idx.requires_grad or k_idx.requires_grad or weights.requires_grad)
+        rows = []
+        for b in range(B):
+            parts = []
+            for s0 in range(0, S, chunk):
+                args = (q_idx[b, s0:s0 + chunk], weights[b, s0:s0 + chunk], k_idx[b, :, 0], safe[b, s0:s0 + chunk])
+                parts.append(checkpoint(_dense_index_scores, *args, use_reentrant=False) if need_grad
+                             else _dense_index_scores(*args))
+            rows.append(torch.cat(parts, dim=0))
+        s = torch.stack(rows)
+    else:
+        ksel = torch.stack([gather_rows(k_idx[b, :, 0], safe[b]) for b in range(B)])  # [B,S,k,D]
+        s = torch.einsum("bshd,bskd->bshk", q_idx.float(), ksel.float())
+        s = (F.relu(s) * weights.float().unsqueeze(-1)).sum(2)
     return s.masked_fill(idx < 0, float("-inf"))
 
 
 def _sparse_chunk(q, kv, v, idx, scale):
     """q [H,Sc,Dq], kv [T,Dq], v [T,Dv], idx [Sc,k] → (out [H,Sc,Dv], teacher [Sc,k], lse [H,Sc])."""
     safe = idx.clamp_min(0).long()
-    ksel, vsel = kv[safe], v[safe]  # [Sc,k,D]
+    T = kv.shape[0]
+    if T <= DENSE_RATIO * idx.shape[1]:
+        # short key stream: every key through one GEMM, the selection as a mask (no gather, no scatter-add)
+        s = torch.matmul(q.float(), kv.float().t()) * scale  # [H,Sc,T]
+        slot = torch.where(idx < 0, T, idx).long()
+        allowed = torch.zeros(idx.shape[0], T + 1, dtype=torch.bool, device=q.device).scatter_(1, slot, True)[:, :T]
+        s = s.masked_fill(~allowed.unsqueeze(0), float("-inf"))
+        lse = torch.logsumexp(s, dim=-1)
+        p = torch.nan_to_num(torch.exp(s - lse.unsqueeze(-1)))  # a row without any visible key
+        out = torch.matmul(p, v.float()).to(q.dtype)
+        teacher = torch.gather(p.detach().sum(0), 1, safe).masked_fill(idx < 0, 0.0)
+        return out, teacher, lse
+    ksel, vsel = gather_rows(kv, safe), gather_rows(v, safe)  # [Sc,k,D]
     s = torch.einsum("hsd,skd->hsk", q.float(), ksel.float()) * scale
     s = s.masked_fill((idx < 0).unsqueeze(0), float("-inf"))
     lse = torch.logsumexp(s, dim=-1)

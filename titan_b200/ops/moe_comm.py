@@ -33,10 +33,20 @@ from titan_b200.parallel.symm_mem import get_workspace
 __all__ = ["moe_forward_ep", "EPContext", "capacity_per_owner"]
 
 CH_COUNTS, CH_DISPATCH, CH_OUT, CH_DONE, CH_BWD_A, CH_BWD_B, CH_BWD_DONE = range(16, 23)
-CAPACITY_FACTOR = 2.0
+CAPACITY_FACTOR = 4.0  # rows an owner rank can take, over the balanced load (`world` = every pair: dropless)
 
 
-def capacity_per_owner(pairs: int, e_local: int, world: int, factor: float = CAPACITY_FACTOR) -> int:
+def set_capacity_factor(factor: float) -> None:
+    """Row capacity of an owner rank's receive buffer in multiples of the balanced load (T·k rows).  A routing that
+    sends more rows to one owner stops the step with a kernel status (nothing is dropped silently)."""
+    global CAPACITY_FACTOR
+    if factor < 1.0:
+        raise ValueError("expert_parallel_capacity_factor must be at least 1")
+    CAPACITY_FACTOR = float(factor)
+
+
+def capacity_per_owner(pairs: int, e_local: int, world: int, factor: float | None = None) -> int:
+    factor = CAPACITY_FACTOR if factor is None else factor
     worst = pairs * world
     cap = min(int(pairs * factor), worst) + (ALIGN - 1) * e_local
     return (cap + ALIGN - 1) // ALIGN * ALIGN

@@ -28,30 +28,9 @@ from torch.utils.checkpoint import checkpoint
 __all__ = ["smla_attention", "li_select"]
 
 
+from titan_b200.ops.dsa import gather_rows
+
 DENSE_RATIO = 4  # a compressed stream at most this many times longer than k is attended densely with a mask
-
-
-class _GatherRows(torch.autograd.Function):
-    """``src[idx]`` for ``src [T, D]`` and integer ``idx [...]``; the backward is ONE scatter-add with fp32 atomics
-    (the stock advanced-indexing backward sorts the indices first: 68 % of a DeepSeek-V4 step when it was used here)."""
-
-    @staticmethod
-    def forward(ctx, src, idx):
-        ctx.save_for_backward(idx)
-        ctx.rows, ctx.dtype = src.shape[0], src.dtype
-        return src[idx]
-
-    @staticmethod
-    def backward(ctx, g):
-        (idx,) = ctx.saved_tensors
-        d = g.shape[-1]
-        acc = torch.zeros(ctx.rows, d, dtype=torch.float32, device=g.device)
-        acc.index_add_(0, idx.reshape(-1), g.reshape(-1, d).float())
-        return acc.to(ctx.dtype), None
-
-
-def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
-    return _GatherRows.apply(src, idx)
 
 
 def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, ratio: int, scale: float,

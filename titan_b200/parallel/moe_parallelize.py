@@ -42,6 +42,13 @@ def apply_moe_ep_tp(model: nn.Module, *, tp_mesh=None, ep_mesh=None, etp_mesh=No
     """``extra_moe_inputs``: positional inputs after the tokens that pass through untouched (DeepSeek-V4 hands the
     token ids to the MoE block for hash routing)."""
     none = (None,) * extra_moe_inputs
+    if ep_mesh is not None and comm_backend == "fused_p2p":
+        from titan_b200.ops import moe_comm
+        from titan_b200.trainer import stash
+
+        cfg = stash.get_trainer_config()
+        if cfg is not None:
+            moe_comm.set_capacity_factor(cfg.parallelism.expert_parallel_capacity_factor)
     for block in getattr(model, layers_attr).values():
         if block is None or not getattr(block, "moe_enabled", False):
             continue
