@@ -113,7 +113,7 @@ def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
 
 def _dense_index_scores(q, w, k, safe):
     """q [Sc,H,D], w [Sc,H], k [T,D], safe [Sc,kk] → scores of the selected keys [Sc,kk] through one GEMM."""
-    s = torch.einsum("shd,td->sht", q.float(), k.float())
+    s = torch.einsum("shd,td->sht", q, k).float()
     s = (F.relu(s) * w.float().unsqueeze(-1)).sum(1)  # [Sc,T]
     return torch.gather(s, 1, safe)
 
@@ -143,20 +143,27 @@ def indexer_scores_selected(q_idx, weights, k_idx, idx, chunk: int = 512):
     return s.masked_fill(idx < 0, float("-inf"))
 
 
-def _sparse_chunk(q, kv, v, idx, scale):
-    """q [H,Sc,Dq], kv [T,Dq], v [T,Dv], idx [Sc,k] → (out [H,Sc,Dv], teacher [Sc,k], lse [H,Sc])."""
+def _sparse_chunk(q, kv, v, idx, scale, want_lse=True):
+    """q [H,Sc,Dq], kv [T,Dq], v [T,Dv], idx [Sc,k] → (out [H,Sc,Dv], teacher [Sc,k], lse [H,Sc]); without
+    ``want_lse`` the dense path skips the extra pass over the logits and returns zeros there."""
     safe = idx.clamp_min(0).long()
     T = kv.shape[0]
     if T <= DENSE_RATIO * idx.shape[1]:
         # short key stream: every key through one GEMM, the selection as a mask (no gather, no scatter-add)
-        s = torch.matmul(q.float(), kv.float().t()) * scale  # [H,Sc,T]
+        # the GEMMs stay in the storage dtype (bf16 tensor cores; an fp32 copy of the operands would run them as TF32
+        # at half the rate and move twice the bytes); softmax statistics are fp32.  The [H,Sc,T] logits are touched by
+        # as few elementwise passes as possible: scale folded into q, mask in place, one fused softmax.
         slot = torch.where(idx < 0, T, idx).long()
         allowed = torch.zeros(idx.shape[0], T + 1, dtype=torch.bool, device=q.device).scatter_(1, slot, True)[:, :T]
-        s = s.masked_fill(~allowed.unsqueeze(0), float("-inf"))
-        lse = torch.logsumexp(s, dim=-1)
-        p = torch.nan_to_num(torch.exp(s - lse.unsqueeze(-1)))  # a row without any visible key
-        out = torch.matmul(p, v.float()).to(q.dtype)
-        teacher = torch.gather(p.detach().sum(0), 1, safe).masked_fill(idx < 0, 0.0)
+        empty = ~allowed.any(dim=1)  # a row without any visible key: give it key 0, zero its output afterwards
+        allowed = allowed | (empty.unsqueeze(1) & (torch.arange(T, device=q.device) == 0).unsqueeze(0))
+        s = torch.matmul(q * scale, kv.t()).float().masked_fill_(~allowed.unsqueeze(0), float("-inf"))  # [H,Sc,T]
+        p = torch.softmax(s, dim=-1)
+        with torch.no_grad():
+            lse = torch.logsumexp(s, dim=-1) if want_lse else s.new_zeros(s.shape[:2])
+        keep = (~empty).to(q.dtype).view(1, -1, 1)
+        out = torch.matmul(p.to(v.dtype), v).to(q.dtype) * keep
+        teacher = torch.gather(p.detach().sum(0), 1, safe).masked_fill((idx < 0) | empty.unsqueeze(1), 0.0)
         return out, teacher, lse
     ksel, vsel = gather_rows(kv, safe), gather_rows(v, safe)  # [Sc,k,D]
     s = torch.einsum("hsd,skd->hsk", q.float(), ksel.float()) * scale
@@ -168,7 +175,7 @@ def _sparse_chunk(q, kv, v, idx, scale):
     return out, p.detach().sum(0), lse
 
 
-def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256):
+def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256, want_lse: bool = True):
     """q [B,H,S,Dq], k [B,1,T,Dq], v [B,1,T,Dv], idx [B,S,topk] → (out [B,H,S,Dv], teacher [B,S,topk], lse [B,H,S])."""
     B, H, S, _ = q.shape
     outs, teach, lses = [], [], []
@@ -176,7 +183,7 @@ def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256):
         ob, tb, lb = [], [], []
         for s0 in range(0, S, chunk):
             s1 = min(s0 + chunk, S)
-            args = (q[b, :, s0:s1], k[b, 0], v[b, 0], idx[b, s0:s1], scale)
+            args = (q[b, :, s0:s1], k[b, 0], v[b, 0], idx[b, s0:s1], scale, want_lse)
             if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad):
                 o, t, l = checkpoint(_sparse_chunk, *args, use_reentrant=False)  # gathered rows are not kept
             else:
@@ -192,7 +199,7 @@ def dsa_attention(q, k, v, *, scale, q_indexer, k_indexer, weights, index_topk: 
     pos_offset = T - S  # with context parallelism the local queries are the tail of the gathered key range
     topk = min(index_topk, T)
     idx, _ = lightning_indexer_topk(q_indexer, weights, k_indexer, topk, pos_offset)
-    out, teacher, _ = sparse_mla_attention(q, k, v, idx, scale)
+    out, teacher, _ = sparse_mla_attention(q, k, v, idx, scale, want_lse=False)
     student = indexer_scores_selected(q_indexer, weights, k_indexer, idx)
     student = torch.where(idx < 0, torch.full_like(student, -1e30), student)  # finite: masked slots get zero mass
     loss = dsa_indexer_loss(teacher.masked_fill(idx < 0, 0.0), student, loss_scale)
