@@ -113,3 +113,51 @@ def test_sparse_mla_dense_mask_and_gather_paths_agree():
         torch.testing.assert_close(x, y)
     for x, y in zip(a[4], b[4]):  # the gather path accumulates its scatter-add in fp32
         torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,T", [(torch.bfloat16, 64), (torch.bfloat16, 8192), (torch.bfloat16, 16384),
+                                     (torch.float32, 1024), (torch.float32, 8192)])
+def test_masked_softmax_kernel_matches_reference(cuda_device, dtype, T):
+    from titan_b200.ops.masked_softmax import masked_softmax, masked_softmax_ref
+
+    torch.manual_seed(0)
+    H, Sc = 3, 40
+    s = (torch.randn(H, Sc, T, device="cuda") * 4).to(dtype)
+    allowed = torch.rand(Sc, T, device="cuda") < 0.3
+    allowed[5] = False  # a query without any visible key
+    a, b = s.clone().requires_grad_(True), s.clone().requires_grad_(True)
+    p, ref = masked_softmax(a, allowed, 0.7), masked_softmax_ref(b, allowed, 0.7)
+    tol = dict(rtol=2e-2, atol=2e-3) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(p.float(), ref.float(), **tol)
+    assert p[:, 5].abs().sum() == 0
+    g = torch.randn_like(p)
+    p.backward(g)
+    ref.backward(g)
+    gtol = dict(rtol=5e-2, atol=5e-3) if dtype == torch.bfloat16 else dict(rtol=1e-3, atol=1e-5)
+    torch.testing.assert_close(a.grad.float(), b.grad.float(), **gtol)
+
+
+@pytest.mark.gpu
+def test_indexer_scores_from_selection_match_recomputed_scores(cuda_device):
+    """Forward values come from the scoring kernel, the backward from one fused kernel + GEMMs: both against the
+    PyTorch scores recomputed at the selected keys."""
+    from titan_b200.ops import dsa
+
+    torch.manual_seed(1)
+    B, S, H, D, T, k = 1, 300, 8, 32, 512, 64
+    q = (torch.randn(B, S, H, D, device="cuda") * 0.5).to(torch.bfloat16)
+    kk = (torch.randn(B, T, 1, D, device="cuda") * 0.5).to(torch.bfloat16)
+    w = torch.rand(B, S, H, device="cuda")
+    idx, vals = dsa.lightning_indexer_topk(q, w, kk, k, T - S)
+    a = [t.clone().requires_grad_(True) for t in (q, w, kk)]
+    b = [t.clone().requires_grad_(True) for t in (q, w, kk)]
+    got = dsa.indexer_scores_from_selection(a[0], a[1], a[2], idx, vals, chunk=128)
+    ref = dsa.indexer_scores_selected(b[0], b[1], b[2], idx)
+    m = idx >= 0
+    torch.testing.assert_close(got[m], ref[m], rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(ref).masked_fill(~m, 0.0)
+    got.masked_fill(~m, 0.0).mul(g).sum().backward()
+    ref.masked_fill(~m, 0.0).mul(g).sum().backward()
+    for x, y, name in zip(a, b, ("dq", "dw", "dk")):
+        torch.testing.assert_close(x.grad.float(), y.grad.float(), rtol=5e-2, atol=5e-2, msg=lambda s, n=name: f"{n}: {s}")

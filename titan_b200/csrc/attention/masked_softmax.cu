@@ -1,0 +1,177 @@
+// Row softmax under a selection mask, forward and backward, for the dense form of sparse attention (every key of a
+// short key stream goes through one GEMM and the top-k selection becomes a mask).  PyTorch needs about ten elementwise
+// passes over the fp32 [heads, queries, keys] logits for this (cast, masked_fill with a broadcast mask, softmax, casts
+// back, and their backward); here the logits are read once and the probabilities written once, in the storage dtype.
+//
+//   P[r, t] = allowed[r % mask_rows, t] ? exp(scale * S[r, t] - m_r) / l_r : 0          (fp32 statistics)
+//   dS[r, t] = scale * P[r, t] * (dP[r, t] - Σ_t' P[r, t'] dP[r, t'])
+//
+// One CTA of 256 threads per row, the row held in registers (up to 64 values per thread: T <= 16384), 16-byte
+// accesses; a row without any allowed key yields zeros.  Rows are [heads * queries]; the mask has one row per query
+// and is shared by the heads (row r uses mask row r % mask_rows).
+//
+// Stands where the reference's sparse attention kernels (`npu_sparse_flash_attention`, K9) apply the top-k selection
+// inside their softmax.
+#include "../common/tb_common.cuh"
+
+namespace {
+using namespace tb;
+
+constexpr int MS_THREADS = 256;
+constexpr int MS_MAX_VECS = 8;  // 16-byte vectors per thread: 8 x 8 bf16 x 256 threads = 16384 columns
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* scratch) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // scratch may still be read from the previous reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = scratch[0];
+#pragma unroll
+  for (int i = 1; i < MS_THREADS / 32; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
+  return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T* __restrict__ S,
+                                                                        const unsigned char* __restrict__ allowed,
+                                                                        T* __restrict__ P, int cols, int mask_rows,
+                                                                        float scale) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float scratch[MS_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* s = S + row * cols;
+  T* p = P + row * cols;
+  const unsigned char* a = allowed + (row % mask_rows) * (long long)cols;
+  float x[MS_MAX_VECS][V];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MS_MAX_VECS; ++i) {
+    const int c = (i * MS_THREADS + threadIdx.x) * V;
+    if (c < cols) {
+      const Vec16<T> v = ld16(s + c);
+      unsigned char m[V];
+      if (V == 8) *reinterpret_cast<uint2*>(m) = *reinterpret_cast<const uint2*>(a + c);
+      else *reinterpret_cast<uint32_t*>(m) = *reinterpret_cast<const uint32_t*>(a + c);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        x[i][k] = m[k] ? to_f(v.v[k]) * scale : -INFINITY;
+        mx = fmaxf(mx, x[i][k]);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) x[i][k] = -INFINITY;
+    }
+  }
+  mx = block_reduce(mx, true, scratch);
+  const bool empty = mx == -INFINITY;
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MS_MAX_VECS; ++i)
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      x[i][k] = empty ? 0.f : __expf(x[i][k] - mx);  // exp(-inf) = 0 for masked columns
+      sum += x[i][k];
+    }
+  sum = block_reduce(sum, false, scratch);
+  const float inv = empty ? 0.f : 1.f / sum;
+#pragma unroll
+  for (int i = 0; i < MS_MAX_VECS; ++i) {
+    const int c = (i * MS_THREADS + threadIdx.x) * V;
+    if (c < cols) {
+      Vec16<T> o;
+#pragma unroll
+      for (int k = 0; k < V; ++k) o.v[k] = from_f<T>(x[i][k] * inv);
+      st16(p + c, o);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T* __restrict__ P,
+                                                                        const T* __restrict__ dP,
+                                                                        T* __restrict__ dS, int cols, float scale) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float scratch[MS_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* p = P + row * cols;
+  const T* g = dP + row * cols;
+  T* d = dS + row * cols;
+  float pv[MS_MAX_VECS][V], gv[MS_MAX_VECS][V];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < MS_MAX_VECS; ++i) {
+    const int c = (i * MS_THREADS + threadIdx.x) * V;
+    if (c < cols) {
+      const Vec16<T> a = ld16(p + c), b = ld16(g + c);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        pv[i][k] = to_f(a.v[k]);
+        gv[i][k] = to_f(b.v[k]);
+        dot = fmaf(pv[i][k], gv[i][k], dot);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) { pv[i][k] = 0.f; gv[i][k] = 0.f; }
+    }
+  }
+  dot = block_reduce(dot, false, scratch);
+#pragma unroll
+  for (int i = 0; i < MS_MAX_VECS; ++i) {
+    const int c = (i * MS_THREADS + threadIdx.x) * V;
+    if (c < cols) {
+      Vec16<T> o;
+#pragma unroll
+      for (int k = 0; k < V; ++k) o.v[k] = from_f<T>(scale * pv[i][k] * (gv[i][k] - dot));
+      st16(d + c, o);
+    }
+  }
+}
+
+}  // namespace
+
+// S, P: [rows, cols] (dtype 0 fp32 / 1 bf16 / 2 fp16), allowed: [mask_rows, cols] bytes (0 = masked).
+// cols a multiple of the 16-byte vector (8 for 16-bit types, 4 for fp32) and at most 256 * 8 vectors.
+TB_API int tb_masked_softmax_fwd(const void* S, const void* allowed, void* P, long long rows, int cols, int mask_rows,
+                                 float scale, int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (cols <= 0 || mask_rows <= 0 || rows > 0x7fffffffLL) return TB_ERR_ARG;
+  const int V = dtype == 0 ? 4 : 8;
+  if (cols % V || cols > MS_THREADS * MS_MAX_VECS * V) return TB_ERR_ARG;
+  if (dtype == 0)
+    masked_softmax_fwd_kernel<float><<<(unsigned)rows, MS_THREADS, 0, st>>>(
+        (const float*)S, (const unsigned char*)allowed, (float*)P, cols, mask_rows, scale);
+  else if (dtype == 1)
+    masked_softmax_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, MS_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)S, (const unsigned char*)allowed, (__nv_bfloat16*)P, cols, mask_rows, scale);
+  else if (dtype == 2)
+    masked_softmax_fwd_kernel<__half><<<(unsigned)rows, MS_THREADS, 0, st>>>(
+        (const __half*)S, (const unsigned char*)allowed, (__half*)P, cols, mask_rows, scale);
+  else
+    return TB_ERR_ARG;
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+TB_API int tb_masked_softmax_bwd(const void* P, const void* dP, void* dS, long long rows, int cols, float scale,
+                                 int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (cols <= 0 || rows > 0x7fffffffLL) return TB_ERR_ARG;
+  const int V = dtype == 0 ? 4 : 8;
+  if (cols % V || cols > MS_THREADS * MS_MAX_VECS * V) return TB_ERR_ARG;
+  if (dtype == 0)
+    masked_softmax_bwd_kernel<float><<<(unsigned)rows, MS_THREADS, 0, st>>>((const float*)P, (const float*)dP,
+                                                                           (float*)dS, cols, scale);
+  else if (dtype == 1)
+    masked_softmax_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, MS_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)P, (const __nv_bfloat16*)dP, (__nv_bfloat16*)dS, cols, scale);
+  else if (dtype == 2)
+    masked_softmax_bwd_kernel<__half><<<(unsigned)rows, MS_THREADS, 0, st>>>((const __half*)P, (const __half*)dP,
+                                                                            (__half*)dS, cols, scale);
+  else
+    return TB_ERR_ARG;
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}

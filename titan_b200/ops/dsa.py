@@ -49,15 +49,19 @@ def lightning_indexer_topk_ref(q_idx, weights, k_idx, topk: int, pos_offset: int
     return idx.to(torch.int32), vals
 
 
+def _scoring_kernels_take(q_idx) -> bool:
+    heads = q_idx.shape[2]
+    return (q_idx.is_cuda and q_idx.dtype in (torch.bfloat16, torch.float16) and heads <= 256
+            and heads & (heads - 1) == 0 and q_idx.shape[3] % 8 == 0)
+
+
 @torch.no_grad()
 def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, ratio: int = 1):
     """q_idx [B,S,H,D], weights [B,S,H], k_idx [B,T,1,D] → (idx [B,S,topk] int32 with -1 padding, vals fp32).
 
     ``ratio`` > 1: the keys are compressed blocks of ``ratio`` tokens; query ``s`` sees the first
     ``(pos_offset + s + 1) // ratio`` of them."""
-    heads = q_idx.shape[2]
-    if (not q_idx.is_cuda or q_idx.dtype not in (torch.bfloat16, torch.float16) or heads > 256
-            or heads & (heads - 1) != 0 or q_idx.shape[3] % 8 != 0):
+    if not _scoring_kernels_take(q_idx):
         return lightning_indexer_topk_ref(q_idx, weights, k_idx, topk, pos_offset, ratio)
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]
@@ -143,6 +147,59 @@ def indexer_scores_selected(q_idx, weights, k_idx, idx, chunk: int = 512):
     return s.masked_fill(idx < 0, float("-inf"))
 
 
+class _IndexScoresAtSelected(torch.autograd.Function):
+    """Index scores at the selected keys whose forward costs nothing (the scoring kernel already produced the values
+    while selecting) and whose backward never builds fp32 [queries, heads, keys] tensors: per query chunk it recomputes
+    ``x = q·kᵀ`` in the storage dtype, runs one kernel for ``dx`` and ``dw`` (`csrc/attention/indexer_bwd.cu`) and two
+    GEMMs for ``dq`` and ``dk``."""
+
+    @staticmethod
+    def forward(ctx, q_idx, weights, k_idx, idx, vals, chunk):
+        ctx.save_for_backward(q_idx, weights, k_idx, idx)
+        ctx.chunk = chunk
+        return vals.float().masked_fill(idx < 0, float("-inf"))
+
+    @staticmethod
+    def backward(ctx, g):
+        import ctypes
+
+        q_idx, weights, k_idx, idx = ctx.saved_tensors
+        B, S, H, D = q_idx.shape
+        T = k_idx.shape[1]
+        P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        _lib.declare("tb_indexer_relu_bwd", [P, P, P, P, P, LL, I, I, I, P])
+        safe = idx.clamp_min(0).long()
+        g = g.float().masked_fill(idx < 0, 0.0)
+        dq = torch.empty_like(q_idx)
+        dw = torch.empty(B, S, H, dtype=torch.float32, device=q_idx.device)
+        dk = torch.zeros(B, T, D, dtype=torch.float32, device=q_idx.device)
+        for b in range(B):
+            kb = k_idx[b, :, 0].contiguous()
+            for s0 in range(0, S, ctx.chunk):
+                s1 = min(s0 + ctx.chunk, S)
+                sc = s1 - s0
+                qc = q_idx[b, s0:s1].reshape(sc * H, D)
+                dense_g = torch.zeros(sc, T, dtype=torch.float32, device=g.device).scatter_add_(1, safe[b, s0:s1],
+                                                                                            g[b, s0:s1])
+                x = torch.matmul(qc, kb.t())  # [sc*H, T], storage dtype
+                dx = torch.empty_like(x)
+                dwc = torch.empty(sc * H, dtype=torch.float32, device=x.device)
+                wc = weights[b, s0:s1].float().contiguous()
+                rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dense_g.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+                                                    dwc.data_ptr(), sc * H, H, T, _lib.dtype_code(x.dtype),
+                                                    _lib.stream_ptr())
+                _lib.check(rc, "indexer_relu_bwd")
+                dq[b, s0:s1] = torch.matmul(dx, kb).view(sc, H, D)
+                dk[b] += torch.matmul(dx.t(), qc).float()
+                dw[b, s0:s1] = dwc.view(sc, H)
+        return dq, dw.to(weights.dtype), dk.to(k_idx.dtype).unsqueeze(2), None, None, None
+
+
+def indexer_scores_from_selection(q_idx, weights, k_idx, idx, vals, chunk: int = 256):
+    """Differentiable scores at the selected keys, given the values the selection kernels already computed."""
+    return _IndexScoresAtSelected.apply(q_idx, weights, k_idx, idx, vals, chunk)
+
+
 def _sparse_chunk(q, kv, v, idx, scale, want_lse=True):
     """q [H,Sc,Dq], kv [T,Dq], v [T,Dv], idx [Sc,k] → (out [H,Sc,Dv], teacher [Sc,k], lse [H,Sc]); without
     ``want_lse`` the dense path skips the extra pass over the logits and returns zeros there."""
@@ -152,18 +209,20 @@ def _sparse_chunk(q, kv, v, idx, scale, want_lse=True):
         # short key stream: every key through one GEMM, the selection as a mask (no gather, no scatter-add)
         # the GEMMs stay in the storage dtype (bf16 tensor cores; an fp32 copy of the operands would run them as TF32
         # at half the rate and move twice the bytes); softmax statistics are fp32.  The [H,Sc,T] logits are touched by
-        # as few elementwise passes as possible: scale folded into q, mask in place, one fused softmax.
+        # as few passes as possible: scale folded into q, mask and softmax in one kernel.
         slot = torch.where(idx < 0, T, idx).long()
         allowed = torch.zeros(idx.shape[0], T + 1, dtype=torch.bool, device=q.device).scatter_(1, slot, True)[:, :T]
-        empty = ~allowed.any(dim=1)  # a row without any visible key: give it key 0, zero its output afterwards
-        allowed = allowed | (empty.unsqueeze(1) & (torch.arange(T, device=q.device) == 0).unsqueeze(0))
-        s = torch.matmul(q * scale, kv.t()).float().masked_fill_(~allowed.unsqueeze(0), float("-inf"))  # [H,Sc,T]
-        p = torch.softmax(s, dim=-1)
+        from titan_b200.ops.masked_softmax import masked_softmax
+
+        s = torch.matmul(q * scale, kv.t())  # [H,Sc,T] in the storage dtype
+        p = masked_softmax(s, allowed)       # one kernel: mask + fp32 softmax, rows without a visible key -> zeros
         with torch.no_grad():
-            lse = torch.logsumexp(s, dim=-1) if want_lse else s.new_zeros(s.shape[:2])
-        keep = (~empty).to(q.dtype).view(1, -1, 1)
-        out = torch.matmul(p.to(v.dtype), v).to(q.dtype) * keep
-        teacher = torch.gather(p.detach().sum(0), 1, safe).masked_fill((idx < 0) | empty.unsqueeze(1), 0.0)
+            if want_lse:
+                lse = torch.logsumexp(s.float().masked_fill(~allowed.unsqueeze(0), float("-inf")), dim=-1)
+            else:
+                lse = s.new_zeros(s.shape[:2], dtype=torch.float32)
+        out = torch.matmul(p.to(v.dtype), v).to(q.dtype)
+        teacher = torch.gather(p.detach().sum(0, dtype=torch.float32), 1, safe).masked_fill(idx < 0, 0.0)
         return out, teacher, lse
     ksel, vsel = gather_rows(kv, safe), gather_rows(v, safe)  # [Sc,k,D]
     s = torch.einsum("hsd,skd->hsk", q.float(), ksel.float()) * scale
@@ -198,9 +257,12 @@ def dsa_attention(q, k, v, *, scale, q_indexer, k_indexer, weights, index_topk: 
     S, T = q.shape[2], k.shape[2]
     pos_offset = T - S  # with context parallelism the local queries are the tail of the gathered key range
     topk = min(index_topk, T)
-    idx, _ = lightning_indexer_topk(q_indexer, weights, k_indexer, topk, pos_offset)
+    idx, vals = lightning_indexer_topk(q_indexer, weights, k_indexer, topk, pos_offset)
     out, teacher, _ = sparse_mla_attention(q, k, v, idx, scale, want_lse=False)
-    student = indexer_scores_selected(q_indexer, weights, k_indexer, idx)
+    if _scoring_kernels_take(q_indexer) and T % 8 == 0:
+        student = indexer_scores_from_selection(q_indexer, weights, k_indexer, idx, vals)
+    else:
+        student = indexer_scores_selected(q_indexer, weights, k_indexer, idx)
     student = torch.where(idx < 0, torch.full_like(student, -1e30), student)  # finite: masked slots get zero mass
     loss = dsa_indexer_loss(teacher.masked_fill(idx < 0, 0.0), student, loss_scale)
     return loss, out
