@@ -146,15 +146,20 @@ def li_select(q_indexer, k_indexer, weights, ratio: int, index_topk: int, offset
     Selection (no gradient) runs on the scoring GEMM + radix-select kernels; the returned scores are recomputed at
     the selected keys only and carry the gradient to the indexer.  ``pos_offset`` is the global position of local
     query 0 (context parallelism: the keys are global, the queries a slice)."""
-    from titan_b200.ops.dsa import lightning_indexer_topk
+    from titan_b200.ops.dsa import _scoring_kernels_take, indexer_scores_from_selection, lightning_indexer_topk
 
     B = q_indexer.shape[0]
     k = min(index_topk, k_indexer.shape[1])
-    idx, _ = lightning_indexer_topk(q_indexer.detach(), weights.detach(), k_indexer.detach().unsqueeze(2), k,
-                                    pos_offset, ratio)
+    idx, vals = lightning_indexer_topk(q_indexer.detach(), weights.detach(), k_indexer.detach().unsqueeze(2), k,
+                                       pos_offset, ratio)
     idx = idx.long()
     safe = idx.clamp(min=0)
     T = k_indexer.shape[1]
+    if _scoring_kernels_take(q_indexer) and T % 8 == 0:
+        # forward values straight from the scoring kernel, fused backward (no [B,S,H,T] tensor in either direction)
+        s = indexer_scores_from_selection(q_indexer, weights, k_indexer.unsqueeze(2), idx, vals)
+        s = torch.where(idx < 0, torch.full_like(s, torch.finfo(q_indexer.dtype).min), s)
+        return torch.where(idx < 0, idx, idx + offset), s
     if T <= DENSE_RATIO * k:
         # short key stream: score all keys with one GEMM per batch row and pick the selected ones (the gradient of a
         # gather along the key axis is a cheap scatter; no [B,S,k,D] tensor is built)
