@@ -291,6 +291,7 @@ def test_sparse_attention_dense_mask_and_gather_paths_agree():
         pick = torch.randperm(vis)[:k] if vis else torch.empty(0, dtype=torch.long)
         idx[0, s, : pick.numel()] = pick + S
     results = []
+    saved = smla.DENSE_RATIO
     for dense_ratio in (4, 0):
         smla.DENSE_RATIO = dense_ratio
         try:
@@ -300,7 +301,7 @@ def test_sparse_attention_dense_mask_and_gather_paths_agree():
             out.square().sum().backward()
             results.append((out.detach(), dist, [t.grad for t in leaves]))
         finally:
-            smla.DENSE_RATIO = 4
+            smla.DENSE_RATIO = saved
     (o1, d1, g1), (o2, d2, g2) = results
     torch.testing.assert_close(o1, o2)
     torch.testing.assert_close(d1, d2)

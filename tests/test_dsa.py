@@ -98,6 +98,7 @@ def test_sparse_mla_dense_mask_and_gather_paths_agree():
         pick = torch.randperm(s + 1)[:k]
         idx[0, s, : pick.numel()] = pick
     results = []
+    saved = dsa.DENSE_RATIO
     for ratio in (4, 0):
         dsa.DENSE_RATIO = ratio
         try:
@@ -107,7 +108,7 @@ def test_sparse_mla_dense_mask_and_gather_paths_agree():
             (out.square().sum() + sc.masked_fill(idx < 0, 0.0).sum()).backward()
             results.append((out.detach(), teacher, lse.detach(), sc.detach(), [t.grad for t in leaves]))
         finally:
-            dsa.DENSE_RATIO = 4
+            dsa.DENSE_RATIO = saved
     a, b = results
     for x, y in zip(a[:4], b[:4]):
         torch.testing.assert_close(x, y)
@@ -117,7 +118,8 @@ def test_sparse_mla_dense_mask_and_gather_paths_agree():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,T", [(torch.bfloat16, 64), (torch.bfloat16, 8192), (torch.bfloat16, 16384),
-                                     (torch.float32, 1024), (torch.float32, 8192)])
+                                     (torch.bfloat16, 40960), (torch.float32, 1024), (torch.float32, 8192),
+                                     (torch.float32, 16384)])
 def test_masked_softmax_kernel_matches_reference(cuda_device, dtype, T):
     from titan_b200.ops.masked_softmax import masked_softmax, masked_softmax_ref
 

@@ -6,8 +6,8 @@
 //   P[r, t] = allowed[r % mask_rows, t] ? exp(scale * S[r, t] - m_r) / l_r : 0          (fp32 statistics)
 //   dS[r, t] = scale * P[r, t] * (dP[r, t] - Σ_t' P[r, t'] dP[r, t'])
 //
-// One CTA of 256 threads per row, the row held in registers (up to 64 values per thread: T <= 16384), 16-byte
-// accesses; a row without any allowed key yields zeros.  Rows are [heads * queries]; the mask has one row per query
+// One CTA of 256 threads per row, the row held in registers (up to 64 values per thread: T <= 16384; wider rows take
+// two passes over global memory), 16-byte accesses; a row without any allowed key yields zeros.  Rows are [heads * queries]; the mask has one row per query
 // and is shared by the heads (row r uses mask row r % mask_rows).
 //
 // Stands where the reference's sparse attention kernels (`npu_sparse_flash_attention`, K9) apply the top-k selection
@@ -128,27 +128,105 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T*
   }
 }
 
+// Rows wider than the register budget: two passes over global memory (online maximum / sum, then the write).
+template <typename T>
+__global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_stream_kernel(const T* __restrict__ S,
+                                                                               const unsigned char* __restrict__ allowed,
+                                                                               T* __restrict__ P, int cols,
+                                                                               int mask_rows, float scale) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float scratch[MS_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* s = S + row * cols;
+  T* p = P + row * cols;
+  const unsigned char* a = allowed + (row % mask_rows) * (long long)cols;
+  float m = -INFINITY, l = 0.f;
+  for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
+    const Vec16<T> v = ld16(s + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      if (a[c + k]) {
+        const float x = to_f(v.v[k]) * scale;
+        if (x > m) { l *= __expf(m - x); m = x; }
+        l += __expf(x - m);
+      }
+    }
+  }
+  const float mb = block_reduce(m, true, scratch);
+  const bool empty = mb == -INFINITY;
+  l = (m == -INFINITY) ? 0.f : l * __expf(m - mb);
+  const float lb = block_reduce(l, false, scratch);
+  const float inv = empty ? 0.f : 1.f / lb;
+  for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
+    const Vec16<T> v = ld16(s + c);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = from_f<T>(a[c + k] ? __expf(to_f(v.v[k]) * scale - mb) * inv : 0.f);
+    st16(p + c, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_stream_kernel(const T* __restrict__ P,
+                                                                               const T* __restrict__ dP,
+                                                                               T* __restrict__ dS, int cols,
+                                                                               float scale) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float scratch[MS_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* p = P + row * cols;
+  const T* g = dP + row * cols;
+  T* d = dS + row * cols;
+  float dot = 0.f;
+  for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
+    const Vec16<T> a = ld16(p + c), b = ld16(g + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) dot = fmaf(to_f(a.v[k]), to_f(b.v[k]), dot);
+  }
+  dot = block_reduce(dot, false, scratch);
+  for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
+    const Vec16<T> a = ld16(p + c), b = ld16(g + c);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = from_f<T>(scale * to_f(a.v[k]) * (to_f(b.v[k]) - dot));
+    st16(d + c, o);
+  }
+}
+
+template <typename T>
+void launch_fwd(const void* S, const void* allowed, void* P, long long rows, int cols, int mask_rows, float scale,
+                cudaStream_t st) {
+  if (cols <= MS_THREADS * MS_MAX_VECS * Vec16<T>::N)
+    masked_softmax_fwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)S, (const unsigned char*)allowed,
+                                                                        (T*)P, cols, mask_rows, scale);
+  else
+    masked_softmax_fwd_stream_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>(
+        (const T*)S, (const unsigned char*)allowed, (T*)P, cols, mask_rows, scale);
+}
+
+template <typename T>
+void launch_bwd(const void* P, const void* dP, void* dS, long long rows, int cols, float scale, cudaStream_t st) {
+  if (cols <= MS_THREADS * MS_MAX_VECS * Vec16<T>::N)
+    masked_softmax_bwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols, scale);
+  else
+    masked_softmax_bwd_stream_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols,
+                                                                               scale);
+}
+
 }  // namespace
 
 // S, P: [rows, cols] (dtype 0 fp32 / 1 bf16 / 2 fp16), allowed: [mask_rows, cols] bytes (0 = masked).
-// cols a multiple of the 16-byte vector (8 for 16-bit types, 4 for fp32) and at most 256 * 8 vectors.
+// cols a multiple of the 16-byte vector (8 for 16-bit types, 4 for fp32); rows of up to 256 * 8 vectors are held in
+// registers, wider ones take two passes over global memory.
 TB_API int tb_masked_softmax_fwd(const void* S, const void* allowed, void* P, long long rows, int cols, int mask_rows,
                                  float scale, int dtype, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols <= 0 || mask_rows <= 0 || rows > 0x7fffffffLL) return TB_ERR_ARG;
-  const int V = dtype == 0 ? 4 : 8;
-  if (cols % V || cols > MS_THREADS * MS_MAX_VECS * V) return TB_ERR_ARG;
-  if (dtype == 0)
-    masked_softmax_fwd_kernel<float><<<(unsigned)rows, MS_THREADS, 0, st>>>(
-        (const float*)S, (const unsigned char*)allowed, (float*)P, cols, mask_rows, scale);
-  else if (dtype == 1)
-    masked_softmax_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, MS_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)S, (const unsigned char*)allowed, (__nv_bfloat16*)P, cols, mask_rows, scale);
-  else if (dtype == 2)
-    masked_softmax_fwd_kernel<__half><<<(unsigned)rows, MS_THREADS, 0, st>>>(
-        (const __half*)S, (const unsigned char*)allowed, (__half*)P, cols, mask_rows, scale);
-  else
-    return TB_ERR_ARG;
+  if (cols % (dtype == 0 ? 4 : 8)) return TB_ERR_ARG;
+  if (dtype == 0) launch_fwd<float>(S, allowed, P, rows, cols, mask_rows, scale, st);
+  else if (dtype == 1) launch_fwd<__nv_bfloat16>(S, allowed, P, rows, cols, mask_rows, scale, st);
+  else if (dtype == 2) launch_fwd<__half>(S, allowed, P, rows, cols, mask_rows, scale, st);
+  else return TB_ERR_ARG;
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;
@@ -158,19 +236,11 @@ TB_API int tb_masked_softmax_bwd(const void* P, const void* dP, void* dS, long l
                                  int dtype, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols <= 0 || rows > 0x7fffffffLL) return TB_ERR_ARG;
-  const int V = dtype == 0 ? 4 : 8;
-  if (cols % V || cols > MS_THREADS * MS_MAX_VECS * V) return TB_ERR_ARG;
-  if (dtype == 0)
-    masked_softmax_bwd_kernel<float><<<(unsigned)rows, MS_THREADS, 0, st>>>((const float*)P, (const float*)dP,
-                                                                           (float*)dS, cols, scale);
-  else if (dtype == 1)
-    masked_softmax_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, MS_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)P, (const __nv_bfloat16*)dP, (__nv_bfloat16*)dS, cols, scale);
-  else if (dtype == 2)
-    masked_softmax_bwd_kernel<__half><<<(unsigned)rows, MS_THREADS, 0, st>>>((const __half*)P, (const __half*)dP,
-                                                                            (__half*)dS, cols, scale);
-  else
-    return TB_ERR_ARG;
+  if (cols % (dtype == 0 ? 4 : 8)) return TB_ERR_ARG;
+  if (dtype == 0) launch_bwd<float>(P, dP, dS, rows, cols, scale, st);
+  else if (dtype == 1) launch_bwd<__nv_bfloat16>(P, dP, dS, rows, cols, scale, st);
+  else if (dtype == 2) launch_bwd<__half>(P, dP, dS, rows, cols, scale, st);
+  else return TB_ERR_ARG;
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

@@ -89,7 +89,7 @@ def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0
     return idx, vals
 
 
-DENSE_RATIO = 4  # a key stream at most this many times longer than top-k is scored densely with a selection mask
+DENSE_RATIO = 64  # a key stream at most this many times longer than top-k is scored densely with a selection mask
 
 
 class _GatherRows(torch.autograd.Function):

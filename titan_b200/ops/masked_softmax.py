@@ -1,9 +1,9 @@
 """Row softmax under a selection mask (`csrc/attention/masked_softmax.cu`): ``softmax(scale·S)`` over the allowed
 columns, zeros elsewhere, in the storage dtype with fp32 statistics; one read and one write of the logits in forward,
-two reads and one write in backward.  ``allowed`` has one row per query and is shared by all heads.
+two reads and one write in backward (rows wider than 16384 columns: one more read each).  ``allowed`` has one row per query and is shared by all heads.
 
 Used by the dense form of sparse attention (`ops/dsa.py`), where PyTorch would spend ~10 elementwise passes over the
-fp32 [heads, queries, keys] logits.  CPU tensors, very wide rows (> 16384 columns) and odd widths use PyTorch.
+fp32 [heads, queries, keys] logits.  CPU tensors and odd widths use PyTorch.
 """
 
 from __future__ import annotations
@@ -17,7 +17,7 @@ from titan_b200.ops import _lib
 __all__ = ["masked_softmax", "masked_softmax_ref"]
 
 _DECLARED = False
-_MAX_COLS = {torch.float32: 8192, torch.bfloat16: 16384, torch.float16: 16384}
+_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
 
 
 def masked_softmax_ref(s: torch.Tensor, allowed: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
@@ -66,7 +66,7 @@ def masked_softmax(s: torch.Tensor, allowed: torch.Tensor, scale: float = 1.0) -
     """s [H, Sc, T] logits, allowed [Sc, T] bool → probabilities [H, Sc, T] in s.dtype."""
     T = s.shape[-1]
     vec = 4 if s.dtype == torch.float32 else 8
-    if s.is_cuda and s.dim() == 3 and s.dtype in _MAX_COLS and T % vec == 0 and T <= _MAX_COLS[s.dtype] \
+    if s.is_cuda and s.dim() == 3 and s.dtype in _DTYPES and T % vec == 0 \
             and allowed.dtype == torch.bool and allowed.shape == s.shape[1:]:
         return _MaskedSoftmax.apply(s, allowed, scale)
     return masked_softmax_ref(s, allowed, scale)

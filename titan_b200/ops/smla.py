@@ -30,7 +30,7 @@ __all__ = ["smla_attention", "li_select"]
 
 from titan_b200.ops.dsa import gather_rows
 
-DENSE_RATIO = 4  # a compressed stream at most this many times longer than k is attended densely with a mask
+DENSE_RATIO = 64  # a compressed stream at most this many times longer than k is attended densely with a mask
 
 
 def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, ratio: int, scale: float,
