@@ -307,3 +307,45 @@ def test_sparse_attention_dense_mask_and_gather_paths_agree():
     torch.testing.assert_close(d1, d2)
     for a, b in zip(g1, g2):  # the gather path accumulates its scatter-add in fp32
         torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("with_idx", [True, False])
+def test_fused_chunk_path_matches_dense_oracle_on_gpu(with_idx):
+    """bf16 on CUDA takes the one-GEMM / masked-softmax-with-sink / one-GEMM path: against the fp32 dense oracle,
+    outputs, the indexer's teacher distribution and all gradients (queries, keys, compressed keys, sink)."""
+    from titan_b200.ops import smla
+
+    torch.manual_seed(7)
+    B, S, H, hd, ratio, k, window = 1, 256, 4, 64, 4, 16, 32
+    Tc = S // ratio
+    dev = "cuda"
+    q = torch.randn(B, S, H, hd, device=dev) * 0.5
+    kv = torch.randn(B, S, hd, device=dev) * 0.5
+    kvc = torch.randn(B, Tc, hd, device=dev) * 0.5
+    sink = torch.randn(H, device=dev)
+    idx = None
+    if with_idx:
+        idx = torch.full((B, S, k), -1, dtype=torch.long, device=dev)
+        for s in range(S):
+            vis = (s + 1) // ratio
+            pick = torch.randperm(vis, device=dev)[:k]
+            idx[0, s, : pick.numel()] = pick + S
+    scale = hd ** -0.5
+    ref_leaves = [t.clone().requires_grad_(True) for t in (q, kv, kvc, sink)]
+    ref, probs = sparse_attention_dense(ref_leaves[0], ref_leaves[1], ref_leaves[3], ref_leaves[2], idx, window, ratio,
+                                        scale)
+    leaves = [t.to(torch.bfloat16).requires_grad_(True) for t in (q, kv, kvc)] + [sink.clone().requires_grad_(True)]
+    out, dist = smla.smla_attention(leaves[0], leaves[1], leaves[3], leaves[2], idx, window, ratio, scale,
+                                    want_dist=with_idx)
+    torch.testing.assert_close(out.float(), ref, rtol=5e-2, atol=3e-2)
+    if with_idx:
+        cmp = probs[..., S:].detach().sum(dim=1) / H
+        want = torch.gather(cmp, -1, (idx - S).clamp(min=0)).masked_fill(idx < 0, 0.0)
+        torch.testing.assert_close(dist, want, rtol=5e-2, atol=2e-2)
+    g = torch.randn_like(ref)
+    ref.backward(g)
+    out.backward(g.to(out.dtype))
+    for a, b, name in zip(leaves, ref_leaves, ("dq", "dkv", "dkvc", "dsink")):
+        torch.testing.assert_close(a.grad.float(), b.grad.float(), rtol=8e-2, atol=6e-2,
+                                   msg=lambda m, n=name: f"{n}: {m}")

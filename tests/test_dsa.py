@@ -129,7 +129,10 @@ def test_masked_softmax_kernel_matches_reference(cuda_device, dtype, T):
     allowed = torch.rand(Sc, T, device="cuda") < 0.3
     allowed[5] = False  # a query without any visible key
     a, b = s.clone().requires_grad_(True), s.clone().requires_grad_(True)
-    p, ref = masked_softmax(a, allowed, 0.7), masked_softmax_ref(b, allowed, 0.7)
+    sink = torch.randn(H, device="cuda") if T % 3 == 1 else None  # some cases with an attention sink
+    sa = sink.clone().requires_grad_(True) if sink is not None else None
+    sb = sink.clone().requires_grad_(True) if sink is not None else None
+    p, ref = masked_softmax(a, allowed, 0.7, sa), masked_softmax_ref(b, allowed, 0.7, sb)
     tol = dict(rtol=2e-2, atol=2e-3) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-6)
     torch.testing.assert_close(p.float(), ref.float(), **tol)
     assert p[:, 5].abs().sum() == 0
@@ -138,6 +141,8 @@ def test_masked_softmax_kernel_matches_reference(cuda_device, dtype, T):
     ref.backward(g)
     gtol = dict(rtol=5e-2, atol=5e-3) if dtype == torch.bfloat16 else dict(rtol=1e-3, atol=1e-5)
     torch.testing.assert_close(a.grad.float(), b.grad.float(), **gtol)
+    if sink is not None:
+        torch.testing.assert_close(sa.grad, sb.grad, rtol=5e-2, atol=5e-2)
 
 
 @pytest.mark.gpu

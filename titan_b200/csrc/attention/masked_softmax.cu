@@ -36,13 +36,14 @@ template <typename T>
 __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T* __restrict__ S,
                                                                         const unsigned char* __restrict__ allowed,
                                                                         T* __restrict__ P, int cols, int mask_rows,
-                                                                        float scale) {
+                                                                        float scale, const float* __restrict__ sink) {
   constexpr int V = Vec16<T>::N;
   __shared__ float scratch[MS_THREADS / 32];
   const long long row = blockIdx.x;
   const T* s = S + row * cols;
   T* p = P + row * cols;
   const unsigned char* a = allowed + (row % mask_rows) * (long long)cols;
+  const float sk = sink != nullptr ? sink[row / mask_rows] : -INFINITY;  // per-head logit without a key
   float x[MS_MAX_VECS][V];
   float mx = -INFINITY;
 #pragma unroll
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
       for (int k = 0; k < V; ++k) x[i][k] = -INFINITY;
     }
   }
-  mx = block_reduce(mx, true, scratch);
+  mx = fmaxf(block_reduce(mx, true, scratch), sk);
   const bool empty = mx == -INFINITY;
   float sum = 0.f;
 #pragma unroll
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
       x[i][k] = empty ? 0.f : __expf(x[i][k] - mx);  // exp(-inf) = 0 for masked columns
       sum += x[i][k];
     }
-  sum = block_reduce(sum, false, scratch);
+  sum = block_reduce(sum, false, scratch) + (empty ? 0.f : __expf(sk - mx));  // the sink only feeds the denominator
   const float inv = empty ? 0.f : 1.f / sum;
 #pragma unroll
   for (int i = 0; i < MS_MAX_VECS; ++i) {
@@ -90,7 +91,8 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
 template <typename T>
 __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T* __restrict__ P,
                                                                         const T* __restrict__ dP,
-                                                                        T* __restrict__ dS, int cols, float scale) {
+                                                                        T* __restrict__ dS, int cols, float scale,
+                                                                        float* __restrict__ dsink_rows) {
   constexpr int V = Vec16<T>::N;
   __shared__ float scratch[MS_THREADS / 32];
   const long long row = blockIdx.x;
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T*
   const T* g = dP + row * cols;
   T* d = dS + row * cols;
   float pv[MS_MAX_VECS][V], gv[MS_MAX_VECS][V];
-  float dot = 0.f;
+  float dot = 0.f, psum = 0.f;
 #pragma unroll
   for (int i = 0; i < MS_MAX_VECS; ++i) {
     const int c = (i * MS_THREADS + threadIdx.x) * V;
@@ -109,6 +111,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T*
         pv[i][k] = to_f(a.v[k]);
         gv[i][k] = to_f(b.v[k]);
         dot = fmaf(pv[i][k], gv[i][k], dot);
+        psum += pv[i][k];
       }
     } else {
 #pragma unroll
@@ -116,6 +119,10 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T*
     }
   }
   dot = block_reduce(dot, false, scratch);
+  if (dsink_rows != nullptr) {  // the sink's probability is what the keys leave: d sink = -(1 - Σ P) · Σ P dP
+    psum = block_reduce(psum, false, scratch);
+    if (threadIdx.x == 0) dsink_rows[row] = -(1.f - psum) * dot;
+  }
 #pragma unroll
   for (int i = 0; i < MS_MAX_VECS; ++i) {
     const int c = (i * MS_THREADS + threadIdx.x) * V;
@@ -133,13 +140,15 @@ template <typename T>
 __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_stream_kernel(const T* __restrict__ S,
                                                                                const unsigned char* __restrict__ allowed,
                                                                                T* __restrict__ P, int cols,
-                                                                               int mask_rows, float scale) {
+                                                                               int mask_rows, float scale,
+                                                                               const float* __restrict__ sink) {
   constexpr int V = Vec16<T>::N;
   __shared__ float scratch[MS_THREADS / 32];
   const long long row = blockIdx.x;
   const T* s = S + row * cols;
   T* p = P + row * cols;
   const unsigned char* a = allowed + (row % mask_rows) * (long long)cols;
+  const float sk = sink != nullptr ? sink[row / mask_rows] : -INFINITY;
   float m = -INFINITY, l = 0.f;
   for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
     const Vec16<T> v = ld16(s + c);
@@ -152,10 +161,10 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_stream_kernel(c
       }
     }
   }
-  const float mb = block_reduce(m, true, scratch);
+  const float mb = fmaxf(block_reduce(m, true, scratch), sk);
   const bool empty = mb == -INFINITY;
   l = (m == -INFINITY) ? 0.f : l * __expf(m - mb);
-  const float lb = block_reduce(l, false, scratch);
+  const float lb = block_reduce(l, false, scratch) + (empty ? 0.f : __expf(sk - mb));
   const float inv = empty ? 0.f : 1.f / lb;
   for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
     const Vec16<T> v = ld16(s + c);
@@ -170,20 +179,25 @@ template <typename T>
 __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_stream_kernel(const T* __restrict__ P,
                                                                                const T* __restrict__ dP,
                                                                                T* __restrict__ dS, int cols,
-                                                                               float scale) {
+                                                                               float scale,
+                                                                               float* __restrict__ dsink_rows) {
   constexpr int V = Vec16<T>::N;
   __shared__ float scratch[MS_THREADS / 32];
   const long long row = blockIdx.x;
   const T* p = P + row * cols;
   const T* g = dP + row * cols;
   T* d = dS + row * cols;
-  float dot = 0.f;
+  float dot = 0.f, psum = 0.f;
   for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
     const Vec16<T> a = ld16(p + c), b = ld16(g + c);
 #pragma unroll
-    for (int k = 0; k < V; ++k) dot = fmaf(to_f(a.v[k]), to_f(b.v[k]), dot);
+    for (int k = 0; k < V; ++k) { dot = fmaf(to_f(a.v[k]), to_f(b.v[k]), dot); psum += to_f(a.v[k]); }
   }
   dot = block_reduce(dot, false, scratch);
+  if (dsink_rows != nullptr) {
+    psum = block_reduce(psum, false, scratch);
+    if (threadIdx.x == 0) dsink_rows[row] = -(1.f - psum) * dot;
+  }
   for (int c = threadIdx.x * V; c < cols; c += MS_THREADS * V) {
     const Vec16<T> a = ld16(p + c), b = ld16(g + c);
     Vec16<T> o;
@@ -195,22 +209,24 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_stream_kernel(c
 
 template <typename T>
 void launch_fwd(const void* S, const void* allowed, void* P, long long rows, int cols, int mask_rows, float scale,
-                cudaStream_t st) {
+                const float* sink, cudaStream_t st) {
   if (cols <= MS_THREADS * MS_MAX_VECS * Vec16<T>::N)
     masked_softmax_fwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)S, (const unsigned char*)allowed,
-                                                                        (T*)P, cols, mask_rows, scale);
+                                                                        (T*)P, cols, mask_rows, scale, sink);
   else
     masked_softmax_fwd_stream_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>(
-        (const T*)S, (const unsigned char*)allowed, (T*)P, cols, mask_rows, scale);
+        (const T*)S, (const unsigned char*)allowed, (T*)P, cols, mask_rows, scale, sink);
 }
 
 template <typename T>
-void launch_bwd(const void* P, const void* dP, void* dS, long long rows, int cols, float scale, cudaStream_t st) {
+void launch_bwd(const void* P, const void* dP, void* dS, long long rows, int cols, float scale, float* dsink_rows,
+                cudaStream_t st) {
   if (cols <= MS_THREADS * MS_MAX_VECS * Vec16<T>::N)
-    masked_softmax_bwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols, scale);
+    masked_softmax_bwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols, scale,
+                                                                        dsink_rows);
   else
     masked_softmax_bwd_stream_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols,
-                                                                               scale);
+                                                                               scale, dsink_rows);
 }
 
 }  // namespace
@@ -218,28 +234,30 @@ void launch_bwd(const void* P, const void* dP, void* dS, long long rows, int col
 // S, P: [rows, cols] (dtype 0 fp32 / 1 bf16 / 2 fp16), allowed: [mask_rows, cols] bytes (0 = masked).
 // cols a multiple of the 16-byte vector (8 for 16-bit types, 4 for fp32); rows of up to 256 * 8 vectors are held in
 // registers, wider ones take two passes over global memory.
+// sink: optional [rows / mask_rows] fp32, one logit per head that joins the denominator only (attention sink).
 TB_API int tb_masked_softmax_fwd(const void* S, const void* allowed, void* P, long long rows, int cols, int mask_rows,
-                                 float scale, int dtype, cudaStream_t st) {
+                                 float scale, const float* sink, int dtype, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols <= 0 || mask_rows <= 0 || rows > 0x7fffffffLL) return TB_ERR_ARG;
   if (cols % (dtype == 0 ? 4 : 8)) return TB_ERR_ARG;
-  if (dtype == 0) launch_fwd<float>(S, allowed, P, rows, cols, mask_rows, scale, st);
-  else if (dtype == 1) launch_fwd<__nv_bfloat16>(S, allowed, P, rows, cols, mask_rows, scale, st);
-  else if (dtype == 2) launch_fwd<__half>(S, allowed, P, rows, cols, mask_rows, scale, st);
+  if (dtype == 0) launch_fwd<float>(S, allowed, P, rows, cols, mask_rows, scale, sink, st);
+  else if (dtype == 1) launch_fwd<__nv_bfloat16>(S, allowed, P, rows, cols, mask_rows, scale, sink, st);
+  else if (dtype == 2) launch_fwd<__half>(S, allowed, P, rows, cols, mask_rows, scale, sink, st);
   else return TB_ERR_ARG;
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;
 }
 
+// dsink_rows: optional [rows] fp32, the sink logit's gradient contribution of every row (the caller sums per head).
 TB_API int tb_masked_softmax_bwd(const void* P, const void* dP, void* dS, long long rows, int cols, float scale,
-                                 int dtype, cudaStream_t st) {
+                                 float* dsink_rows, int dtype, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols <= 0 || rows > 0x7fffffffLL) return TB_ERR_ARG;
   if (cols % (dtype == 0 ? 4 : 8)) return TB_ERR_ARG;
-  if (dtype == 0) launch_bwd<float>(P, dP, dS, rows, cols, scale, st);
-  else if (dtype == 1) launch_bwd<__nv_bfloat16>(P, dP, dS, rows, cols, scale, st);
-  else if (dtype == 2) launch_bwd<__half>(P, dP, dS, rows, cols, scale, st);
+  if (dtype == 0) launch_bwd<float>(P, dP, dS, rows, cols, scale, dsink_rows, st);
+  else if (dtype == 1) launch_bwd<__nv_bfloat16>(P, dP, dS, rows, cols, scale, dsink_rows, st);
+  else if (dtype == 2) launch_bwd<__half>(P, dP, dS, rows, cols, scale, dsink_rows, st);
   else return TB_ERR_ARG;
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);

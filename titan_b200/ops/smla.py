@@ -43,11 +43,42 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, 
     t0 = max(0, s0 + koff - window + 1)
     kwin = kv[t0: s1 + koff]  # [W, hd]
     qh = q.transpose(0, 1)  # [H, Sc, hd]
-    logit_w = torch.matmul(qh, kwin.t()).float() * scale  # [H, Sc, W]
     spos = torch.arange(s0, s1, device=q.device).unsqueeze(1)
     kpos = spos + koff
     tpos = torch.arange(t0, s1 + koff, device=q.device).unsqueeze(0)
-    logit_w = logit_w.masked_fill(((tpos > kpos) | (tpos <= kpos - window)).unsqueeze(0), float("-inf"))
+    outside = (tpos > kpos) | (tpos <= kpos - window)  # [Sc, W]
+    dense_ok = cidx is None or (kvc is not None and kvc.shape[0] <= DENSE_RATIO * cidx.shape[1])
+    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and dense_ok:
+        # One GEMM over [window keys | compressed keys], one kernel for mask + sink + softmax, one GEMM back: the shared
+        # KV latent is key and value at once, so the concatenated key block serves both products.
+        from titan_b200.ops.masked_softmax import masked_softmax
+
+        W = kwin.shape[0]
+        blocks, masks, c_end = [kwin], [~outside], 0
+        if kvc is not None and ratio > 1:
+            if cidx is not None:
+                c_end = kvc.shape[0]
+                slot = torch.where(cidx < 0, c_end, cidx).long()  # empty slots point at a scratch column
+                masks.append(torch.zeros(Sc, c_end + 1, dtype=torch.bool, device=q.device)
+                             .scatter_(1, slot, True)[:, :c_end])
+            else:
+                c_end = min((qpos0 + s1) // ratio, kvc.shape[0])
+                masks.append(torch.arange(c_end, device=q.device).unsqueeze(0) < (qpos0 + spos + 1) // ratio)
+            blocks.append(kvc[:c_end])
+        pad = (-(W + c_end)) % 8  # the kernel reads 16-byte vectors
+        if pad:
+            blocks.append(kv.new_zeros(pad, hd))
+            masks.append(torch.zeros(Sc, pad, dtype=torch.bool, device=q.device))
+        keys = torch.cat(blocks, dim=0) if len(blocks) > 1 else kwin
+        allowed = torch.cat(masks, dim=1) if len(masks) > 1 else masks[0]
+        p = masked_softmax(torch.matmul(qh * scale, keys.t()), allowed, 1.0, sink)  # [H, Sc, T]
+        out = torch.matmul(p, keys).transpose(0, 1)
+        if cidx is not None and c_end > 0 and want_dist:
+            mass = p[..., W: W + c_end].detach().sum(0, dtype=torch.float32) / n_heads_total  # [Sc, Tc]
+            return out, torch.gather(mass, 1, cidx.clamp(min=0).long())
+        return (out,)
+    logit_w = torch.matmul(qh, kwin.t()).float() * scale  # [H, Sc, W]
+    logit_w = logit_w.masked_fill(outside.unsqueeze(0), float("-inf"))
     parts = [logit_w]
     ksel = None
     dense_sel = False
