@@ -213,6 +213,32 @@ def bench_lowp(iters):
              cublas_bf16_tflops=fl / lib_ms / 1e9, vs_bf16_peak=fl / gemm_ms / 1e9 / tf_peak, peak=tag)
 
 
+def bench_sparse(iters):
+    """Kernels of the dense form of sparse attention: masked softmax (forward / backward) and the indexer-score
+    backward, with the bytes they must move against the measured copy bandwidth."""
+    from titan_b200.ops.masked_softmax import masked_softmax
+
+    _, bw_peak, tag = peaks()
+    H, Sc, T = 16, 512, 8192
+    s_ = torch.randn(H, Sc, T, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    allowed = torch.rand(Sc, T, device="cuda") < 0.25
+    sink = torch.zeros(H, device="cuda")
+    g = torch.randn(H, Sc, T, device="cuda", dtype=torch.bfloat16)
+    fwd = timeit(lambda: masked_softmax(s_.detach(), allowed, 1.0, sink), iters)
+    p_ = masked_softmax(s_, allowed, 1.0, sink)
+
+    def bwd_only():
+        s_.grad = None
+        p_.backward(g, retain_graph=True)
+
+    bwd = timeit(bwd_only, iters)
+    n = H * Sc * T
+    emit(kernel="masked_softmax_fwd", shape=[H, Sc, T], ms=fwd, gbs=(4 * n + Sc * T) / fwd / 1e6,
+         frac_of_copy_bw=(4 * n + Sc * T) / fwd / 1e6 / bw_peak, peak=tag)
+    emit(kernel="masked_softmax_bwd", shape=[H, Sc, T], ms=bwd, gbs=6 * n / bwd / 1e6,
+         frac_of_copy_bw=6 * n / bwd / 1e6 / bw_peak, peak=tag, note="includes the autograd wrapper and the sink reduction")
+
+
 def profile_case(name: str, launches: int = 3) -> None:
     """One small workload (inputs larger than L2, well under 1 GB on the device), launched a few times: the
     target of a profiler capture.  Prints nothing but the case name; timings come from the bench modes."""
@@ -261,6 +287,35 @@ def profile_case(name: str, launches: int = 3) -> None:
         pa = pack_scale_atoms(torch.randint(120, 134, (8192, 128), dtype=torch.uint8, device=dev))
         pb = pack_scale_atoms(torch.randint(120, 134, (4096, 128), dtype=torch.uint8, device=dev))
         fn = lambda: mxfp8_gemm(aq, pa, bq, pb, packed=True)  # noqa: E731
+    elif name == "masked_softmax":
+        from titan_b200.ops.masked_softmax import masked_softmax
+
+        # 16 heads x 512 queries x 8192 keys in bf16 (134 MB of logits: larger than L2), a quarter of the keys allowed
+        s_ = torch.randn(16, 512, 8192, device=dev, dtype=bf, requires_grad=True)
+        allowed = torch.rand(512, 8192, device=dev) < 0.25
+        sink = torch.zeros(16, device=dev)
+        g = torch.randn(16, 512, 8192, device=dev, dtype=bf)
+
+        def fn():
+            s_.grad = None
+            masked_softmax(s_, allowed, 1.0, sink).backward(g)
+    elif name == "indexer_relu_bwd":
+        import ctypes
+
+        from titan_b200.ops import _lib
+
+        P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        _lib.declare("tb_indexer_relu_bwd", [P, P, P, P, P, LL, I, I, I, P])
+        sc, heads, keys = 128, 64, 8192  # x: 128 x 64 x 8192 bf16 = 134 MB
+        x = torch.randn(sc * heads, keys, device=dev, dtype=bf)
+        dscore = torch.randn(sc, keys, device=dev)
+        w = torch.rand(sc * heads, device=dev)
+        dx, dw = torch.empty_like(x), torch.empty(sc * heads, device=dev)
+
+        def fn():
+            rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dscore.data_ptr(), w.data_ptr(), dx.data_ptr(),
+                                                dw.data_ptr(), sc * heads, heads, keys, 1, _lib.stream_ptr())
+            _lib.check(rc, "indexer_relu_bwd")
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     for _ in range(launches):
@@ -274,7 +329,7 @@ def main():
     ap.add_argument("--only", default="gemm,elementwise")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--profile-case", default=None,
-                    help="run one small case a few times and exit (gemm | gemm_wgrad | rmsnorm_bwd | indexer_topk | flash_fwd | mxfp8_gemm)")
+                    help="run one small case a few times and exit (gemm | gemm_wgrad | rmsnorm_bwd | indexer_topk | flash_fwd | mxfp8_gemm | masked_softmax | indexer_relu_bwd)")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)
@@ -288,6 +343,8 @@ def main():
         bench_attention(args.iters)
     if "lowp" in which:
         bench_lowp(args.iters)
+    if "sparse" in which:
+        bench_sparse(args.iters)
 
 
 if __name__ == "__main__":

@@ -32,7 +32,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* scrat
   return r;
 }
 
-template <typename T>
+template <typename T, int NV>
 __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T* __restrict__ S,
                                                                         const unsigned char* __restrict__ allowed,
                                                                         T* __restrict__ P, int cols, int mask_rows,
@@ -44,10 +44,10 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
   T* p = P + row * cols;
   const unsigned char* a = allowed + (row % mask_rows) * (long long)cols;
   const float sk = sink != nullptr ? sink[row / mask_rows] : -INFINITY;  // per-head logit without a key
-  float x[MS_MAX_VECS][V];
+  float x[NV][V];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < MS_MAX_VECS; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = (i * MS_THREADS + threadIdx.x) * V;
     if (c < cols) {
       const Vec16<T> v = ld16(s + c);
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
   const bool empty = mx == -INFINITY;
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < MS_MAX_VECS; ++i)
+  for (int i = 0; i < NV; ++i)
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       x[i][k] = empty ? 0.f : __expf(x[i][k] - mx);  // exp(-inf) = 0 for masked columns
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
   sum = block_reduce(sum, false, scratch) + (empty ? 0.f : __expf(sk - mx));  // the sink only feeds the denominator
   const float inv = empty ? 0.f : 1.f / sum;
 #pragma unroll
-  for (int i = 0; i < MS_MAX_VECS; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = (i * MS_THREADS + threadIdx.x) * V;
     if (c < cols) {
       Vec16<T> o;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_fwd_kernel(const T*
   }
 }
 
-template <typename T>
+template <typename T, int NV>
 __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T* __restrict__ P,
                                                                         const T* __restrict__ dP,
                                                                         T* __restrict__ dS, int cols, float scale,
@@ -99,10 +99,10 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T*
   const T* p = P + row * cols;
   const T* g = dP + row * cols;
   T* d = dS + row * cols;
-  float pv[MS_MAX_VECS][V], gv[MS_MAX_VECS][V];
+  float pv[NV][V], gv[NV][V];
   float dot = 0.f, psum = 0.f;
 #pragma unroll
-  for (int i = 0; i < MS_MAX_VECS; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = (i * MS_THREADS + threadIdx.x) * V;
     if (c < cols) {
       const Vec16<T> a = ld16(p + c), b = ld16(g + c);
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_kernel(const T*
     if (threadIdx.x == 0) dsink_rows[row] = -(1.f - psum) * dot;
   }
 #pragma unroll
-  for (int i = 0; i < MS_MAX_VECS; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = (i * MS_THREADS + threadIdx.x) * V;
     if (c < cols) {
       Vec16<T> o;
@@ -210,23 +210,36 @@ __global__ void __launch_bounds__(MS_THREADS) masked_softmax_bwd_stream_kernel(c
 template <typename T>
 void launch_fwd(const void* S, const void* allowed, void* P, long long rows, int cols, int mask_rows, float scale,
                 const float* sink, cudaStream_t st) {
-  if (cols <= MS_THREADS * MS_MAX_VECS * Vec16<T>::N)
-    masked_softmax_fwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)S, (const unsigned char*)allowed,
-                                                                        (T*)P, cols, mask_rows, scale, sink);
+  // the row lives in registers: as few vectors per thread as the width needs (fewer registers, more rows in flight)
+  const int per = MS_THREADS * Vec16<T>::N;
+#define TB_MS_FWD(NV)                                                                                              \
+  masked_softmax_fwd_kernel<T, NV><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)S, (const unsigned char*)allowed, \
+                                                                          (T*)P, cols, mask_rows, scale, sink)
+  if (cols <= per) TB_MS_FWD(1);
+  else if (cols <= 2 * per) TB_MS_FWD(2);
+  else if (cols <= 4 * per) TB_MS_FWD(4);
+  else if (cols <= MS_MAX_VECS * per) TB_MS_FWD(8);
   else
     masked_softmax_fwd_stream_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>(
         (const T*)S, (const unsigned char*)allowed, (T*)P, cols, mask_rows, scale, sink);
+#undef TB_MS_FWD
 }
 
 template <typename T>
 void launch_bwd(const void* P, const void* dP, void* dS, long long rows, int cols, float scale, float* dsink_rows,
                 cudaStream_t st) {
-  if (cols <= MS_THREADS * MS_MAX_VECS * Vec16<T>::N)
-    masked_softmax_bwd_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols, scale,
-                                                                        dsink_rows);
+  const int per = MS_THREADS * Vec16<T>::N;
+#define TB_MS_BWD(NV)                                                                                            \
+  masked_softmax_bwd_kernel<T, NV><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols, \
+                                                                          scale, dsink_rows)
+  if (cols <= per) TB_MS_BWD(1);
+  else if (cols <= 2 * per) TB_MS_BWD(2);
+  else if (cols <= 4 * per) TB_MS_BWD(4);
+  else if (cols <= MS_MAX_VECS * per) TB_MS_BWD(8);
   else
     masked_softmax_bwd_stream_kernel<T><<<(unsigned)rows, MS_THREADS, 0, st>>>((const T*)P, (const T*)dP, (T*)dS, cols,
                                                                                scale, dsink_rows);
+#undef TB_MS_BWD
 }
 
 }  // namespace
