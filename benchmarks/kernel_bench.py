@@ -211,6 +211,32 @@ def bench_lowp(iters):
              tile128_ms=t128, tile256_ms=t256,
              with_quantise_ms=whole_ms, with_quantise_tflops=fl / whole_ms / 1e9, cublas_bf16_ms=lib_ms,
              cublas_bf16_tflops=fl / lib_ms / 1e9, vs_bf16_peak=fl / gemm_ms / 1e9 / tf_peak, peak=tag)
+    # the quantisers: one pass that writes both views against the two single-axis passes plus the bf16 transpose they need
+    from titan_b200.lowp.mx import mx_quantize_dual
+    from titan_b200.lowp.mx_linear import mx_linear
+
+    _, bw_peak, _ = peaks()
+    for R, C in [(8192, 4096), (8192, 14336)]:
+        x = torch.randn(R, C, device="cuda", dtype=torch.bfloat16)
+        dual_ms = timeit(lambda: mx_quantize_dual(x), iters)
+        row_ms = timeit(lambda: mx_quantize(x, -1), iters)
+        t_ms = timeit(lambda: mx_quantize(x.t().contiguous(), -1), iters)
+        nbytes = R * C * (2 + 2 * (1 + 1 / 32))
+        emit(kernel="mx_quantize_dual", shape=[R, C], ms=dual_ms, gbs=nbytes / dual_ms / 1e6,
+             frac_of_copy_bw=nbytes / dual_ms / 1e6 / bw_peak, separate_passes_ms=row_ms + t_ms, peak=tag)
+    for T_, N, K in [(8192, 4096, 4096), (8192, 14336, 4096)]:
+        x = torch.randn(T_, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        w = (torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02).requires_grad_()
+        g = torch.randn(T_, N, device="cuda", dtype=torch.bfloat16)
+
+        def step(lin):
+            x.grad = w.grad = None
+            lin(x, w).backward(g)
+
+        mx_ms = timeit(lambda: step(mx_linear), iters)
+        bf_ms = timeit(lambda: step(torch.nn.functional.linear), iters)
+        emit(kernel="mx_linear_fwd_bwd", shape=[T_, N, K], ms=mx_ms, tflops=6.0 * T_ * N * K / mx_ms / 1e9,
+             bf16_linear_ms=bf_ms, bf16_linear_tflops=6.0 * T_ * N * K / bf_ms / 1e9, speedup=bf_ms / mx_ms)
 
 
 def bench_sparse(iters):

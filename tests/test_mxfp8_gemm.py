@@ -36,3 +36,72 @@ def test_kernel_matches_dequantised_reference(M, N, K, tile_n):
     _lib.shared_status().raise_if_set("mxfp8 gemm")
     err = (out.float() - ref).abs().max() / ref.abs().max()
     assert err < 8e-3, err  # bf16 output rounding only: the operands are exact
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tile_n", [0, 128])
+def test_grouped_modes_match_per_expert_products(tile_n, cuda_device):
+    """Forward (expert picks its weight rows), input gradient (expert picks a contraction slice of the transposed
+    weight) and weight gradient (contraction over the expert's rows), with an expert without rows and padding rows
+    after the last group."""
+    from titan_b200.lowp.mx import mx_dequantize_ref, mx_quantize_dual
+    from titan_b200.ops.mxfp8_gemm import GROUP_B_ROWS, GROUP_B_SLICE, GROUP_K, mxfp8_grouped_gemm
+
+    torch.manual_seed(11)
+    E, N, K = 4, 384, 256
+    sizes = [256, 0, 128, 384]
+    T = sum(sizes) + 128  # one tile of padding rows at the end
+    offs = torch.tensor(sizes, device="cuda").cumsum(0).to(torch.int32)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.1)
+    g = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    xq1, xs1, xq2t, xs2t = mx_quantize_dual(x)
+    wq1, ws1, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K))
+    gq1, gs1, gq2t, gs2t = mx_quantize_dual(g)
+    deq = lambda q, s: mx_dequantize_ref(q, s, -1, torch.float32)  # noqa: E731
+    xd, wd, gd = deq(xq1, xs1), deq(wq1, ws1).view(E, N, K), deq(gq1, gs1)
+    wtd = deq(wq2t, ws2t).view(K, E, N)       # weight blocked down its N rows, transposed
+    gtd, xtd = deq(gq2t, gs2t), deq(xq2t, xs2t)  # [N, T], [K, T]
+
+    y = mxfp8_grouped_gemm(xq1, xs1, wq1, ws1, offs, GROUP_B_ROWS, tile_n=tile_n).float()
+    dx = mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE, tile_n=tile_n).float()
+    dw = mxfp8_grouped_gemm(gq2t, gs2t, xq2t, xs2t, offs, GROUP_K, tile_n=tile_n).float().view(E, N, K)
+    torch.cuda.synchronize()
+    start = 0
+    for e, end in enumerate(offs.tolist()):
+        if end > start:
+            ref_y = xd[start:end] @ wd[e].t()
+            ref_dx = gd[start:end] @ wtd[:, e].t()
+            ref_dw = gtd[:, start:end] @ xtd[:, start:end].t()
+            for got, ref in ((y[start:end], ref_y), (dx[start:end], ref_dx), (dw[e], ref_dw)):
+                assert torch.allclose(got, ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+                assert (got - ref).pow(2).sum() < 1e-4 * ref.pow(2).sum()
+        else:
+            assert dw[e].abs().max() == 0  # an expert without rows gets a zero gradient, not stale memory
+        start = end
+    assert y[start:].abs().max() == 0 and dx[start:].abs().max() == 0  # padding rows are written as zeros
+
+
+@pytest.mark.gpu
+def test_aligned_grouped_mm_autograd_matches_the_loop_over_experts(cuda_device):
+    from titan_b200.lowp.mx_linear import mx_grouped_mm
+    from titan_b200.ops import _lib
+
+    torch.manual_seed(12)
+    E, N, K = 3, 256, 128
+    sizes = [128, 256, 0]
+    offs = torch.tensor(sizes, device="cuda").cumsum(0).to(torch.int32)
+    T = sum(sizes)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.1).requires_grad_()
+    g = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    before = _lib.launch_count()
+    y = mx_grouped_mm(x, w, offs, aligned=True)
+    y.backward(g)
+    assert _lib.launch_count() - before == 7  # 4 quantiser passes + 3 grouped GEMMs, whatever the number of experts
+    got = (y.detach().float(), x.grad.float(), w.grad.float())
+    x.grad = w.grad = None
+    y2 = mx_grouped_mm(x, w, offs)
+    y2.backward(g)
+    for a, b in zip(got, (y2.detach().float(), x.grad.float(), w.grad.float())):
+        assert (a - b).pow(2).sum() <= 1e-4 * b.pow(2).sum()

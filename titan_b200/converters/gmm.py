@@ -49,9 +49,9 @@ class FusedGroupedExperts(Module):
         w13, w2 = self._local(self.w13), self._local(self.w2)
         mx = getattr(self, "mx_round_mode", None)
         if mx is not None:  # MXFP8 experts: both GEMMs block-quantised along their contraction dims
-            h13 = self.mx_grouped_mm(xp, w13.to(xp.dtype), offs, mx)
+            h13 = self.mx_grouped_mm(xp, w13.to(xp.dtype), offs, mx, aligned=True)  # groups are 128-row multiples
             h = swiglu_fused(h13, scores, self.swiglu_limit)
-            return self.mx_grouped_mm(h, w2.to(xp.dtype), offs, mx)
+            return self.mx_grouped_mm(h, w2.to(xp.dtype), offs, mx, aligned=True)
         h13 = grouped_linear(xp, w13.to(xp.dtype), offs)
         h = swiglu_fused(h13, scores, self.swiglu_limit)
         return grouped_linear(h, w2.to(xp.dtype), offs)

@@ -131,6 +131,85 @@ __global__ void __launch_bounds__(256) mx_dequant_kernel(const uint8_t* __restri
     st16(out + e0, o);
   }
 }
+// Both layouts from ONE read: a CTA stages a [64 rows x 128 columns] tile in shared memory, then every thread quantises
+// one 1x32 block along the row (q1 [R, C], s1 [R, C/32]) and one 32x1 block down the rows, which it writes TRANSPOSED
+// (q2t [C, R], s2t [C, R/32]): the K-major operand a GEMM contracting over the rows wants (wgrad: tokens; dgrad: the
+// weight's output features), with no bf16 transpose copy in between.  Either output may be absent (null pointer).
+constexpr int DUAL_ROWS = 64, DUAL_COLS = 128, DUAL_STRIDE = DUAL_COLS + 8;  // +16 bytes per row: 16-byte aligned rows
+
+template <typename T>
+__global__ void __launch_bounds__(256) mx_quant_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__ q1,
+                                                            uint8_t* __restrict__ s1, uint8_t* __restrict__ q2t,
+                                                            uint8_t* __restrict__ s2t, long long rows, int cols,
+                                                            int rceil) {
+  __shared__ __align__(16) T tile[DUAL_ROWS * DUAL_STRIDE];
+  const int t = threadIdx.x;
+  const long long r0 = (long long)blockIdx.x * DUAL_ROWS;
+  const int c0 = blockIdx.y * DUAL_COLS;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int idx = j * 256 + t;
+    const int r = idx / 16, c8 = (idx % 16) * 8;
+    Vec16<T> v;
+    if (r0 + r < rows && c0 + c8 < cols) {
+      v = ld16(x + (r0 + r) * cols + c0 + c8);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v.v[i] = from_f<T>(0.f);
+    }
+    st16(tile + r * DUAL_STRIDE + c8, v);
+  }
+  __syncthreads();
+  if (q1 != nullptr) {
+    const int r = t / 4, blk = t % 4;
+    if (r0 + r < rows && c0 + blk * 32 < cols) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const Vec16<T> u = ld16(tile + r * DUAL_STRIDE + blk * 32 + j * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j * 8 + i] = to_f(u.v[i]);
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      const int e = block_exponent(amax, rceil);
+      const float inv = exp2f((float)-e);
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        packed[i] = (uint32_t)to_e4m3(v[4 * i] * inv) | ((uint32_t)to_e4m3(v[4 * i + 1] * inv) << 8) |
+                    ((uint32_t)to_e4m3(v[4 * i + 2] * inv) << 16) | ((uint32_t)to_e4m3(v[4 * i + 3] * inv) << 24);
+      uint4* dst = reinterpret_cast<uint4*>(q1 + (r0 + r) * cols + c0 + blk * 32);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      s1[(r0 + r) * (cols / 32) + c0 / 32 + blk] = (uint8_t)(e + 127);
+    }
+  }
+  if (q2t != nullptr) {
+    const int c = t % DUAL_COLS, rb = t / DUAL_COLS;
+    if (c0 + c < cols && r0 + rb * 32 < rows) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = to_f(tile[(rb * 32 + i) * DUAL_STRIDE + c]);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      const int e = block_exponent(amax, rceil);
+      const float inv = exp2f((float)-e);
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        packed[i] = (uint32_t)to_e4m3(v[4 * i] * inv) | ((uint32_t)to_e4m3(v[4 * i + 1] * inv) << 8) |
+                    ((uint32_t)to_e4m3(v[4 * i + 2] * inv) << 16) | ((uint32_t)to_e4m3(v[4 * i + 3] * inv) << 24);
+      // rows % 32 == 0 and r0 + rb * 32 is a multiple of 32: the 32-byte run is 16-byte aligned
+      uint4* dst = reinterpret_cast<uint4*>(q2t + (long long)(c0 + c) * rows + r0 + rb * 32);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      s2t[(long long)(c0 + c) * (rows / 32) + r0 / 32 + rb] = (uint8_t)(e + 127);
+    }
+  }
+}
 }  // namespace
 
 // x: [rows, cols] bf16 (dtype 1) or fp16 (dtype 2).  axis -1: cols % 32 == 0, scales [rows, cols/32].
@@ -173,6 +252,31 @@ TB_API int tb_mx_dequantize(const void* q, const void* scales, void* out, long l
   const int grid = (int)min((n8 + 255) / 256, (long long)148 * 16);
   mx_dequant_kernel<<<grid, 256, 0, st>>>((const uint8_t*)q, (const uint8_t*)scales, (__nv_bfloat16*)out, rows, cols,
                                           axis == -2 ? 1 : 0);
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+// One pass over x [rows, cols] (bf16 dtype 1 / fp16 dtype 2; rows % 32 == 0, cols % 32 == 0) producing
+//   q1 [rows, cols] e4m3 + s1 [rows, cols/32]   (blocks along the row), and / or
+//   q2t [cols, rows] e4m3 + s2t [cols, rows/32] (blocks down the rows, written transposed).
+// A null q1 or q2t skips that output.
+TB_API int tb_mx_quantize_dual(const void* x, void* q1, void* s1, void* q2t, void* s2t, long long rows, int cols,
+                               int round, int dtype, cudaStream_t st) {
+  if (rows == 0 || cols == 0) return 0;
+  if ((dtype != 1 && dtype != 2) || rows % 32 != 0 || cols % 32 != 0) return TB_ERR_ARG;
+  if ((q1 == nullptr) != (s1 == nullptr) || (q2t == nullptr) != (s2t == nullptr) || (q1 == nullptr && q2t == nullptr))
+    return TB_ERR_ARG;
+  const long long row_tiles = (rows + DUAL_ROWS - 1) / DUAL_ROWS;
+  const int col_tiles = (cols + DUAL_COLS - 1) / DUAL_COLS;
+  if (row_tiles > 0x7fffffffLL || col_tiles > 65535) return TB_ERR_ARG;
+  dim3 grid((unsigned)row_tiles, (unsigned)col_tiles);
+  if (dtype == 1)
+    mx_quant_dual_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)q1, (uint8_t*)s1,
+                                                              (uint8_t*)q2t, (uint8_t*)s2t, rows, cols, round);
+  else
+    mx_quant_dual_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, (uint8_t*)q1, (uint8_t*)s1, (uint8_t*)q2t,
+                                                       (uint8_t*)s2t, rows, cols, round);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

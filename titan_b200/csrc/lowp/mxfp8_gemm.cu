@@ -51,12 +51,41 @@ struct Cfg {
   static_assert(SF_TMEM_BASE + STAGES * SF_TMEM_PER_STAGE <= TMEM_COLS && NACC * XBN <= SF_TMEM_BASE, "TMEM budget");
 };
 
+// Grouped forms (rows of the token operand sorted by expert, every group a multiple of 128 rows, `offs` = cumulative
+// group ends on the device):
+//   GROUP_B_ROWS   C[T, N]   = A[T, K] . B[e]^T     B stacked by rows [E*N, K]: the tile's expert picks its B rows
+//   GROUP_B_SLICE  C[T, N]   = A[T, K] . B_e^T      B [N, E*K]: the expert picks a K-slice of B (a weight quantised
+//                                                   along its output features and transposed in one pass)
+//   GROUP_K        C[e][M,N] = A[M, T_e] . B[N, T_e]^T   the contraction runs over the expert's own token range
+// A tile whose contraction range is empty (rows past the last group; an expert without tokens) is written as zeros.
+enum XMode : int { X_PLAIN = 0, X_GROUP_B_ROWS = 1, X_GROUP_K = 2, X_GROUP_B_SLICE = 3 };
+
 struct XParams {
   int M, N, K;
   const uint8_t* sfa;  // [M/128][K/128][512]
-  const uint8_t* sfb;  // [N/128][K/128][512]
+  const uint8_t* sfb;  // [B rows/128][B stages][512]
   int* status;
+  int mode, groups;
+  const int* offs;     // [groups] cumulative row ends (multiples of 128)
 };
+
+struct XTile {
+  int m0, n0;      // tile origin inside one problem
+  int b_row;       // first B row of the tile
+  int b_ks;        // stage offset of B along its contraction dim
+  int c_row;       // first output row
+  int ks0, ks1;    // contraction stages [ks0, ks1)
+};
+
+// first group whose end lies above `row`, or `groups` when there is none
+__device__ __forceinline__ int group_of_row(const int* __restrict__ offs, int groups, int row) {
+  int lo = 0, hi = groups;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(offs + mid) > row) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
 
 // instruction descriptor of kind::mxf8f6f4 with block scaling: [4,6) B scale id | [7,10) A format (0 = e4m3) |
 // [10,13) B format | 15/16 A/B major (0 = K) | [17,23) N >> 3 | 23 scale format (1 = ue8m0) | [24,29) M >> 4 |
@@ -128,38 +157,56 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   const int num_m = p.M / BM, num_n = (p.N + XBN - 1) / XBN, kstages = p.K / XBK;
-  const int num_tiles = num_m * num_n;
+  const int tiles_per_problem = num_m * num_n;
+  const int num_tiles = p.mode == X_GROUP_K ? tiles_per_problem * p.groups : tiles_per_problem;
+  const int b_stages = p.mode == X_GROUP_B_SLICE ? kstages * p.groups : kstages;  // scale atoms per B row block
 
-  auto tile_of = [&](int t, int& m0, int& n0) {  // grouped raster: GROUP_M row tiles share their B columns in L2
+  auto tile_of = [&](int t) {  // grouped raster: GROUP_M row tiles share their B columns in L2
+    XTile ti;
+    const int problem = t / tiles_per_problem;
+    t -= problem * tiles_per_problem;
     const int per_group = GROUP_M * num_n;
     const int group = t / per_group, first_m = group * GROUP_M;
     const int gsize = min(num_m - first_m, GROUP_M);
     const int in_group = t - group * per_group;
-    m0 = (first_m + in_group % gsize) * BM;
-    n0 = (in_group / gsize) * XBN;
+    ti.m0 = (first_m + in_group % gsize) * BM;
+    ti.n0 = (in_group / gsize) * XBN;
+    ti.b_row = ti.n0; ti.b_ks = 0; ti.c_row = ti.m0; ti.ks0 = 0; ti.ks1 = kstages;
+    if (p.mode == X_GROUP_B_ROWS || p.mode == X_GROUP_B_SLICE) {
+      const int e = group_of_row(p.offs, p.groups, ti.m0);
+      if (e >= p.groups) ti.ks1 = 0;  // padding rows past the last group
+      else if (p.mode == X_GROUP_B_ROWS) ti.b_row = e * p.N + ti.n0;
+      else ti.b_ks = e * kstages;
+    } else if (p.mode == X_GROUP_K) {
+      const int begin = problem == 0 ? 0 : __ldg(p.offs + problem - 1);
+      const int end = __ldg(p.offs + problem);
+      ti.ks0 = min(max(begin / XBK, 0), kstages);
+      ti.ks1 = min(max(end / XBK, ti.ks0), kstages);
+      ti.c_row = problem * p.M + ti.m0;
+    }
+    return ti;
   };
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m0, n0;
-        tile_of(t, m0, n0);
+        const XTile ti = tile_of(t);
+        const int m0 = ti.m0, n0 = ti.n0;
         const bool second_b = C::B_ATOMS == 2 && n0 + 128 < p.N;  // the tile's upper 128 columns exist
-        for (int ks = 0; ks < kstages; ++ks) {
+        for (int ks = ti.ks0; ks < ti.ks1; ++ks) {
           if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
             ok = false; break;
           }
           mbar_expect_tx(&full_bar[stage], XA_STAGE + XB_STAGE + (second_b ? 3 : 2) * SF_ATOM);
           tma_load_2d(smem_a + stage * XA_STAGE, &tmap_a, &full_bar[stage], ks * XBK, m0);
-          tma_load_2d(smem_b + stage * XB_STAGE, &tmap_b, &full_bar[stage], ks * XBK, n0);
+          tma_load_2d(smem_b + stage * XB_STAGE, &tmap_b, &full_bar[stage], (ks + ti.b_ks) * XBK, ti.b_row);
           uint8_t* sf = smem_sf + stage * XSF_STAGE;
           bulk_g2s(sf, p.sfa + ((long long)(m0 / 128) * kstages + ks) * SF_ATOM, SF_ATOM, &full_bar[stage]);
-          bulk_g2s(sf + SF_ATOM, p.sfb + ((long long)(n0 / 128) * kstages + ks) * SF_ATOM, SF_ATOM, &full_bar[stage]);
-          if (second_b)
-            bulk_g2s(sf + 2 * SF_ATOM, p.sfb + ((long long)(n0 / 128 + 1) * kstages + ks) * SF_ATOM, SF_ATOM,
-                     &full_bar[stage]);
+          const uint8_t* sfb0 = p.sfb + ((long long)(ti.b_row / 128) * b_stages + ks + ti.b_ks) * SF_ATOM;
+          bulk_g2s(sf + SF_ATOM, sfb0, SF_ATOM, &full_bar[stage]);
+          if (second_b) bulk_g2s(sf + 2 * SF_ATOM, sfb0 + (long long)b_stages * SF_ATOM, SF_ATOM, &full_bar[stage]);
           if (++stage == XSTAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -169,12 +216,14 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const XTile ti = tile_of(t);
+        if (ti.ks0 >= ti.ks1) continue;  // nothing to contract: the epilogue writes zeros without an accumulator
         if (!wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_EMPTY); }
           break;
         }
         tc_fence_after();
-        for (int ks = 0; ks < kstages; ++ks) {
+        for (int ks = ti.ks0; ks < ti.ks1; ++ks) {
           if (!wait_bounded(&full_bar[stage], phase, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA); }
             ok = false; break;
@@ -194,7 +243,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, 2);
             const uint64_t db = make_smem_desc(sb + k * 32, 16, 1024, 2);
             umma_mxf8(tmem_base + acc * XBN, da, db, idesc_mxf8(BM, XBN, (uint32_t)k), sfa_t, sfb_t,
-                      (ks > 0 || k > 0) ? 1u : 0u);
+                      (ks > ti.ks0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == XSTAGES) { stage = 0; phase ^= 1; }
@@ -208,9 +257,10 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const bool issuer = warp == 2 && lane == 0;
     int acc = 0; uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      int m0, n0;
-      tile_of(t, m0, n0);
-      bool ok = wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
+      const XTile ti = tile_of(t);
+      const int n0 = ti.n0;
+      const bool zero_tile = ti.ks0 >= ti.ks1;  // uniform over the four epilogue warps
+      bool ok = zero_tile || wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
       if (!ok && lane == 0 && *abort_flag == 0) {
         *abort_flag = 1;
         if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL);
@@ -239,12 +289,17 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + (box * 2 + cc) * 32, r);
-          tmem_ld_wait();
           uint32_t pk[16];
+          if (zero_tile) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            for (int i = 0; i < 16; ++i) pk[i] = 0u;
+          } else {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + (box * 2 + cc) * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t chunk = (uint32_t)(cc * 4 + i) ^ (uint32_t)(row_in_tile & 7);  // 128B swizzle
@@ -253,7 +308,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                          : "memory");
           }
         }
-        if (box == XBN / 64 - 1) {  // all reads of the accumulator are done
+        if (!zero_tile && box == XBN / 64 - 1) {  // all reads of the accumulator are done
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
@@ -262,11 +317,11 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (issuer) {
           const int x = n0 + box * 64;
-          if (x < p.N) tma_store_2d(&tmap_c, smem_c, x, m0);
+          if (x < p.N) tma_store_2d(&tmap_c, smem_c, x, ti.c_row);
           tma_store_commit();
         }
       }
-      if (++acc == NACC) { acc = 0; acc_phase ^= 1; }
+      if (!zero_tile && ++acc == NACC) { acc = 0; acc_phase ^= 1; }
     }
     if (issuer) tma_store_wait_all<0>();
   }
@@ -295,13 +350,18 @@ int launch_x(const void* A, const void* B, void* C, const XParams& p, cudaStream
   if (int rc = tbh::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.K,
                                  BM, XBK, 3))
     return rc;
-  if (int rc = tbh::make_tmap_2d(&tb_, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.N, (uint64_t)p.K,
-                                 (uint64_t)p.K, XBN, XBK, 3))
+  const uint64_t g = p.mode == X_PLAIN ? 1 : (uint64_t)p.groups;
+  const uint64_t b_rows = p.mode == X_GROUP_B_ROWS ? g * p.N : (uint64_t)p.N;
+  const uint64_t b_cols = p.mode == X_GROUP_B_SLICE ? g * p.K : (uint64_t)p.K;
+  const uint64_t c_rows = p.mode == X_GROUP_K ? g * p.M : (uint64_t)p.M;
+  if (int rc = tbh::make_tmap_2d(&tb_, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_rows, b_cols, b_cols, XBN, XBK, 3))
     return rc;
-  if (int rc = tbh::make_tmap_2d(&tc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.M, (uint64_t)p.N,
+  if (int rc = tbh::make_tmap_2d(&tc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c_rows, (uint64_t)p.N,
                                  (uint64_t)p.N * 2, BM, 64, 3))
     return rc;
-  const int tiles = (p.M / BM) * ((p.N + XBN - 1) / XBN);
+  const long long tiles_ll = (long long)(p.M / BM) * ((p.N + XBN - 1) / XBN) * (p.mode == X_GROUP_K ? p.groups : 1);
+  if (tiles_ll > 0x7fffffffLL) return TB_ERR_ARG;
+  const int tiles = (int)tiles_ll;
   const int grid = tiles < sm_count_x() ? tiles : sm_count_x();
   TB_CUDA_CHECK(cudaFuncSetAttribute(mxfp8_gemm_kernel<XBN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg<XBN>::SMEM));
@@ -320,7 +380,28 @@ TB_API int tb_mxfp8_gemm(const void* A, const void* B, const void* sfa, const vo
   if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % 8 || K % XBK) return TB_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return TB_ERR_ARG;
   if (tile_n != 0 && tile_n != 128 && tile_n != 256) return TB_ERR_ARG;
-  XParams p{M, N, K, reinterpret_cast<const uint8_t*>(sfa), reinterpret_cast<const uint8_t*>(sfb), status};
+  XParams p{M, N, K, reinterpret_cast<const uint8_t*>(sfa), reinterpret_cast<const uint8_t*>(sfb), status, X_PLAIN, 1,
+            nullptr};
+  if (tile_n == 0) tile_n = 256;
+  return tile_n == 128 ? launch_x<128>(A, B, C, p, st) : launch_x<256>(A, B, C, p, st);
+}
+
+// Grouped block-scaled GEMMs over expert-sorted rows whose groups are multiples of 128 rows.  `offs` [groups] int32 on
+// the device: cumulative group ends.  M, N, K describe ONE problem; the operands are
+//   mode 1: A [M = all rows, K], B [groups*N, K] (N % 128 == 0),  C [M, N]
+//   mode 3: A [M = all rows, K], B [N, groups*K],                 C [M, N]
+//   mode 2: A [M, K = all rows], B [N, K],                        C [groups*M, N]   (contraction over each group's rows)
+// with scale atoms laid out like the operands: [rows/128][contraction stages][512].
+TB_API int tb_mxfp8_grouped_gemm(const void* A, const void* B, const void* sfa, const void* sfb, void* C, int M, int N,
+                                 int K, const int* offs, int groups, int mode, int tile_n, int* status,
+                                 cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % 8 || K % XBK || groups <= 0 || offs == nullptr) return TB_ERR_ARG;
+  if (mode != X_GROUP_B_ROWS && mode != X_GROUP_K && mode != X_GROUP_B_SLICE) return TB_ERR_ARG;
+  if (mode == X_GROUP_B_ROWS && N % 128) return TB_ERR_ARG;  // every expert's scale atoms start on a row block
+  if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return TB_ERR_ARG;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return TB_ERR_ARG;
+  XParams p{M, N, K, reinterpret_cast<const uint8_t*>(sfa), reinterpret_cast<const uint8_t*>(sfb), status, mode, groups,
+            offs};
   if (tile_n == 0) tile_n = 256;
   return tile_n == 128 ? launch_x<128>(A, B, C, p, st) : launch_x<256>(A, B, C, p, st);
 }

@@ -3,6 +3,9 @@
 * `mx_quantize(x, axis, round_mode)` → ``(q, scales)``: ``q`` has x's shape (float8_e4m3fn), ``scales`` is uint8 with
   the quantised axis divided by 32.  ``axis=-1`` blocks run along rows (the contraction dim of ``[M, K]``); ``axis=-2``
   blocks run down 32 consecutive rows (operands contracted over their first dim).
+* `mx_quantize_dual(x)` → ``(q1, s1, q2t, s2t)`` from ONE read of ``x [R, C]``: the row-blocked pair of ``axis=-1`` and
+  the column-blocked pair written TRANSPOSED (``q2t [C, R]``, ``s2t [C, R/32]``), i.e. the K-major operand of a GEMM
+  that contracts over R.  Forward and backward of an MX linear need both views of every operand.
 * `mx_dequantize(q, scales, axis)` → bf16 (exact: e4m3 × 2^e fits bf16).
 * round modes: ``"rceil"`` picks the smallest power of two that keeps the block maximum ≤ 448 (no clipping);
   ``"floor"`` is the OCP rule ``floor(log2 amax) − 8`` (the top of a block may saturate).
@@ -22,7 +25,8 @@ import torch
 
 from titan_b200.ops import _lib
 
-__all__ = ["mx_quantize", "mx_dequantize", "mx_quantize_ref", "mx_dequantize_ref", "mx_fake_quantize", "BLOCK", "sqnr"]
+__all__ = ["mx_quantize", "mx_dequantize", "mx_quantize_ref", "mx_dequantize_ref", "mx_fake_quantize", "BLOCK", "sqnr",
+           "mx_quantize_dual"]
 
 BLOCK = 32
 E4M3_MAX = 448.0
@@ -35,6 +39,7 @@ def _declare():
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         _lib.declare("tb_mx_quantize", [P, P, P, LL, I, I, I, I, P])
         _lib.declare("tb_mx_dequantize", [P, P, P, LL, I, I, P])
+        _lib.declare("tb_mx_quantize_dual", [P, P, P, P, P, LL, I, I, I, P])
         _DECLARED = True
 
 
@@ -95,6 +100,36 @@ def mx_quantize(x: torch.Tensor, axis: int = -1, round_mode: str = "rceil"):
                                    {"floor": 0, "rceil": 1}[round_mode], _lib.dtype_code(x.dtype), _lib.stream_ptr())
     _lib.check(rc, "mx_quantize")
     return q.view(torch.float8_e4m3fn), s
+
+
+def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool = True, transposed: bool = True):
+    """x [R, C] (R, C multiples of 32) → ``(q1 [R, C], s1 [R, C/32], q2t [C, R], s2t [C, R/32])``; a view that is not
+    asked for (``rows=False`` / ``transposed=False``) comes back as ``None, None``.  ``q2t, s2t`` equal
+    ``mx_quantize(x.t().contiguous(), -1)``.
+
+    Parity: `npu_dynamic_mx_quant_with_dual_axis` as used by experiments/ao_npu/torchao_npu/ops/mx_ops.py:62-194."""
+    if x.dim() != 2 or x.shape[0] % BLOCK or x.shape[1] % BLOCK:
+        raise ValueError(f"mx_quantize_dual wants a 2-D tensor with both dims multiples of {BLOCK}, got {tuple(x.shape)}")
+    if not (rows or transposed):
+        raise ValueError("mx_quantize_dual: ask for at least one view")
+    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)):
+        q1, s1 = mx_quantize_ref(x, -1, round_mode) if rows else (None, None)
+        q2t, s2t = mx_quantize_ref(x.t().contiguous(), -1, round_mode) if transposed else (None, None)
+        return q1, s1, q2t, s2t
+    _declare()
+    x = x.contiguous()
+    R, C = x.shape
+    u8 = dict(dtype=torch.uint8, device=x.device)
+    q1 = torch.empty(R, C, **u8) if rows else None
+    s1 = torch.empty(R, C // BLOCK, **u8) if rows else None
+    q2t = torch.empty(C, R, **u8) if transposed else None
+    s2t = torch.empty(C, R // BLOCK, **u8) if transposed else None
+    p = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+    rc = _lib.lib().tb_mx_quantize_dual(x.data_ptr(), p(q1), p(s1), p(q2t), p(s2t), R, C,
+                                        {"floor": 0, "rceil": 1}[round_mode], _lib.dtype_code(x.dtype), _lib.stream_ptr())
+    _lib.check(rc, "mx_quantize_dual")
+    f8 = lambda t: t.view(torch.float8_e4m3fn) if t is not None else None  # noqa: E731
+    return f8(q1), s1, f8(q2t), s2t
 
 
 def mx_dequantize(q: torch.Tensor, scales: torch.Tensor, axis: int = -1, dtype=torch.bfloat16):

@@ -12,6 +12,14 @@ same numbers through quantise-dequantise + a bf16 / fp32 matmul: the quantised o
 (e4m3 × 2^e), accumulation is fp32 either way.  Grouped experts (`mx_grouped_mm`) quantise per group along the token
 axis for wgrad.
 
+Quantise once.  When every dim is a multiple of 32, `MXFP8MM` reads each operand once per pass with the dual-axis
+kernel (`mx_quantize_dual`): the forward quantises ``x`` along K for its own GEMM and down the token rows, transposed,
+for wgrad, and saves ONLY that fp8 copy (1 byte + 1/32 per element instead of the bf16 activation: half the saved
+bytes, and no bf16 transpose in backward); the backward quantises ``g`` once into both views and the weight once into
+its transposed view.  The weight is saved by reference rather than as a second quantised copy, so an FSDP-sharded
+weight costs no unsharded bytes between forward and backward.  Parity for this form: `_MXQuantMM`
+(experiments/ao_npu/torchao_npu/ops/mx_ops.py:62-194), which saves quantised copies of both operands.
+
 Parity: `NpuMXFP8MM` (torchtitan_npu/patches/torchao_npu/mx_linear.py:26-100) and `NpuMXFP8GroupedMM`
 (patches/torchao_npu/mxfp8_grouped_mm.py:22-170).
 """
@@ -21,7 +29,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from titan_b200.lowp.mx import BLOCK, mx_fake_quantize, mx_quantize
+from titan_b200.lowp.mx import BLOCK, mx_dequantize, mx_fake_quantize, mx_quantize, mx_quantize_dual
 
 __all__ = ["mx_linear", "mx_grouped_mm", "MXFP8MM"]
 
@@ -59,6 +67,20 @@ def _mm(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
     return a @ b_t.t()
 
 
+def _gemm_q(aq, sa, bq, sb, dtype) -> torch.Tensor:
+    """``dequant(aq, sa) · dequant(bq, sb)ᵀ`` for operands already quantised along their shared last dim."""
+    if aq.is_cuda:
+        from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, mxfp8_gemm_supported
+
+        if mxfp8_gemm_supported(aq.shape[0], bq.shape[0], aq.shape[1]):
+            return mxfp8_gemm(aq, sa, bq, sb).to(dtype)
+    return _mm(mx_dequantize(aq, sa, -1, dtype), mx_dequantize(bq, sb, -1, dtype))
+
+
+def _once_ok(*dims: int) -> bool:
+    return all(d > 0 and d % BLOCK == 0 for d in dims)
+
+
 class MXFP8MM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, round_mode: str = "rceil"):
@@ -66,15 +88,36 @@ class MXFP8MM(torch.autograd.Function):
         if x2.dtype == torch.float32 and x2.is_cuda:
             x2 = x2.to(torch.bfloat16)
         wq = w.to(x2.dtype)
-        y = _mm_mx(x2, wq, round_mode)
-        ctx.save_for_backward(x2, wq)
         ctx.meta = (x.shape, x.dtype, w.dtype, round_mode)
+        ctx.once = _once_ok(x2.shape[0], x2.shape[1], w.shape[0])
+        if ctx.once:
+            xq1, xs1, xq2t, xs2t = mx_quantize_dual(x2.contiguous(), round_mode, transposed=ctx.needs_input_grad[1])
+            wq1, ws1, _, _ = mx_quantize_dual(wq.contiguous(), round_mode, transposed=False)
+            y = _gemm_q(xq1, xs1, wq1, ws1, x2.dtype)
+            ctx.compute_dtype = x2.dtype
+            ctx.save_for_backward(xq2t, xs2t, wq)
+        else:
+            y = _mm_mx(x2, wq, round_mode)
+            ctx.save_for_backward(x2, wq)
         return y.to(x.dtype).reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, g):
-        x2, w = ctx.saved_tensors
         shape, x_dt, w_dt, rm = ctx.meta
+        if ctx.once:
+            xq2t, xs2t, w = ctx.saved_tensors
+            dt = ctx.compute_dtype
+            need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+            g2 = g.reshape(-1, g.shape[-1]).to(dt).contiguous()
+            gq1, gs1, gq2t, gs2t = mx_quantize_dual(g2, rm, rows=need_dx, transposed=need_dw)
+            dx = dw = None
+            if need_dx:  # dx = g · w: contraction over N, the weight blocked down its N rows and read transposed
+                _, _, wq2t, ws2t = mx_quantize_dual(w.contiguous(), rm, rows=False)
+                dx = _gemm_q(gq1, gs1, wq2t, ws2t, dt).to(x_dt).reshape(shape)
+            if need_dw:  # dw = gᵀ · x: contraction over tokens, both operands blocked down the token rows
+                dw = _gemm_q(gq2t, gs2t, xq2t, xs2t, dt).to(w_dt)
+            return dx, dw, None
+        x2, w = ctx.saved_tensors
         g2 = g.reshape(-1, g.shape[-1]).to(x2.dtype)
         # dx = g · w: contraction over N → g blocked along its rows' N, w blocked down its N rows
         dx = _mm_mx(g2, w.t().contiguous(), rm)
@@ -86,6 +129,44 @@ class MXFP8MM(torch.autograd.Function):
 def mx_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, round_mode: str = "rceil"):
     y = MXFP8MM.apply(x, weight, round_mode)
     return y if bias is None else y + bias
+
+
+class _MXGroupedMMAligned(torch.autograd.Function):
+    """Grouped MXFP8 product over rows whose groups are multiples of 128 (the padded expert-major layout): three
+    launches of the grouped block-scaled GEMM, operands quantised once each by the dual-axis kernel, no host sync.
+    x [T, K], w [E, N, K], offs int32 [E] on the device → [T, N]; rows past the last group come back as zeros."""
+
+    @staticmethod
+    def forward(ctx, x, w, offs, round_mode):
+        from titan_b200.ops.mxfp8_gemm import GROUP_B_ROWS, mxfp8_grouped_gemm
+
+        E, N, K = w.shape
+        xq1, xs1, xq2t, xs2t = mx_quantize_dual(x.contiguous(), round_mode, transposed=ctx.needs_input_grad[1])
+        wq1, ws1, _, _ = mx_quantize_dual(w.reshape(E * N, K).contiguous(), round_mode, transposed=False)
+        ctx.save_for_backward(xq2t, xs2t, w, offs)
+        ctx.round_mode = round_mode
+        return mxfp8_grouped_gemm(xq1, xs1, wq1, ws1, offs, GROUP_B_ROWS).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        from titan_b200.ops.mxfp8_gemm import GROUP_B_SLICE, GROUP_K, mxfp8_grouped_gemm
+
+        xq2t, xs2t, w, offs = ctx.saved_tensors
+        E, N, K = w.shape
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gq1, gs1, gq2t, gs2t = mx_quantize_dual(g.contiguous(), ctx.round_mode, rows=need_dx, transposed=need_dw)
+        dx = dw = None
+        if need_dx:  # every expert's weight blocked down its N rows, transposed in the same pass: [K, E*N]
+            _, _, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K).contiguous(), ctx.round_mode, rows=False)
+            dx = mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE).to(g.dtype)
+        if need_dw:  # gᵀ [N, T] · xᵀ [K, T]ᵀ over each expert's own rows → [E*N, K]
+            dw = mxfp8_grouped_gemm(gq2t, gs2t, xq2t, xs2t, offs, GROUP_K).view(E, N, K).to(w.dtype)
+        return dx, dw, None, None
+
+
+def _aligned_ok(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and offs.is_cuda
+            and x.shape[0] % 128 == 0 and x.shape[0] > 0 and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0)
 
 
 class _MXGroupedMM(torch.autograd.Function):
@@ -124,6 +205,11 @@ class _MXGroupedMM(torch.autograd.Function):
         return dx, dw, None, None
 
 
-def mx_grouped_mm(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, round_mode: str = "rceil") -> torch.Tensor:
-    """Grouped MXFP8 GEMM: rows ``[offs[e-1], offs[e])`` of ``x`` go through ``w[e]ᵀ``."""
+def mx_grouped_mm(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, round_mode: str = "rceil", *,
+                  aligned: bool = False) -> torch.Tensor:
+    """Grouped MXFP8 GEMM: rows ``[offs[e-1], offs[e])`` of ``x`` go through ``w[e]ᵀ``.  ``aligned=True`` is the
+    caller's promise that every group is a multiple of 128 rows (the padded expert-major layout): on CUDA that form runs
+    as one grouped tensor-core launch per product instead of a loop over experts."""
+    if aligned and _aligned_ok(x, w, offs):
+        return _MXGroupedMMAligned.apply(x, w, offs.to(torch.int32), round_mode)
     return _MXGroupedMM.apply(x, w, offs, round_mode)

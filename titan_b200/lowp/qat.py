@@ -13,6 +13,11 @@ Quantisers (`weight_config.kind`):
                      (e2m1, 1×32) fake-quant pre-pass (``mxfp4_prepass=True``);
 * ``mxfp4``        – 1×32 blocks, e8m0 scale, e2m1 elements.
 
+``compute="real"`` (kinds ``mx`` and ``block_fp8``) goes one step further for the modules that own a matching weight:
+an `nn.Linear` runs `mx_linear` / `block_fp8_linear` and a grouped-experts module runs the grouped forms, i.e. real
+block-scaled FP8 GEMMs on the tensor cores with fp8 saved activations, instead of a bf16 GEMM on fake-quantised values.
+Filters may be two-argument ``(fqn, parameter)`` callables or the three-argument predicates of `lowp.filters`.
+
 Parity: the experimental `torchao_npu` package of the reference (experiments/ao_npu/torchao_npu/configs.py,
 quantization/quant_configs.py:24-104, quant_primitives/{mx,block_fp8}.py, wrapper_tensors/*.py): its tensor-subclass
 wrappers become parametrisations here, which FSDP2 and DCP handle without extra hooks because the stored parameter
@@ -133,9 +138,10 @@ class ParamSwapConfig:
     step: str = "prepare"  # prepare | convert
     weight_config: QuantizeConfig = field(default_factory=QuantizeConfig)
     activation_config: QuantizeConfig | None = None
-    params_filter_fn: Callable[[str, nn.Parameter], bool] | None = None
-    """(fully qualified parameter name, parameter) → quantise it?  Default: every ≥2-D ``weight`` / expert matrix
-    outside embeddings, norms and the output projection."""
+    params_filter_fn: Callable[..., bool] | None = None
+    """(fully qualified parameter name, parameter[, owning module]) → quantise it?  Default: every ≥2-D ``weight`` /
+    expert matrix outside embeddings, norms and the output projection."""
+    compute: str = "fake"  # fake: quantise-dequantise + bf16 GEMM | real: block-scaled FP8 GEMMs (mx, block_fp8)
 
 
 def _default_filter(name: str, p: nn.Parameter) -> bool:
@@ -145,11 +151,83 @@ def _default_filter(name: str, p: nn.Parameter) -> bool:
     return leaf in ("weight", "w1", "w2", "w3", "w13")
 
 
+def _local(t):
+    return t.to_local() if t is not None and hasattr(t, "to_local") else t
+
+
+def _install_real(mod: nn.Module, wcfg: QuantizeConfig) -> bool:
+    """Route ``mod``'s own GEMMs through real low-precision kernels; False when the module type has no such form."""
+    import types
+
+    from titan_b200.lowp.block_fp8 import block_fp8_grouped_mm, block_fp8_linear
+    from titan_b200.lowp.mx_linear import mx_grouped_mm, mx_linear
+
+    rm, pre = wcfg.round_mode, wcfg.mxfp4_prepass
+    if isinstance(mod, nn.Linear):
+        if wcfg.kind == "mx":
+            fwd = lambda self_, x: mx_linear(x, _local(self_.weight), _local(self_.bias), rm)  # noqa: E731
+        else:
+            fwd = lambda self_, x: block_fp8_linear(x, _local(self_.weight), _local(self_.bias), round_mode=rm,  # noqa: E731
+                                                    mxfp4_prepass=pre)
+        mod._lowp_plain_forward = mod.__dict__.get("forward")
+        mod.forward = types.MethodType(fwd, mod)
+    elif hasattr(mod, "w2") and (hasattr(mod, "w13") or hasattr(mod, "w1")) and hasattr(mod, "num_experts"):
+        mod.mx_round_mode = rm  # grouped experts consult this flag and call the function stored beside it
+        if wcfg.kind == "mx":
+            mod.mx_grouped_mm = mx_grouped_mm
+        else:
+            mod.mx_grouped_mm = lambda x, w, offs, r, aligned=False: block_fp8_grouped_mm(  # noqa: E731
+                x, w, offs, round_mode=r, mxfp4_prepass=pre)
+    else:
+        return False
+    mod._lowp_real = wcfg
+    return True
+
+
+def _remove_real(mod: nn.Module) -> list[str]:
+    """Bake the quantised values into the weights of a module converted by `_install_real` and restore its forward."""
+    wcfg = mod._lowp_real
+    names = []
+    with torch.no_grad():
+        for pname, p in mod.named_parameters(recurse=False):
+            if p.dim() >= 2:
+                local = _local(p)
+                local.copy_(fake_quantize(local, wcfg))
+                names.append(pname)
+    if isinstance(mod, nn.Linear):
+        if mod.__dict__.get("_lowp_plain_forward") is None:
+            mod.__dict__.pop("forward", None)
+        else:
+            mod.forward = mod._lowp_plain_forward
+        mod.__dict__.pop("_lowp_plain_forward", None)
+    else:
+        for attr in ("mx_round_mode", "mx_grouped_mm"):
+            mod.__dict__.pop(attr, None)
+    del mod._lowp_real
+    return names
+
+
 def quantize_params(model: nn.Module, cfg: ParamSwapConfig) -> list[str]:
     """Install (``prepare``) or bake-and-remove (``convert``) the quantising wrappers; returns the affected names."""
-    keep = cfg.params_filter_fn or _default_filter
+    from titan_b200.lowp.filters import call_filter
+
+    user = cfg.params_filter_fn
+    if cfg.compute not in ("fake", "real"):
+        raise ValueError(f"ParamSwapConfig.compute must be 'fake' or 'real', got {cfg.compute!r}")
+    if cfg.compute == "real" and cfg.weight_config.kind not in ("mx", "block_fp8"):
+        raise ValueError("compute='real' exists for the 'mx' and 'block_fp8' quantisers")
     touched = []
     for mod_name, mod in list(model.named_modules()):
+        keep = (lambda fq, p, _m=mod: call_filter(user, fq, p, _m)) if user is not None else _default_filter
+        if cfg.step == "convert" and hasattr(mod, "_lowp_real"):
+            touched += [f"{mod_name}.{n}" if mod_name else n for n in _remove_real(mod)]
+            continue
+        if cfg.step == "prepare" and cfg.compute == "real":
+            own = [(n, p) for n, p in mod.named_parameters(recurse=False)
+                   if keep(f"{mod_name}.{n}" if mod_name else n, p)]
+            if own and not hasattr(mod, "_lowp_real") and _install_real(mod, cfg.weight_config):
+                touched += [f"{mod_name}.{n}" if mod_name else n for n, _ in own]
+            continue
         for pname, p in list(mod.named_parameters(recurse=False)):
             fq = f"{mod_name}.{pname}" if mod_name else pname
             if cfg.step == "prepare":
@@ -191,7 +269,7 @@ class QuantizeConverter(ModelConverter):
     def convert(self, model: nn.Module) -> None:
         base = self.config.base_config
         if self.config.filter_fn is not None:
-            base = ParamSwapConfig(step=base.step, weight_config=base.weight_config,
+            base = ParamSwapConfig(step=base.step, weight_config=base.weight_config, compute=base.compute,
                                    activation_config=base.activation_config, params_filter_fn=self.config.filter_fn)
         self.converted = quantize_params(model, base)
         if not self.converted:

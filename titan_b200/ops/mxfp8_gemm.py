@@ -4,6 +4,12 @@
 `pack_scale_atoms` lays the ``[rows, K/32]`` scale bytes out the way the kernel's `tcgen05.cp` wants them: atoms of
 128 rows × 4 K-blocks (512 bytes, byte ``(row % 32)·16 + (row // 32 % 4)·4 + block % 4``), stored ``[row block][K/128]``.
 
+`mxfp8_grouped_gemm` runs the three products of a grouped-experts layer over expert-sorted rows (groups padded to
+multiples of 128 rows, cumulative ends on the device) as ONE launch each, with no host synchronisation:
+``GROUP_B_ROWS`` (forward: the tile's expert picks its rows of the stacked weight), ``GROUP_B_SLICE`` (input gradient:
+the expert picks a contraction slice of the transposed weight) and ``GROUP_K`` (weight gradient: the contraction runs
+over the expert's own rows).
+
 Parity: `npu_quant_matmul` with MX scales as used by torchtitan_npu/patches/torchao_npu/mx_linear.py:26-100.
 """
 
@@ -15,7 +21,10 @@ import torch
 
 from titan_b200.ops import _lib
 
-__all__ = ["pack_scale_atoms", "mxfp8_gemm", "mxfp8_gemm_supported", "mxfp8_gemm_ref"]
+__all__ = ["pack_scale_atoms", "mxfp8_gemm", "mxfp8_gemm_supported", "mxfp8_gemm_ref", "mxfp8_grouped_gemm",
+           "GROUP_B_ROWS", "GROUP_K", "GROUP_B_SLICE"]
+
+GROUP_B_ROWS, GROUP_K, GROUP_B_SLICE = 1, 2, 3
 
 _DECLARED = False
 
@@ -69,3 +78,48 @@ def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.T
                                   int(tile_n), _lib.shared_status().ptr, _lib.stream_ptr())
     _lib.check(rc, "mxfp8_gemm")
     return out
+
+
+def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor, offs: torch.Tensor,
+                       mode: int, *, tile_n: int = 0) -> torch.Tensor:
+    """Grouped block-scaled GEMM; ``offs`` int32 [E] on the device, cumulative group ends, every group a multiple of
+    128 rows.  Operands are quantised along their last dim, scales ``[rows, last/32]`` uint8 (packed here).
+
+    * ``GROUP_B_ROWS``:  aq [T, K], bq [E*N, K]  → [T, N]     (N % 128 == 0)
+    * ``GROUP_B_SLICE``: aq [T, K], bq [N, E*K]  → [T, N]
+    * ``GROUP_K``:       aq [M, T], bq [N, T]    → [E*M, N]   (contraction over each group's rows)
+
+    Rows of the output past the last group, and the weight gradient of an expert without rows, are zeros."""
+    global _GROUPED_DECLARED
+    E = offs.numel()
+    if offs.dtype != torch.int32 or not offs.is_cuda:
+        raise ValueError("mxfp8_grouped_gemm: offs must be an int32 tensor on the device")
+    M, K = aq.shape
+    if mode == GROUP_B_ROWS:
+        N, rows_out = bq.shape[0] // E, M
+        ok = bq.shape[0] == E * N and bq.shape[1] == K and N % 128 == 0
+    elif mode == GROUP_B_SLICE:
+        N, rows_out = bq.shape[0], M
+        ok = bq.shape[1] == E * K
+    elif mode == GROUP_K:
+        N, rows_out = bq.shape[0], E * M
+        ok = bq.shape[1] == K
+    else:
+        raise ValueError(f"mxfp8_grouped_gemm: unknown mode {mode}")
+    if not (ok and aq.is_cuda and mxfp8_gemm_supported(M, N, K)):
+        raise ValueError(f"mxfp8_grouped_gemm: unsupported problem mode={mode} A={tuple(aq.shape)} B={tuple(bq.shape)} E={E}")
+    if not _GROUPED_DECLARED:
+        P, I = ctypes.c_void_p, ctypes.c_int
+        _lib.declare("tb_mxfp8_grouped_gemm", [P, P, P, P, P, I, I, I, P, I, I, I, P, P])
+        _GROUPED_DECLARED = True
+    sa, sb = pack_scale_atoms(sa), pack_scale_atoms(sb)
+    aq, bq = aq.contiguous(), bq.contiguous()
+    out = torch.empty(rows_out, N, dtype=torch.bfloat16, device=aq.device)
+    rc = _lib.lib().tb_mxfp8_grouped_gemm(aq.data_ptr(), bq.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(),
+                                          M, N, K, offs.data_ptr(), E, int(mode), int(tile_n),
+                                          _lib.shared_status().ptr, _lib.stream_ptr())
+    _lib.check(rc, "mxfp8_grouped_gemm")
+    return out
+
+
+_GROUPED_DECLARED = False
