@@ -239,6 +239,29 @@ def bench_lowp(iters):
              bf16_linear_ms=bf_ms, bf16_linear_tflops=6.0 * T_ * N * K / bf_ms / 1e9, speedup=bf_ms / mx_ms)
 
 
+    # grouped experts (DeepSeek 16B shapes: 49152 routed rows, 8 local experts): one grouped block-scaled launch per
+    # product against the bf16 grouped GEMM of the padded path
+    from titan_b200.lowp.mx_linear import mx_grouped_mm
+    from titan_b200.ops.moe import grouped_linear
+
+    E, rows = 8, 49152
+    offs = torch.full((E,), rows // E, device="cuda", dtype=torch.int32).cumsum(0).to(torch.int32)
+    for N, K in [(2816, 2048), (2048, 1408)]:
+        x = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        w = (torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.02).requires_grad_()
+        g = torch.randn(rows, N, device="cuda", dtype=torch.bfloat16)
+
+        def gstep(fn):
+            x.grad = w.grad = None
+            fn().backward(g)
+
+        mx_ms = timeit(lambda: gstep(lambda: mx_grouped_mm(x, w, offs, aligned=True)), iters)
+        bf_ms = timeit(lambda: gstep(lambda: grouped_linear(x, w, offs)), iters)
+        fl = 6.0 * rows * N * K
+        emit(kernel="mx_grouped_mm_fwd_bwd", shape=[rows, E, N, K], ms=mx_ms, tflops=fl / mx_ms / 1e9,
+             bf16_grouped_ms=bf_ms, bf16_grouped_tflops=fl / bf_ms / 1e9, speedup=bf_ms / mx_ms)
+
+
 def bench_sparse(iters):
     """Kernels of the dense form of sparse attention: masked softmax (forward / backward) and the indexer-score
     backward, with the bytes they must move against the measured copy bandwidth."""
@@ -342,6 +365,13 @@ def profile_case(name: str, launches: int = 3) -> None:
             rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dscore.data_ptr(), w.data_ptr(), dx.data_ptr(),
                                                 dw.data_ptr(), sc * heads, heads, keys, 1, _lib.stream_ptr())
             _lib.check(rc, "indexer_relu_bwd")
+    elif name == "mx_quantize_dual":
+        from titan_b200.lowp.mx import mx_quantize_dual
+
+        x = torch.randn(16384, 4096, device=dev, dtype=bf)  # 134 MB in, 138 MB out
+
+        def fn():
+            mx_quantize_dual(x)
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     for _ in range(launches):

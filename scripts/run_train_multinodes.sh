@@ -10,16 +10,28 @@
 # (reference: scripts/run_train_multinodes.sh:20-75)
 set -euo pipefail
 
-export NCCL_SOCKET_IFNAME=${NCCL_SOCKET_IFNAME:-$(ip -o -4 addr show scope global | awk '$2 != "docker0" {print $2; exit}')}
-export GLOO_SOCKET_IFNAME=${GLOO_SOCKET_IFNAME:-${NCCL_SOCKET_IFNAME}}
+# COMM_MODE=fake_backend: one process, no rendezvous: builds the model for the full world size and runs one step on
+# fake collectives (a dry run of the recipe and of the command line).
+if [ -n "${COMM_MODE:-}" ]; then
+    cd "$(dirname "$0")/.."
+    NGPU="${NGPU:-8}" LOCAL_RANK=0 exec python -m "${TRAIN_FILE:-titan_b200.entry}" \
+        --module "${MODULE:-deepseek_v32}" --config "${CONFIG:-deepseek_v32_671b_61layers_4k}" \
+        --comm.mode="${COMM_MODE}" --training.steps=1 "$@"
+fi
+
+if command -v ip > /dev/null 2>&1; then
+    export NCCL_SOCKET_IFNAME=${NCCL_SOCKET_IFNAME:-$(ip -o -4 addr show scope global | awk '$2 != "docker0" {print $2; exit}')}
+    LOCAL_HOST=${LOCAL_HOST:-$(ip addr show "${NCCL_SOCKET_IFNAME}" | grep "inet " | awk '{print $2}' | cut -d'/' -f1 | head -n1)}
+fi
+[ -n "${NCCL_SOCKET_IFNAME:-}" ] && export GLOO_SOCKET_IFNAME=${GLOO_SOCKET_IFNAME:-${NCCL_SOCKET_IFNAME}}
 export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:True}
 export CUDA_DEVICE_MAX_CONNECTIONS=${CUDA_DEVICE_MAX_CONNECTIONS:-1}
 export TORCH_NCCL_AVOID_RECORD_STREAMS=1
 export LOG_RANK=${LOG_RANK:-0}
 export PYTHONUNBUFFERED=1
 
-LOCAL_HOST=${LOCAL_HOST:-$(ip addr show "${NCCL_SOCKET_IFNAME}" | grep "inet " | awk '{print $2}' | cut -d'/' -f1 | head -n1)}
-LOCAL_HOST=${LOCAL_HOST:-$(hostname -I | awk '{print $1}')}
+LOCAL_HOST=${LOCAL_HOST:-$(hostname -I 2> /dev/null | awk '{print $1}')}
+LOCAL_HOST=${LOCAL_HOST:-127.0.0.1}
 if [[ -n "${NODE_IPS:-}" ]]; then
     read -r -a IPs <<< "${NODE_IPS//,/ }"
 else

@@ -1,4 +1,5 @@
 import dataclasses
+import os
 
 import pytest
 
@@ -67,3 +68,37 @@ def test_to_dict_is_plain():
     d = configs.TrainerConfig().to_dict()
     assert d["training"]["seq_len"] == 2048 and isinstance(d["profiling"]["profile_ranks"], list)
     assert dataclasses.is_dataclass(configs.TrainerConfig())
+
+
+def test_union_sections_switch_with_a_variant_token():
+    from titan_b200.config.configs import ChatDataLoaderConfig, DSV4EncoderConfig
+    from titan_b200.config.manager import ConfigManager
+
+    cfg = ConfigManager().parse_args([
+        "--module", "deepseek_v4", "--config", "debug_deepseek_v4_single_node_1b", "--training.seq_len", "1152",
+        "dataloader:chat_data_loader_config", "--dataloader.dataset_path", "parquet", "--dataloader.data_files", "a.parquet",
+        "dataloader.chat_encoder:dsv4_encoder_config", "--dataloader.chat_encoder.mode", "thinking"])
+    assert isinstance(cfg.dataloader, ChatDataLoaderConfig) and cfg.dataloader.data_files == "a.parquet"
+    assert isinstance(cfg.dataloader.chat_encoder, DSV4EncoderConfig) and cfg.dataloader.chat_encoder.mode == "thinking"
+    with pytest.raises(SystemExit):
+        ConfigManager().parse_args(["--module", "llama3", "--config", "llama3_debugmodel", "dataloader:no_such_loader"])
+
+
+def test_example_scripts_parse_with_the_real_config_parser(tmp_path):
+    """Every example launcher runs through the launch scripts with the validator in place of the trainer."""
+    import glob
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    assets = tmp_path / "hf"
+    assets.mkdir()
+    (assets / "tokenizer.json").write_text("{}")
+    env = dict(os.environ, TRAIN_FILE="titan_b200.config.validate", COMM_MODE="fake_backend", NGPU="8",
+               HF_ASSETS_PATH=str(assets), HF_CKPT=str(assets), DATA_FILES="x.parquet", NODE_RANK="0", NNODES="1",
+               PYTHONPATH=root)
+    scripts = sorted(glob.glob(os.path.join(root, "examples", "*", "*.sh")))
+    assert len(scripts) >= 10
+    for sh in scripts:
+        out = subprocess.run(["bash", sh], env=env, capture_output=True, text=True, cwd=str(tmp_path))
+        assert out.returncode == 0, f"{sh}:\n{out.stdout[-2000:]}\n{out.stderr[-2000:]}"
+        assert '"_type": "TrainerConfig"' in out.stdout, sh

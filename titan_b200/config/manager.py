@@ -7,6 +7,13 @@ full import path) whose ``config_registry`` module defines recipe functions;
 fields.  Booleans accept ``--section.flag`` / ``--section.no-flag``; list fields
 take comma-separated values; hyphens and underscores are interchangeable.
 
+A field whose type is a union of config classes (the data loader: text, chat,
+synthetic or multimodal; the chat encoder) is switched with a bare
+``section:variant`` token, the variant being the class name in snake case
+(``dataloader:chat_data_loader_config``); the section is replaced by that
+class's defaults and later ``--section.field`` overrides apply to it, so put
+the token before them.
+
 Parity: launch path of the reference (torchtitan_npu/entry.py:31-32,
 scripts/run_train.sh:25-39, docs/feature_guides/checkpoint.md:62-73).
 """
@@ -128,11 +135,35 @@ def _lookup(cfg, dotted: str):
     raise KeyError(f"unknown config field --{dotted} (section has {sorted(types_)})")
 
 
+def _snake(name: str) -> str:
+    import re
+
+    return re.sub(r"(?<=[a-z0-9])(?=[A-Z])|(?<=[A-Z])(?=[A-Z][a-z])", "_", name).lower()
+
+
+def _switch_variant(cfg, token: str) -> None:
+    """``section[.sub]:variant`` → replace that field with the defaults of the named member of its union type."""
+    dotted, _, variant = token.partition(":")
+    owner, name, tp, negated = _lookup(cfg, dotted)
+    alts, _ = _strip_optional(tp)
+    classes = [a for a in alts if isinstance(a, type) and is_dataclass(a)]
+    want = variant.replace("-", "_").lower()
+    for cls in classes:
+        if _snake(cls.__name__) == want or cls.__name__.lower() == want:
+            setattr(owner, name, cls())
+            return
+    raise SystemExit(f"{token!r}: --{dotted} takes one of {[_snake(c.__name__) for c in classes]}")
+
+
 def apply_overrides(cfg: TrainerConfig, argv: list[str]) -> TrainerConfig:
-    """Apply ``--a.b value`` / ``--a.b=value`` / ``--a.flag`` / ``--a.no-flag`` in place."""
+    """Apply ``--a.b value`` / ``--a.b=value`` / ``--a.flag`` / ``--a.no-flag`` / ``a:variant`` in place."""
     i = 0
     while i < len(argv):
         tok = argv[i]
+        if not tok.startswith("--") and ":" in tok:
+            _switch_variant(cfg, tok)
+            i += 1
+            continue
         if not tok.startswith("--"):
             raise SystemExit(f"unexpected argument {tok!r}")
         key, eq, val = tok[2:].partition("=")

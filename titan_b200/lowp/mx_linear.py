@@ -134,18 +134,25 @@ def mx_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None =
 class _MXGroupedMMAligned(torch.autograd.Function):
     """Grouped MXFP8 product over rows whose groups are multiples of 128 (the padded expert-major layout): three
     launches of the grouped block-scaled GEMM, operands quantised once each by the dual-axis kernel, no host sync.
-    x [T, K], w [E, N, K], offs int32 [E] on the device → [T, N]; rows past the last group come back as zeros."""
+    x [T, K], w [E, N, K], offs int32 [E] on the device → [T, N]; rows past the last group come back as zeros.  The
+    buffer may have a ragged tail (capacity that is not a multiple of 128): the last group ends on a multiple of 128, so
+    those rows are never routed to and only need a defined value."""
 
     @staticmethod
     def forward(ctx, x, w, offs, round_mode):
         from titan_b200.ops.mxfp8_gemm import GROUP_B_ROWS, mxfp8_grouped_gemm
 
         E, N, K = w.shape
-        xq1, xs1, xq2t, xs2t = mx_quantize_dual(x.contiguous(), round_mode, transposed=ctx.needs_input_grad[1])
+        T = x.shape[0]
+        used = T // 128 * 128
+        xq1, xs1, xq2t, xs2t = mx_quantize_dual(x[:used].contiguous(), round_mode, transposed=ctx.needs_input_grad[1])
         wq1, ws1, _, _ = mx_quantize_dual(w.reshape(E * N, K).contiguous(), round_mode, transposed=False)
         ctx.save_for_backward(xq2t, xs2t, w, offs)
-        ctx.round_mode = round_mode
-        return mxfp8_grouped_gemm(xq1, xs1, wq1, ws1, offs, GROUP_B_ROWS).to(x.dtype)
+        ctx.round_mode, ctx.rows = round_mode, T
+        y = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        if used < T:
+            y[used:].zero_()
+        return mxfp8_grouped_gemm(xq1, xs1, wq1, ws1, offs, GROUP_B_ROWS, out=y)
 
     @staticmethod
     def backward(ctx, g):
@@ -153,12 +160,18 @@ class _MXGroupedMMAligned(torch.autograd.Function):
 
         xq2t, xs2t, w, offs = ctx.saved_tensors
         E, N, K = w.shape
+        T = ctx.rows
+        used = T // 128 * 128
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        gq1, gs1, gq2t, gs2t = mx_quantize_dual(g.contiguous(), ctx.round_mode, rows=need_dx, transposed=need_dw)
+        gq1, gs1, gq2t, gs2t = mx_quantize_dual(g[:used].contiguous(), ctx.round_mode, rows=need_dx,
+                                                transposed=need_dw)
         dx = dw = None
         if need_dx:  # every expert's weight blocked down its N rows, transposed in the same pass: [K, E*N]
             _, _, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K).contiguous(), ctx.round_mode, rows=False)
-            dx = mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE).to(g.dtype)
+            dx = torch.empty(T, K, dtype=torch.bfloat16, device=g.device)
+            if used < T:
+                dx[used:].zero_()
+            mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE, out=dx)
         if need_dw:  # gᵀ [N, T] · xᵀ [K, T]ᵀ over each expert's own rows → [E*N, K]
             dw = mxfp8_grouped_gemm(gq2t, gs2t, xq2t, xs2t, offs, GROUP_K).view(E, N, K).to(w.dtype)
         return dx, dw, None, None
@@ -166,7 +179,7 @@ class _MXGroupedMMAligned(torch.autograd.Function):
 
 def _aligned_ok(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor) -> bool:
     return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and offs.is_cuda
-            and x.shape[0] % 128 == 0 and x.shape[0] > 0 and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0)
+            and x.shape[0] >= 128 and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0)
 
 
 class _MXGroupedMM(torch.autograd.Function):

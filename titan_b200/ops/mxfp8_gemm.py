@@ -81,7 +81,7 @@ def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.T
 
 
 def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor, offs: torch.Tensor,
-                       mode: int, *, tile_n: int = 0) -> torch.Tensor:
+                       mode: int, *, tile_n: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
     """Grouped block-scaled GEMM; ``offs`` int32 [E] on the device, cumulative group ends, every group a multiple of
     128 rows.  Operands are quantised along their last dim, scales ``[rows, last/32]`` uint8 (packed here).
 
@@ -89,7 +89,8 @@ def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb:
     * ``GROUP_B_SLICE``: aq [T, K], bq [N, E*K]  → [T, N]
     * ``GROUP_K``:       aq [M, T], bq [N, T]    → [E*M, N]   (contraction over each group's rows)
 
-    Rows of the output past the last group, and the weight gradient of an expert without rows, are zeros."""
+    Rows of the output past the last group, and the weight gradient of an expert without rows, are zeros.  ``out``
+    (bf16, contiguous, at least as many rows as the result) receives the result in its leading rows."""
     global _GROUPED_DECLARED
     E = offs.numel()
     if offs.dtype != torch.int32 or not offs.is_cuda:
@@ -114,7 +115,11 @@ def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb:
         _GROUPED_DECLARED = True
     sa, sb = pack_scale_atoms(sa), pack_scale_atoms(sb)
     aq, bq = aq.contiguous(), bq.contiguous()
-    out = torch.empty(rows_out, N, dtype=torch.bfloat16, device=aq.device)
+    if out is None:
+        out = torch.empty(rows_out, N, dtype=torch.bfloat16, device=aq.device)
+    elif not (out.dtype == torch.bfloat16 and out.is_contiguous() and out.dim() == 2 and out.shape[1] == N
+              and out.shape[0] >= rows_out and out.device == aq.device):
+        raise ValueError("mxfp8_grouped_gemm: `out` must be a contiguous bf16 [>= rows, N] tensor on the same device")
     rc = _lib.lib().tb_mxfp8_grouped_gemm(aq.data_ptr(), bq.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(),
                                           M, N, K, offs.data_ptr(), E, int(mode), int(tile_n),
                                           _lib.shared_status().ptr, _lib.stream_ptr())
