@@ -201,7 +201,7 @@ def test_mx_linear_on_gpu_uses_kernels(cuda_device):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(256, 512), (96, 160), (64, 4096)])
+@pytest.mark.parametrize("shape", [(256, 512), (96, 160), (64, 4096), (384, 128)])
 @pytest.mark.parametrize("round_mode", ["rceil", "floor"])
 def test_mx_dual_axis_kernel_matches_both_single_axis_references(shape, round_mode, cuda_device):
     torch.manual_seed(6)
@@ -215,6 +215,12 @@ def test_mx_dual_axis_kernel_matches_both_single_axis_references(shape, round_mo
     assert torch.equal(s2t, st) and torch.equal(q2t.view(torch.uint8), qt.view(torch.uint8))
     only_t = mx_quantize_dual(x, round_mode, rows=False)
     assert only_t[0] is None and torch.equal(only_t[2].view(torch.uint8), qt.view(torch.uint8))
+    if R % 128 == 0 and C % 128 == 0:  # scales straight in the GEMM's atom order
+        from titan_b200.ops.mxfp8_gemm import pack_scale_atoms
+
+        a1, p1, a2, p2 = mx_quantize_dual(x, round_mode, atoms=True)
+        assert torch.equal(a1.view(torch.uint8), qr.view(torch.uint8)) and torch.equal(p1, pack_scale_atoms(sr))
+        assert torch.equal(a2.view(torch.uint8), qt.view(torch.uint8)) and torch.equal(p2, pack_scale_atoms(st))
 
 
 def test_block_fp8_linear_reuses_one_weight_quantisation_for_forward_and_dgrad():

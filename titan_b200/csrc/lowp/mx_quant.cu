@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(DUAL_THREADS) mx_quant_dual_kernel(const T* __
                                                                      uint8_t* __restrict__ s1,
                                                                      uint8_t* __restrict__ q2t,
                                                                      uint8_t* __restrict__ s2t, long long rows,
-                                                                     int cols, int rceil) {
+                                                                     int cols, int rceil, int atoms) {
   using P2 = typename Pair<T>::type;
   __shared__ __align__(16) uint8_t smem[DUAL_SMEM];
   __shared__ uint32_t s1_stage[DUAL_ROWS], s2_stage[DUAL_COLS];  // 4 scale bytes per tile row / tile column
@@ -284,7 +284,14 @@ __global__ void __launch_bounds__(DUAL_THREADS) mx_quant_dual_kernel(const T* __
         *reinterpret_cast<uint4*>(q1 + (r0 + r) * cols + c0 + ch * 16) =
             reinterpret_cast<const uint4*>(q1_stage + r * DUAL_COLS)[ch ^ (r & 7)];
     }
-    if (t < DUAL_ROWS && r0 + t < rows) {
+    if (atoms) {
+      // the tile's 128 rows x 4 blocks are exactly one 512-byte scale atom of the block-scaled GEMM:
+      // byte (row % 32) * 16 + (row / 32) * 4 + block, atoms stored [row block][column block]
+      if (t < DUAL_ROWS) {
+        uint8_t* atom = s1 + ((r0 / DUAL_ROWS) * (long long)(cols / DUAL_COLS) + c0 / DUAL_COLS) * 512;
+        *reinterpret_cast<uint32_t*>(atom + (t % 32) * 16 + (t / 32) * 4) = s1_stage[t];
+      }
+    } else if (t < DUAL_ROWS && r0 + t < rows) {
       const int sc = cols / 32;  // scale bytes per row of s1
       uint8_t* dst = s1 + (r0 + t) * sc + c0 / 32;
       if (sc % 4 == 0) {  // c0 / 32 is a multiple of 4: an aligned word (a row of sc % 4 == 0 has whole tiles only)
@@ -304,7 +311,13 @@ __global__ void __launch_bounds__(DUAL_THREADS) mx_quant_dual_kernel(const T* __
         *reinterpret_cast<uint4*>(q2t + (long long)(c0 + c) * rows + r0 + ch * 16) =
             reinterpret_cast<const uint4*>(q2_stage + c * DUAL_ROWS)[ch ^ ((c >> 1) & 7)];
     }
-    if (t >= DUAL_ROWS && c0 + (t - DUAL_ROWS) < cols) {  // the other half of the CTA takes the column scales
+    if (atoms) {
+      if (t >= DUAL_ROWS) {  // the transposed operand's rows are this tile's columns, its blocks this tile's row blocks
+        const int c = t - DUAL_ROWS;
+        uint8_t* atom = s2t + ((long long)(c0 / DUAL_COLS) * (rows / DUAL_ROWS) + r0 / DUAL_ROWS) * 512;
+        *reinterpret_cast<uint32_t*>(atom + (c % 32) * 16 + (c / 32) * 4) = s2_stage[c];
+      }
+    } else if (t >= DUAL_ROWS && c0 + (t - DUAL_ROWS) < cols) {  // the other half of the CTA takes the column scales
       const int c = t - DUAL_ROWS;
       const long long sr = rows / 32;  // scale bytes per row of s2t
       uint8_t* dst = s2t + (long long)(c0 + c) * sr + r0 / 32;
@@ -367,11 +380,13 @@ TB_API int tb_mx_dequantize(const void* q, const void* scales, void* out, long l
 // One pass over x [rows, cols] (bf16 dtype 1 / fp16 dtype 2; rows % 32 == 0, cols % 32 == 0) producing
 //   q1 [rows, cols] e4m3 + s1 [rows, cols/32]   (blocks along the row), and / or
 //   q2t [cols, rows] e4m3 + s2t [cols, rows/32] (blocks down the rows, written transposed).
-// A null q1 or q2t skips that output.
+// A null q1 or q2t skips that output.  atoms != 0 (rows % 128 == 0 and cols % 128 == 0) writes the scales in the
+// 512-byte atom order the block-scaled GEMM reads: s1 as [rows/128][cols/128][512], s2t as [cols/128][rows/128][512].
 TB_API int tb_mx_quantize_dual(const void* x, void* q1, void* s1, void* q2t, void* s2t, long long rows, int cols,
-                               int round, int dtype, cudaStream_t st) {
+                               int round, int dtype, int atoms, cudaStream_t st) {
   if (rows == 0 || cols == 0) return 0;
   if ((dtype != 1 && dtype != 2) || rows % 32 != 0 || cols % 32 != 0) return TB_ERR_ARG;
+  if (atoms && (rows % DUAL_ROWS != 0 || cols % DUAL_COLS != 0)) return TB_ERR_ARG;
   if ((q1 == nullptr) != (s1 == nullptr) || (q2t == nullptr) != (s2t == nullptr) || (q1 == nullptr && q2t == nullptr))
     return TB_ERR_ARG;
   const long long row_tiles = (rows + DUAL_ROWS - 1) / DUAL_ROWS;
@@ -380,10 +395,10 @@ TB_API int tb_mx_quantize_dual(const void* x, void* q1, void* s1, void* q2t, voi
   dim3 grid((unsigned)row_tiles, (unsigned)col_tiles);
   if (dtype == 1)
     mx_quant_dual_kernel<__nv_bfloat16><<<grid, DUAL_THREADS, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)q1, (uint8_t*)s1,
-                                                              (uint8_t*)q2t, (uint8_t*)s2t, rows, cols, round);
+                                                              (uint8_t*)q2t, (uint8_t*)s2t, rows, cols, round, atoms);
   else
     mx_quant_dual_kernel<__half><<<grid, DUAL_THREADS, 0, st>>>((const __half*)x, (uint8_t*)q1, (uint8_t*)s1, (uint8_t*)q2t,
-                                                       (uint8_t*)s2t, rows, cols, round);
+                                                       (uint8_t*)s2t, rows, cols, round, atoms);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

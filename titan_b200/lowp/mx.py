@@ -39,7 +39,7 @@ def _declare():
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         _lib.declare("tb_mx_quantize", [P, P, P, LL, I, I, I, I, P])
         _lib.declare("tb_mx_dequantize", [P, P, P, LL, I, I, P])
-        _lib.declare("tb_mx_quantize_dual", [P, P, P, P, P, LL, I, I, I, P])
+        _lib.declare("tb_mx_quantize_dual", [P, P, P, P, P, LL, I, I, I, I, P])
         _DECLARED = True
 
 
@@ -102,31 +102,46 @@ def mx_quantize(x: torch.Tensor, axis: int = -1, round_mode: str = "rceil"):
     return q.view(torch.float8_e4m3fn), s
 
 
-def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool = True, transposed: bool = True):
+def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool = True, transposed: bool = True,
+                     atoms: bool = False):
     """x [R, C] (R, C multiples of 32) → ``(q1 [R, C], s1 [R, C/32], q2t [C, R], s2t [C, R/32])``; a view that is not
     asked for (``rows=False`` / ``transposed=False``) comes back as ``None, None``.  ``q2t, s2t`` equal
-    ``mx_quantize(x.t().contiguous(), -1)``.
+    ``mx_quantize(x.t().contiguous(), -1)``.  ``atoms=True`` (both dims multiples of 128) returns the scales in the
+    packed 512-byte atom order of the block-scaled GEMM (`ops.mxfp8_gemm.pack_scale_atoms`): ``s1 [R/128, C/128, 512]``,
+    ``s2t [C/128, R/128, 512]``, ready for ``mxfp8_gemm(..., packed=True)`` with no repacking pass.
 
     Parity: `npu_dynamic_mx_quant_with_dual_axis` as used by experiments/ao_npu/torchao_npu/ops/mx_ops.py:62-194."""
     if x.dim() != 2 or x.shape[0] % BLOCK or x.shape[1] % BLOCK:
         raise ValueError(f"mx_quantize_dual wants a 2-D tensor with both dims multiples of {BLOCK}, got {tuple(x.shape)}")
     if not (rows or transposed):
         raise ValueError("mx_quantize_dual: ask for at least one view")
+    if atoms and (x.shape[0] % 128 or x.shape[1] % 128):
+        raise ValueError("mx_quantize_dual(atoms=True) needs both dims to be multiples of 128")
     if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)):
         q1, s1 = mx_quantize_ref(x, -1, round_mode) if rows else (None, None)
         q2t, s2t = mx_quantize_ref(x.t().contiguous(), -1, round_mode) if transposed else (None, None)
+        if atoms:
+            from titan_b200.ops.mxfp8_gemm import pack_scale_atoms
+
+            s1 = pack_scale_atoms(s1) if rows else None
+            s2t = pack_scale_atoms(s2t) if transposed else None
         return q1, s1, q2t, s2t
     _declare()
     x = x.contiguous()
     R, C = x.shape
     u8 = dict(dtype=torch.uint8, device=x.device)
     q1 = torch.empty(R, C, **u8) if rows else None
-    s1 = torch.empty(R, C // BLOCK, **u8) if rows else None
     q2t = torch.empty(C, R, **u8) if transposed else None
-    s2t = torch.empty(C, R // BLOCK, **u8) if transposed else None
+    if atoms:
+        s1 = torch.empty(R // 128, C // 128, 512, **u8) if rows else None
+        s2t = torch.empty(C // 128, R // 128, 512, **u8) if transposed else None
+    else:
+        s1 = torch.empty(R, C // BLOCK, **u8) if rows else None
+        s2t = torch.empty(C, R // BLOCK, **u8) if transposed else None
     p = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
     rc = _lib.lib().tb_mx_quantize_dual(x.data_ptr(), p(q1), p(s1), p(q2t), p(s2t), R, C,
-                                        {"floor": 0, "rceil": 1}[round_mode], _lib.dtype_code(x.dtype), _lib.stream_ptr())
+                                        {"floor": 0, "rceil": 1}[round_mode], _lib.dtype_code(x.dtype), int(atoms),
+                                        _lib.stream_ptr())
     _lib.check(rc, "mx_quantize_dual")
     f8 = lambda t: t.view(torch.float8_e4m3fn) if t is not None else None  # noqa: E731
     return f8(q1), s1, f8(q2t), s2t

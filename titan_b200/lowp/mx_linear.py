@@ -72,6 +72,8 @@ def _gemm_q(aq, sa, bq, sb, dtype) -> torch.Tensor:
     if aq.is_cuda:
         from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, mxfp8_gemm_supported
 
+        if sa.dim() == 3:  # scales already in the GEMM's atom order (only produced for shapes the kernel takes)
+            return mxfp8_gemm(aq, sa, bq, sb, packed=True).to(dtype)
         if mxfp8_gemm_supported(aq.shape[0], bq.shape[0], aq.shape[1]):
             return mxfp8_gemm(aq, sa, bq, sb).to(dtype)
     return _mm(mx_dequantize(aq, sa, -1, dtype), mx_dequantize(bq, sb, -1, dtype))
@@ -79,6 +81,11 @@ def _gemm_q(aq, sa, bq, sb, dtype) -> torch.Tensor:
 
 def _once_ok(*dims: int) -> bool:
     return all(d > 0 and d % BLOCK == 0 for d in dims)
+
+
+def _atoms_ok(t: torch.Tensor, *dims: int) -> bool:
+    """The quantiser can emit the GEMM's scale layout directly: CUDA 16-bit input, every dim a multiple of 128."""
+    return t.is_cuda and t.dtype in (torch.bfloat16, torch.float16) and all(d % 128 == 0 for d in dims)
 
 
 class MXFP8MM(torch.autograd.Function):
@@ -91,8 +98,10 @@ class MXFP8MM(torch.autograd.Function):
         ctx.meta = (x.shape, x.dtype, w.dtype, round_mode)
         ctx.once = _once_ok(x2.shape[0], x2.shape[1], w.shape[0])
         if ctx.once:
-            xq1, xs1, xq2t, xs2t = mx_quantize_dual(x2.contiguous(), round_mode, transposed=ctx.needs_input_grad[1])
-            wq1, ws1, _, _ = mx_quantize_dual(wq.contiguous(), round_mode, transposed=False)
+            ctx.atoms = at = _atoms_ok(x2, x2.shape[0], x2.shape[1], w.shape[0])
+            xq1, xs1, xq2t, xs2t = mx_quantize_dual(x2.contiguous(), round_mode, transposed=ctx.needs_input_grad[1],
+                                                    atoms=at)
+            wq1, ws1, _, _ = mx_quantize_dual(wq.contiguous(), round_mode, transposed=False, atoms=at)
             y = _gemm_q(xq1, xs1, wq1, ws1, x2.dtype)
             ctx.compute_dtype = x2.dtype
             ctx.save_for_backward(xq2t, xs2t, wq)
@@ -109,10 +118,10 @@ class MXFP8MM(torch.autograd.Function):
             dt = ctx.compute_dtype
             need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
             g2 = g.reshape(-1, g.shape[-1]).to(dt).contiguous()
-            gq1, gs1, gq2t, gs2t = mx_quantize_dual(g2, rm, rows=need_dx, transposed=need_dw)
+            gq1, gs1, gq2t, gs2t = mx_quantize_dual(g2, rm, rows=need_dx, transposed=need_dw, atoms=ctx.atoms)
             dx = dw = None
             if need_dx:  # dx = g · w: contraction over N, the weight blocked down its N rows and read transposed
-                _, _, wq2t, ws2t = mx_quantize_dual(w.contiguous(), rm, rows=False)
+                _, _, wq2t, ws2t = mx_quantize_dual(w.contiguous(), rm, rows=False, atoms=ctx.atoms)
                 dx = _gemm_q(gq1, gs1, wq2t, ws2t, dt).to(x_dt).reshape(shape)
             if need_dw:  # dw = gᵀ · x: contraction over tokens, both operands blocked down the token rows
                 dw = _gemm_q(gq2t, gs2t, xq2t, xs2t, dt).to(w_dt)
@@ -145,14 +154,15 @@ class _MXGroupedMMAligned(torch.autograd.Function):
         E, N, K = w.shape
         T = x.shape[0]
         used = T // 128 * 128
-        xq1, xs1, xq2t, xs2t = mx_quantize_dual(x[:used].contiguous(), round_mode, transposed=ctx.needs_input_grad[1])
-        wq1, ws1, _, _ = mx_quantize_dual(w.reshape(E * N, K).contiguous(), round_mode, transposed=False)
+        xq1, xs1, xq2t, xs2t = mx_quantize_dual(x[:used].contiguous(), round_mode, transposed=ctx.needs_input_grad[1],
+                                                atoms=True)
+        wq1, ws1, _, _ = mx_quantize_dual(w.reshape(E * N, K).contiguous(), round_mode, transposed=False, atoms=True)
         ctx.save_for_backward(xq2t, xs2t, w, offs)
         ctx.round_mode, ctx.rows = round_mode, T
         y = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
         if used < T:
             y[used:].zero_()
-        return mxfp8_grouped_gemm(xq1, xs1, wq1, ws1, offs, GROUP_B_ROWS, out=y)
+        return mxfp8_grouped_gemm(xq1, xs1, wq1, ws1, offs, GROUP_B_ROWS, out=y, packed=True)
 
     @staticmethod
     def backward(ctx, g):
@@ -164,16 +174,17 @@ class _MXGroupedMMAligned(torch.autograd.Function):
         used = T // 128 * 128
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gq1, gs1, gq2t, gs2t = mx_quantize_dual(g[:used].contiguous(), ctx.round_mode, rows=need_dx,
-                                                transposed=need_dw)
+                                                transposed=need_dw, atoms=True)
         dx = dw = None
         if need_dx:  # every expert's weight blocked down its N rows, transposed in the same pass: [K, E*N]
-            _, _, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K).contiguous(), ctx.round_mode, rows=False)
+            _, _, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K).contiguous(), ctx.round_mode, rows=False,
+                                                atoms=True)
             dx = torch.empty(T, K, dtype=torch.bfloat16, device=g.device)
             if used < T:
                 dx[used:].zero_()
-            mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE, out=dx)
+            mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE, out=dx, packed=True)
         if need_dw:  # gᵀ [N, T] · xᵀ [K, T]ᵀ over each expert's own rows → [E*N, K]
-            dw = mxfp8_grouped_gemm(gq2t, gs2t, xq2t, xs2t, offs, GROUP_K).view(E, N, K).to(w.dtype)
+            dw = mxfp8_grouped_gemm(gq2t, gs2t, xq2t, xs2t, offs, GROUP_K, packed=True).view(E, N, K).to(w.dtype)
         return dx, dw, None, None
 
 

@@ -81,9 +81,11 @@ def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.T
 
 
 def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor, offs: torch.Tensor,
-                       mode: int, *, tile_n: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+                       mode: int, *, tile_n: int = 0, out: torch.Tensor | None = None,
+                       packed: bool = False) -> torch.Tensor:
     """Grouped block-scaled GEMM; ``offs`` int32 [E] on the device, cumulative group ends, every group a multiple of
-    128 rows.  Operands are quantised along their last dim, scales ``[rows, last/32]`` uint8 (packed here).
+    128 rows.  Operands are quantised along their last dim, scales ``[rows, last/32]`` uint8 (packed here) or, with
+    ``packed``, already in atom order (`mx_quantize_dual(..., atoms=True)`).
 
     * ``GROUP_B_ROWS``:  aq [T, K], bq [E*N, K]  → [T, N]     (N % 128 == 0)
     * ``GROUP_B_SLICE``: aq [T, K], bq [N, E*K]  → [T, N]
@@ -113,7 +115,8 @@ def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb:
         P, I = ctypes.c_void_p, ctypes.c_int
         _lib.declare("tb_mxfp8_grouped_gemm", [P, P, P, P, P, I, I, I, P, I, I, I, P, P])
         _GROUPED_DECLARED = True
-    sa, sb = pack_scale_atoms(sa), pack_scale_atoms(sb)
+    if not packed:
+        sa, sb = pack_scale_atoms(sa), pack_scale_atoms(sb)
     aq, bq = aq.contiguous(), bq.contiguous()
     if out is None:
         out = torch.empty(rows_out, N, dtype=torch.bfloat16, device=aq.device)
