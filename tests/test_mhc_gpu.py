@@ -48,6 +48,37 @@ def test_mhc_pre_matches_reference(T, D):
     assert rel(base.grad, br.grad) < 3e-2, (base.grad, br.grad)
 
 
+@pytest.mark.parametrize("T,D", [(37, 256), (16, 4096)])
+def test_hc_head_runs_the_fused_pre_kernel_and_matches_reference(T, D):
+    from titan_b200.ops import _lib
+
+    dev = "cuda"
+    x = torch.randn(T, 4, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    fn = (torch.randn(4, 4 * D, device=dev) * 0.05).requires_grad_()
+    scale = (torch.randn(1, device=dev) * 0.5 + 1.0).requires_grad_()
+    base = (torch.randn(4, device=dev) * 0.3).requires_grad_()
+    mhc.set_fused(pre=True)
+    try:
+        before = _lib.launch_count()
+        y = mhc.hc_head(x, fn, scale, base)
+        assert _lib.launch_count() > before
+    finally:
+        mhc.set_fused(pre=False)
+    xr = x.detach().float().requires_grad_()
+    fnr, sr, br = (t.detach().clone().requires_grad_() for t in (fn, scale, base))
+    yr = mhc.hc_head_ref(xr, fnr, sr, br)
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    gy = torch.randn_like(yr)
+    (y.float() * gy).sum().backward()
+    (yr * gy).sum().backward()
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=5e-2, atol=5e-2)
+
+    def rel(a, b):
+        return (a.float() - b).norm() / b.norm().clamp_min(1e-6)
+
+    assert rel(fn.grad, fnr.grad) < 3e-2 and rel(scale.grad, sr.grad) < 3e-2 and rel(base.grad, br.grad) < 3e-2
+
+
 @pytest.mark.parametrize("T,D", [(33, 256), (16, 4096), (3, 7168)])
 def test_mhc_post_matches_reference(T, D):
     from titan_b200.ops.mhc_cuda import mhc_post

@@ -22,7 +22,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-__all__ = ["hc_split_sinkhorn", "hc_pre", "hc_post", "hc_head", "hc_pre_ref", "hc_post_ref", "set_fused"]
+__all__ = ["hc_split_sinkhorn", "hc_pre", "hc_post", "hc_head", "hc_pre_ref", "hc_post_ref", "hc_head_ref", "set_fused"]
 
 _FUSED = {"pre": False, "post": False}
 
@@ -101,6 +101,20 @@ def hc_post(x, residual, post, comb):
 def hc_head(x, head_fn, head_scale, head_base, hc_eps: float = 1e-6, norm_eps: float = 1e-6):
     """Collapse the streams: x [.., hc, D] → [.., D] with weights ``sigmoid(mix·scale + base) + eps``."""
     head_fn, head_scale, head_base = _local(head_fn), _local(head_scale), _local(head_base)
+    if (_FUSED["pre"] and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-2] == 4 and x.shape[-1] % 8 == 0
+            and x.shape[-1] <= 8192):
+        # the collapse is the "pre" third of `hc_pre` (same RMS, same sigmoid weights, same weighted sum) with no
+        # post / comb outputs: run the fused kernel on parameters padded with zero rows (one Sinkhorn pass on zeros)
+        from titan_b200.ops import mhc_cuda
+
+        fn24 = torch.cat([head_fn.float(), head_fn.new_zeros(20, head_fn.shape[1], dtype=torch.float32)], dim=0)
+        scale3 = torch.cat([head_scale.float().reshape(1), head_scale.new_zeros(2, dtype=torch.float32)])
+        base24 = torch.cat([head_base.float(), head_base.new_zeros(20, dtype=torch.float32)])
+        return mhc_cuda.mhc_pre(x, fn24, scale3, base24, 1, hc_eps, norm_eps)[0]
+    return hc_head_ref(x, head_fn, head_scale, head_base, hc_eps, norm_eps)
+
+
+def hc_head_ref(x, head_fn, head_scale, head_base, hc_eps: float = 1e-6, norm_eps: float = 1e-6):
     shape, dtype = x.shape, x.dtype
     xf = x.flatten(-2).float()
     rsqrt = torch.rsqrt(xf.square().mean(-1, keepdim=True) + norm_eps)
