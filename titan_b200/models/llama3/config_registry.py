@@ -70,6 +70,18 @@ def llama3_8b() -> TrainerConfig:
     )
 
 
+def llama3_8b_mxfp8() -> TrainerConfig:
+    """`llama3_8b` with every attention and feed-forward projection in MXFP8 (block-scaled tensor-core GEMMs for
+    forward, input gradient and weight gradient; fp8 saved activations); embeddings, norms and the output head stay
+    bf16."""
+    from titan_b200.lowp.mx_converter import MXFP8Converter
+
+    cfg = llama3_8b()
+    cfg.model_converters.converters.append(
+        MXFP8Converter.Config(recipe_name="mxfp8_rceil", fqns=["attention.w", "feed_forward.w"]))
+    return cfg
+
+
 def llama3_8b_baseline() -> TrainerConfig:
     """Same model and shapes on library ops only (cuBLAS / SDPA / NCCL) with the upstream selective-AC rule (every
     second matmul recomputed): the on-box comparator."""
