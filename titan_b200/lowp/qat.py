@@ -226,7 +226,10 @@ def quantize_params(model: nn.Module, cfg: ParamSwapConfig) -> list[str]:
             own = [(n, p) for n, p in mod.named_parameters(recurse=False)
                    if keep(f"{mod_name}.{n}" if mod_name else n, p)]
             if own and not hasattr(mod, "_lowp_real") and _install_real(mod, cfg.weight_config):
-                touched += [f"{mod_name}.{n}" if mod_name else n for n, _ in own]
+                # the module's forward is what changes, so every matrix it owns now runs (and is later baked) in low
+                # precision, not only the ones the filter named
+                touched += [f"{mod_name}.{n}" if mod_name else n
+                            for n, p in mod.named_parameters(recurse=False) if p.dim() >= 2]
             continue
         for pname, p in list(mod.named_parameters(recurse=False)):
             fq = f"{mod_name}.{pname}" if mod_name else pname
