@@ -32,6 +32,17 @@ if ROOT not in sys.path:
 METRIC = "train_tokens_per_sec"
 
 
+
+def _compute_dtype(cfg) -> str:
+    """The dtype the GEMMs run in: a recipe with a low-precision converter is reported as such, never as bf16."""
+    names = [getattr(c, "name", str(c)) for c in cfg.model_converters.converters]
+    base = "bf16" if cfg.training.dtype == "bfloat16" else cfg.training.dtype
+    if "mxfp8" in names:
+        return f"mxfp8 (block-scaled e4m3 GEMMs, fp32 accumulate; everything else {base})"
+    if "quantize" in names:
+        return f"quantised weights ({base} compute)"
+    return base
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -277,7 +288,7 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16" if cfg.training.dtype == "bfloat16" else cfg.training.dtype, "data": "synthetic",
+            "dtype": _compute_dtype(cfg), "data": "synthetic",
             "impl": args.impl,
             "config": {
                 "model": f"{cfg.model.name}-{cfg.model.flavor}", "recipe": recipe,
