@@ -32,8 +32,7 @@ class FusedMoE(MoE):
         x2 = x.reshape(-1, dim)
         T = x2.shape[0]
         r = self.router
-        logits = F.linear(x2.float(), r.gate.weight.float() if not hasattr(r.gate.weight, "to_local")
-                          else r.gate.weight.to_local().float())
+        logits = F.linear(x2.float(), r.gate_weight().float())
         forced = None
         if r.hash:
             forced = r.tid2eid[input_ids.flatten()]
@@ -68,7 +67,7 @@ class FusedMoE(MoE):
         else:
             xp = moe_ops.permute(x2, plan)
             yp = experts(xp, plan.offs, padded=True)
-            out = moe_ops.combine(yp, plan, T, weights=gate, base=base)
+            out = moe_ops.combine(yp, plan, T, weights=self.full_grad(gate), base=base)
         return out.reshape(bs, slen, dim)
 
 

@@ -318,7 +318,8 @@ inline int ensure_context(const void*) {
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements, row pitch `ld_bytes`; box = [box_rows, box_cols].
 // swizzle: 0 none, 1 = 32B, 2 = 64B, 3 = 128B (CUtensorMapSwizzle values).
 inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes, uint64_t rows,
-                        uint64_t cols, uint64_t ld_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle) {
+                        uint64_t cols, uint64_t ld_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle,
+                        int l2_promotion = (int)CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
   auto fn = encode_fn();
   if (fn == nullptr) return TB_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld_bytes & 15) != 0) return TB_ERR_ARG;
@@ -328,7 +329,7 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  (CUtensorMapSwizzle)swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  (CUtensorMapSwizzle)swizzle, (CUtensorMapL2promotion)l2_promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r + 2000;
 }
 // 3-D tensor [d2, d1, d0] (d0 innermost), strides in bytes for d1 and d2.

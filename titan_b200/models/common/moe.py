@@ -71,6 +71,13 @@ class TokenChoiceTopKRouter(Module):
             self.register_buffer("tid2eid", build_hash_routing_table(vocab_size, self.num_experts, self.top_k),
                                  persistent=True)
 
+    def gate_weight(self) -> torch.Tensor:
+        """Local gate weight.  Under tensor parallelism it is replicated; when every rank routes only its own
+        sequence slice (``tokens_sharded``) the gradient is a partial sum and is reduced over the mesh."""
+        from titan_b200.parallel.tensor_parallel import replicated_param_local
+
+        return replicated_param_local(self.gate.weight, partial_grad=getattr(self, "tokens_sharded", False))
+
     def _scores(self, logits: torch.Tensor) -> torch.Tensor:
         if self.score_func == "sigmoid":
             return torch.sigmoid(logits)
@@ -96,9 +103,7 @@ class TokenChoiceTopKRouter(Module):
 
     def forward(self, x: torch.Tensor, expert_bias: torch.Tensor | None = None, input_ids: torch.Tensor | None = None):
         """x [T, dim] → (top_scores [T, k] fp32, selected [T, k] int64, tokens_per_expert [E] fp32)."""
-        w = self.gate.weight
-        w = w.to_local() if hasattr(w, "to_local") else w  # replicated under tensor parallelism
-        logits = F.linear(x.float(), w.float())  # routing in fp32
+        logits = F.linear(x.float(), self.gate_weight().float())  # routing in fp32
         scores = self._scores(logits)
         if self.hash:
             if input_ids is None:
@@ -223,6 +228,16 @@ class MoE(Module):
         self.register_buffer("tokens_per_expert", torch.zeros(args.num_experts, dtype=torch.float32),
                              persistent=False)
 
+    def full_grad(self, gate_values: torch.Tensor) -> torch.Tensor:
+        """Gate values that multiply a routed output which is a PARTIAL sum over tensor-parallel ranks receive a
+        partial gradient; it is summed over ``tp_partial_group`` (set by the parallelize plan) in backward."""
+        group = getattr(self, "tp_partial_group", None)
+        if group is None or not gate_values.requires_grad:
+            return gate_values
+        from titan_b200.parallel.expert_parallel import _AllReduceGrad
+
+        return _AllReduceGrad.apply(gate_values, group)
+
     def forward(self, x: torch.Tensor, input_ids: torch.Tensor | None = None) -> torch.Tensor:
         bs, slen, dim = x.shape
         x2 = x.reshape(-1, dim)
@@ -235,7 +250,7 @@ class MoE(Module):
             routed_in = (routed_in.float() * scores_sorted.reshape(-1, 1)).to(x.dtype)
         routed_out = self.experts(routed_in, counts)
         if not self.score_before_experts:
-            routed_out = (routed_out.float() * scores_sorted.reshape(-1, 1)).to(x.dtype)
+            routed_out = (routed_out.float() * self.full_grad(scores_sorted).reshape(-1, 1)).to(x.dtype)
         out = self.shared_experts(x2) if self.shared_experts is not None else torch.zeros_like(x2)
         out = out.index_add(0, token_idx, routed_out.to(out.dtype))
         return out.reshape(bs, slen, dim)

@@ -50,6 +50,7 @@ def _declare(L) -> None:
         "tb_cross_entropy_fwd": [P, P, P, P, LL, I, LL, LL, I, P, P],
         "tb_cross_entropy_bwd": [P, P, P, P, P, LL, I, LL, LL, I, P],
         "tb_gemm_bf16": [P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P],
+        "tb_gemm_auto": [P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, LL, I, P, P],
         "tb_grouped_gemm_m": [P, P, P, P, I, I, I, I, I, I, P, P],
         "tb_grouped_gemm_k": [P, P, P, P, I, I, I, I, I, I, P, P],
         "tb_router_topk": [P, P, P, P, P, P, P, I, I, I, I, I, F, P, P],

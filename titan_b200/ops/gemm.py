@@ -1,7 +1,9 @@
 """tcgen05 GEMM: Python entry points, a `linear` autograd function and oracles.
 
 ``gemm(a, b, a_mn=False, b_mn=False)`` computes ``A · B`` for bf16/fp16 operands on the
-tcgen05 tensor cores with fp32 accumulation in tensor memory (`csrc/gemm/gemm_bf16.cu`).
+tcgen05 tensor cores with fp32 accumulation in tensor memory.  Large problems run on CTA pairs
+(`csrc/gemm/gemm_pair.cuh`: ``cta_group::2``, 256 x 256 tiles, the last partial wave cut along the
+contraction), small ones on the single-CTA engine (`csrc/gemm/gemm_bf16.cu`); ``policy`` forces either.
 `a_mn` / `b_mn` say how each operand is *stored* (see that file); `linear(x, w)` uses the
 three storage combinations so forward, input-gradient and weight-gradient run without transposes:
 
@@ -30,9 +32,30 @@ def supported(a: torch.Tensor, b: torch.Tensor) -> bool:
             and a.dim() == 2 and b.dim() == 2)
 
 
+_POLICY = {"auto": 0, "single": 1, "pair": 2}
+_WS: dict = {}
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    """Zero-filled partial-sum workspace of the pair kernel's tail split, one per (device, stream): the kernel
+    leaves it zeroed, and calls on one stream are ordered, so every GEMM of that stream shares it."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WS.get(key)
+    if ws is None:
+        fn = _lib.lib().tb_gemm_ws_bytes
+        fn.restype, fn.argtypes = _lib.c_longlong, []
+        ws = torch.zeros(int(fn()), dtype=torch.uint8, device=device)
+        _WS[key] = ws
+    return ws
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
-         out_dtype: torch.dtype | None = None, accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
-    """A · B.  a: [M,K] (or [K,M] if a_mn); b: [N,K] (or [K,N] if b_mn) → [M,N]."""
+         out_dtype: torch.dtype | None = None, accumulate: bool = False, max_ctas: int = 0,
+         policy: str = "auto", split_tail: bool = True) -> torch.Tensor:
+    """A · B.  a: [M,K] (or [K,M] if a_mn); b: [N,K] (or [K,N] if b_mn) → [M,N].
+
+    ``policy``: "auto" picks CTA pairs for problems that fill the GPU, "single" / "pair" force a kernel.
+    ``split_tail=False`` keeps the pair kernel's last partial wave as whole tiles (no workspace)."""
     if not supported(a, b):
         raise _lib.KernelError(f"gemm: unsupported operands {a.dtype}{tuple(a.shape)} x {b.dtype}{tuple(b.shape)}")
     if a.stride(-1) != 1:
@@ -58,10 +81,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if b.stride(0) % 8 or b.data_ptr() % 16:
         b = _aligned_copy(b)
     status = _lib.shared_status()
-    rc = _lib.lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+    ws = _workspace(a.device) if split_tail and policy != "single" else None
+    rc = _lib.lib().tb_gemm_auto(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                                  out.stride(0), int(a_mn), int(b_mn), _lib.dtype_code(a.dtype),
-                                 int(out_dtype == torch.float32), int(accumulate), int(max_ctas), status.ptr,
-                                 _lib.stream_ptr())
+                                 int(out_dtype == torch.float32), int(accumulate), _POLICY[policy],
+                                 None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
+                                 int(max_ctas), status.ptr, _lib.stream_ptr())
     _lib.check(rc, "gemm_bf16")
     return out
 

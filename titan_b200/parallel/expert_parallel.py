@@ -6,7 +6,13 @@
 * `FusedExpertParallel`   – same placement; dispatch/combine run as ONE kernel each over peer
   memory (`titan_b200.ops.moe_comm`): rows are written straight into the owner's expert-major buffer.
 * `ExpertTensorParallel`  – 2-D ``[ep, etp]``: dim 0 over ep, ``w1/w3`` dim 1 and ``w2`` dim 2 over etp.
-* `TensorParallel`        – experts replicated over tokens, weights split over ``tp`` (output all-reduced).
+* `TensorParallel`        – every rank sees all tokens, weights split over ``tp`` on the hidden dim.
+
+Both tensor-parallel styles leave the routed output as a PARTIAL sum over the tp / etp ranks: the MoE block
+declares its output ``Partial()`` and the reduce-scatter back to the sequence shard adds the ranks up once.  In
+backward the gradient of the (replicated) routed input is the matching partial sum and is all-reduced where the
+tokens enter the experts.  A fused ``w13 = [w1 | w3]`` weight is split so that every rank holds
+``[w1_shard | w3_shard]`` (the layout `checkpoint.weight_utils` fuses and splits).
 * `permute / unpermute`   – the local re-routing used by the dispatch and by the single-process dry run.
 
 Under a fake process group the result of the count exchange is meaningless, so splits are taken
@@ -24,7 +30,7 @@ import torch.distributed as dist
 import torch.nn as nn
 from torch.distributed._functional_collectives import all_to_all_single, all_to_all_single_autograd
 from torch.distributed.device_mesh import DeviceMesh
-from torch.distributed.tensor import Shard, distribute_module, distribute_tensor
+from torch.distributed.tensor import DTensor, Shard, distribute_module, distribute_tensor
 from torch.distributed.tensor.parallel import ParallelStyle
 
 from titan_b200.parallel.fake_pg import is_fake_process_group
@@ -142,65 +148,76 @@ class FusedExpertParallel(ExpertParallel):
         return module
 
 
+def _shard_hidden(pname: str, p: torch.Tensor, device_mesh, lead: tuple = ()):
+    """Placement of one expert weight under (expert) tensor parallelism: ``w1 / w3 / w13`` on the hidden rows
+    (dim 1), ``w2`` on its hidden columns (dim 2); ``lead`` are the placements of leading mesh axes (EP)."""
+    if pname == "w13":
+        # [E, 2H, D] holds w1 above w3: every rank takes its rows of BOTH halves
+        w1, w3 = p.data.chunk(2, dim=1)
+        l1 = distribute_tensor(w1, device_mesh, [*lead, Shard(1)]).to_local()
+        l3 = distribute_tensor(w3, device_mesh, [*lead, Shard(1)]).to_local()
+        local = torch.cat([l1, l3], dim=1)
+        return DTensor.from_local(local, device_mesh, [*lead, Shard(1)], run_check=False, shape=p.shape,
+                                  stride=p.stride())
+    dim = 2 if pname == "w2" else 1
+    return distribute_tensor(p, device_mesh, [*lead, Shard(dim)])
+
+
+class _AllReduceGrad(torch.autograd.Function):
+    """Identity whose gradient is summed over ``group`` (a replicated input consumed by per-rank weight shards)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 class TensorParallel(ParallelStyle):
-    """Experts see all tokens; ``w1/w3`` are split on the hidden dim (1), ``w2`` on its input dim (2)."""
+    """Experts see all tokens; ``w1/w3`` are split on the hidden dim (1), ``w2`` on its input dim (2).  The output
+    stays a partial sum over the mesh (see the module docstring)."""
 
     @staticmethod
     def _partition_fn(name, mod, device_mesh):
         for pname, p in list(mod.named_parameters(recurse=False)):
             if p is None:
                 continue
-            if pname == "w13":
-                # the fused [E, 2H, D] weight holds w1 above w3: a split on dim 1 would hand w1 to one rank and w3 to
-                # the other instead of halving both
-                raise NotImplementedError("tensor-parallel experts need separate w1 / w3 weights: remove the "
-                                          "b200_gmm converter or use expert parallelism without expert TP")
-            dim = 2 if pname == "w2" else 1
-            mod.register_parameter(pname, nn.Parameter(distribute_tensor(p, device_mesh, [Shard(dim)])))
+            mod.register_parameter(pname, nn.Parameter(_shard_hidden(pname, p, device_mesh)))
 
     @staticmethod
-    def _output_fn(mod, out, device_mesh):
-        out = out.contiguous()
-        return _AllReduceSum.apply(out, device_mesh.get_group())
+    def _input_fn(mod, inputs, device_mesh):
+        x = inputs[0]
+        if isinstance(x, torch.Tensor) and x.requires_grad:
+            x = _AllReduceGrad.apply(x, device_mesh.get_group())
+        return (x, *inputs[1:])
 
     def _apply(self, module, device_mesh):
-        return distribute_module(module, device_mesh, partition_fn=self._partition_fn, output_fn=self._output_fn)
-
-
-class _AllReduceSum(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, group):
-        x = x.clone()
-        dist.all_reduce(x, group=group)
-        return x
-
-    @staticmethod
-    def backward(ctx, g):
-        return g, None
+        return distribute_module(module, device_mesh, partition_fn=self._partition_fn, input_fn=self._input_fn)
 
 
 class ExpertTensorParallel(ExpertParallel):
     """2-D mesh ``[ep, etp]``: EP on dim 0, TP on the hidden dim."""
 
     def _token_dispatch(self, mod, inputs, device_mesh):
-        return super()._token_dispatch(mod, inputs, device_mesh["ep"])
+        x = inputs[0]
+        if x.requires_grad:  # every etp rank dispatches the same tokens to its own hidden slice of the experts
+            x = _AllReduceGrad.apply(x, device_mesh["etp"].get_group())
+        return super()._token_dispatch(mod, (x, *inputs[1:]), device_mesh["ep"])
 
     def _token_combine(self, mod, routed_output, device_mesh):
-        routed_output = _AllReduceSum.apply(routed_output.contiguous(), device_mesh["etp"].get_group())
-        return super()._token_combine(mod, routed_output, device_mesh["ep"])
+        return super()._token_combine(mod, routed_output, device_mesh["ep"])  # partial over etp
 
     @staticmethod
     def _partition_fn_2d(name, mod, device_mesh):
         for pname, p in list(mod.named_parameters(recurse=False)):
             if p is None:
                 continue
-            if pname == "w13":
-                # the fused [E, 2H, D] weight holds w1 above w3: a split on dim 1 would hand w1 to one rank and w3 to
-                # the other instead of halving both
-                raise NotImplementedError("tensor-parallel experts need separate w1 / w3 weights: remove the "
-                                          "b200_gmm converter or use expert parallelism without expert TP")
-            dim = 2 if pname == "w2" else 1
-            mod.register_parameter(pname, nn.Parameter(distribute_tensor(p, device_mesh, [Shard(0), Shard(dim)])))
+            mod.register_parameter(pname, nn.Parameter(_shard_hidden(pname, p, device_mesh, (Shard(0),))))
 
     def _apply(self, module, device_mesh):
         return distribute_module(module, device_mesh, partition_fn=self._partition_fn_2d,

@@ -47,6 +47,10 @@ def update_expert_bias(model_parts: list[nn.Module], parallel_dims) -> None:
     if not rows:
         return
     mat = torch.vstack(rows)
+    # layers whose tokens stay sequence-sharded over tensor-parallel ranks count per-rank slices
+    slice_group = next((g for g in (getattr(m, "counts_group", None) for m in moes) if g is not None), None)
+    if slice_group is not None and dist.is_initialized():
+        dist.all_reduce(mat, group=slice_group, op=dist.ReduceOp.SUM)
     loss_mesh = parallel_dims.get_optional_mesh("loss") if (parallel_dims is not None and dist.is_initialized()) else None
     if loss_mesh is not None:
         dist.all_reduce(mat, group=loss_mesh.get_group(), op=dist.ReduceOp.SUM)
