@@ -1,9 +1,18 @@
-"""Headline benchmark: Llama-3 8B pretraining step (FSDP2, bf16 params/compute, fp32 reduce,
-seq 8192, local batch 1, selective AC, AdamW) — whole-job training tokens/s, device-timed.
+"""Headline benchmark: Llama-3 8B pretraining step (FSDP2 over the N GPUs, bf16 params/compute, fp32 gradient
+reduction, seq 8192, local batch 1, selective activation checkpointing, AdamW) — whole-job training tokens/s,
+device-timed.
 
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
     python bench.py --impl reference ...                      (the unmodified reference, if it can run here)
     python bench.py --impl baseline ...                       (this framework on library ops only)
+
+One invocation measures up to three arms back to back in the same process(es), each on a freshly built trainer:
+  1. the product arm (`value`, `e2e`): recipe `llama3_8b` (this framework's kernels, selective checkpointing);
+  2. the library arm (`baseline`): the same model, checkpointing rule, reshard policy and optimizer maths on
+     cuBLAS / cuDNN-SDPA / torch fused AdamW / NCCL only; `vs_baseline` = product tokens/s ÷ library tokens/s;
+  3. the product recipe without recomputation (`variants.activation_checkpoint_none`), reported beside the headline,
+     never as `value`.
+`--arms product` runs the first arm only.
 
 Two timed regions of K steps each, both bracketed by barrier + synchronize and timed with CUDA
 events, max over ranks:
@@ -59,6 +68,8 @@ def parse_args():
     ap.add_argument("--breakdown", type=int, default=0, metavar="ROWS",
                     help="after timing, profile one more step and write the top ROWS kernels by device time")
     ap.add_argument("--breakdown-out", default="kernel_breakdown.txt")
+    ap.add_argument("--arms", default="product,library,noac",
+                    help="which arms to measure in this invocation: product[,library][,noac]")
     ap.add_argument("--set", action="append", default=[], metavar="SECTION.FIELD=VALUE",
                     help="extra recipe overrides, e.g. --set parallelism.expert_parallel_degree=2 (repeatable)")
     return ap.parse_args()
@@ -137,11 +148,12 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- our arms
-def build_config(args):
+def build_config(args, impl: str, ac_override: str | None = None):
     from titan_b200.config.manager import resolve_recipe
     from titan_b200.protocols.converter import get_model_converter_config
 
-    recipe = args.config or ("llama3_8b" if args.impl == "ours" else "llama3_8b_baseline")
+    recipe = args.config if (args.config and impl == args.impl) else (
+        "llama3_8b" if impl == "ours" else "llama3_8b_baseline")
     cfg = resolve_recipe(args.module, recipe)
     if args.seq_len:
         cfg.training.seq_len = args.seq_len
@@ -149,10 +161,10 @@ def build_config(args):
         cfg.training.local_batch_size = args.local_batch
     if args.flavor:
         cfg.model.flavor = args.flavor
-    if args.converters is not None:
+    if args.converters is not None and impl == "ours":
         cfg.model_converters.converters = [get_model_converter_config(n) for n in args.converters.split(",") if n]
-    if args.ac:
-        cfg.activation_checkpoint.mode = args.ac
+    if ac_override or args.ac:
+        cfg.activation_checkpoint.mode = ac_override or args.ac
     if args.set:
         from titan_b200.config.manager import apply_overrides
 
@@ -164,35 +176,23 @@ def build_config(args):
     return cfg, recipe
 
 
-def main() -> int:
-    args = parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
+def run_arm(args, impl: str, *, ac_override: str | None = None, with_e2e: bool = True, sample_clocks: bool = True,
+            breakdown: bool = False) -> dict:
+    """Build a trainer for one arm, time it, tear it down.  Returns the measurements (identical on every rank)."""
+    import gc
 
     import torch
     import torch.distributed as dist
 
-    if not torch.cuda.is_available():
-        print(json.dumps({"metric": METRIC, "error": "no CUDA device"}))
-        return 1
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            print(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus}", file=sys.stderr)
-            return 2
+    from titan_b200.ops import _lib
+
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    os.environ.setdefault("LOG_RANK", "0")
-
-    from titan_b200.ops import _lib
-    from titan_b200.trainer.loss import IGNORE_INDEX  # noqa: F401
-
-    cfg, recipe = build_config(args)
+    cfg, recipe = build_config(args, impl, ac_override)
+    torch.cuda.reset_peak_memory_stats()
     trainer = cfg.build()
     device = trainer.device
     K, W = args.steps, args.warmup
-    if W < 3:
-        print("warning: fewer than 3 warm-up steps", file=sys.stderr)
 
     def barrier():
         if dist.is_initialized():
@@ -226,7 +226,7 @@ def main() -> int:
         trainer.step += 1
         trainer.train_step(sit)
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
     launches0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -240,25 +240,28 @@ def main() -> int:
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
 
     # ---- region 2: end to end through the public loop: pinned host → device each step, loss → host each step
-    h2d = d2h = 0
-    losses = []
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(K):
-        trainer.step += 1
-        trainer.train_step(loader_iter)  # loader_iter pulls a fresh pinned batch and copies it to the device
-        loss_host = trainer._last_loss.to("cpu", non_blocking=False)
-        losses.append(float(loss_host))
-    e3.record()
-    torch.cuda.synchronize()
-    barrier()
-    e2e_ms = max_over_ranks(e2.elapsed_time(e3))
+    e2e = None
+    if with_e2e:
+        losses = []
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record()
+        for _ in range(K):
+            trainer.step += 1
+            trainer.train_step(loader_iter)  # pulls a fresh pinned batch and copies it to the device
+            loss_host = trainer._last_loss.to("cpu", non_blocking=False)
+            losses.append(float(loss_host))
+        e3.record()
+        torch.cuda.synchronize()
+        barrier()
+        e2e_ms = max_over_ranks(e2.elapsed_time(e3))
+        e2e = {"value": tokens_per_step / (e2e_ms / K / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": 2 * tokens_per_step_rank * 8,  # int64 inputs + labels per rank and step
+               "d2h_bytes_per_step": 4 if cfg.training.dtype == "float32" else trainer._last_loss.element_size(),
+               "ms_per_step": e2e_ms / K, "last_loss": losses[-1] if losses else None}
     clocks = sampler.stop() if sampler is not None else None
-    h2d = 2 * tokens_per_step_rank * 8  # int64 inputs + labels per rank and step
-    d2h = 4 if cfg.training.dtype == "float32" else trainer._last_loss.element_size()
 
-    if args.breakdown:
+    if breakdown and args.breakdown:
         # one extra step under the profiler, after (never inside) the timed regions: shares of device time per kernel
         from torch.profiler import ProfilerActivity, profile
 
@@ -274,41 +277,96 @@ def main() -> int:
             print(f"kernel breakdown of one step written to {args.breakdown_out}", file=sys.stderr)
 
     _lib.shared_status().raise_if_set("bench")  # any kernel-reported failure invalidates the run
-    mem_gib = torch.cuda.max_memory_allocated() / 2 ** 30
-    if rank == 0:
-        ms_per_step = dev_ms / K
-        value = tokens_per_step / (ms_per_step / 1e3)
-        e2e_value = tokens_per_step / (e2e_ms / K / 1e3)
-        from titan_b200.utils.device import get_peak_flops
+    from titan_b200.utils.device import get_peak_flops
 
-        mfu = 100.0 * trainer.flops_per_token * (value / args.gpus) / get_peak_flops()
-        pd = trainer.parallel_dims
-        par = "+".join(f"{n}{v}" for n, v in (("fsdp", pd.dp_shard), ("hsdp", pd.dp_replicate), ("tp", pd.tp),
-                                               ("cp", pd.cp), ("pp", pd.pp), ("ep", pd.ep)) if v > 1) or "single"
-        out = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": _compute_dtype(cfg), "data": "synthetic",
-            "impl": args.impl,
-            "config": {
-                "model": f"{cfg.model.name}-{cfg.model.flavor}", "recipe": recipe,
-                "global_batch": cfg.training.local_batch_size * dp, "seq_len": cfg.training.seq_len,
-                "parallelism": par, "activation_checkpoint": (cfg.activation_checkpoint.mode if cfg.activation_checkpoint.mode != "selective"
-                                          else f"selective/{cfg.activation_checkpoint.selective_ac_option}"),
-                "optimizer": f"{cfg.optimizer.name}/{cfg.optimizer.implementation}",
-                "converters": [getattr(c, "name", str(c)) for c in cfg.model_converters.converters],
-                "l2": "inputs larger than L2 (weights + activations >> 126 MB); no explicit flush",
-                "params": trainer.nparams,
-            },
-            "tokens_per_sec_per_gpu": value / args.gpus, "mfu_pct_of_nominal_bf16": mfu,
-            "max_memory_allocated_gib": mem_gib,
-            "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / K, "last_loss": losses[-1] if losses else None},
-            "gpu_launches": launches,
-        }
-        print(json.dumps(out), flush=True)
+    ms_per_step = dev_ms / K
+    value = tokens_per_step / (ms_per_step / 1e3)
+    pd = trainer.parallel_dims
+    par = "+".join(f"{n}{v}" for n, v in (("fsdp", pd.dp_shard), ("hsdp", pd.dp_replicate), ("tp", pd.tp),
+                                           ("cp", pd.cp), ("pp", pd.pp), ("ep", pd.ep)) if v > 1) or "single"
+    ac = cfg.activation_checkpoint
+    out = {
+        "impl": impl, "recipe": recipe, "value": value, "ms_per_step": ms_per_step, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": launches, "dtype": _compute_dtype(cfg),
+        "mfu_pct_of_nominal_bf16": 100.0 * trainer.flops_per_token * (value / args.gpus) / get_peak_flops(),
+        "max_memory_allocated_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+        "config": {
+            "model": f"{cfg.model.name}-{cfg.model.flavor}", "recipe": recipe,
+            "global_batch": cfg.training.local_batch_size * dp, "seq_len": cfg.training.seq_len, "parallelism": par,
+            "activation_checkpoint": ac.mode if ac.mode != "selective" else f"selective/{ac.selective_ac_option}",
+            "fsdp_reshard_after_forward": cfg.parallelism.fsdp_reshard_after_forward,
+            "fsdp_fused_collectives": bool(getattr(cfg.parallelism, "fsdp_fused_collectives", False)) and dp > 1,
+            "optimizer": f"{cfg.optimizer.name}/{cfg.optimizer.implementation}",
+            "converters": [getattr(c, "name", str(c)) for c in cfg.model_converters.converters],
+            "l2": "inputs larger than L2 (weights + activations >> 126 MB); no explicit flush",
+            "params": trainer.nparams,
+        },
+    }
     trainer.close()
+    del trainer, staged, sit, loader_iter
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return out
+
+
+def main() -> int:
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"metric": METRIC, "error": "no CUDA device"}))
+        return 1
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus}", file=sys.stderr)
+            return 2
+    rank = int(os.environ.get("RANK", "0"))
+    os.environ.setdefault("LOG_RANK", "0")
+    if args.warmup < 3:
+        print("warning: fewer than 3 warm-up steps", file=sys.stderr)
+
+    arms = set(args.arms.split(","))
+    main_arm = run_arm(args, args.impl, breakdown=True)
+    baseline = variant = None
+    if args.impl == "ours" and "library" in arms:
+        baseline = run_arm(args, "baseline", sample_clocks=False)
+    if args.impl == "ours" and "noac" in arms and main_arm["config"]["activation_checkpoint"] != "none":
+        variant = run_arm(args, "ours", ac_override="none", with_e2e=False, sample_clocks=False)
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": main_arm["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_arm["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (main_arm["value"] / baseline["value"]) if baseline else None,
+            "dtype": main_arm["dtype"], "data": "synthetic", "impl": args.impl, "config": main_arm["config"],
+            "tokens_per_sec_per_gpu": main_arm["value"] / args.gpus,
+            "mfu_pct_of_nominal_bf16": main_arm["mfu_pct_of_nominal_bf16"],
+            "max_memory_allocated_gib": main_arm["max_memory_allocated_gib"],
+            "clocks": main_arm["clocks"], "e2e": main_arm["e2e"], "gpu_launches": main_arm["gpu_launches"],
+        }
+        if baseline:
+            out["baseline"] = {
+                "what": "same model, checkpointing rule, reshard policy and step on library kernels only (cuBLAS, "
+                        "cuDNN SDPA, torch fused AdamW, NCCL), measured in this invocation after the product arm",
+                "recipe": baseline["recipe"], "value": baseline["value"], "ms_per_step": baseline["ms_per_step"],
+                "e2e_value": baseline["e2e"]["value"] if baseline["e2e"] else None,
+                "e2e_vs_baseline": (main_arm["e2e"]["value"] / baseline["e2e"]["value"])
+                if (baseline["e2e"] and main_arm["e2e"]) else None,
+                "config": baseline["config"],
+            }
+        if variant:
+            out["variants"] = {"activation_checkpoint_none": {
+                "value": variant["value"], "ms_per_step": variant["ms_per_step"],
+                "max_memory_allocated_gib": variant["max_memory_allocated_gib"],
+                "note": "the product recipe without recomputation (fits in 180 GB); not the headline configuration"}}
+        print(json.dumps(out), flush=True)
     if dist.is_initialized():
         dist.destroy_process_group()
     return 0

@@ -71,6 +71,38 @@ def test_text_loader_packs_and_resumes(tmp_path):
         o.load_state_dict(state)
 
 
+def test_enwiki_eod_and_alpaca_datasets_from_bundled_assets(monkeypatch):
+    import os
+
+    from titan_b200.data.text_datasets import _alpaca_text
+
+    monkeypatch.chdir(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # default paths are repo-relative
+    tok = ByteTokenizer()
+    wiki = TextDataLoader(dataset="enwiki-eod", dataset_path=None, tokenizer=tok, seq_len=64, batch_size=2, dp_rank=0,
+                          dp_world_size=1, infinite=False, pin_memory=False)
+    batch, labels = next(iter(wiki))
+    assert batch["input"].shape == (2, 64) and labels.shape == (2, 64)
+    flat = torch.cat([batch["input"].reshape(-1), labels[:, -1:].reshape(-1)])
+    assert tok.decode([t for t in flat.tolist() if t < 256]).startswith("A tensor core is a matrix")
+    # every article ends with the end-of-document token before the next one starts
+    first_article_len = 1 + len(   # BOS, then the text
+        "A tensor core is a matrix multiply-accumulate unit inside a streaming multiprocessor. It multiplies small "
+        "tiles of low-precision numbers and accumulates the products at higher precision.")
+    stream = []
+    for b, _ in TextDataLoader(dataset="enwiki-eod", dataset_path=None, tokenizer=tok, seq_len=64, batch_size=1,
+                               dp_rank=0, dp_world_size=1, infinite=False, pin_memory=False):
+        stream.extend(b["input"][0].tolist())
+    assert stream[first_article_len] == tok.eos_id and stream[first_article_len + 1] == tok.bos_id
+
+    alp = TextDataLoader(dataset="alpaca", dataset_path=None, tokenizer=tok, seq_len=48, batch_size=1, dp_rank=0,
+                         dp_world_size=1, infinite=False, pin_memory=False)
+    text = tok.decode([t for t in next(iter(alp))[0]["input"][0].tolist() if t < 256])
+    assert text.startswith("Below is an instruction that describes a task.")
+    assert "### Input:\ngood morning" in _alpaca_text({"instruction": "Translate.", "input": "good morning",
+                                                        "output": "bonjour"})
+    assert _alpaca_text({"text": "ready-made", "instruction": "ignored"}) == "ready-made"
+
+
 def test_validate_messages_rules():
     ok = [{"role": "system", "content": "s"}, {"role": "user", "content": "u"},
           {"role": "assistant", "content": "", "tool_calls": [1]}, {"role": "tool", "content": "r1"},

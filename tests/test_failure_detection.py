@@ -123,3 +123,38 @@ def test_device_wait_on_a_flag_nobody_sets_runs_out_and_reports(cuda_device):
     _lib.lib().tb_wait_flags(flags.data_ptr(), 0, 2, ctypes.c_uint(7), status.data_ptr(), _lib.stream_ptr())
     torch.cuda.synchronize()
     assert status.item() == 0 and (torch.ones(4, device="cuda") * 2).sum().item() == 8
+
+
+def test_kernel_status_word_stops_the_training_loop(tmp_path, monkeypatch):
+    """A non-zero kernel status word (here: 'index out of bounds', written by hand into a stand-in word on the host)
+    makes the trainer raise at the next log step instead of carrying on with incomplete outputs."""
+    from titan_b200 import entry
+    from titan_b200.ops._lib import KernelError
+    from titan_b200.trainer import kernel_status
+    from titan_b200.trainer.trainer import Trainer
+
+    word = torch.zeros(1, dtype=torch.int32)
+    orig_init = kernel_status.KernelStatusMonitor.__init__
+    monkeypatch.setattr(kernel_status.KernelStatusMonitor, "__init__",
+                        lambda self, fn=None: orig_init(self, lambda: word))
+    orig_step = Trainer.train_step
+    steps = []
+
+    def step(self, it):
+        steps.append(self.step)
+        if self.step == 2:
+            word.fill_(6)   # what a kernel would have written
+        return orig_step(self, it)
+
+    monkeypatch.setattr(Trainer, "train_step", step)
+    for k, v in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29684"), ("RANK", "0"), ("WORLD_SIZE", "1")):
+        monkeypatch.setenv(k, v)
+    with pytest.raises(KernelError, match="index out of bounds"):
+        entry.main(["--module", "llama3", "--config", "llama3_debugmodel", "--comm.backend", "gloo",
+                    "--training.steps", "6", "--metrics.log_freq", "4", "--job.dump_folder", str(tmp_path)])
+    assert steps[-1] <= 3, steps   # seen by the non-blocking poll one step later, well before the log step
+    assert int(word.item()) == 0   # the word is cleared when it is reported
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -1,6 +1,8 @@
 """Hardware-free end-to-end tier: Llama-3 debug model, CPU/gloo, world_size=2 FSDP, fp32."""
 
 import os
+
+import torch
 import re
 import subprocess
 import sys
@@ -41,6 +43,12 @@ def test_llama3_debug_fsdp2_gloo_ten_steps_checkpoint_roundtrip(tmp_path):
     log2 = _run(base + ["--training.steps", "12"], port=29542)
     assert "loaded checkpoint" in log2 and "training starts at step 11" in log2
     assert len(_losses(log2)) == 2
+    # the per-rank token counter continues from the checkpoint: 12 steps x 4 sequences x 512 tokens
+    import torch.distributed.checkpoint as dcp
+
+    seen = {"train_state.ntokens_seen": torch.zeros((), dtype=torch.int64)}
+    dcp.load(seen, checkpoint_id=str(tmp_path / "checkpoint" / "step-12"))
+    assert int(seen["train_state.ntokens_seen"]) == 12 * 4 * 512, seen
     # a checkpoint written by 2 ranks loads into 1 rank (DCP reshards)
     log3 = _run(base + ["--training.steps", "13"], nproc=1)
     assert "training starts at step 13" in log3

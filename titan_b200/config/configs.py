@@ -194,6 +194,10 @@ class ParallelismConfig:
     EP ranks makes it dropless.  A routing beyond it stops the step with a kernel status (nothing is dropped)."""
     fsdp_fused_collectives: bool = False
     """Fuse FSDP all-gather into the consuming GEMM and cast/scale into reduce-scatter."""
+    fsdp_reduce_scatter: Literal["auto", "nccl", "peer_memory"] = "auto"
+    """Gradient reduce-scatter of FSDP2: `nccl` = stock (fp32 bucket through NCCL), `peer_memory` = bf16 bucket in
+    symmetric memory reduced by one kernel over NVLink peer loads, `auto` = `peer_memory` for CUDA jobs whose FSDP
+    group is 2..8 GPUs of one node."""
     dedicated_ep_group: bool = True
     """Give EP its own communicator so FSDP and EP traffic overlap (reference train.py:136-175)."""
 

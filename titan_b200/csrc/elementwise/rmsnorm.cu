@@ -221,6 +221,7 @@ TB_API int tb_rmsnorm_bwd(const void* g, const void* x, const void* w, const flo
 // Allocation-free variant (declaration and contract: rmsnorm_noalloc.h).
 #include "rmsnorm_noalloc.h"
 
+#include <atomic>
 #include <mutex>
 
 // Scratch for the per-CTA partial sums of dw.  In host code this name is only a handle for the symbol, not a
@@ -229,23 +230,27 @@ static __device__ __align__(256) float g_rmsnorm_noalloc_scratch[TB_RMSNORM_NOAL
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_noalloc_scratch_ptr[kMaxDevices] = {};
-std::mutex g_noalloc_mutex;
+std::atomic<float*> g_noalloc_scratch_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;  // taken only while a device's address is resolved for the first time
 
-// Device address of the scratch array on the current device; resolved on the first call per device.
+// Device address of the scratch array on the current device.  After the first call per device this is one
+// acquire load: no lock on the path of a latency-critical caller.
 int noalloc_scratch_for_current_device(float** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TB_NOALLOC_ERR_SYMBOL;
-  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
-  if (g_noalloc_scratch_ptr[dev] == nullptr) {
-    float* p = nullptr;
-    if (cudaGetSymbolAddress((void**)&p, g_rmsnorm_noalloc_scratch) != cudaSuccess || p == nullptr) {
-      (void)cudaGetLastError();
-      return TB_NOALLOC_ERR_SYMBOL;
+  float* p = g_noalloc_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    p = g_noalloc_scratch_ptr[dev].load(std::memory_order_relaxed);
+    if (p == nullptr) {
+      if (cudaGetSymbolAddress((void**)&p, g_rmsnorm_noalloc_scratch) != cudaSuccess || p == nullptr) {
+        (void)cudaGetLastError();
+        return TB_NOALLOC_ERR_SYMBOL;
+      }
+      g_noalloc_scratch_ptr[dev].store(p, std::memory_order_release);
     }
-    g_noalloc_scratch_ptr[dev] = p;
   }
-  *out = g_noalloc_scratch_ptr[dev];
+  *out = p;
   return 0;
 }
 

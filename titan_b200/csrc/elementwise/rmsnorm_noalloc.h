@@ -20,7 +20,11 @@
  *     before any work is queued; `tb_rmsnorm_bwd_noalloc_strerror` turns a code into text.
  *   - The function calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the device address of the scratch array (once per device, with
- *     that device current).  Make that first call before starting any stream capture.
+ *     that device current, under a lock); every later call reads the cached address without taking any lock.
+ *     Make that first call before starting any stream capture.
+ *   - The scratch used is the one of the CURRENT device (cudaGetDevice) at the time of the call: `stream` must
+ *     belong to that device.  A stream of another device is not detected and would run the kernel against the
+ *     wrong device's array.
  *   - All calls on a device share the one array, and it keeps the contents of the previous call.  The kernel
  *     overwrites every partial row it later reads, so nothing needs clearing, but two calls that overlap on
  *     the GPU (different streams, no ordering between them) race on the array: order them.

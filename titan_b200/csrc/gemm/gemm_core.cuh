@@ -142,6 +142,26 @@ __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, vol
   }
 }
 
+// Same wait for the roles that are NOT on the critical path of MMA issue (epilogue warps waiting for a finished
+// accumulator, the TMA producer waiting for a free stage).  Such a warp shares its scheduler with the MMA-issuing
+// warp or the producer; a hot polling loop would take issue slots from them, so it sleeps between polls.
+__device__ __forceinline__ bool wait_bounded_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                     unsigned sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  uint32_t it = 0;
+  while (true) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 255u) == 0u) {
+      if (*abort_flag != 0) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_NS) return false;
+    }
+  }
+}
+
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

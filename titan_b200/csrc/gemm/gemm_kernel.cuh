@@ -199,7 +199,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
               ay = s * p.M + tl.m0;
             }
           }
-          if (!wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          if (!wait_bounded_relaxed(&empty_bar[stage], phase ^ 1, abort_flag, 64)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
             ok = false; break;
           }
@@ -229,6 +229,18 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(BM, BN, p.is_bf16 != 0, p.a_mn != 0, p.b_mn != 0);
+      // Descriptors of stage 0, k-step 0.  This thread is alone on its warp: every instruction between two MMAs
+      // delays the next one, so the loop only adds stage / k offsets to the start-address field (low word).
+      // K-major : rows of 128 B, 8-row swizzle atoms 1024 B apart (SBO); a K step of 16 elements = +32 B
+      // MN-major: 64-element (128 B) runs along M/N, K rows 128 B apart, 8-row atoms 1024 B apart (SBO),
+      //           next 64-wide M/N block 8192 B further (LBO); a K step of 16 rows = +2048 B
+      const uint64_t da0 = p.a_mn ? make_smem_desc(smem_u32(smem_a), 8192, 1024, 2)
+                                  : make_smem_desc(smem_u32(smem_a), 16, 1024, 2);
+      const uint64_t db0 = p.b_mn ? make_smem_desc(smem_u32(smem_b), 8192, 1024, 2)
+                                  : make_smem_desc(smem_u32(smem_b), 16, 1024, 2);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t a_k = p.a_mn ? (2048u >> 4) : (32u >> 4), b_k = p.b_mn ? (2048u >> 4) : (32u >> 4);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t acc_phase = 0;
       for (int t = cta; t < num_tiles && ok; t += ncta) {
@@ -240,25 +252,20 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accum = 0;  // the first MMA of a tile overwrites the accumulator
         for (int kb = 0; kb < tl.kblocks; ++kb) {
           if (!wait_bounded(&full_bar[stage], phase, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA); }
             ok = false; break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
-          const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major : rows of 128 B, 8-row swizzle atoms 1024 B apart (SBO); a K step of 16 elements = +32 B
-            // MN-major: 64-element (128 B) runs along M/N, K rows 128 B apart, 8-row atoms 1024 B apart (SBO),
-            //           next 64-wide M/N block 8192 B further (LBO); a K step of 16 rows = +2048 B
-            const uint64_t da = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024, 2)
-                                       : make_smem_desc(sa + k * 32, 16, 1024, 2);
-            const uint64_t db = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024, 2)
-                                       : make_smem_desc(sb + k * 32, 16, 1024, 2);
-            umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)stage * (B_STAGE_BYTES >> 4);
+          umma_f16_lohi(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accum);
+          umma_f16_lohi(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
+          umma_f16_lohi(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, idesc, 1u);
+          umma_f16_lohi(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, idesc, 1u);
+          accum = 1u;
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -274,7 +281,7 @@ gemm_tcgen05_kernel(const __grid_constant__ AMaps amaps, const __grid_constant__
     for (int t = cta; t < num_tiles; t += ncta) {
       const Tile tl = get_tile(p, s_offs, t);
       if (tile_is_future(p, tl.m0, tl.n0)) continue;
-      bool ok = wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
+      bool ok = wait_bounded_relaxed(&tmem_full_bar[acc], acc_phase, abort_flag, 256);
       if (!ok && lane == 0 && *abort_flag == 0) {
         *abort_flag = 1;
         if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL);

@@ -112,6 +112,20 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, 
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_f16_pair_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                   uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // arrive on the barrier at `cluster_addr` once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
@@ -205,7 +219,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int brow = w.n0 + (int)cta_rank * HN;   // this CTA's rows of B (columns of the output)
         for (int kb = 0; kb < w.kblocks; ++kb) {
           const int k0 = (w.kb0 + kb) * BK;
-          if (!tbg::wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          if (!tbg::wait_bounded_relaxed(&empty_bar[stage], phase ^ 1, abort_flag, 64)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
             ok = false; break;
           }
@@ -240,6 +254,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
       const uint32_t idesc = make_idesc_f16(TM, TN, p.is_bf16 != 0, p.a_mn != 0, p.b_mn != 0);
+      // Descriptors of stage 0, k-step 0; everything that changes afterwards is the start-address field in the low
+      // word.  K-major : rows of 128 B, 8-row swizzle atoms 1024 B apart (SBO); a K step of 16 elements = +32 B.
+      // MN-major: 64-element (128 B) runs along M/N, K rows 128 B apart, 8-row atoms 1024 B apart (SBO), next
+      //           64-wide M/N block 8192 B further (LBO); a K step of 16 rows = +2048 B.
+      const uint64_t da0 = p.a_mn ? make_smem_desc(smem_u32(smem_a), 8192, 1024, 2)
+                                  : make_smem_desc(smem_u32(smem_a), 16, 1024, 2);
+      const uint64_t db0 = p.b_mn ? make_smem_desc(smem_u32(smem_b), 8192, 1024, 2)
+                                  : make_smem_desc(smem_u32(smem_b), 16, 1024, 2);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t a_k = p.a_mn ? (2048u >> 4) : (32u >> 4), b_k = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t a_k2 = 2 * a_k, a_k3 = 3 * a_k, b_k2 = 2 * b_k, b_k3 = 3 * b_k;
+      // empty barriers of both CTAs as shared::cluster addresses (a CTA's window is linear: + 8 bytes per stage)
+      const uint32_t eb0 = mapa(smem_u32(&empty_bar[0]), 0), eb1 = mapa(smem_u32(&empty_bar[0]), 1);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t acc_phase = 0;
       for (int u = pair; u < units && ok; u += npairs) {
@@ -250,26 +278,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TN;
+        uint32_t accum = 0;   // the first MMA of a unit overwrites the accumulator
         for (int kb = 0; kb < w.kblocks; ++kb) {
           if (!tbg::wait_bounded(&full_bar[stage], phase, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA); }
             ok = false; break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
-          const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // same canonical layouts as the single-CTA kernel; each CTA holds 128 rows of either operand
-            const uint64_t da = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024, 2)
-                                       : make_smem_desc(sa + k * 32, 16, 1024, 2);
-            const uint64_t db = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024, 2)
-                                       : make_smem_desc(sb + k * 32, 16, 1024, 2);
-            umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          const uint32_t eb = smem_u32(&empty_bar[stage]);
-          umma_commit_pair(mapa(eb, 0));
-          umma_commit_pair(mapa(eb, 1));
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)stage * (B_STAGE_BYTES >> 4);
+          umma_f16_pair_lohi(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accum);
+          umma_f16_pair_lohi(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
+          umma_f16_pair_lohi(d_tmem, a_lo + a_k2, a_hi, b_lo + b_k2, b_hi, idesc, 1u);
+          umma_f16_pair_lohi(d_tmem, a_lo + a_k3, a_hi, b_lo + b_k3, b_hi, idesc, 1u);
+          accum = 1u;
+          umma_commit_pair(eb0 + (uint32_t)stage * 8u);
+          umma_commit_pair(eb1 + (uint32_t)stage * 8u);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (ok) {
@@ -287,7 +311,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0; uint32_t acc_phase = 0;
     for (int u = pair; u < units; u += npairs) {
       const Unit w = get_unit(p, u);
-      bool ok = tbg::wait_bounded(&tmem_full_bar[acc], acc_phase, abort_flag);
+      bool ok = tbg::wait_bounded_relaxed(&tmem_full_bar[acc], acc_phase, abort_flag, 256);
       if (!ok && lane == 0 && *abort_flag == 0) {
         *abort_flag = 1;
         if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL);

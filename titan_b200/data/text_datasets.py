@@ -2,13 +2,16 @@
 
 A dataset is a registry entry ``name → (loader(path) → iterable of samples, text_of(sample) → str)``.  Built in:
 ``c4`` / ``c4_test`` / ``c4_validation`` read JSON-lines (``{"text": ...}``) or a `datasets` folder from
-``dataset_path``; ``text`` reads plain ``.txt`` files (one document per file or per blank-line block).  Documents are
+``dataset_path``; ``text`` reads plain ``.txt`` files (one document per file or per blank-line block);
+``enwiki-eod`` (encyclopedia articles, one per sample, each closed by the end-of-document token) and ``alpaca``
+(instruction / input / output records rendered with the Alpaca prompt, or their ready-made ``text`` column) read the
+same file formats and default to ``tests/assets/enwiki`` / ``tests/assets/alpaca`` when no path is given.  Documents are
 sharded round-robin over data-parallel ranks, tokenised with BOS/EOS, concatenated into a token buffer and cut into
 ``seq_len + 1 + extra`` windows (``extra`` = MTP look-ahead tokens); the position inside the stream (sample index and
 leftover token buffer) is checkpointed, so a resumed run sees the continuation of the same stream.
 
-Parity: the upstream `HuggingFaceTextDataLoader` with the reference's MTP sequence-length extension
-(torchtitan_npu/patches/torchtitan/hf_datasets.py:71-121).
+Parity: the upstream `HuggingFaceTextDataLoader` with the reference's extra datasets and MTP sequence-length
+extension (torchtitan_npu/patches/torchtitan/hf_datasets.py:35-121).
 """
 
 from __future__ import annotations
@@ -30,8 +33,9 @@ def register_text_dataset(name: str, loader: Callable[[str | None], Iterable], t
     _REGISTRY[name] = (loader, text_of)
 
 
-def _jsonl_or_hf(split: str):
+def _jsonl_or_hf(split: str, default_path: str | None = None):
     def load(path: str | None):
+        path = path or default_path
         if not path:
             raise FileNotFoundError("dataloader.dataset_path is required (there is no network access to a hub)")
         files = sorted(glob.glob(os.path.join(path, "**", "*.jsonl"), recursive=True) +
@@ -68,6 +72,25 @@ def _txt(path: str | None):
 for _name, _split in (("c4", "train"), ("c4_test", "train"), ("c4_validation", "validation")):
     register_text_dataset(_name, _jsonl_or_hf(_split), lambda s: s["text"])
 register_text_dataset("text", _txt, lambda s: s["text"])
+
+_ALPACA_WITH_INPUT = ("Below is an instruction that describes a task, paired with an input that provides further "
+                      "context. Write a response that appropriately completes the request.\n\n"
+                      "### Instruction:\n{instruction}\n\n### Input:\n{input}\n\n### Response:\n{output}")
+_ALPACA_NO_INPUT = ("Below is an instruction that describes a task. Write a response that appropriately completes "
+                    "the request.\n\n### Instruction:\n{instruction}\n\n### Response:\n{output}")
+
+
+def _alpaca_text(sample) -> str:
+    if sample.get("text"):
+        return sample["text"]
+    template = _ALPACA_WITH_INPUT if sample.get("input") else _ALPACA_NO_INPUT
+    return template.format(instruction=sample.get("instruction", ""), input=sample.get("input", ""),
+                           output=sample.get("output", ""))
+
+
+register_text_dataset("enwiki-eod", _jsonl_or_hf("train", os.path.join("tests", "assets", "enwiki")),
+                      lambda s: s["text"])
+register_text_dataset("alpaca", _jsonl_or_hf("train", os.path.join("tests", "assets", "alpaca")), _alpaca_text)
 
 
 class TextDataLoader:

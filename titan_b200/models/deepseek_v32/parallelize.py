@@ -144,9 +144,10 @@ def parallelize_deepseekv32(model: nn.Module, *, parallel_dims, training, model_
                        reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce], pp_enabled=pd.pp_enabled,
                        cpu_offload=training.enable_cpu_offload,
                        reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward,
+            reduce_scatter=parallelism.fsdp_reduce_scatter,
                        ep_degree=pd.ep if edp is not None else 1, edp_mesh=edp,
                        gradient_divide_factor=pd.fsdp_gradient_divide_factor)
     elif pd.dp_replicate_enabled:
-        apply_replicate(model, pd.get_mesh("dp_replicate"), param_dtype=DTYPE_MAP[training.mixed_precision_param],
+        apply_replicate(model, pd.get_mesh(("dp_replicate", "fsdp")), param_dtype=DTYPE_MAP[training.mixed_precision_param],
                         reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce])
     return model

@@ -49,7 +49,8 @@ def llama3_debugmodel_b200() -> TrainerConfig:
 
 
 def llama3_8b() -> TrainerConfig:
-    """Llama-3 8B pretraining: FSDP2, bf16 params/compute, fp32 reduce, seq 8192, local batch 1, no recomputation."""
+    """Llama-3 8B pretraining: FSDP2, bf16 params/compute, fp32 reduce, seq 8192, local batch 1, selective
+    activation checkpointing (contractions and attention kept, element-wise work recomputed), AdamW."""
     return TrainerConfig(
         model=ModelConfigRef(name="llama3", flavor="8B"),
         metrics=MetricsConfig(log_freq=10),
@@ -62,12 +63,19 @@ def llama3_8b() -> TrainerConfig:
         # and step instead of two (+1.4 % tokens/s on 8 GPUs)
         parallelism=ParallelismConfig(data_parallel_shard_degree=-1, fsdp_reshard_after_forward="never"),
         checkpoint=CheckpointConfig(interval=500),
-        # no activation checkpointing: an 8B model at seq 8192 peaks at 112 GB on ONE 180 GB GPU (weights, gradients
-        # and fp32 AdamW state are 96 GB of that; sharded runs need far less), so nothing is recomputed.  The selective
-        # rule that keeps every matmul output (`op_save_all_mm`) costs 2 % of the step and saves 9 GB.
-        activation_checkpoint=ActivationCheckpointConfig(mode="none", selective_ac_option="op_save_all_mm"),
+        # selective checkpointing with the rule that keeps every contraction (GEMM, attention) and recomputes norms,
+        # rotary embedding, SwiGLU and residual adds: about 2 % of the step for 9 GB.  `llama3_8b_noac` drops it (an 8B
+        # model at seq 8192 peaks at 112 GB on ONE 180 GB GPU, 96 GB of it weights, gradients and fp32 AdamW state).
+        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op_save_all_mm"),
         model_converters=ModelConvertersConfig(converters=_fused_converters()),
     )
+
+
+def llama3_8b_noac() -> TrainerConfig:
+    """`llama3_8b` without activation checkpointing (fits a 180 GB GPU even unsharded)."""
+    cfg = llama3_8b()
+    cfg.activation_checkpoint.mode = "none"
+    return cfg
 
 
 def llama3_8b_mxfp8() -> TrainerConfig:
@@ -83,12 +91,19 @@ def llama3_8b_mxfp8() -> TrainerConfig:
 
 
 def llama3_8b_baseline() -> TrainerConfig:
-    """Same model and shapes on library ops only (cuBLAS / SDPA / NCCL) with the upstream selective-AC rule (every
-    second matmul recomputed): the on-box comparator."""
+    """Same model, shapes, checkpointing rule and FSDP reshard policy as `llama3_8b` on library ops only (cuBLAS,
+    cuDNN SDPA, torch fused AdamW, NCCL collectives issued by FSDP2): the on-box comparator."""
     cfg = llama3_8b()
     cfg.model_converters = ModelConvertersConfig(converters=[])
     cfg.optimizer.implementation = "fused"
-    cfg.activation_checkpoint.mode = "selective"
+    cfg.parallelism.fsdp_fused_collectives = False
+    return cfg
+
+
+def llama3_8b_baseline_upstream_ac() -> TrainerConfig:
+    """`llama3_8b_baseline` with the upstream selective rule (every second matmul recomputed) and upstream's
+    reshard-after-forward default."""
+    cfg = llama3_8b_baseline()
     cfg.activation_checkpoint.selective_ac_option = "op"
     cfg.parallelism.fsdp_reshard_after_forward = "default"
     return cfg

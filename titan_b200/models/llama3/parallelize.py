@@ -155,11 +155,12 @@ def parallelize_llama(
             pp_enabled=parallel_dims.pp_enabled,
             cpu_offload=training.enable_cpu_offload,
             reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward,
+            reduce_scatter=parallelism.fsdp_reduce_scatter,
         )
     elif parallel_dims.dp_replicate_enabled:
         apply_replicate(
             model,
-            parallel_dims.get_mesh("dp_replicate"),
+            parallel_dims.get_mesh(("dp_replicate", "fsdp")),
             param_dtype=DTYPE_MAP[training.mixed_precision_param],
             reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce],
         )

@@ -45,8 +45,9 @@ def parallelize_vlm(model: nn.Module, *, parallel_dims, training, model_converte
         apply_fsdp(model, dp_mesh, param_dtype=DTYPE_MAP[training.mixed_precision_param],
                    reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce], pp_enabled=False,
                    cpu_offload=training.enable_cpu_offload,
-                   reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward)
+                   reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward,
+            reduce_scatter=parallelism.fsdp_reduce_scatter)
     elif pd.dp_replicate_enabled:
-        apply_replicate(model, pd.get_mesh("dp_replicate"), param_dtype=DTYPE_MAP[training.mixed_precision_param],
+        apply_replicate(model, pd.get_mesh(("dp_replicate", "fsdp")), param_dtype=DTYPE_MAP[training.mixed_precision_param],
                         reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce])
     return model

@@ -32,7 +32,7 @@ def _declare():
 
 def flash_attention_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
     """q [B, H, S, D] / k [B, Hkv, S, D] views of [B, S, H, D] storage."""
-    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and q.shape[2] % 128 == 0
+    return ((q.is_cuda or q.is_meta) and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and q.shape[2] % 128 == 0
             and q.shape[2] == k.shape[2] and q.shape[1] % k.shape[1] == 0)
 
 
@@ -45,22 +45,30 @@ def _library(q, k, v, scale):
     return F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=q.shape[1] != k.shape[1])
 
 
+def _flash_fwd_launch(q, k, v, scale):
+    """q [B, H, S, D], k / v [B, Hkv, S, D] → (out [B, H, S, D] as a view of [B, S, H, D] storage, lse [B, H, S])."""
+    _declare()
+    qb, kb, vb = _bshd(q), _bshd(k), _bshd(v)
+    B, S, H, D = qb.shape
+    out = torch.empty_like(qb)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    rc = _lib.lib().tb_flash_attn_fwd(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      B, S, H, kb.shape[2], D, float(scale), _lib.shared_status().ptr,
+                                      _lib.stream_ptr())
+    _lib.check(rc, "flash_attn_fwd")
+    return out.transpose(1, 2), lse
+
+
 class _FlashFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale):
-        _declare()
-        qb, kb, vb = _bshd(q), _bshd(k), _bshd(v)
-        B, S, H, D = qb.shape
-        out = torch.empty_like(qb)
-        lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
-        rc = _lib.lib().tb_flash_attn_fwd(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                          B, S, H, kb.shape[2], D, float(scale), _lib.shared_status().ptr,
-                                          _lib.stream_ptr())
-        _lib.check(rc, "flash_attn_fwd")
+        from titan_b200.ops.registry import ops
+
+        out, lse = ops.flash_attention_fwd(q, k, v, float(scale))
         ctx.save_for_backward(q, k, v)
         ctx.scale = scale
         ctx.lse = lse
-        return out.transpose(1, 2)  # [B, H, S, D] view
+        return out
 
     @staticmethod
     def backward(ctx, g):

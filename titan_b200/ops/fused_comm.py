@@ -221,6 +221,28 @@ def castscale_reduce_scatter_baseline(bucket, scale, out_dtype, group):
     return out.to(out_dtype)
 
 
+def grad_slots(group, nbytes: int) -> _Slots:
+    """The two alternating bucket slots of the gradient reduce-scatter in `group`'s symmetric workspace, each at
+    least ``nbytes`` large (creating or growing the workspace is a collective over the group)."""
+    return _slots(group, "grad", nbytes, CH_GRAD_READY, CH_GRAD_DONE)
+
+
+def reduce_scatter_slot(slot, numel: int, in_dtype: torch.dtype, out: torch.Tensor, scale: float) -> None:
+    """Reduce-scatter a bucket that already sits in a slot from `grad_slots().acquire()`: ``slot`` is
+    ``(slots, index, byte offset)``.  Runs on the current stream: publish "my bucket is complete", wait for every
+    peer's, reduce this rank's chunk from all buckets into ``out``, then mark the slot as read."""
+    slots, index, off = slot
+    ws = slots.ws
+    epoch = ws.next_epoch(CH_GRAD_READY)
+    ws.signal(CH_GRAD_READY, epoch)
+    ws.wait(CH_GRAD_READY, epoch)
+    rc = _lib.lib().tb_castscale_rs(ws.ptr_array(off), out.data_ptr(), numel // ws.world, ws.rank, ws.world,
+                                    float(scale), _lib.dtype_code(in_dtype), _lib.dtype_code(out.dtype),
+                                    _lib.stream_ptr())
+    _lib.check(rc, "castscale_rs")
+    slots.release(index)
+
+
 def castscale_reduce_scatter(bucket: torch.Tensor, scale: float, out_dtype: torch.dtype = torch.float32,
                              group=None) -> torch.Tensor:
     """``scale · Σ_ranks bucket`` restricted to this rank's chunk, fp32 accumulation, cast to `out_dtype`."""

@@ -99,12 +99,19 @@ def _aligned_copy(t: torch.Tensor) -> torch.Tensor:
     return buf[:, :cols]
 
 
+def _op():
+    """The dispatcher ops (`torch.ops.titan_b200`): selective AC, `torch.compile` and meta runs see these."""
+    from titan_b200.ops import registry
+
+    return registry.ops
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
+        y = _op().gemm(x2, w)
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -116,15 +123,16 @@ class _LinearFn(torch.autograd.Function):
             g2 = g2.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(g2, w, b_mn=True).view(x.shape)
+            dx = _op().gemm(g2, w, False, True).view(x.shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(g2, x2, a_mn=True, b_mn=True)
+            dw = _op().gemm(g2, x2, True, True)
         return dx, dw
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T (+ bias)`` on the tcgen05 kernel (CUDA bf16/fp16), else `F.linear`."""
-    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and x.shape[-1] % 8 == 0 \
+    if (x.is_cuda or x.is_meta) and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype \
+            and x.shape[-1] % 8 == 0 \
             and w.shape[0] % 8 == 0:
         y = _LinearFn.apply(x, w)
         return y if bias is None else y + bias

@@ -289,17 +289,21 @@ class _GroupedLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, offs):
         x, w = x.contiguous(), w.contiguous()
         ctx.save_for_backward(x, w, offs)
-        return _gg_m(x, w, offs, w.shape[1], False)
+        from titan_b200.ops.registry import ops
+
+        return ops.grouped_gemm_m(x, w, offs, w.shape[1], False)
 
     @staticmethod
     def backward(ctx, g):
         x, w, offs = ctx.saved_tensors
         g = g.contiguous()
         dx = dw = None
+        from titan_b200.ops.registry import ops
+
         if ctx.needs_input_grad[0]:
-            dx = _gg_m(g, w, offs, w.shape[2], True)        # dy · W[g]      (W stored [N, K] = "[K', N']")
+            dx = ops.grouped_gemm_m(g, w, offs, w.shape[2], True)   # dy · W[g]   (W stored [N, K] = "[K', N']")
         if ctx.needs_input_grad[1]:
-            dw = _gg_k(g, x, offs, w.shape[0])              # dyᵀ · x per group
+            dw = ops.grouped_gemm_k(g, x, offs, w.shape[0])         # dyᵀ · x per group
         return dx, dw, None
 
 

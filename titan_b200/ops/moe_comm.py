@@ -220,14 +220,3 @@ def moe_forward_ep(x2, gate, idx, experts, group, *, base=None, score_before_exp
     xp = _EPDispatch.apply(x2, None, ep)
     yp = experts(xp, ep.offs_local, padded=True)
     return _EPCombine.apply(yp, gate, base, ep)
-
-
-# entry points used by the `FusedExpertParallel` style when the MoE layer itself is not converted
-def dispatch(routed_input, num_tokens_per_expert, group):
-    raise NotImplementedError(
-        "FusedExpertParallel needs the `b200_moe_dispatch` converter: the fused dispatch works on (token, slot) "
-        "pairs and a device-side plan, not on the pre-sorted rows of the NCCL path")
-
-
-def combine(routed_output, ticket, group):
-    raise NotImplementedError("see `dispatch`")

@@ -65,18 +65,22 @@ def rms_norm_bwd(g: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps):
-        y, rstd = rms_norm_fwd(x, w, eps)
+        from titan_b200.ops.registry import ops
+
+        y, rstd = ops.rms_norm_fwd(x, w, eps)
         ctx.save_for_backward(x, w, rstd)
         return y
 
     @staticmethod
     def backward(ctx, g):
+        from titan_b200.ops.registry import ops
+
         x, w, rstd = ctx.saved_tensors
-        dx, dw = rms_norm_bwd(g, x, w, rstd)
+        dx, dw = ops.rms_norm_bwd(g, x, w, rstd)
         return dx, dw, None
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    if x.is_cuda:
+    if x.is_cuda or x.is_meta:  # meta tensors take the operator's fake kernel (shapes and saved tensors as on a GPU)
         return _RMSNormFn.apply(x, w, eps)
     return F.rms_norm(x, (x.shape[-1],), w, eps)

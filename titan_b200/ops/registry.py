@@ -1,0 +1,229 @@
+"""Dispatcher registration of the sm_100a kernels: ``torch.ops.titan_b200.*``.
+
+Every kernel launcher is also a PyTorch operator with a CUDA implementation (the ctypes call into
+``libtitan_b200.so``) and a fake (meta) implementation that only computes output shapes.  That buys three things
+a bare ctypes call cannot give:
+
+* **selective activation checkpointing** sees the op: the save list (`parallel.activation_checkpoint`) names
+  ``titan_b200::gemm`` and the other contraction ops, so a checkpointed block keeps their outputs instead of running
+  every GEMM a second time in backward;
+* **`torch.compile(fullgraph=True)`** traces through a converted model (Dynamo inlines the autograd functions of
+  `titan_b200.ops.*` and finds operators with fake kernels inside);
+* **meta-device runs** (the memory simulator, `--comm.mode fake_backend` dry runs) execute converted models
+  without touching the GPU library.
+
+The autograd wiring stays in the `torch.autograd.Function` classes of the op modules; they call the operators
+registered here.  The counterpart in the reference is its meta registration of the fused NPU ops
+(torchtitan_npu/patches/torch_npu/_meta_registrations.py:9-70).
+"""
+
+from __future__ import annotations
+
+import torch
+
+__all__ = ["ops", "CONTRACTION_OPS"]
+
+_LIB = torch.library.Library("titan_b200", "DEF")
+ops = torch.ops.titan_b200
+
+
+def _define(schema: str, cuda_impl, fake_impl) -> None:
+    name = schema.split("(", 1)[0]
+    _LIB.define(schema)
+    _LIB.impl(name, cuda_impl, "CUDA")
+    torch.library.register_fake(f"titan_b200::{name}", fake_impl, lib=_LIB)
+
+
+# ---------------------------------------------------------------------------------------------- GEMM
+def _gemm_cuda(a, b, a_mn=False, b_mn=False, out_fp32=False):
+    from titan_b200.ops.gemm import gemm
+
+    return gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32 if out_fp32 else None)
+
+
+def _gemm_fake(a, b, a_mn=False, b_mn=False, out_fp32=False):
+    m = a.shape[1] if a_mn else a.shape[0]
+    n = b.shape[1] if b_mn else b.shape[0]
+    return a.new_empty((m, n), dtype=torch.float32 if out_fp32 else a.dtype)
+
+
+_define("gemm(Tensor a, Tensor b, bool a_mn=False, bool b_mn=False, bool out_fp32=False) -> Tensor", _gemm_cuda,
+        _gemm_fake)
+
+
+def _grouped_gemm_m_cuda(a, b, offs, n, b_mn):
+    from titan_b200.ops.moe import _gg_m
+
+    return _gg_m(a, b, offs, n, b_mn)
+
+
+def _grouped_gemm_m_fake(a, b, offs, n, b_mn):
+    return a.new_empty((a.shape[0], n))
+
+
+_define("grouped_gemm_m(Tensor a, Tensor b, Tensor offs, int n, bool b_mn) -> Tensor", _grouped_gemm_m_cuda,
+        _grouped_gemm_m_fake)
+
+
+def _grouped_gemm_k_cuda(a, b, offs, groups):
+    from titan_b200.ops.moe import _gg_k
+
+    return _gg_k(a, b, offs, groups)
+
+
+def _grouped_gemm_k_fake(a, b, offs, groups):
+    return a.new_empty((groups, a.shape[1], b.shape[1]))
+
+
+_define("grouped_gemm_k(Tensor a, Tensor b, Tensor offs, int groups) -> Tensor", _grouped_gemm_k_cuda,
+        _grouped_gemm_k_fake)
+
+
+# ---------------------------------------------------------------------------------------------- RMSNorm
+def _rms_fwd_cuda(x, w, eps):
+    from titan_b200.ops.norm import rms_norm_fwd
+
+    return rms_norm_fwd(x, w, eps)
+
+
+def _rms_fwd_fake(x, w, eps):
+    rows = x.numel() // x.shape[-1] if x.shape[-1] else 0
+    return torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty((rows,), dtype=torch.float32)
+
+
+_define("rms_norm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)", _rms_fwd_cuda, _rms_fwd_fake)
+
+
+def _rms_bwd_cuda(g, x, w, rstd):
+    from titan_b200.ops.norm import rms_norm_bwd
+
+    return rms_norm_bwd(g, x, w, rstd)
+
+
+def _rms_bwd_fake(g, x, w, rstd):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(w)
+
+
+_define("rms_norm_bwd(Tensor g, Tensor x, Tensor w, Tensor rstd) -> (Tensor, Tensor)", _rms_bwd_cuda, _rms_bwd_fake)
+
+
+# ---------------------------------------------------------------------------------------------- SwiGLU
+def _swiglu_fwd_cuda(gate, up, score, rows, hidden, pitch, limit):
+    from titan_b200.ops.swiglu import _fwd
+
+    return _fwd(gate, up if up is not None else gate[:, hidden:], score, rows, hidden, pitch, limit)
+
+
+def _swiglu_fwd_fake(gate, up, score, rows, hidden, pitch, limit):
+    return gate.new_empty((rows, hidden))
+
+
+_define("swiglu_fwd(Tensor gate, Tensor? up, Tensor? score, int rows, int hidden, int pitch, float limit) -> Tensor",
+        _swiglu_fwd_cuda, _swiglu_fwd_fake)
+
+
+def _swiglu_bwd_cuda(gout, gate, up, score, rows, hidden, pitch, limit):
+    from titan_b200.ops.swiglu import _bwd
+
+    return _bwd(gout, gate, up, score, rows, hidden, pitch, limit)
+
+
+def _swiglu_bwd_fake(gout, gate, up, score, rows, hidden, pitch, limit):
+    dgate = torch.empty_like(gate)
+    dup = torch.empty_like(up) if up is not None else gate.new_empty((0,))
+    dscore = gout.new_empty((rows,), dtype=torch.float32) if score is not None else gout.new_empty((0,))
+    return dgate, dup, dscore
+
+
+_define("swiglu_bwd(Tensor gout, Tensor gate, Tensor? up, Tensor? score, int rows, int hidden, int pitch, "
+        "float limit) -> (Tensor, Tensor, Tensor)", _swiglu_bwd_cuda, _swiglu_bwd_fake)
+
+
+# ---------------------------------------------------------------------------------------------- RoPE
+def _rope_cuda(x, cache, positions, interleaved, inverse):
+    from titan_b200.ops.rope import _launch
+
+    return _launch(x, cache, positions, interleaved, inverse)
+
+
+def _rope_fake(x, cache, positions, interleaved, inverse):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+_define("rope(Tensor x, Tensor cache, Tensor? positions, bool interleaved, bool inverse) -> Tensor", _rope_cuda,
+        _rope_fake)
+
+
+# ---------------------------------------------------------------------------------------------- cross-entropy
+def _ce_fwd_cuda(x, labels, ignore_index):
+    from titan_b200.ops.cross_entropy import _fwd_rows
+
+    return _fwd_rows(x, labels, ignore_index)
+
+
+def _ce_fwd_fake(x, labels, ignore_index):
+    rows = x.shape[0]
+    return x.new_empty((rows,), dtype=torch.float32), x.new_empty((rows,), dtype=torch.float32)
+
+
+_define("cross_entropy_fwd(Tensor x, Tensor labels, int ignore_index) -> (Tensor, Tensor)", _ce_fwd_cuda, _ce_fwd_fake)
+
+
+def _ce_bwd_cuda(x, labels, lse, gscale, ignore_index):
+    from titan_b200.ops.cross_entropy import _bwd_rows
+
+    return _bwd_rows(x, labels, lse, gscale, ignore_index, False)
+
+
+def _ce_bwd_fake(x, labels, lse, gscale, ignore_index):
+    return torch.empty_like(x)
+
+
+_define("cross_entropy_bwd(Tensor x, Tensor labels, Tensor lse, Tensor gscale, int ignore_index) -> Tensor",
+        _ce_bwd_cuda, _ce_bwd_fake)
+
+
+def _ce_bwd_inplace_cuda(x, labels, lse, gscale, ignore_index):
+    from titan_b200.ops.cross_entropy import _bwd_rows
+
+    _bwd_rows(x, labels, lse, gscale, ignore_index, True)
+
+
+def _ce_bwd_inplace_fake(x, labels, lse, gscale, ignore_index):
+    return None
+
+
+# the gradient overwrites the logits (the vocabulary-sized tensor is not held twice)
+_define("cross_entropy_bwd_(Tensor(a!) x, Tensor labels, Tensor lse, Tensor gscale, int ignore_index) -> ()",
+        _ce_bwd_inplace_cuda, _ce_bwd_inplace_fake)
+
+
+# ---------------------------------------------------------------------------------------------- flash attention
+def _flash_fwd_cuda(q, k, v, scale):
+    from titan_b200.ops.flash_attention import _flash_fwd_launch
+
+    return _flash_fwd_launch(q, k, v, scale)
+
+
+def _flash_fwd_fake(q, k, v, scale):
+    b, h, s, d = q.shape
+    return q.new_empty((b, s, h, v.shape[-1])).transpose(1, 2), q.new_empty((b, h, s), dtype=torch.float32)
+
+
+_define("flash_attention_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)", _flash_fwd_cuda,
+        _flash_fwd_fake)
+
+
+# Ops whose outputs selective activation checkpointing keeps (contractions: recomputing them costs real FLOPs).
+CONTRACTION_OPS = (ops.gemm.default, ops.grouped_gemm_m.default, ops.grouped_gemm_k.default,
+                   ops.flash_attention_fwd.default)
+
+
+def _register_with_sac() -> None:
+    from titan_b200.parallel.activation_checkpoint import register_sac_save_op
+
+    for op in CONTRACTION_OPS:
+        register_sac_save_op(op)
+
+
+_register_with_sac()

@@ -45,13 +45,17 @@ class _RopeFn(torch.autograd.Function):
         ctx.interleaved, ctx.inverse = interleaved, inverse
         ctx.save_for_backward(cache, positions if positions is not None else torch.empty(0))
         ctx.has_pos = positions is not None
-        return _launch(x, cache, positions, interleaved, inverse)
+        from titan_b200.ops.registry import ops
+
+        return ops.rope(x, cache, positions, interleaved, inverse)
 
     @staticmethod
     def backward(ctx, g):
         cache, pos = ctx.saved_tensors
         # the rotation is orthogonal: its transpose is the rotation by the negative angle
-        return _launch(g, cache, pos if ctx.has_pos else None, ctx.interleaved, not ctx.inverse), None, None, None, None
+        from titan_b200.ops.registry import ops
+
+        return ops.rope(g, cache, pos if ctx.has_pos else None, ctx.interleaved, not ctx.inverse), None, None, None, None
 
 
 def _launch(x: torch.Tensor, cache: torch.Tensor, positions, interleaved: bool, inverse: bool) -> torch.Tensor:
@@ -79,7 +83,7 @@ def _launch(x: torch.Tensor, cache: torch.Tensor, positions, interleaved: bool, 
 def rope_apply(x: torch.Tensor, cache: torch.Tensor, positions=None, *, interleaved: bool = True,
                inverse: bool = False) -> torch.Tensor:
     """Rotate `x` [B, S, H, D]; CUDA → kernel, CPU → oracle."""
-    if not x.is_cuda:
+    if not (x.is_cuda or x.is_meta):
         if interleaved:
             c = cache if cache.is_complex() else torch.view_as_complex(cache.float().reshape(cache.shape[0], -1, 2))
             return rope_ref.apply_rotary_emb_single_complex(x, c, positions, inverse=inverse)

@@ -36,6 +36,23 @@ def _fwd(gate, up, score, rows, H, in_pitch, limit):
     return out
 
 
+def _bwd(gout, gate, up, score, rows, H, pitch, limit):
+    """→ (dgate, dup, dscore).  ``up is None``: gate and up are the halves of one [rows, 2H] tensor and the gradient
+    comes back as one tensor of that shape in ``dgate`` (``dup`` is empty).  Without a score ``dscore`` is empty."""
+    if up is None:
+        dgate = torch.empty_like(gate)
+        up_, dup_, dup = gate[:, H:], dgate[:, H:], gate.new_empty(0)
+    else:
+        dgate, dup = torch.empty_like(gate), torch.empty_like(up)
+        up_, dup_ = up, dup
+    dscore = torch.empty(rows, dtype=torch.float32, device=gout.device) if score is not None else gout.new_empty(0)
+    rc = _lib.lib().tb_swiglu_bwd(gout.data_ptr(), gate.data_ptr(), up_.data_ptr(), dgate.data_ptr(), dup_.data_ptr(),
+                                  _lib.ptr(score), dscore.data_ptr() if score is not None else None, rows, H, pitch, H,
+                                  float(limit), _lib.dtype_code(gout.dtype), _lib.stream_ptr())
+    _lib.check(rc, "swiglu_bwd")
+    return dgate, dup, dscore
+
+
 class _SwiGLUFn(torch.autograd.Function):
     """`fused` = gate and up are the two halves of one [rows, 2H] tensor."""
 
@@ -55,26 +72,21 @@ class _SwiGLUFn(torch.autograd.Function):
             score = score.reshape(-1).float().contiguous()
         ctx.meta = (rows, H, pitch, float(limit), fused, score is not None)
         ctx.score32 = score
-        return _fwd(gate, up, score, rows, H, pitch, limit)
+        from titan_b200.ops.registry import ops
+
+        return ops.swiglu_fwd(gate, None if fused else up, score, rows, H, pitch, float(limit))
 
     @staticmethod
     def backward(ctx, gout):
         rows, H, pitch, limit, fused, has_score = ctx.meta
         gout = gout.contiguous()
         saved = ctx.saved_tensors  # read once: activation checkpointing forbids a second unpack
+        from titan_b200.ops.registry import ops
+
         if fused:
-            x = saved[0]
-            gate, up = x, x[:, H:]
-            dx = torch.empty_like(x)
-            dgate, dup = dx, dx[:, H:]
+            dx, _, dscore = ops.swiglu_bwd(gout, saved[0], None, ctx.score32, rows, H, pitch, limit)
         else:
-            gate, up = saved[0], saved[1]
-            dgate, dup = torch.empty_like(gate), torch.empty_like(up)
-        dscore = torch.empty(rows, dtype=torch.float32, device=gout.device) if has_score else None
-        rc = _lib.lib().tb_swiglu_bwd(gout.data_ptr(), gate.data_ptr(), up.data_ptr(), dgate.data_ptr(), dup.data_ptr(),
-                                      _lib.ptr(ctx.score32), _lib.ptr(dscore), rows, H, pitch, H, limit,
-                                      _lib.dtype_code(gout.dtype), _lib.stream_ptr())
-        _lib.check(rc, "swiglu_bwd")
+            dgate, dup, dscore = ops.swiglu_bwd(gout, saved[0], saved[1], ctx.score32, rows, H, pitch, limit)
         ds = None
         if has_score:
             orig = saved[-1]
@@ -86,7 +98,7 @@ class _SwiGLUFn(torch.autograd.Function):
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor, score: torch.Tensor | None = None, limit: float = 0.0):
     """silu(gate) * up over the last dim; any leading shape."""
-    if not gate.is_cuda:
+    if not (gate.is_cuda or gate.is_meta):
         return swiglu_ref(gate.reshape(-1, gate.shape[-1]), up.reshape(-1, up.shape[-1]), score, limit).view(gate.shape)
     shape = gate.shape
     out = _SwiGLUFn.apply(gate.reshape(-1, shape[-1]), up.reshape(-1, shape[-1]), score, limit, False)
@@ -95,7 +107,7 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor, score: torch.Tensor | None = No
 
 def swiglu_fused(x13: torch.Tensor, score: torch.Tensor | None = None, limit: float = 0.0):
     """`x13` [rows, 2H] = gate | up → [rows, H]."""
-    if not x13.is_cuda:
+    if not (x13.is_cuda or x13.is_meta):
         H = x13.shape[-1] // 2
         return swiglu_ref(x13[..., :H], x13[..., H:], score, limit)
     return _SwiGLUFn.apply(x13, None, score, limit, True)

@@ -115,6 +115,7 @@ def apply_ac(model: nn.Module, ac_config, *, layers_attr: str = "layers") -> Non
     """Wrap each transformer block of ``model.<layers_attr>`` in place."""
     if ac_config.mode == "none":
         return
+    from titan_b200.ops import registry  # noqa: F401  (adds the sm_100a contraction ops to the save list)
     force_shapes: set[tuple[int, ...]] = set()
     for fqn in ac_config.per_op_sac_force_recompute_mm_shapes_by_fqns:
         for name, sub in model.named_modules():

@@ -8,3 +8,4 @@ from titan_b200.parallel.context_parallel.registry import (  # noqa: F401
     registered_strategies,
 )
 from titan_b200.parallel.context_parallel import ulysses  # noqa: F401,E402  (registers itself)
+from titan_b200.parallel.context_parallel import varlen_cp  # noqa: F401,E402  (registers itself)

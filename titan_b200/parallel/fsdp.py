@@ -70,9 +70,11 @@ def apply_fsdp(
     layers_attr: str = "layers",
     extra_modules: tuple[str, ...] = (),
     ignored_params: set | None = None,
+    reduce_scatter: str = "nccl",
 ) -> nn.Module:
     """Shard `model` block by block over `dp_mesh` (1-D = FSDP, 2-D = HSDP).  ``ignored_params``: parameters that
-    another mechanism already shards (the fused-collective linears) and FSDP2 must leave alone."""
+    another mechanism already shards (the fused-collective linears) and FSDP2 must leave alone.  ``reduce_scatter``:
+    `nccl`, `peer_memory` or `auto` (see `titan_b200.parallel.fsdp_comm`)."""
     mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
     cfg = {"mesh": dp_mesh, "mp_policy": mp}
     if ignored_params:
@@ -118,15 +120,29 @@ def apply_fsdp(
     fully_shard(model, **cfg, reshard_after_forward=reshard)
     if gradient_divide_factor is not None and ep_degree > 1:
         model.set_gradient_divide_factor(float(gradient_divide_factor))
+    if not cpu_offload:
+        from titan_b200.parallel.fsdp_comm import install_peer_reduce_scatter, peer_reduce_scatter_wanted
+
+        if peer_reduce_scatter_wanted(reduce_scatter, dp_mesh, dp_mesh.device_type):
+            model._peer_reduce_scatter = install_peer_reduce_scatter(model, dp_mesh, wire_dtype=param_dtype)
     return model
 
 
 def apply_replicate(model: nn.Module, dp_mesh: DeviceMesh, *, param_dtype=torch.bfloat16,
                     reduce_dtype=torch.float32, layers_attr: str = "layers") -> nn.Module:
-    """Pure data parallel expressed as FSDP2 that never reshards (replicate-with-FSDP)."""
+    """Pure data parallel expressed as FSDP2 that never reshards (replicate-with-FSDP).
+
+    ``dp_mesh`` is the 2-D ``(dp_replicate, fsdp)`` mesh with a trivial shard axis, sliced from a mesh that covers
+    the whole job (`ParallelDims.get_mesh(("dp_replicate", "fsdp"))`): every rank then creates the same process
+    groups in the same order.  A 1-D mesh is accepted only when it spans the whole job, where building the 2-D
+    layout locally is equally collective; with tp / pp / cp ranks alongside, per-rank sub-meshes would call
+    `new_group` with rank lists that differ between ranks."""
     mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
     if dp_mesh.ndim == 1:
-        # a (replicate, 1) mesh: all-reduce over the replicate axis, trivial shard axis
+        import torch.distributed as dist
+
+        if dist.is_initialized() and dp_mesh.size() != dist.get_world_size():
+            raise ValueError("apply_replicate needs the 2-D (dp_replicate, fsdp) mesh when other parallel axes exist")
         ranks = dp_mesh.mesh.view(-1, 1)
         dp_mesh = DeviceMesh(dp_mesh.device_type, ranks, mesh_dim_names=("dp_replicate", "dp_shard_1"))
     for _, block in _blocks(model, layers_attr):

@@ -1,0 +1,156 @@
+"""FSDP2 gradient reduce-scatter over NVLink peer memory (``parallelism.fsdp_reduce_scatter``).
+
+Stock FSDP2 reduces gradients in three passes per parameter group: the bf16 gradients are copied AND cast into one
+fp32 bucket, NCCL reduce-scatters that bucket (4 bytes per element on the wire, kernels that hold SMs while the
+backward GEMMs run), and the fp32 result is handed on.  `PeerMemoryReduceScatter` plugs into FSDP2's communication
+hook (`FSDPModule.set_custom_reduce_scatter`) and shortens this to
+
+    copy-in  bf16 gradients → bf16 bucket that lives in symmetric memory (no cast, 2 bytes per element)
+    reduce   ONE kernel reads this rank's chunk of every peer's bucket with plain peer loads, adds in fp32,
+             scales and writes the fp32 (or bf16) shard                              (`tb_castscale_rs`)
+
+so half the bytes cross NVLink, the cast pass disappears and the sum is still accumulated in fp32 from the same
+bf16 inputs NCCL would have been given.  Two bucket slots alternate; a slot is reused only after every peer has
+signalled that it finished reading it (epoch flags, bounded waits that report through the kernel status word).
+
+FSDP2 asks the hook for memory twice per reduction (`allocate`: first the bucket, then the output) and both
+requests name the reduce dtype; the bucket is handed out in the wire dtype (the dtype of the gradients) instead.
+On CPU / gloo and for reductions the kernel does not cover (other dtypes, a pre-multiplied NCCL op) the hook
+falls back to a library reduce-scatter with the same result.
+
+Parity: the FSDP2 collectives the reference inherits (torchtitan_npu/models/deepseek_v32/parallelize.py:255-284).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.distributed.fsdp._fully_shard._fsdp_api import ReduceScatter
+
+__all__ = ["PeerMemoryReduceScatter", "install_peer_reduce_scatter", "peer_reduce_scatter_wanted", "max_bucket_numel"]
+
+
+class PeerMemoryReduceScatter(ReduceScatter):
+    def __init__(self, group, wire_dtype: torch.dtype = torch.bfloat16, reserve_numel: int = 0):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.wire_dtype = wire_dtype
+        self._bucket_next = True       # FSDP2 allocates the bucket first, then the output, per reduction
+        self._slot = None              # (slots, slot index, byte offset) of the bucket handed out last
+        self.calls = 0                 # reductions done by the peer-memory kernel (tests, bench records)
+        self.fallback_calls = 0
+        if reserve_numel and torch.cuda.is_available():
+            from titan_b200.ops import fused_comm
+
+            # size the symmetric workspace once, for the largest parameter group: growing it later is a collective
+            fused_comm.grad_slots(group, reserve_numel * torch.empty((), dtype=wire_dtype).element_size())
+
+    # ---- memory
+    def allocate(self, size, *, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        numel = math.prod(int(s) for s in size)
+        if not self._bucket_next:
+            self._bucket_next = True
+            return torch.empty(numel, dtype=dtype, device=device)
+        self._bucket_next = False
+        self._slot = None
+        if device.type != "cuda":
+            return torch.empty(numel, dtype=self.wire_dtype, device=device)
+        from titan_b200.ops import fused_comm
+
+        slots = fused_comm.grad_slots(self.group, numel * torch.empty((), dtype=self.wire_dtype).element_size())
+        slot, off = slots.acquire()   # the stream waits here until the peers have finished with this slot's last use
+        self._slot = (slots, slot, off)
+        return slots.ws.view(off, (numel,), self.wire_dtype)
+
+    # ---- reduction
+    def _scale_for(self, op) -> float | None:
+        if op == dist.ReduceOp.SUM:
+            return 1.0
+        if op == dist.ReduceOp.AVG:
+            return 1.0 / self.world
+        return None   # a pre-multiplied sum object: library path
+
+    def __call__(self, output_tensor: torch.Tensor, input_tensor: torch.Tensor, group, op, async_op: bool = False):
+        scale = self._scale_for(op)
+        slot = self._slot
+        self._slot = None
+        kernel_ok = (slot is not None and scale is not None and input_tensor.is_cuda
+                     and input_tensor.dtype in (torch.bfloat16, torch.float32)
+                     and output_tensor.dtype in (torch.bfloat16, torch.float32)
+                     and input_tensor.numel() == output_tensor.numel() * self.world
+                     and (output_tensor.numel() * input_tensor.element_size()) % 16 == 0)
+        if kernel_ok:
+            from titan_b200.ops import fused_comm
+
+            fused_comm.reduce_scatter_slot(slot, input_tensor.numel(), input_tensor.dtype, output_tensor, scale)
+            self.calls += 1
+            return None
+        if slot is not None:
+            slot[0].release(slot[1])
+        self.fallback_calls += 1
+        wide = input_tensor if input_tensor.dtype == output_tensor.dtype else input_tensor.to(output_tensor.dtype)
+        return dist.reduce_scatter_tensor(output=output_tensor, input=wide, group=group, op=op, async_op=async_op)
+
+
+def max_bucket_numel(model: nn.Module, world: int) -> int:
+    """Largest gradient bucket FSDP2 will build for `model`: per FSDP parameter group, every parameter padded on
+    dim 0 to a multiple of ``world``."""
+    from torch.distributed.fsdp import FSDPModule
+
+    best = 0
+    seen: set[int] = set()
+    # inner groups first: a parameter belongs to the innermost FSDP module that contains it
+    mods = [m for m in model.modules() if isinstance(m, FSDPModule)]
+    for m in reversed(mods):
+        total = 0
+        for p in m.parameters():
+            if id(p) in seen:
+                continue
+            seen.add(id(p))
+            shape = tuple(p.shape)
+            rows = shape[0] if shape else 1
+            rest = math.prod(shape[1:]) if len(shape) > 1 else 1
+            total += -(-rows // world) * world * rest
+        best = max(best, total)
+    return best
+
+
+def peer_reduce_scatter_wanted(setting: str, dp_mesh, device_type: str) -> bool:
+    """``auto``: on for CUDA jobs whose FSDP group sits inside one NVSwitch domain (2..8 ranks of one node)."""
+    if setting == "nccl":
+        return False
+    shard_mesh = dp_mesh if dp_mesh.ndim == 1 else dp_mesh[dp_mesh.mesh_dim_names[-1]]
+    n = shard_mesh.size()
+    import os
+
+    one_node = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1"))) == \
+        int(os.environ.get("WORLD_SIZE", "1"))
+    ok = device_type == "cuda" and 2 <= n <= 8 and one_node
+    if setting == "peer_memory" and not ok and device_type == "cuda":
+        raise ValueError("fsdp_reduce_scatter=peer_memory needs an FSDP group of 2..8 GPUs on one node")
+    return ok or setting == "peer_memory"
+
+
+def install_peer_reduce_scatter(model: nn.Module, dp_mesh, wire_dtype: torch.dtype) -> PeerMemoryReduceScatter | None:
+    """Give every FSDP module of `model` whose shard group is ``dp_mesh``'s shard axis the peer-memory hook."""
+    from torch.distributed.fsdp import FSDPModule
+
+    shard_mesh = dp_mesh if dp_mesh.ndim == 1 else dp_mesh[dp_mesh.mesh_dim_names[-1]]
+    group = shard_mesh.get_group()
+    world = shard_mesh.size()
+    if world < 2:
+        return None
+    comm = PeerMemoryReduceScatter(group, wire_dtype, reserve_numel=max_bucket_numel(model, world))
+    for m in model.modules():
+        if not isinstance(m, FSDPModule):
+            continue
+        state = m._get_fsdp_state()
+        pg = getattr(state, "_fsdp_param_group", None)
+        other = getattr(pg.mesh_info, "shard_process_group", None) if pg is not None else None
+        if other is None or other.group_name != group.group_name:
+            continue   # e.g. experts sharded on their own mesh keep the library collective
+        m.set_custom_reduce_scatter(comm)
+    return comm

@@ -7,11 +7,18 @@ it is freed — the peak of that curve is the activation footprint under the cho
 checkpoint mode.  Static terms (parameter, gradient and optimizer shards, FSDP all-gather /
 reduce-scatter buffers) follow from `ParallelDims` arithmetic:
 
-    params   Σ numel / shard(p) · store bytes          shard = fsdp·tp (dense), efsdp·ep·etp (experts), / pp
-    grads    same · grad bytes
-    optim    2 · 4 B · local params (AdamW fp32 moments); 0 on the device with Swap/Virtual optimizers
-    fsdp buf 2 · largest unit (unsharded over fsdp) · param bytes  +  reduce-scatter staging in reduce dtype
-    activ.   tracker peak / (tp · cp)  (sequence-parallel and context-parallel shard activations)
+    params    Σ numel / shard(p) · store bytes          shard = fsdp·tp (dense), efsdp·ep·etp (experts), / pp
+    optim     2 · 4 B · local params (AdamW fp32 moments); 0 on the device with Swap/Virtual optimizers
+    gathered  FSDP only: unsharded compute copies that stay resident: every unit with
+              ``fsdp_reshard_after_forward = never``, two units (current + prefetched) otherwise
+    fsdp buf  all-gather output of the next unit + the gradient bucket of one unit (wire dtype of the chosen
+              reduce-scatter) + the unit's unsharded gradients while they wait for the reduction
+    dynamic   peak over the forward + backward TIMELINE of (live activations + gradients created so far); a
+              gradient counts in full while its layer is in backward and as its 1 / fsdp shard once reduced.
+              Activation bytes are divided by tp · cp (sequence- and context-parallel shards).
+
+The peak of a step is NOT activations + gradients: gradients appear while activations are being freed, so on one
+GPU an 8B model peaks at the START of backward (weights + optimizer state + all activations, no gradient yet).
 
 The estimate is checked against the HBM budget (180 GB by default) and reports link traffic per
 step with the time it costs at NVLink bandwidth.  The fake-backend dry run (`--comm.mode
@@ -66,8 +73,33 @@ class MetaMemoryTracker(TorchDispatchMode):
         self.peak = max(self.peak, self.current)
         weakref.finalize(st, self._release, key)
 
+    def reweight(self, t: torch.Tensor, factor: float) -> None:
+        """Count the storage of ``t`` as ``factor`` of its size from now on (a gradient that has been reduce-scattered
+        keeps 1 / fsdp of its bytes on this rank)."""
+        try:
+            key = id(t.untyped_storage())
+        except Exception:
+            return
+        n = self._seen.get(key)
+        if n is None:
+            return
+        new = int(n * factor)
+        self._seen[key] = new
+        self.current -= n - new
+
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
         out = func(*args, **(kwargs or {}))
+        # storages that came IN with the arguments are not allocations of this op: a view of a parameter (``w.t()``)
+        # shares the parameter's storage, which the static terms already count
+        for leaf in tree_flatten((args, kwargs or {}))[0]:
+            if isinstance(leaf, torch.Tensor):
+                try:
+                    key = id(leaf.untyped_storage())
+                except Exception:
+                    continue
+                if key not in self._seen:
+                    self._seen[key] = 0
+                    weakref.finalize(leaf.untyped_storage(), self._release, key)
         for leaf in tree_flatten(out)[0]:
             if isinstance(leaf, torch.Tensor):
                 self._track(leaf)
@@ -92,16 +124,19 @@ class MemoryReport:
     comm_bytes_per_step: dict = field(default_factory=dict)
     comm_seconds_per_step: float = 0.0
     notes: list = field(default_factory=list)
+    bytes_gathered_params: int = 0
+    bytes_dynamic_peak: int = 0
+    bytes_grads_at_peak: int = 0
 
     def summary(self) -> str:
         g = lambda b: f"{b / GIB:8.2f} GiB"  # noqa: E731
         lines = [
             f"memory estimate per rank ({self.world_size} ranks, {self.parallelism})",
             f"  parameters        {g(self.bytes_params)}   ({self.params_local:,} of {self.params_total:,} params)",
-            f"  gradients         {g(self.bytes_grads)}",
+            f"  gradients         {g(self.bytes_grads)}   (at the end of backward; {g(self.bytes_grads_at_peak)} at the peak)",
             f"  optimizer (HBM)   {g(self.bytes_optimizer_device)}   (+{g(self.bytes_optimizer_host)} pinned host)",
-            f"  FSDP buffers      {g(self.bytes_fsdp_buffers)}",
-            f"  activations       {g(self.bytes_activations)}",
+            f"  FSDP buffers      {g(self.bytes_fsdp_buffers)}   (+{g(self.bytes_gathered_params)} gathered weights kept)",
+            f"  activations       {g(self.bytes_activations)}   (live at the peak of the forward + backward timeline)",
             f"  total             {g(self.bytes_total)}   budget {g(self.budget_bytes)}   "
             f"{'FITS' if self.fits else 'DOES NOT FIT'}",
             f"  link traffic/step {json.dumps({k: round(v / GIB, 3) for k, v in self.comm_bytes_per_step.items()})} GiB"
@@ -127,7 +162,12 @@ class _FlashStandIn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v):
-        out = torch.empty(*q.shape[:-1], v.shape[-1], dtype=q.dtype, device=q.device)
+        # the fused kernels return the output in the memory layout of q ([B, S, H, D] storage seen as [B, H, S, D]):
+        # the `transpose(1, 2).contiguous()` that follows in the models is then free
+        if q.shape[-1] == v.shape[-1]:
+            out = torch.empty_like(q)
+        else:
+            out = torch.empty(*q.shape[:-1], v.shape[-1], dtype=q.dtype, device=q.device)
         lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
         ctx.save_for_backward(q, k, v, out, lse)
         return out
@@ -142,18 +182,33 @@ def _sdpa_stand_in(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scal
     return _FlashStandIn.apply(q, k, v)
 
 
-def _measure_activations(model, model_config, training, loss_fn, num_mtp: int) -> int:
-    """Peak bytes of one forward+backward on meta tensors (parameters and their grads excluded)."""
+def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad_keep: dict) -> tuple[int, int]:
+    """One forward + backward on meta tensors.  Returns (peak bytes of activations + gradients-so-far, gradient
+    bytes inside that peak).  ``grad_keep[param] = fraction`` of a parameter's gradient that stays on this rank once
+    it has been reduced (1 on one GPU, 1 / fsdp under FSDP, ...)."""
     import torch.nn.functional as F
 
     b, s = training.local_batch_size, training.seq_len
     tokens = torch.empty(b, s, dtype=torch.int64, device="meta")
     labels = torch.empty(b, s + num_mtp, dtype=torch.int64, device="meta")
-    grads_bytes = sum(p.numel() * p.element_size() for p in model.parameters() if p.requires_grad)
     real_sdpa = F.scaled_dot_product_attention
     F.scaled_dot_product_attention = _sdpa_stand_in
+    hooks = []
+    grads_live = {"bytes": 0, "at_peak": 0, "peak": 0}
     try:
         with MetaMemoryTracker() as tr:
+            def on_grad(p):
+                keep = grad_keep.get(p, 1.0)
+                n = p.grad.numel() * p.grad.element_size()
+                tr.reweight(p.grad, keep)
+                grads_live["bytes"] += int(n * keep)
+                if tr.peak > grads_live["peak"]:
+                    # the gradient was created at full size before this hook ran: the new peak holds all of it
+                    grads_live["peak"], grads_live["at_peak"] = tr.peak, grads_live["bytes"] - int(n * keep) + n
+
+            for p in model.parameters():
+                if p.requires_grad:
+                    hooks.append(p.register_post_accumulate_grad_hook(on_grad))
             out = model(tokens)
             loss = loss_fn(out, labels)
             del out
@@ -161,10 +216,12 @@ def _measure_activations(model, model_config, training, loss_fn, num_mtp: int) -
             peak = tr.peak
     finally:
         F.scaled_dot_product_attention = real_sdpa
-    # parameter gradients are created during backward and accounted separately
+        for h in hooks:
+            h.remove()
+    at_peak = grads_live["at_peak"] if grads_live["peak"] == peak else 0
     for p in model.parameters():
         p.grad = None
-    return max(peak - grads_bytes, 0)
+    return peak, at_peak
 
 
 def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> MemoryReport:
@@ -229,20 +286,38 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
     if cfg.optimizer.swap_optimizer:
         # one slice of the state is resident at a time while the step streams through
         bytes_opt_dev = int(opt_bytes / max(cfg.optimizer.swap_optimizer_times, 1)) * 2
-    bytes_fsdp = 0
+    peer_rs = fsdp > 1 and getattr(par, "fsdp_reduce_scatter", "nccl") != "nccl" and fsdp <= 8
+    wire = pb if peer_rs else rb               # bytes per element of the gradient bucket
+    bytes_fsdp = bytes_gathered = 0
     if fsdp > 1:
-        bytes_fsdp = int(2 * largest_unit * pb + largest_unit * rb * (1 + 1 / fsdp))
+        # next unit's all-gather output + one unit's unsharded gradients + its reduction bucket and output
+        bytes_fsdp = int(largest_unit * pb + largest_unit * pb + largest_unit * wire + largest_unit * rb / fsdp)
+        dense_gathered = sum(v for k, v in per_layer.items())
+        if par.fsdp_reshard_after_forward == "never":
+            bytes_gathered = int(dense_gathered * pb)
+        else:
+            bytes_gathered = int(min(dense_gathered, 2 * largest_unit) * pb)
         if sb != pb:
             notes.append("parameters are stored in a wider dtype than they are gathered in")
 
-    # ---- activations from the meta run
+    # ---- forward + backward timeline on meta tensors
     loss_fn = spec.build_loss_fn(None, trainer_config=cfg) if spec.build_loss_fn else None
     if cfg.activation_checkpoint.mode != "none":
         from titan_b200.parallel.activation_checkpoint import apply_ac
 
         apply_ac(model, cfg.activation_checkpoint)
+    grad_keep = {}
+    for name, p in model.named_parameters():
+        if _is_expert(name):
+            shard = pd.efsdp * pd.ep * (pd.etp if pd.etp_enabled else 1)
+        else:
+            shard = fsdp * (pd.tp if (p.dim() >= 2 and pd.tp_enabled) else 1)
+        grad_keep[p] = 1.0 / shard
+    grads_at_peak = 0
     try:
-        act = _measure_activations(model, mc, cfg.training, loss_fn, cfg.training.num_mtp_modules)
+        dyn, grads_at_peak = _measure_timeline(model, mc, cfg.training, loss_fn, cfg.training.num_mtp_modules,
+                                               grad_keep)
+        act = max(dyn - grads_at_peak, 0)
     except Exception as e:  # an op without a meta kernel: fall back to a closed-form bound
         L, d = mc.n_layers, mc.dim
         tok = cfg.training.local_batch_size * cfg.training.seq_len
@@ -250,6 +325,13 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         act = int(tok * d * pb * per_layer_act * L + tok * mc.vocab_size * (pb + 4))
         notes.append(f"activation term from the closed-form bound ({type(e).__name__}: {str(e)[:80]})")
     act = int(act / (pd.tp * pd.cp) / pd.pp)
+    grads_at_peak = int(grads_at_peak / pd.pp)
+    dyn_peak = act + grads_at_peak
+    if fsdp > 1 and par.fsdp_reshard_after_forward == "never":
+        # nothing is gathered in backward, and the first reduction starts only after the last layer's backward has
+        # freed that layer's activations: only what the reduction needs beyond them adds to the peak
+        n_units = max(getattr(mc, "n_layers", 1), 1)
+        bytes_fsdp = max(0, int(largest_unit * (pb + wire) + largest_unit * rb / fsdp) - act // n_units)
 
     # ---- link traffic per step (bytes sent+received by one rank)
     comm = {}
@@ -269,7 +351,9 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         comm["ep_all_to_all"] = tok * topk * mc.dim * pb * (pd.ep - 1) / pd.ep * 4 * n_moe / pd.pp
     seconds = sum(comm.values()) / (link_gbs * 1e9)
 
-    total_bytes = bytes_params + bytes_grads + bytes_opt_dev + bytes_fsdp + act
+    # the optimizer step runs after backward with every local gradient present and no activation left
+    at_step = bytes_params + bytes_grads + bytes_opt_dev
+    total_bytes = max(bytes_params + bytes_opt_dev + bytes_fsdp + bytes_gathered + dyn_peak, at_step)
     budget = int(cfg.memory_sim.hbm_budget_gib * 1e9)
     return MemoryReport(
         world_size=world_size,
@@ -278,6 +362,7 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         params_total=int(total), params_local=int(local), bytes_params=bytes_params, bytes_grads=bytes_grads,
         bytes_optimizer_device=bytes_opt_dev, bytes_optimizer_host=bytes_opt_host, bytes_fsdp_buffers=bytes_fsdp,
         bytes_activations=act, bytes_total=total_bytes, budget_bytes=budget, fits=total_bytes <= budget,
+        bytes_gathered_params=bytes_gathered, bytes_dynamic_peak=dyn_peak, bytes_grads_at_peak=grads_at_peak,
         comm_bytes_per_step={k: float(v) for k, v in comm.items()}, comm_seconds_per_step=seconds, notes=notes)
 
 

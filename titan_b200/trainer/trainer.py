@@ -39,6 +39,7 @@ from titan_b200.protocols.converter import ModelConvertersContainer
 from titan_b200.protocols.model_spec import get_model_spec
 from titan_b200.trainer import stash
 from titan_b200.trainer.gc import GarbageCollection
+from titan_b200.trainer.kernel_status import KernelStatusMonitor
 from titan_b200.trainer.loss import IGNORE_INDEX
 from titan_b200.trainer.metrics import MetricsProcessor
 from titan_b200.trainer.profiling import maybe_enable_memory_snapshot, maybe_enable_profiling
@@ -206,6 +207,7 @@ class Trainer:
         self.ntokens_seen = 0
         self.loss_history: list[float] = []
         self._cache_emptied = False
+        self.kernel_status = KernelStatusMonitor()
         logger.info("trainer ready: world %d, dp_shard %d, dp_replicate %d, tp %d, cp %d, pp %d, ep %d; "
                     "global batch %d, grad-accum %d", world_size, pd.dp_shard, pd.dp_replicate, pd.tp, pd.cp, pd.pp,
                     pd.ep, cfg.training.global_batch_size, self.gradient_accumulation_steps)
@@ -381,7 +383,9 @@ class Trainer:
         mp = self.metrics_processor
         mp.steps_since_last_log += 1
         if not mp.should_log(self.step):
+            self.kernel_status.poll(f"step {self.step}")
             return
+        self.kernel_status.check(f"step {self.step}")  # the log below syncs anyway
         if loss_mesh is not None:
             if pd.pp_enabled and not self.pp_has_last_stage:
                 loss = torch.zeros_like(loss)
@@ -402,6 +406,7 @@ class Trainer:
         cfg = self.config
         self.checkpointer.load(step=cfg.checkpoint.load_step)
         self.step = self.train_state.step
+        self.ntokens_seen = self.train_state.ntokens_seen
         if cfg.checkpoint.create_seed_checkpoint:
             if int(os.environ.get("WORLD_SIZE", "1")) != 1:
                 raise RuntimeError("a seed checkpoint must be created by a single process")
@@ -427,6 +432,8 @@ class Trainer:
                 self.train_step(data_iterator)
                 self.train_state.step = self.step
                 self.train_state.ntokens_seen = self.ntokens_seen
+                if self.checkpointer._should_save(self.step, last_step=(self.step == cfg.training.steps)):
+                    self.kernel_status.check(f"before the checkpoint of step {self.step}")
                 self.checkpointer.save(self.step, last_step=(self.step == cfg.training.steps))
                 if prof is not None:
                     prof.step()
