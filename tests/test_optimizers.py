@@ -152,6 +152,69 @@ def test_muon_split_and_step():
     sched.step()
 
 
+class _MuonNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.tok_embeddings = nn.Embedding(10, 8)
+        self.wq = nn.Linear(8, 16, bias=False)
+        self.wk = nn.Linear(16, 8, bias=False)
+        self.norm = nn.LayerNorm(8)
+        self.experts_w = nn.Parameter(torch.randn(2, 8, 8))
+        self.output = nn.Linear(8, 10, bias=False)
+
+    def forward(self, t):
+        h = self.norm(self.wk(self.wq(self.tok_embeddings(t))))
+        return self.output(h @ self.experts_w[0])
+
+
+def _muon_steps(opt, m, n=3):
+    g = torch.Generator().manual_seed(5)
+    for _ in range(n):
+        opt.zero_grad()
+        m(torch.randint(0, 10, (4, 5), generator=g)).pow(2).mean().backward()
+        opt.step()
+
+
+def test_swap_muon_matches_resident_muon_and_checkpoints_every_state():
+    """Swap-Muon keeps the Muon momenta AND the AdamW moments in host arenas: same parameters as the resident
+    optimizer after 3 steps, nothing left in `optimizer.state` between steps, and a state dict with every momentum and
+    moment that a resident optimizer loads (and the other way round)."""
+    torch.manual_seed(0)
+    ref_m = _MuonNet()
+    m = copy.deepcopy(ref_m)
+    base = dict(name="Muon", lr=1e-2, weight_decay=0.01)
+    ref = containers.build_optimizers([ref_m], OptimizerConfig(**base))
+    opt = containers.build_optimizers([m], OptimizerConfig(**base, swap_optimizer=True, swap_merge_buckets=1))
+    assert isinstance(opt.muon[0], muon.SwapDistributedMuon)
+    assert len(opt.muon[0]._merge_groups(list(opt.muon[0].params_list))) == 3   # one matrix per merge group here
+    _muon_steps(ref, ref_m)
+    _muon_steps(opt, m)
+    for (n, a), b in zip(ref_m.named_parameters(), m.parameters()):
+        torch.testing.assert_close(b, a, rtol=1e-5, atol=1e-6, msg=lambda s, n=n: f"{n}: {s}")
+    assert all("momentum_buffer" not in st for st in opt.muon[0].state.values())
+    sd = opt.state_dict()
+    assert {"state.wq.weight.momentum_buffer", "state.experts_w.momentum_buffer", "state.norm.weight.exp_avg",
+            "state.output.weight.exp_avg_sq", "state.tok_embeddings.weight.step"} <= set(sd)
+    ref_sd = ref.state_dict()
+    torch.testing.assert_close(sd["state.wq.weight.momentum_buffer"], ref_sd["state.wq.weight.momentum_buffer"])
+    torch.testing.assert_close(sd["state.norm.weight.exp_avg"], ref_sd["state.norm.weight.exp_avg"])
+    # resident checkpoint -> swapped optimizer, one more step on both: still equal
+    torch.manual_seed(0)
+    m2 = copy.deepcopy(ref_m)
+    opt2 = containers.build_optimizers([m2], OptimizerConfig(**base, swap_optimizer=True, swap_merge_buckets=2))
+    opt2.load_state_dict(ref_sd)
+    _muon_steps(ref, ref_m, 1)
+    _muon_steps(opt2, m2, 1)
+    for a, b in zip(ref_m.parameters(), m2.parameters()):
+        torch.testing.assert_close(b, a, rtol=1e-5, atol=1e-6)
+    # swapped checkpoint -> resident optimizer
+    m3 = copy.deepcopy(m)
+    opt3 = containers.build_optimizers([m3], OptimizerConfig(**base))
+    opt3.load_state_dict(sd)
+    torch.testing.assert_close(opt3.state_dict()["state.wk.weight.momentum_buffer"],
+                               sd["state.wk.weight.momentum_buffer"])
+
+
 def test_lr_schedule_shape():
     f = lambda s, **k: containers.linear_warmup_stable_decay(s, warmup_steps=2, stable_steps=3, decay_steps=4, **k)
     vals = [f(s, decay_type="linear", min_lr_factor=0.1) for s in range(9)]

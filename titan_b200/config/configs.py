@@ -127,6 +127,8 @@ class OptimizerConfig:
     muon_ns_steps: int = 5
     muon_adjust_lr_fn: Literal["original", "match_rms_adamw"] | None = "match_rms_adamw"
     muon_hybrid_ns: bool = False
+    muon_extra_reduce_for_hsdp: bool = False
+    """Average the Muon update over the `dp_replicate` ranks after Newton-Schulz (keeps HSDP replicas bit-identical)."""
     extra_param_group_split_rules: list[dict] | None = None
     swap_merge_buckets: int = 1
 

@@ -12,7 +12,9 @@ Routing by how a parameter is distributed:
     experts, no communication;
   * FSDP-sharded matrices (dim-0 shards): parameters are processed in buckets of `world` matrices; one
     all-to-all gives every rank ONE whole matrix of the bucket, it runs Newton–Schulz, a second all-to-all
-    returns the update shards;
+    returns the update shards; tensor-parallel shards are all-gathered over ``tp`` before that exchange and the
+    update is sliced back; under HSDP the exchange stays inside the shard group and the update may be averaged over
+    the replicas (``muon_extra_reduce_for_hsdp``);
   * replicated matrices (DDP / single device): owner-computes with snake-interleaved ownership (largest first)
     and an all-gather of the updates; on one rank this degenerates to a plain local update.
 
@@ -40,7 +42,8 @@ from torch.optim import Optimizer
 
 from titan_b200.utils.logging import logger
 
-__all__ = ["zeropower_via_newtonschulz5", "normalise_update", "DistributedMuon", "split_parameters_for_muon",
+__all__ = ["zeropower_via_newtonschulz5", "normalise_update", "DistributedMuon", "SwapDistributedMuon",
+           "split_parameters_for_muon",
            "MuonHybridOptimizersContainer", "build_muon_optimizers", "COEFF_PRIMARY", "COEFF_SECONDARY"]
 
 COEFF_PRIMARY = (3.4445, -4.7750, 2.0315)
@@ -87,6 +90,18 @@ def _lmo(g, steps, hybrid, adjust):
     return normalise_update(zeropower_via_newtonschulz5(g, steps=steps, hybrid_ns=hybrid), adjust)
 
 
+def _all_to_all(recv: list[torch.Tensor], send: list[torch.Tensor], group) -> None:
+    """List all-to-all of flat tensors as ONE variable-split `all_to_all_single` (also what gloo offers)."""
+    inp = torch.cat([t.reshape(-1) for t in send])
+    out = torch.empty(sum(t.numel() for t in recv), dtype=inp.dtype, device=inp.device)
+    dist.all_to_all_single(out, inp, output_split_sizes=[t.numel() for t in recv],
+                           input_split_sizes=[t.numel() for t in send], group=group)
+    o = 0
+    for t in recv:
+        t.copy_(out[o:o + t.numel()].view(t.shape))
+        o += t.numel()
+
+
 def _snake(items: list, w: int) -> list:
     if w <= 1:
         return items
@@ -119,7 +134,8 @@ def split_parameters_for_muon(model_parts: list[nn.Module]):
 
 class DistributedMuon(Optimizer):
     def __init__(self, params, names: list[str], *, lr=1e-3, momentum=0.95, nesterov=True, weight_decay=0.0,
-                 ns_steps=5, adjust_lr_fn="match_rms_adamw", hybrid_ns=False, dp_group=None):
+                 ns_steps=5, adjust_lr_fn="match_rms_adamw", hybrid_ns=False, dp_group=None,
+                 extra_reduce_for_hsdp: bool = False):
         if isinstance(params, list) and params and isinstance(params[0], dict):
             groups = params
         else:
@@ -130,6 +146,7 @@ class DistributedMuon(Optimizer):
         flat = [p for g in self.param_groups for p in g["params"]]
         self.names = {id(p): n for p, n in zip(flat, names)}
         self.dp_group = dp_group
+        self.extra_reduce_for_hsdp = extra_reduce_for_hsdp
         self.comm_calls = 0
 
     # ---- classification
@@ -168,6 +185,17 @@ class DistributedMuon(Optimizer):
             pl.mul_(1 - lr * wd)
         pl.add_(ul.to(pl.dtype), alpha=-lr)
 
+    # ---- momentum residency (overridden by the swapped variant)
+    def _merge_groups(self, params: list) -> list[list]:
+        """Parameters are updated group by group; every group's momentum is on the device while it is processed."""
+        return [params]
+
+    def _acquire(self, params: list, upcoming: list | None) -> None:
+        pass
+
+    def _release(self, params: list) -> None:
+        pass
+
     # ---- step
     @torch.no_grad()
     def step(self, closure=None):
@@ -176,80 +204,130 @@ class DistributedMuon(Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for group in self.param_groups:
-            kinds: dict[str, list] = {"expert": [], "fsdp": [], "ddp": [], "local": []}
-            for p in group["params"]:
-                if p.grad is None:
-                    continue
-                kinds[self._kind(p)].append((p, self._effective_grad(p, group)))
-            steps, hyb, adj = group["backend_steps"], group["hybrid_ns"], group["adjust_lr_fn"]
-            for p, g in kinds["local"] + kinds["expert"]:
-                gl = g.to_local() if isinstance(g, DTensor) else g
-                if gl.numel() == 0:
-                    continue
-                self._apply(p, _lmo(gl, steps, hyb, adj), group)
-            if kinds["fsdp"]:
-                self._step_fsdp(kinds["fsdp"], group)
-            if kinds["ddp"]:
-                self._step_ddp(kinds["ddp"], group)
+            active = [p for p in group["params"] if p.grad is not None]
+            chunks = self._merge_groups(active)
+            for ci, chunk in enumerate(chunks):
+                self._acquire(chunk, chunks[ci + 1] if ci + 1 < len(chunks) else None)
+                kinds: dict[str, list] = {"expert": [], "fsdp": [], "ddp": [], "local": []}
+                for p in chunk:
+                    kinds[self._kind(p)].append((p, self._effective_grad(p, group)))
+                steps, hyb, adj = group["backend_steps"], group["hybrid_ns"], group["adjust_lr_fn"]
+                for p, g in kinds["local"] + kinds["expert"]:
+                    gl = g.to_local() if isinstance(g, DTensor) else g
+                    if gl.numel() == 0:
+                        continue
+                    self._apply(p, _lmo(gl, steps, hyb, adj), group)
+                if kinds["fsdp"]:
+                    self._step_fsdp(kinds["fsdp"], group)
+                if kinds["ddp"]:
+                    self._step_ddp(kinds["ddp"], group)
+                self._release(chunk)
         return loss
 
+    # ---- how a sharded matrix is laid out over its mesh
+    @staticmethod
+    def _layout(p: DTensor):
+        """→ (fsdp mesh dim | None, tp mesh dim | None, tensor dim split by tp, replicate mesh dim | None).  Mesh axes
+        are told apart by name: ``tp`` splits for tensor parallelism, ``dp_replicate*`` replicates (HSDP), every other
+        sharding axis is a data-parallel (FSDP) split of dim 0."""
+        mesh = p.device_mesh
+        names = mesh.mesh_dim_names or tuple(f"dim{i}" for i in range(mesh.ndim))
+        fsdp_dim = tp_dim = tp_tensor_dim = rep_dim = None
+        for i, (name, pl) in enumerate(zip(names, p.placements)):
+            if mesh.size(i) == 1:
+                continue
+            if isinstance(pl, Shard) or type(pl).__name__ == "_StridedShard":
+                if name == "tp":
+                    tp_dim, tp_tensor_dim = i, pl.dim
+                elif pl.dim == 0 and fsdp_dim is None:
+                    fsdp_dim = i
+                else:
+                    return None
+            elif name.startswith("dp_replicate"):
+                rep_dim = i
+        return fsdp_dim, tp_dim, tp_tensor_dim, rep_dim
+
     def _step_fsdp(self, items, group) -> None:
-        """Buckets of `world` dim-0-sharded matrices: a2a shards → owner orthogonalises → a2a updates back."""
+        """Buckets of `world` dim-0-sharded matrices: a2a shards → owner orthogonalises → a2a updates back.
+
+        Tensor-parallel shards are all-gathered over ``tp`` first (every tp rank then takes part in the same exchange
+        over its own data-parallel group and keeps its slice of the update); under HSDP the exchange runs inside the
+        shard group and the update can be averaged over the replicas (``extra_reduce_for_hsdp``) so that they stay
+        bit-identical.  When FSDP and TP both split dim 0 the gathered rows arrive in (data rank, tp rank) order
+        instead of (tp rank, data rank): Newton-Schulz commutes with row permutations, so nothing is reordered."""
         steps, hyb, adj = group["backend_steps"], group["hybrid_ns"], group["adjust_lr_fn"]
-        by_mesh: dict = {}
+        by_key: dict = {}
         for p, g in items:
-            by_mesh.setdefault(id(p.device_mesh), []).append((p, g))
-        for lst in by_mesh.values():
-            mesh = lst[0][0].device_mesh
-            if mesh.ndim != 1 or not all(isinstance(p.placements[0], Shard) and p.placements[0].dim == 0 for p, _ in lst):
-                # uncommon layouts: gather, orthogonalise everywhere, keep the local slice
+            lay = self._layout(p)
+            key = (id(p.device_mesh), lay) if lay is not None and lay[0] is not None else None
+            by_key.setdefault(key, []).append((p, g))
+        for key, lst in by_key.items():
+            if key is None:
+                # layouts the exchange does not cover: gather, orthogonalise everywhere, keep the local slice
                 for p, g in lst:
                     full = g.full_tensor()
                     u = _lmo(full, steps, hyb, adj)
                     self._apply(p, self._slice_like(p, u), group)
                 continue
-            pg = mesh.get_group()
+            mesh = lst[0][0].device_mesh
+            fsdp_dim, tp_dim, tp_tensor_dim, rep_dim = key[1]
+            pg = mesh.get_group(fsdp_dim)
+            tp_pg = mesh.get_group(tp_dim) if tp_dim is not None else None
+            rep_pg = mesh.get_group(rep_dim) if (rep_dim is not None and self.extra_reduce_for_hsdp) else None
             world, rank = dist.get_world_size(pg), dist.get_rank(pg)
-            lst.sort(key=lambda t: t[0].numel(), reverse=True)
+            tp_world = dist.get_world_size(tp_pg) if tp_pg is not None else 1
+            tp_rank = dist.get_rank(tp_pg) if tp_pg is not None else 0
+
+            def local_rows(p, g):
+                """This data rank's rows of the matrix with the tp split undone."""
+                gl = g.to_local().contiguous().bfloat16()
+                if tp_pg is None:
+                    return gl
+                parts = [torch.empty_like(gl) for _ in range(tp_world)]
+                dist.all_gather(parts, gl, group=tp_pg)
+                self.comm_calls += 1
+                return torch.cat(parts, dim=tp_tensor_dim)
+
+            lst = sorted(lst, key=lambda t: t[0].numel(), reverse=True)
             for b0 in range(0, len(lst), world):
                 bucket = lst[b0:b0 + world]
-                send = []
-                for j in range(world):  # rank j will own matrix j of the bucket
-                    if j < len(bucket):
-                        send.append(bucket[j][1].to_local().contiguous().bfloat16().reshape(-1))
-                    else:
-                        send.append(torch.empty(0, dtype=torch.bfloat16, device=bucket[0][1].to_local().device))
-                recv = None
+                rows_of = [local_rows(p, g) for p, g in bucket]
+                dev = rows_of[0].device
+                empty = lambda: torch.empty(0, dtype=torch.bfloat16, device=dev)  # noqa: E731
+                send = [rows_of[j].reshape(-1) if j < len(bucket) else empty() for j in range(world)]
                 if rank < len(bucket):
                     p_own = bucket[rank][0]
-                    rows = [self._shard_rows(p_own.shape[0], r, world) for r in range(world)]
                     cols = math.prod(p_own.shape[1:])
-                    recv = [torch.empty(rw * cols, dtype=torch.bfloat16, device=send[0].device) for rw in rows]
+                    if tp_pg is None:
+                        rows = [self._shard_rows(p_own.shape[0], r, world) for r in range(world)]
+                    else:  # even splits only (checked by the DTensor layout of tensor-parallel linears)
+                        rows = [p_own.shape[0] // world] * world
+                    recv = [torch.empty(rw * cols, dtype=torch.bfloat16, device=dev) for rw in rows]
                 else:
-                    recv = [torch.empty(0, dtype=torch.bfloat16, device=send[0].device) for _ in range(world)]
-                dist.all_to_all(recv, send, group=pg)
+                    recv = [empty() for _ in range(world)]
+                _all_to_all(recv, send, pg)
                 self.comm_calls += 1
-                back_send = [torch.empty(0, dtype=torch.bfloat16, device=send[0].device) for _ in range(world)]
+                back_send = [empty() for _ in range(world)]
                 if rank < len(bucket):
                     p_own = bucket[rank][0]
                     full = torch.cat(recv).view(p_own.shape)
                     u = _lmo(full, steps, hyb, adj).reshape(p_own.shape[0], -1)
+                    if rep_pg is not None:
+                        dist.all_reduce(u, group=rep_pg, op=dist.ReduceOp.AVG)
+                        self.comm_calls += 1
                     r0 = 0
                     for r in range(world):
-                        rw = self._shard_rows(p_own.shape[0], r, world)
-                        back_send[r] = u[r0:r0 + rw].contiguous().reshape(-1)
-                        r0 += rw
-                back_recv = []
-                for j in range(world):
-                    if j < len(bucket):
-                        back_recv.append(torch.empty(bucket[j][0].to_local().numel(), dtype=torch.bfloat16,
-                                                     device=send[0].device))
-                    else:
-                        back_recv.append(torch.empty(0, dtype=torch.bfloat16, device=send[0].device))
-                dist.all_to_all(back_recv, back_send, group=pg)
+                        back_send[r] = u[r0:r0 + rows[r]].contiguous().reshape(-1)
+                        r0 += rows[r]
+                back_recv = [torch.empty(rows_of[j].numel(), dtype=torch.bfloat16, device=dev) if j < len(bucket)
+                             else empty() for j in range(world)]
+                _all_to_all(back_recv, back_send, pg)
                 self.comm_calls += 1
                 for j, (p, _) in enumerate(bucket):
-                    self._apply(p, back_recv[j].view(p.to_local().shape), group)
+                    u_rows = back_recv[j].view(rows_of[j].shape)
+                    if tp_pg is not None:
+                        u_rows = u_rows.chunk(tp_world, dim=tp_tensor_dim)[tp_rank]
+                    self._apply(p, u_rows.reshape(p.to_local().shape), group)
 
     @staticmethod
     def _shard_rows(n: int, r: int, world: int) -> int:
@@ -285,6 +363,130 @@ class DistributedMuon(Optimizer):
                 self._apply(p, gathered[owner[i]][: p.numel()].view(p.shape), group)
 
 
+class SwapDistributedMuon(DistributedMuon):
+    """Muon whose momentum buffers live in pinned host memory between (and during most of) the step.
+
+    All momenta of the optimizer sit in ONE pinned arena in parameter order.  `step()` walks the parameters in
+    merge groups of ``swap_merge_buckets`` exchange buckets (``buckets x data-parallel world`` matrices); while one
+    group is orthogonalised its momenta are on the device, the next group's are already being copied in on a side
+    stream and the previous group's are draining back on another, so at most three groups of momentum are resident.
+    On CPU (hardware-free tests) the buffers are plain views of the arena.
+
+    Parity: `SwapMuonState` / the Muon swap hooks of the reference
+    (torchtitan_npu/patches/optimizer/swap_optimizer.py:693-1092, muon_optimizer.py:665-753)."""
+
+    def __init__(self, params, names, *, swap_merge_buckets: int = 1, **kw):
+        super().__init__(params, names, **kw)
+        self.swap_merge_buckets = max(int(swap_merge_buckets), 1)
+        self.params_list = [p for g in self.param_groups for p in g["params"]]
+        locs = [p.to_local() if isinstance(p, DTensor) else p for p in self.params_list]
+        self.offsets = [0]
+        for t in locs:
+            self.offsets.append(self.offsets[-1] + t.numel())
+        self.index = {id(p): i for i, p in enumerate(self.params_list)}
+        self.on_cuda = any(t.is_cuda for t in locs)
+        dtype = locs[0].dtype if locs else torch.float32
+        self.mom_host = torch.zeros(self.offsets[-1], dtype=dtype, pin_memory=self.on_cuda)
+        self.h2d_stream = self.d2h_stream = None
+        self._inflight: dict[int, tuple] = {}     # id(p) -> (device buffer, "loaded" event) of prefetched momenta
+        self._draining: list = []                 # (device buffer, "offloaded" event) kept alive until the copy landed
+        self.h2d_bytes = self.d2h_bytes = 0
+
+    def host_view(self, p) -> torch.Tensor:
+        i = self.index[id(p)]
+        loc = p.to_local() if isinstance(p, DTensor) else p
+        return self.mom_host[self.offsets[i]:self.offsets[i + 1]].view(loc.shape)
+
+    def synchronize(self) -> None:
+        if self.d2h_stream is not None:
+            self.d2h_stream.synchronize()
+        self._draining.clear()
+
+    def _merge_groups(self, params: list) -> list[list]:
+        world = 1
+        for p in params:
+            if isinstance(p, DTensor) and p.device_mesh.size() > 1:
+                lay = self._layout(p)
+                if lay is not None and lay[0] is not None:
+                    world = max(world, p.device_mesh.size(lay[0]))
+        n = max(self.swap_merge_buckets * world, 1)
+        ordered = sorted(params, key=lambda q: q.numel(), reverse=True)   # the exchange buckets are cut in this order
+        return [ordered[i:i + n] for i in range(0, len(ordered), n)]
+
+    def _fetch(self, params: list) -> None:
+        dev = next(((p.to_local() if isinstance(p, DTensor) else p).device for p in params), None)
+        if dev is None or dev.type != "cuda":
+            return
+        if self.h2d_stream is None:
+            self.h2d_stream, self.d2h_stream = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            self.h2d_stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(self.h2d_stream):
+            for p in params:
+                if id(p) in self._inflight:
+                    continue
+                host = self.host_view(p)
+                buf = torch.empty(host.shape, dtype=host.dtype, device=dev)
+                buf.copy_(host, non_blocking=True)
+                self.h2d_bytes += host.numel() * host.element_size()
+                ev = torch.cuda.Event()
+                ev.record(self.h2d_stream)
+                self._inflight[id(p)] = (buf, ev)
+
+    def _acquire(self, params: list, upcoming: list | None) -> None:
+        if not self.on_cuda:
+            for p in params:
+                self.state[p]["momentum_buffer"] = self.host_view(p)
+            return
+        # the arena may still be receiving the previous step's momenta
+        if self.d2h_stream is not None:
+            self.h2d_stream.wait_stream(self.d2h_stream)
+        self._fetch(params)
+        if upcoming:
+            self._fetch(upcoming)
+        main = torch.cuda.current_stream()
+        for p in params:
+            buf, ev = self._inflight.pop(id(p))
+            main.wait_event(ev)
+            buf.record_stream(main)
+            self.state[p]["momentum_buffer"] = buf
+        self._draining = [(b, e) for b, e in self._draining if not e.query()]
+
+    def _release(self, params: list) -> None:
+        if not self.on_cuda:
+            for p in params:
+                self.state[p].pop("momentum_buffer", None)   # the arena view was updated in place
+            return
+        main = torch.cuda.current_stream()
+        updated = torch.cuda.Event()
+        updated.record(main)
+        with torch.cuda.stream(self.d2h_stream):
+            self.d2h_stream.wait_event(updated)
+            for p in params:
+                buf = self.state[p].pop("momentum_buffer", None)
+                if buf is None:
+                    continue
+                host = self.host_view(p)
+                host.copy_(buf, non_blocking=True)
+                self.d2h_bytes += host.numel() * host.element_size()
+                ev = torch.cuda.Event()
+                ev.record(self.d2h_stream)
+                self._draining.append((buf, ev))
+
+    def _effective_grad(self, p, group):
+        g = p.grad
+        mom = group["momentum"]
+        if 0 < mom < 1:
+            buf = self.state[p]["momentum_buffer"]
+            gl = g.to_local() if isinstance(g, DTensor) else g
+            buf.lerp_(gl.to(buf.dtype), 1 - mom)
+            out = gl.lerp(buf.to(gl.dtype), mom) if group["nesterov"] else buf
+            if isinstance(g, DTensor):
+                out = DTensor.from_local(out, g.device_mesh, g.placements, run_check=False, shape=g.shape,
+                                         stride=g.stride())
+            return out
+        return g
+
+
 class MuonHybridOptimizersContainer(Optimizer, Stateful):
     """Muon for matrices + AdamW for the rest, one pair per model part."""
 
@@ -302,10 +504,16 @@ class MuonHybridOptimizersContainer(Optimizer, Stateful):
         for part in model_parts:
             mp, mn, ap, an = split_parameters_for_muon([part])
             groups, names = _build_param_groups(mp, mn, opt_cfg.extra_param_group_split_rules)
-            self.muon.append(DistributedMuon(groups, names, lr=muon_lr, momentum=opt_cfg.muon_momentum,
-                                             nesterov=opt_cfg.muon_enable_nesterov, weight_decay=opt_cfg.weight_decay,
-                                             ns_steps=opt_cfg.muon_ns_steps, adjust_lr_fn=opt_cfg.muon_adjust_lr_fn,
-                                             hybrid_ns=opt_cfg.muon_hybrid_ns, dp_group=dp_group))
+            muon_kw = dict(lr=muon_lr, momentum=opt_cfg.muon_momentum, nesterov=opt_cfg.muon_enable_nesterov,
+                           weight_decay=opt_cfg.weight_decay, ns_steps=opt_cfg.muon_ns_steps,
+                           adjust_lr_fn=opt_cfg.muon_adjust_lr_fn, hybrid_ns=opt_cfg.muon_hybrid_ns, dp_group=dp_group,
+                           extra_reduce_for_hsdp=getattr(opt_cfg, "muon_extra_reduce_for_hsdp", False))
+            if swap:
+                self.muon.append(SwapDistributedMuon(groups, names,
+                                                     swap_merge_buckets=getattr(opt_cfg, "swap_merge_buckets", 1),
+                                                     **muon_kw))
+            else:
+                self.muon.append(DistributedMuon(groups, names, **muon_kw))
             if ap:
                 if swap:
                     from titan_b200.optim.swap_optimizer import SwapAdamW
@@ -340,28 +548,75 @@ class MuonHybridOptimizersContainer(Optimizer, Stateful):
             o.zero_grad(*a, **k)
 
     def state_dict(self) -> dict[str, Any]:
+        """Flat per-FQN keys.  Swapped halves (AdamW moments, Muon momenta) are emitted from their pinned arenas as
+        CPU tensors with the parameter's sharding, under the same keys a resident optimizer writes, so a checkpoint
+        taken with swapping loads without it and vice versa."""
+        from titan_b200.optim.swap_optimizer import _wrap_like, param_fqns, swap_adamw_state_dict
+
         opts = StateDictOptions(flatten_optimizer_state_dict=True)
         out: dict[str, Any] = {}
+        fqns = param_fqns(self.model_parts)
         for part, mu in zip(self.model_parts, self.muon):
-            out.update(get_optimizer_state_dict(part, mu, options=opts))
+            if isinstance(mu, SwapDistributedMuon):
+                mu.synchronize()
+                for grp in mu.param_groups:
+                    for p in grp["params"]:
+                        for fqn in fqns.get(id(p), []):
+                            out[f"state.{fqn}.momentum_buffer"] = _wrap_like(p, mu.host_view(p))
+                            for k, v in grp.items():
+                                if k != "params":
+                                    out[f"param_groups.{fqn}.{k}"] = v
+            else:
+                out.update(get_optimizer_state_dict(part, mu, options=opts))
         for part, ad in zip(self.model_parts, self.adamw):
             if hasattr(ad, "host_views"):
-                continue  # swapped AdamW state is emitted by its own container when used standalone
-            out.update(get_optimizer_state_dict(part, ad, options=opts))
+                out.update(swap_adamw_state_dict(ad, fqns))
+            else:
+                out.update(get_optimizer_state_dict(part, ad, options=opts))
         return out
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        from titan_b200.optim.swap_optimizer import param_fqns, swap_adamw_load_state_dict
+
         opts = StateDictOptions(flatten_optimizer_state_dict=True)
+        fqns = param_fqns(self.model_parts)
         for part, mu in zip(self.model_parts, self.muon):
-            set_optimizer_state_dict(part, mu, optim_state_dict=state_dict, options=opts)
+            if isinstance(mu, SwapDistributedMuon):
+                mu.synchronize()
+                for grp in mu.param_groups:
+                    for p in grp["params"]:
+                        fqn = next((f for f in fqns.get(id(p), []) if f"state.{f}.momentum_buffer" in state_dict),
+                                   None)
+                        if fqn is None:
+                            continue
+                        src = state_dict[f"state.{fqn}.momentum_buffer"]
+                        src = src.to_local() if isinstance(src, DTensor) else src
+                        mu.host_view(p).copy_(src.to(mu.mom_host.dtype))
+                        for k in list(grp.keys()):
+                            if k != "params" and f"param_groups.{fqn}.{k}" in state_dict:
+                                grp[k] = state_dict[f"param_groups.{fqn}.{k}"]
+            else:
+                set_optimizer_state_dict(part, mu, optim_state_dict=state_dict, options=opts)
+        swapped = [ad for ad in self.adamw if hasattr(ad, "host_views")]
+        if swapped:
+            swap_adamw_load_state_dict(swapped, fqns, state_dict)
         for part, ad in zip(self.model_parts, self.adamw):
             if not hasattr(ad, "host_views"):
-                set_optimizer_state_dict(part, ad, optim_state_dict=state_dict, options=opts)
+                # a checkpoint written by the swapped optimizer has no entries for the hyper-parameters that only
+                # torch's AdamW knows (maximize, foreach, ...): keep this optimizer's own values for those
+                filled = dict(state_dict)
+                for grp in ad.param_groups:
+                    for p in grp["params"]:
+                        for fqn in fqns.get(id(p), []):
+                            for k, v in grp.items():
+                                if k != "params":
+                                    filled.setdefault(f"param_groups.{fqn}.{k}", v)
+                set_optimizer_state_dict(part, ad, optim_state_dict=filled, options=opts)
 
     def init_cache_state_dict(self) -> None:
-        for ad in self.adamw:
-            if hasattr(ad, "synchronize"):
-                ad.synchronize()
+        for o in [*self.adamw, *self.muon]:
+            if hasattr(o, "synchronize"):
+                o.synchronize()
 
 
 def _build_param_groups(params, names, rules):

@@ -37,7 +37,8 @@ from torch.optim import Optimizer
 from titan_b200.optim.fused_adamw import adamw_multi_tensor, adamw_reference_step
 from titan_b200.utils.logging import logger
 
-__all__ = ["SwapOptimizersContainer", "SwapAdamW", "param_fqns"]
+__all__ = ["SwapOptimizersContainer", "SwapAdamW", "param_fqns", "swap_adamw_state_dict",
+           "swap_adamw_load_state_dict"]
 
 _PREFIXES = ("_checkpoint_wrapped_module.", "_orig_mod.", "module.")
 
@@ -211,6 +212,31 @@ class SwapAdamW(Optimizer):
                                  vmax=self.vmax_host[a:b].view(shape) if self.vmax_host is not None else None)
 
 
+def _wrap_like(p, host_view: torch.Tensor):
+    if isinstance(p, DTensor):
+        return DTensor.from_local(host_view, p.device_mesh, p.placements, run_check=False, shape=p.shape,
+                                  stride=p.stride())
+    return host_view
+
+
+def swap_adamw_state_dict(o: "SwapAdamW", fqns: dict[int, list[str]]) -> dict[str, Any]:
+    """Flat checkpoint keys of one swapped optimizer; the tensors are views of its pinned arenas."""
+    o.synchronize()
+    out: dict[str, Any] = {}
+    for p in o.params_list:
+        views = o.host_views(p)
+        g = o.group_of[id(p)]
+        for fqn in fqns.get(id(p), []):
+            for k, v in views.items():
+                out[f"state.{fqn}.{k}"] = _wrap_like(p, v)
+            out[f"state.{fqn}.step"] = torch.tensor(float(o.steps[id(p)]))
+            for k, v in g.items():
+                if k != "params":
+                    out[f"param_groups.{fqn}.{k}"] = (v.detach().cpu().clone() if torch.is_tensor(v)
+                                                      else copy.deepcopy(v))
+    return out
+
+
 class SwapOptimizersContainer(Optimizer, Stateful):
     state_keys = ("exp_avg", "exp_avg_sq", "max_exp_avg_sq")
 
@@ -250,69 +276,62 @@ class SwapOptimizersContainer(Optimizer, Stateful):
         self.synchronize()
 
     # ---- checkpoint
-    @staticmethod
-    def _wrap_like(p, host_view: torch.Tensor):
-        if isinstance(p, DTensor):
-            return DTensor.from_local(host_view, p.device_mesh, p.placements, run_check=False, shape=p.shape,
-                                      stride=p.stride())
-        return host_view
+    _wrap_like = staticmethod(_wrap_like)
 
     def state_dict(self) -> dict[str, Any]:
         self.synchronize()  # the offload lane owns the arenas until its copies land
         out: dict[str, Any] = {}
         for o in self.optimizers:
-            for p in o.params_list:
-                views = o.host_views(p)
-                g = o.group_of[id(p)]
-                for fqn in self.fqns.get(id(p), []):
-                    for k, v in views.items():
-                        out[f"state.{fqn}.{k}"] = self._wrap_like(p, v)
-                    out[f"state.{fqn}.step"] = torch.tensor(float(o.steps[id(p)]))
-                    for k, v in g.items():
-                        if k != "params":
-                            out[f"param_groups.{fqn}.{k}"] = (v.detach().cpu().clone() if torch.is_tensor(v)
-                                                              else copy.deepcopy(v))
+            out.update(swap_adamw_state_dict(o, self.fqns))
         return out
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         self.synchronize()
-        backup = [(o, o.m_host.clone(), o.v_host.clone(), None if o.vmax_host is None else o.vmax_host.clone(),
-                   dict(o.steps), [dict(g) for g in o.param_groups]) for o in self.optimizers]
-        try:
-            for o in self.optimizers:
-                for p in o.params_list:
-                    fqns = self.fqns.get(id(p), [])
-                    fqn = next((f for f in fqns if f"state.{f}.exp_avg" in state_dict), None)
-                    if fqn is None:
-                        continue
-                    views = o.host_views(p)
-                    for k, dst in views.items():
-                        src = state_dict.get(f"state.{fqn}.{k}")
-                        if src is None:
-                            if k == "max_exp_avg_sq":
-                                continue
-                            raise KeyError(f"state.{fqn}.{k} missing from the optimizer checkpoint")
-                        src = _local(src)
-                        if tuple(src.shape) != tuple(dst.shape):
-                            raise ValueError(f"state.{fqn}.{k}: shape {tuple(src.shape)} != {tuple(dst.shape)}")
-                        dst.copy_(src.to(torch.float32))
-                    st = state_dict.get(f"state.{fqn}.step")
-                    if st is not None:
-                        o.steps[id(p)] = int(float(st))
-                    g = o.group_of[id(p)]
-                    for k in list(g.keys()):
-                        key = f"param_groups.{fqn}.{k}"
-                        if k != "params" and key in state_dict:
-                            g[k] = state_dict[key]
-        except Exception:
-            for o, m, v, x, steps, groups in backup:
-                o.m_host.copy_(m); o.v_host.copy_(v)
-                if x is not None:
-                    o.vmax_host.copy_(x)
-                o.steps = steps
-                for g, old in zip(o.param_groups, groups):
-                    params = g["params"]
-                    g.clear(); g.update(old); g["params"] = params
-            raise
+        swap_adamw_load_state_dict(self.optimizers, self.fqns, state_dict)
         if torch.cuda.is_available():
             torch.cuda.empty_cache()
+
+
+def swap_adamw_load_state_dict(optimizers: list["SwapAdamW"], fqns_of: dict[int, list[str]],
+                               state_dict: dict[str, Any]) -> None:
+    """Transactional load into the pinned arenas of ``optimizers``: on any error the previous state is restored."""
+    for o in optimizers:
+        o.synchronize()
+    backup = [(o, o.m_host.clone(), o.v_host.clone(), None if o.vmax_host is None else o.vmax_host.clone(),
+               dict(o.steps), [dict(g) for g in o.param_groups]) for o in optimizers]
+    try:
+        for o in optimizers:
+            for p in o.params_list:
+                fqns = fqns_of.get(id(p), [])
+                fqn = next((f for f in fqns if f"state.{f}.exp_avg" in state_dict), None)
+                if fqn is None:
+                    continue
+                views = o.host_views(p)
+                for k, dst in views.items():
+                    src = state_dict.get(f"state.{fqn}.{k}")
+                    if src is None:
+                        if k == "max_exp_avg_sq":
+                            continue
+                        raise KeyError(f"state.{fqn}.{k} missing from the optimizer checkpoint")
+                    src = _local(src)
+                    if tuple(src.shape) != tuple(dst.shape):
+                        raise ValueError(f"state.{fqn}.{k}: shape {tuple(src.shape)} != {tuple(dst.shape)}")
+                    dst.copy_(src.to(torch.float32))
+                st = state_dict.get(f"state.{fqn}.step")
+                if st is not None:
+                    o.steps[id(p)] = int(float(st))
+                g = o.group_of[id(p)]
+                for k in list(g.keys()):
+                    key = f"param_groups.{fqn}.{k}"
+                    if k != "params" and key in state_dict:
+                        g[k] = state_dict[key]
+    except Exception:
+        for o, m, v, x, steps, groups in backup:
+            o.m_host.copy_(m); o.v_host.copy_(v)
+            if x is not None:
+                o.vmax_host.copy_(x)
+            o.steps = steps
+            for g, old in zip(o.param_groups, groups):
+                params = g["params"]
+                g.clear(); g.update(old); g["params"] = params
+        raise
