@@ -40,3 +40,23 @@ def test_async_tp2_reproduces_single_rank_step(tmp_path):
                             "--parallelism.tensor_parallel_degree", "2",
                             "--parallelism.enable_async_tensor_parallel"], 2, 29651), 2)
     assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)
+
+
+import pytest
+
+
+@pytest.mark.parametrize("module,config,port", [("deepseek_v3", "deepseek_v3_debugmodel", 29655),
+                                                ("qwen3", "qwen3_debugmodel", 29658)])
+def test_async_tp_fuses_row_parallel_linears_of_other_models(tmp_path, module, config, port):
+    """The model-independent half of async TP (GEMM -> reduce-scatter for every row-parallel linear that returns to
+    the sequence shard) on an MLA + MoE model and on Qwen3: a TP2 run with the switch on reproduces one rank."""
+    folder = str(tmp_path / "run")
+    common = ["--module", module, "--config", config, "--training.seq_len", "128", "--comm.backend", "gloo",
+              "--training.local_batch_size", "1", "--job.dump_folder", folder, "--checkpoint.enable",
+              "--checkpoint.interval", "1", "--training.steps", "2"]
+    ref = step_line(launch(common, 1, port), 2)
+    log = launch([*common, "--checkpoint.load_step", "1", "--parallelism.data_parallel_shard_degree", "1",
+                  "--parallelism.tensor_parallel_degree", "2", "--parallelism.enable_async_tensor_parallel"], 2,
+                 port + 1)
+    got = step_line(log, 2)
+    assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)

@@ -1,0 +1,80 @@
+"""Swap and Virtual optimizers on a GPU against the resident fused AdamW: bit-identical parameters after three
+steps (all three run the same multi-tensor kernel; only where the moments live differs), moments actually off the
+device, and peak device memory of the swap pipeline as its docstring states (two slots of two or three moments)."""
+
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(device):
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(512, 1024, bias=False), nn.LayerNorm(1024), nn.Linear(1024, 1024),
+                         nn.Linear(1024, 256, bias=False)).to(device=device, dtype=torch.bfloat16)
+
+
+def _steps(model, opt, n=3):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for _ in range(n):
+        opt.zero_grad()
+        x = torch.randn(64, 512, device="cuda", dtype=torch.bfloat16, generator=g)
+        model(x).float().pow(2).mean().backward()
+        opt.step()
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("amsgrad", [False, True])
+def test_swap_adamw_is_bit_identical_to_resident_fused_adamw(cuda_device, amsgrad):
+    from titan_b200.optim.fused_adamw import FusedAdamW
+    from titan_b200.optim.swap_optimizer import SwapAdamW
+
+    ref_model = _model(cuda_device)
+    model = copy.deepcopy(ref_model)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, amsgrad=amsgrad)
+    ref = FusedAdamW(list(ref_model.parameters()), **kw)
+    opt = SwapAdamW(list(model.parameters()), swap_times=4, **kw)
+    assert len(opt.slices) >= 3 and opt.m_host.is_pinned() and not opt.m_host.is_cuda
+    _steps(ref_model, ref)
+    before = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    _steps(model, opt)
+    opt.synchronize()
+    for a, b in zip(ref_model.parameters(), model.parameters()):
+        assert torch.equal(a, b)
+    # the moments on the host equal the resident ones
+    p0, q0 = next(iter(ref_model.parameters())), next(iter(model.parameters()))
+    assert torch.equal(ref.state[p0]["exp_avg"].cpu().float().reshape(-1),
+                       opt.host_views(q0)["exp_avg"].reshape(-1))
+    # staging: 2 slots x (2 or 3) moments x slot_numel fp32, nothing else stays on the device
+    staging = 2 * (3 if amsgrad else 2) * opt.slot_numel * 4
+    held = torch.cuda.memory_allocated() - before
+    assert held <= staging + (1 << 20), (held, staging)
+    opt.release_staging()
+    assert torch.cuda.memory_allocated() - before < (1 << 20)
+
+
+def test_virtual_adamw_with_a_budget_smaller_than_the_model(cuda_device):
+    from titan_b200.optim.fused_adamw import FusedAdamW
+    from titan_b200.optim.virtual_optimizer import VirtualAdamW, VirtualAllocator
+
+    ref_model = _model(cuda_device)
+    model = copy.deepcopy(ref_model)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ref = FusedAdamW(list(ref_model.parameters()), **kw)
+    # 6 MB: both moments of the first matrix (2 x 2 MiB) fit, the second matrix (2 x 4 MiB) does not
+    alloc = VirtualAllocator(6e-3)
+    opt = VirtualAdamW(list(model.parameters()), allocator=alloc, **kw)
+    _steps(ref_model, ref)
+    _steps(model, opt)
+    for a, b in zip(ref_model.parameters(), model.parameters()):
+        assert torch.equal(a, b)
+    params = list(model.parameters())
+    assert id(params[0]) in opt.virtual_params and id(params[2]) not in opt.virtual_params
+    m0 = opt.state[params[0]]["exp_avg"]
+    assert not m0.is_cuda and m0.is_pinned()            # read and written in place over the host link
+    assert opt.state[params[2]]["exp_avg"].is_cuda      # beyond the budget: ordinary device state
+    assert torch.equal(m0.float(), ref.state[next(iter(ref_model.parameters()))]["exp_avg"].cpu().float())

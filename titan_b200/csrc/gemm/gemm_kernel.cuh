@@ -14,10 +14,7 @@ int launch(const AMaps& am, const CUtensorMap& tb_, const CMaps& cm, const GemmP
 // chunk to the GEMM CTAs through a local flag.  Chunks are visited in ring order starting at the next rank.
 // One thread drives bulk asynchronous copies (peer global -> shared -> local global) through a ring of
 // COPY_BUFS shared buffers, so a CTA keeps ~190 KB in flight on the link without spending registers or
-// issue slots; no multicast is involved.  A copier owns whole chunks.  Dealing the 32 KB pieces of one chunk to all
-// copiers (so that chunks complete one by one) was measured on 2 GPUs and gained nothing (fsdp weight gather
-// 8192x28672x4096: 1.80 ms either way), and a completion counter per PIECE (an atomic round trip per 32 KB) cost
-// a third of the copy rate (2.40 ms).
+// issue slots; no multicast is involved.  A copier owns whole chunks (one completion flag per chunk, not per piece).
 constexpr int COPY_PIECE = 32 * 1024;
 constexpr int COPY_BUFS = 6;
 

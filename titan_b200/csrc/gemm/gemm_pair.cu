@@ -32,15 +32,15 @@ double plan_cost(int tiles, int pairs, int full_waves, int s, double part_overhe
 }
 }  // namespace
 
-static int g_diag = 0;  // DIAG
+// Tuning knobs (process-wide): tile rows walked together, ring depth in use (2..STAGES), L2 promotion of the operand
+// tensor maps (CUtensorMapL2promotion: 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B).  Non-positive values restore defaults.
 static int g_group_m = 8, g_stages = STAGES, g_promo = 3;
 TB_API int tb_gemm_pair_tune(int group_m, int stages, int promo) {
   g_group_m = group_m > 0 ? group_m : 8;
   g_stages = stages >= 2 && stages <= STAGES ? stages : STAGES;
-  g_promo = promo;
+  g_promo = promo >= 0 && promo <= 3 ? promo : 3;
   return 0;
 }
-TB_API int tb_gemm_pair_diag(int d) { g_diag = d; return 0; }  // DIAG
 TB_API long long tb_gemm_ws_bytes() { return (long long)(tbg::sm_count() / 2) * TILE_WS_BYTES + TICKET_BYTES; }
 
 // policy: 0 = choose, 1 = single-CTA engine, 2 = CTA pairs.  ws may be null (no tail split).
@@ -71,7 +71,6 @@ TB_API int tb_gemm_auto(const void* A, const void* B, void* C, int M, int N, int
   PairParams p = {};
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.out_fp32 = out_fp32; p.is_bf16 = dtype == 1;
   p.accumulate = accumulate; p.ldc = ldc; p.C = C; p.status = status;
-  p.diag = g_diag;  // DIAG
   p.group_m = g_group_m; p.stages = g_stages;
   if (!out_fp32 && !accumulate) {
     if (int rc = tbh::make_tmap_2d(&tc, C, dt, 2, M, N, (uint64_t)ldc * 2, HM, 64, 3)) return rc;

@@ -53,7 +53,6 @@ struct PairParams {
   int split;               // 1 = no split
   float* ws;               // [tail tiles][256 x 256] fp32 partial sums, zero between launches
   unsigned int* tickets;   // [2 x tail tiles] arrival counters (one per CTA half), zero between launches
-  int diag;                // DIAG
   int group_m;             // tile rows walked together (L2 reuse of the B panels)
   int stages;              // ring depth actually used (<= STAGES)
 };
@@ -223,11 +222,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_EMPTY); }
             ok = false; break;
           }
-          if (p.diag & 2) {  // DIAG
-            if (leader) mbar_arrive(&full_bar[stage]);
-            if (++stage == p.stages) { stage = 0; phase ^= 1; }
-            continue;
-          }
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
           const uint32_t fb = mapa(smem_u32(&full_bar[stage]), 0);
           uint8_t* sa = smem_a + stage * A_STAGE_BYTES;
@@ -337,13 +331,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t taddr = tmem_base + acc * TN + ((uint32_t)(q * 32) << 16);
       const uint32_t tmem_empty_leader = mapa(smem_u32(&tmem_empty_bar[acc]), 0);
       bool finish = true;   // this unit writes the output (whole tile, or last arriving part of a tail tile)
-      if (p.diag & 1) {  // DIAG: no epilogue work
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote(tmem_empty_leader);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        continue;
-      }
 
       if (w.tail >= 0) {
         // add this part's fp32 partial into the tile's workspace; the last part to arrive finishes the tile

@@ -38,6 +38,7 @@ __all__ = [
     "AwaitRowwiseParallel",
     "PrepareModuleInputOutputWithBwdAllReduce",
     "SequenceShardedLinear",
+    "FusedRowwiseParallel",
     "ReplicateParams",
     "norm_weight_local",
     "replicated_param_local",
@@ -51,7 +52,20 @@ _ASYNC_TP = {"enabled": False}
 def parallelize_module(module: nn.Module, device_mesh: DeviceMesh | None = None, parallelize_plan=None, **kwargs):
     for updater in active_plan_updaters():
         parallelize_plan = updater.update(parallelize_plan)
+    if _ASYNC_TP["enabled"] and isinstance(parallelize_plan, dict):
+        # async tensor parallelism, model-independent half: every row-parallel linear whose output goes back to the
+        # sequence shard runs its reduce-scatter inside the GEMM (any model plan; embeddings and biased linears keep
+        # their original style)
+        parallelize_plan = {k: (FusedRowwiseParallel(v) if _is_seq_rowwise(v) else v)
+                            for k, v in parallelize_plan.items()}
     return _torch_parallelize_module(module, device_mesh, parallelize_plan, **kwargs)
+
+
+def _is_seq_rowwise(style) -> bool:
+    return (type(style) in (RowwiseParallel, AwaitRowwiseParallel)
+            and tuple(getattr(style, "output_layouts", ())) == (Shard(1),)
+            and tuple(getattr(style, "input_layouts", ())) == (Shard(-1),)
+            and getattr(style, "use_local_output", True))
 
 
 class NoParallel(ParallelStyle):
@@ -191,6 +205,42 @@ class ShardOnly(ParallelStyle):
             placement = Shard(self.dim) if p.dim() > self.dim else Replicate()
             module.register_parameter(name, nn.Parameter(distribute_tensor(p.data, device_mesh, [placement]),
                                                          requires_grad=p.requires_grad))
+        return module
+
+
+class FusedRowwiseParallel(ParallelStyle):
+    """`RowwiseParallel(output_layouts=Shard(1))` with the reduce-scatter fused into the GEMM: the weight keeps its
+    input-feature shard, the forward multiplies the local activations and the epilogue of the GEMM stores every tile
+    into the staging slot of the rank that owns those sequence rows (`titan_b200.parallel.async_tp.linear_rs`).
+    One sequence per rank takes the fused kernel; other batch shapes, biased linears and non-linear modules (the
+    embedding) fall back to the wrapped style or to a library reduce-scatter with the same result."""
+
+    def __init__(self, fallback: ParallelStyle):
+        super().__init__()
+        self.fallback = fallback
+
+    def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
+        if not isinstance(module, nn.Linear) or module.bias is not None:
+            return self.fallback._apply(module, device_mesh)
+        from torch.distributed.tensor import Partial
+
+        module.register_parameter("weight", nn.Parameter(
+            distribute_tensor(module.weight.data, device_mesh, [Shard(1)]), requires_grad=module.weight.requires_grad))
+        group = device_mesh.get_group()
+
+        def forward(x, _m=module):
+            from titan_b200.parallel.async_tp import linear_rs
+
+            w = _m.weight.to_local()
+            if isinstance(x, DTensor):
+                x = x.to_local()
+            if x.dim() == 3 and x.shape[0] == 1:
+                return linear_rs(x[0].to(w.dtype), w, group).unsqueeze(0)
+            y = torch.nn.functional.linear(x, w)
+            return DTensor.from_local(y, device_mesh, [Partial()]).redistribute(placements=[Shard(1)]).to_local()
+
+        module.forward = forward
+        module._async_tp = "gemm_reduce_scatter"
         return module
 
 
