@@ -60,3 +60,16 @@ def test_async_tp_fuses_row_parallel_linears_of_other_models(tmp_path, module, c
                  port + 1)
     got = step_line(log, 2)
     assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)
+
+
+def test_tcgen05_linear_converter_keeps_tensor_parallel_semantics(tmp_path):
+    """`b200_linear` under TP2 multiplies the local shards itself (column shard -> Shard(-1), row shard -> Partial):
+    the step has to equal the single-rank step (on CPU the local products run through the library)."""
+    folder = str(tmp_path / "run")
+    common = ["--module", "llama3", "--config", "llama3_debugmodel", "--training.seq_len", "128", "--comm.backend",
+              "gloo", "--training.local_batch_size", "2", "--job.dump_folder", folder, "--checkpoint.enable",
+              "--checkpoint.interval", "1", "--training.steps", "2", "--model_converters.converters", "b200_linear"]
+    ref = step_line(launch(common, 1, 29661), 2)
+    got = step_line(launch([*common, "--checkpoint.load_step", "1", "--parallelism.data_parallel_shard_degree", "1",
+                            "--parallelism.tensor_parallel_degree", "2"], 2, 29662), 2)
+    assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)

@@ -1,4 +1,4 @@
-"""FSDP2 with the peer-memory reduce-scatter hook.  On CPU / gloo the hook's bookkeeping runs (bucket handed out
+"""FSDP2 with the peer-memory reduce-scatter and all-gather hooks.  On CPU / gloo the hook's bookkeeping runs (bucket handed out
 in the wire dtype, output in the reduce dtype, library reduction) and must reproduce stock FSDP2 step for step;
 the kernel itself is covered on GPUs by tests/test_fused_comm_multigpu.py and the 2-GPU case below."""
 
@@ -19,7 +19,7 @@ def test_hook_reproduces_stock_fsdp2_on_gloo(tmp_path):
     ref = losses(launch([*common, "--job.dump_folder", str(tmp_path / "a"), "--parallelism.fsdp_reduce_scatter", "nccl"],
                         2, 29690))
     got = losses(launch([*common, "--job.dump_folder", str(tmp_path / "b"), "--parallelism.fsdp_reduce_scatter",
-                         "peer_memory"], 2, 29691))
+                         "peer_memory", "--parallelism.fsdp_all_gather", "peer_memory"], 2, 29691))
     assert len(ref) == 4 and got == ref, (got, ref)
 
 
@@ -48,7 +48,7 @@ def test_two_gpus_peer_memory_matches_nccl(tmp_path):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
                "127.0.0.1", "--master-port", str(port), "-m", "titan_b200.entry", "--module", "llama3", "--config",
                "llama3_debugmodel_b200", "--training.steps", "4", "--debug.seed", "3", "--job.dump_folder",
-               str(tmp_path / mode), "--parallelism.fsdp_reduce_scatter", mode]
+               str(tmp_path / mode), "--parallelism.fsdp_reduce_scatter", mode, "--parallelism.fsdp_all_gather", mode]
         res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
         assert res.returncode == 0, (res.stdout + res.stderr)[-4000:]
         return losses(res.stdout + res.stderr)

@@ -1,0 +1,67 @@
+"""Sparse MLA kernel (gathered key tiles on tcgen05) against the fp32 gather oracle: output, log-sum-exp, teacher,
+empty slots, sink logits, head groups, and gradients through the chunked backward."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(S, H, T, K, dq=576, dv=512, empty=0.1, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = (torch.randn(S, H, dq, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    kv = (torch.randn(T, dq, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(T, device="cuda", generator=g)[:K] for _ in range(S)]).to(torch.int32)
+    if empty:
+        idx = torch.where(torch.rand(S, K, device="cuda", generator=g) < empty, torch.full_like(idx, -1), idx)
+    return q, kv, idx
+
+
+@pytest.mark.parametrize("S,H,T,K,dq,dv", [(8, 16, 512, 128, 576, 512), (40, 16, 4096, 256, 576, 512),
+                                           (16, 32, 1024, 384, 576, 512), (8, 64, 1024, 128, 576, 512),
+                                           (12, 16, 700, 256, 192, 128)])
+def test_forward_matches_gather_oracle(cuda_device, S, H, T, K, dq, dv):
+    from titan_b200.ops import _lib
+    from titan_b200.ops.sparse_mla import sparse_mla_forward, sparse_mla_forward_ref, sparse_mla_supported
+
+    q, kv, idx = _case(S, H, T, K, dq, dv)
+    assert sparse_mla_supported(q, kv, idx, dv)
+    scale = dq ** -0.5
+    out, lse, teacher = sparse_mla_forward(q, kv, idx, scale, dv)
+    _lib.shared_status().raise_if_set("sparse_mla")
+    ro, rl, rt = sparse_mla_forward_ref(q, kv, idx, scale, dv)
+    torch.testing.assert_close(lse, rl, rtol=1e-3, atol=2e-3)
+    torch.testing.assert_close(out.float(), ro.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(teacher, rt, rtol=2e-2, atol=2e-3)
+
+
+def test_sink_and_fully_empty_rows(cuda_device):
+    from titan_b200.ops.sparse_mla import sparse_mla_forward, sparse_mla_forward_ref
+
+    q, kv, idx = _case(8, 16, 512, 128)
+    idx[3] = -1                                   # a query without any key
+    sink = torch.randn(16, device="cuda")
+    scale = 576 ** -0.5
+    out, lse, teacher = sparse_mla_forward(q, kv, idx, scale, 512, sink=sink)
+    ro, rl, rt = sparse_mla_forward_ref(q, kv, idx, scale, 512, sink=sink)
+    torch.testing.assert_close(lse, rl, rtol=1e-3, atol=2e-3)
+    torch.testing.assert_close(out.float(), ro.float(), rtol=2e-2, atol=2e-2)
+    assert float(out[3].abs().max()) == 0.0       # only the sink holds mass there
+    out2, lse2, _ = sparse_mla_forward(q, kv, idx, scale, 512)
+    assert torch.isinf(lse2[3]).all() and float(out2[3].abs().max()) == 0.0
+
+
+def test_backward_matches_autograd_of_the_oracle(cuda_device):
+    from titan_b200.ops.sparse_mla import sparse_mla, sparse_mla_forward_ref
+
+    q, kv, idx = _case(24, 16, 512, 128, empty=0.2)
+    scale = 576 ** -0.5
+    q1, kv1 = q.clone().requires_grad_(), kv.clone().requires_grad_()
+    out, teacher, lse = sparse_mla(q1, kv1, idx, scale, 512, chunk=16)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr = q.float().requires_grad_(), kv.float().requires_grad_()
+    ro, _, _ = sparse_mla_forward_ref(qr, kr, idx, scale, 512)
+    ro.backward(g.float())
+    torch.testing.assert_close(q1.grad.float(), qr.grad, rtol=5e-2, atol=2e-2)
+    torch.testing.assert_close(kv1.grad.float(), kr.grad, rtol=5e-2, atol=3e-2)

@@ -196,6 +196,10 @@ class ParallelismConfig:
     EP ranks makes it dropless.  A routing beyond it stops the step with a kernel status (nothing is dropped)."""
     fsdp_fused_collectives: bool = False
     """Fuse FSDP all-gather into the consuming GEMM and cast/scale into reduce-scatter."""
+    fsdp_all_gather: Literal["auto", "nccl", "peer_memory"] = "auto"
+    """Parameter all-gather of FSDP2: `nccl` = stock, `peer_memory` = copy-engine pulls from the peers' symmetric
+    buffers (no SMs taken from the overlapping GEMMs), `auto` = `peer_memory` under the conditions of
+    `fsdp_reduce_scatter`."""
     fsdp_reduce_scatter: Literal["auto", "nccl", "peer_memory"] = "auto"
     """Gradient reduce-scatter of FSDP2: `nccl` = stock (fp32 bucket through NCCL), `peer_memory` = bf16 bucket in
     symmetric memory reduced by one kernel over NVLink peer loads, `auto` = `peer_memory` for CUDA jobs whose FSDP

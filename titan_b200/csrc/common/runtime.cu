@@ -22,3 +22,11 @@ TB_API int tb_bind_device(int device) {
   TB_CUDA_CHECK(cudaFree(nullptr));
   return 0;
 }
+
+// One asynchronous device-to-device copy on `st` (copy engine; `src` may be a peer GPU's memory mapped into this
+// process).  Collectives that should not occupy SMs (the FSDP parameter all-gather) are built from these.
+TB_API int tb_peer_copy(void* dst, const void* src, long long bytes, cudaStream_t st) {
+  if (bytes <= 0) return 0;
+  TB_CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, st));
+  return 0;
+}

@@ -145,6 +145,7 @@ def parallelize_deepseekv32(model: nn.Module, *, parallel_dims, training, model_
                        cpu_offload=training.enable_cpu_offload,
                        reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward,
             reduce_scatter=parallelism.fsdp_reduce_scatter,
+            all_gather=parallelism.fsdp_all_gather,
                        ep_degree=pd.ep if edp is not None else 1, edp_mesh=edp,
                        gradient_divide_factor=pd.fsdp_gradient_divide_factor)
     elif pd.dp_replicate_enabled:

@@ -67,7 +67,10 @@ def llama3_8b() -> TrainerConfig:
         # rotary embedding, SwiGLU and residual adds: about 2 % of the step for 9 GB.  `llama3_8b_noac` drops it (an 8B
         # model at seq 8192 peaks at 112 GB on ONE 180 GB GPU, 96 GB of it weights, gradients and fp32 AdamW state).
         activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op_save_all_mm"),
-        model_converters=ModelConvertersConfig(converters=_fused_converters()),
+        # every operator of the block that this framework owns: norms, rotary embedding, SwiGLU, the loss and all
+        # projections (tcgen05 GEMMs); attention stays on the fused library kernel
+        model_converters=ModelConvertersConfig(
+            converters=[*_fused_converters(), get_model_converter_config("b200_linear")]),
     )
 
 

@@ -156,6 +156,7 @@ def parallelize_llama(
             cpu_offload=training.enable_cpu_offload,
             reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward,
             reduce_scatter=parallelism.fsdp_reduce_scatter,
+            all_gather=parallelism.fsdp_all_gather,
         )
     elif parallel_dims.dp_replicate_enabled:
         apply_replicate(

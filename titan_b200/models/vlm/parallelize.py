@@ -46,7 +46,8 @@ def parallelize_vlm(model: nn.Module, *, parallel_dims, training, model_converte
                    reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce], pp_enabled=False,
                    cpu_offload=training.enable_cpu_offload,
                    reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward,
-            reduce_scatter=parallelism.fsdp_reduce_scatter)
+            reduce_scatter=parallelism.fsdp_reduce_scatter,
+            all_gather=parallelism.fsdp_all_gather)
     elif pd.dp_replicate_enabled:
         apply_replicate(model, pd.get_mesh(("dp_replicate", "fsdp")), param_dtype=DTYPE_MAP[training.mixed_precision_param],
                         reduce_dtype=DTYPE_MAP[training.mixed_precision_reduce])

@@ -68,6 +68,7 @@ def _declare(L) -> None:
         "tb_rs_reduce": [P, P, c_uint, P, LL, I, I, P, P],
         "tb_castscale_rs": [P, P, LL, I, I, F, I, I, P],
         "tb_put": [P, I, P, LL, P],
+        "tb_peer_copy": [P, P, LL, P],
         "tb_gemm_a2a_scatter": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, c_uint, P, P],
         "tb_a2a_gather_gemm": [P, P, P, P, P, I, I, I, I, I, I, I, I, P, c_uint, P, P],
     }

@@ -1,0 +1,122 @@
+"""Sparse multi-head latent attention on the tcgen05 kernel (`csrc/attention/sparse_mla_fwd.cu`).
+
+``sparse_mla_forward(q, kv, idx, scale, dv)`` attends every query to its selected rows of the shared one-head KV latent
+only: the kernel gathers 128 selected rows at a time into shared memory and runs both contractions on the tensor
+cores, so memory and work are O(S * top-k) however long the key stream is.  It returns the output, the log-sum-exp and
+the head-summed probabilities (the teacher of the lightning indexer's KL loss), all exact (two passes over the keys).
+
+`SparseMLAFunction` adds autograd: the backward recomputes the probabilities from the saved log-sum-exp in query
+chunks (row gather, scatter-add of the latent gradient), so nothing of size [S, T] exists in either direction.
+
+Parity: `npu_sparse_flash_attention` with `softmax_lse` output (torchtitan_npu/converters/kernels/dsa.py:195-277) and
+`sparse_flash_mla` / `sparse_flash_mla_grad` (converters/kernels/npu_smla.py:59-1348).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from titan_b200.ops import _lib
+
+__all__ = ["sparse_mla_supported", "sparse_mla_forward", "sparse_mla_forward_ref", "sparse_mla"]
+
+_DECLARED = False
+
+
+def _declare():
+    global _DECLARED
+    if not _DECLARED:
+        P, I, Fl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        _lib.declare("tb_sparse_mla_fwd", [P, P, P, P, P, P, P, I, I, I, I, I, I, Fl, P, P])
+        _DECLARED = True
+
+
+def sparse_mla_supported(q: torch.Tensor, kv: torch.Tensor, idx: torch.Tensor, dv: int) -> bool:
+    """q [S, H, Dq], kv [T, Dq], idx [S, K]."""
+    H, dq = q.shape[1], q.shape[2]
+    return (q.is_cuda and q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and H % 16 == 0
+            and dq % 64 == 0 and dq <= 576 and dv % 128 == 0 and dv <= min(512, dq) and idx.shape[1] % 128 == 0)
+
+
+def sparse_mla_forward_ref(q, kv, idx, scale: float, dv: int, sink: torch.Tensor | None = None):
+    """fp32 oracle: gather, softmax over the selected keys (+ an optional per-head sink logit in the denominator)."""
+    S, H, _ = q.shape
+    safe = idx.clamp_min(0).long()
+    ksel = kv.float()[safe]                                  # [S, K, Dq]
+    s = torch.einsum("shd,skd->shk", q.float(), ksel) * scale
+    s = s.masked_fill((idx < 0).unsqueeze(1), float("-inf"))
+    if sink is not None:
+        s_all = torch.cat([s, sink.float().view(1, H, 1).expand(S, H, 1)], dim=-1)
+        lse = torch.logsumexp(s_all, dim=-1)
+    else:
+        lse = torch.logsumexp(s, dim=-1)
+    p = torch.nan_to_num(torch.exp(s - lse.unsqueeze(-1)))
+    out = torch.einsum("shk,skd->shd", p, ksel[..., :dv])
+    return out.to(q.dtype), lse, p.sum(1)
+
+
+def sparse_mla_forward(q, kv, idx, scale: float, dv: int, sink: torch.Tensor | None = None, want_teacher=True):
+    """q [S, H, Dq] bf16, kv [T, Dq] bf16 (values = first ``dv`` columns), idx [S, K] int32 (-1 = empty slot)
+    → (out [S, H, dv], lse [S, H] fp32, teacher [S, K] fp32 or None)."""
+    _declare()
+    S, H, dq = q.shape
+    T, K = kv.shape[0], idx.shape[1]
+    q, kv = q.contiguous(), kv.contiguous()
+    idx = idx.to(torch.int32).contiguous()
+    out = torch.empty(S, H, dv, dtype=q.dtype, device=q.device)
+    lse = torch.empty(S, H, dtype=torch.float32, device=q.device)
+    teacher = torch.zeros(S, K, dtype=torch.float32, device=q.device) if want_teacher else None
+    sk = sink.float().contiguous() if sink is not None else None
+    rc = _lib.lib().tb_sparse_mla_fwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      _lib.ptr(teacher), _lib.ptr(sk), S, H, T, K, dq, dv, float(scale),
+                                      _lib.shared_status().ptr, _lib.stream_ptr())
+    _lib.check(rc, "sparse_mla_fwd")
+    return out, lse, teacher
+
+
+class SparseMLAFunction(torch.autograd.Function):
+    """(q, kv, idx) → (out, teacher, lse).  ``kv`` carries keys AND values (first ``dv`` columns); its gradient sums
+    both roles.  `teacher` and `lse` carry no gradient."""
+
+    @staticmethod
+    def forward(ctx, q, kv, idx, scale, dv, sink, chunk):
+        out, lse, teacher = sparse_mla_forward(q, kv, idx, scale, dv, sink)
+        ctx.save_for_backward(q, kv, idx, lse, out, sink if sink is not None else torch.empty(0, device=q.device))
+        ctx.scale, ctx.dv, ctx.chunk, ctx.has_sink = scale, dv, chunk, sink is not None
+        ctx.mark_non_differentiable(teacher, lse)
+        return out, teacher, lse
+
+    @staticmethod
+    def backward(ctx, g_out, _gt, _gl):
+        q, kv, idx, lse, out, sink = ctx.saved_tensors
+        S, H, dq = q.shape
+        dv, scale = ctx.dv, ctx.scale
+        dq_ = torch.empty_like(q)
+        dkv = torch.zeros(kv.shape[0], dq, dtype=torch.float32, device=kv.device)
+        dsink = torch.zeros(H, dtype=torch.float32, device=q.device) if ctx.has_sink else None
+        delta = (g_out.float() * out.float()).sum(-1)                    # [S, H]
+        for s0 in range(0, S, ctx.chunk):
+            s1 = min(s0 + ctx.chunk, S)
+            ix = idx[s0:s1]
+            safe = ix.clamp_min(0).long()
+            ksel = kv[safe]                                              # [sc, K, Dq] storage dtype
+            sc = torch.einsum("shd,skd->shk", q[s0:s1], ksel).float() * scale
+            p = torch.exp(sc - lse[s0:s1].unsqueeze(-1)).masked_fill((ix < 0).unsqueeze(1), 0.0)
+            go = g_out[s0:s1]
+            dp = torch.einsum("shd,skd->shk", go, ksel[..., :dv]).float()
+            ds = (p * (dp - delta[s0:s1].unsqueeze(-1)) * scale).to(q.dtype)
+            dq_[s0:s1] = torch.einsum("shk,skd->shd", ds, ksel)
+            dk_rows = torch.einsum("shk,shd->skd", ds, q[s0:s1]).float()  # score path, [sc, K, Dq]
+            dk_rows[..., :dv] += torch.einsum("shk,shd->skd", p.to(q.dtype), go).float()   # value path
+            dkv.index_add_(0, safe.reshape(-1), dk_rows.reshape(-1, dq))
+            if dsink is not None:
+                ps = torch.exp(sink.float().view(1, H) - lse[s0:s1])      # probability mass on the sink
+                dsink -= (ps * delta[s0:s1]).sum(0)
+        return dq_, dkv.to(kv.dtype), None, None, None, (dsink.to(sink.dtype) if dsink is not None else None), None
+
+
+def sparse_mla(q, kv, idx, scale: float, dv: int, sink: torch.Tensor | None = None, chunk: int = 128):
+    """Differentiable sparse MLA → (out [S, H, dv], teacher [S, K], lse [S, H])."""
+    return SparseMLAFunction.apply(q, kv, idx, scale, dv, sink, chunk)

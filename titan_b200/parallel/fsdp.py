@@ -71,6 +71,7 @@ def apply_fsdp(
     extra_modules: tuple[str, ...] = (),
     ignored_params: set | None = None,
     reduce_scatter: str = "nccl",
+    all_gather: str = "nccl",
 ) -> nn.Module:
     """Shard `model` block by block over `dp_mesh` (1-D = FSDP, 2-D = HSDP).  ``ignored_params``: parameters that
     another mechanism already shards (the fused-collective linears) and FSDP2 must leave alone.  ``reduce_scatter``:
@@ -123,8 +124,12 @@ def apply_fsdp(
     if not cpu_offload:
         from titan_b200.parallel.fsdp_comm import install_peer_reduce_scatter, peer_reduce_scatter_wanted
 
+        from titan_b200.parallel.fsdp_comm import install_peer_all_gather
+
         if peer_reduce_scatter_wanted(reduce_scatter, dp_mesh, dp_mesh.device_type):
             model._peer_reduce_scatter = install_peer_reduce_scatter(model, dp_mesh, wire_dtype=param_dtype)
+        if peer_reduce_scatter_wanted(all_gather, dp_mesh, dp_mesh.device_type):
+            model._peer_all_gather = install_peer_all_gather(model, dp_mesh, param_dtype=param_dtype)
     return model
 
 

@@ -1,4 +1,13 @@
-"""FSDP2 gradient reduce-scatter over NVLink peer memory (``parallelism.fsdp_reduce_scatter``).
+"""FSDP2 collectives over NVLink peer memory (``parallelism.fsdp_reduce_scatter``, ``parallelism.fsdp_all_gather``).
+
+Parameter all-gather (`PeerMemoryAllGather`): FSDP2 writes this rank's shards into its chunk of a gather buffer and
+calls an all-gather; here the buffer lives in symmetric memory and every rank PULLS the other chunks with plain
+asynchronous device-to-device copies, which run on the copy engines.  No SM is taken from the GEMMs that run while
+the next layer's weights arrive (an NCCL all-gather holds a few dozen CTAs for its whole duration), and the bytes
+cross NVLink once, at copy-engine rate.  Three buffer slots rotate; a slot is rewritten only after every peer has
+signalled that it pulled its chunk.
+
+Gradient reduce-scatter (`PeerMemoryReduceScatter`):
 
 Stock FSDP2 reduces gradients in three passes per parameter group: the bf16 gradients are copied AND cast into one
 fp32 bucket, NCCL reduce-scatters that bucket (4 bytes per element on the wire, kernels that hold SMs while the
@@ -28,9 +37,10 @@ import math
 import torch
 import torch.distributed as dist
 import torch.nn as nn
-from torch.distributed.fsdp._fully_shard._fsdp_api import ReduceScatter
+from torch.distributed.fsdp._fully_shard._fsdp_api import AllGather, ReduceScatter
 
-__all__ = ["PeerMemoryReduceScatter", "install_peer_reduce_scatter", "peer_reduce_scatter_wanted", "max_bucket_numel"]
+__all__ = ["PeerMemoryReduceScatter", "PeerMemoryAllGather", "install_peer_reduce_scatter", "install_peer_all_gather",
+           "peer_reduce_scatter_wanted", "max_bucket_numel"]
 
 
 class PeerMemoryReduceScatter(ReduceScatter):
@@ -95,6 +105,75 @@ class PeerMemoryReduceScatter(ReduceScatter):
         return dist.reduce_scatter_tensor(output=output_tensor, input=wide, group=group, op=op, async_op=async_op)
 
 
+class PeerMemoryAllGather(AllGather):
+    """FSDP2 all-gather as copy-engine pulls from the peers' symmetric buffers (see the module docstring)."""
+
+    SLOTS = 3
+    CH_READY, CH_DONE = 8, 9   # flag channels of the workspace (0..7 belong to `ops.fused_comm`)
+
+    def __init__(self, group, reserve_bytes: int = 0):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.ws = None
+        self.slot_bytes = 0
+        self.uses = 0
+        self.last_done = [0] * self.SLOTS
+        self._pending = None          # (slot, byte offset) handed out by the last `allocate`
+        self.calls = self.fallback_calls = 0
+        if reserve_bytes and torch.cuda.is_available():
+            self._ensure(reserve_bytes)
+
+    def _ensure(self, nbytes: int) -> None:
+        from titan_b200.parallel.symm_mem import get_workspace
+
+        need = (nbytes + 1023) // 1024 * 1024
+        if self.ws is None or need > self.slot_bytes:
+            self.slot_bytes = need
+            self.ws = get_workspace(self.group, self.SLOTS * need, "fsdp_ag")   # collective when it (re)allocates
+            self.last_done = [0] * self.SLOTS
+
+    def allocate(self, size, *, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        numel = math.prod(int(s) for s in size)
+        self._pending = None
+        if device.type != "cuda":
+            return torch.empty(numel, dtype=dtype, device=device)
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        self._ensure(nbytes)
+        slot = self.uses % self.SLOTS
+        self.uses += 1
+        if self.last_done[slot]:
+            self.ws.wait(self.CH_DONE, self.last_done[slot])   # every peer has pulled what this slot held before
+        off = slot * self.slot_bytes
+        self._pending = (slot, off)
+        return self.ws.view(off, (numel,), dtype)
+
+    def __call__(self, output_tensor: torch.Tensor, input_tensor: torch.Tensor, group, async_op: bool = False):
+        pend = self._pending
+        self._pending = None
+        if pend is None or not output_tensor.is_cuda:
+            self.fallback_calls += 1
+            return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
+        from titan_b200.ops import _lib
+
+        slot, off = pend
+        ws = self.ws
+        chunk = input_tensor.numel() * input_tensor.element_size()
+        ready = ws.next_epoch(self.CH_READY)
+        ws.signal(self.CH_READY, ready)      # my chunk is in place (the stream is ordered after FSDP's copy-in)
+        ws.wait(self.CH_READY, ready)        # ... and so is everybody else's
+        L, st = _lib.lib(), _lib.stream_ptr()
+        for d in range(1, self.world):       # ring order: spreads the pulls over the peers
+            r = (self.rank + d) % self.world
+            rc = L.tb_peer_copy(ws.data_ptr(self.rank, off + r * chunk), ws.data_ptr(r, off + r * chunk), chunk, st)
+            _lib.check(rc, "peer_copy")
+        done = ws.next_epoch(self.CH_DONE)
+        ws.signal(self.CH_DONE, done)        # I no longer read the peers' copies of this slot
+        self.last_done[slot] = done
+        self.calls += 1
+        return None
+
+
 def max_bucket_numel(model: nn.Module, world: int) -> int:
     """Largest gradient bucket FSDP2 will build for `model`: per FSDP parameter group, every parameter padded on
     dim 0 to a multiple of ``world``."""
@@ -132,6 +211,28 @@ def peer_reduce_scatter_wanted(setting: str, dp_mesh, device_type: str) -> bool:
     if setting == "peer_memory" and not ok and device_type == "cuda":
         raise ValueError("fsdp_reduce_scatter=peer_memory needs an FSDP group of 2..8 GPUs on one node")
     return ok or setting == "peer_memory"
+
+
+def install_peer_all_gather(model: nn.Module, dp_mesh, param_dtype: torch.dtype) -> PeerMemoryAllGather | None:
+    """Give every FSDP module of `model` whose shard group is ``dp_mesh``'s shard axis the copy-engine all-gather."""
+    from torch.distributed.fsdp import FSDPModule
+
+    shard_mesh = dp_mesh if dp_mesh.ndim == 1 else dp_mesh[dp_mesh.mesh_dim_names[-1]]
+    group = shard_mesh.get_group()
+    world = shard_mesh.size()
+    if world < 2:
+        return None
+    esize = torch.empty((), dtype=param_dtype).element_size()
+    comm = PeerMemoryAllGather(group, reserve_bytes=max_bucket_numel(model, world) * esize)
+    for m in model.modules():
+        if not isinstance(m, FSDPModule):
+            continue
+        pg = getattr(m._get_fsdp_state(), "_fsdp_param_group", None)
+        other = getattr(pg.mesh_info, "shard_process_group", None) if pg is not None else None
+        if other is None or other.group_name != group.group_name:
+            continue
+        m.set_custom_all_gather(comm)
+    return comm
 
 
 def install_peer_reduce_scatter(model: nn.Module, dp_mesh, wire_dtype: torch.dtype) -> PeerMemoryReduceScatter | None:
