@@ -382,6 +382,50 @@ def bench_sparse(iters):
          frac_of_copy_bw=6 * n / bwd / 1e6 / bw_peak, peak=tag, note="includes the autograd wrapper and the sink reduction")
 
 
+def bench_sparse_mla(iters):
+    """Sparse MLA (DeepSeek sparse attention core): the tcgen05 kernel on gathered key tiles against the dense-masked
+    form (one GEMM over all keys + masked softmax + one GEMM) at growing key streams, forward only and forward +
+    backward.  16 heads, 576-dim latent keys, 512-dim values, top-2048 keys per query."""
+    from titan_b200.ops.dsa import _sparse_chunk
+    from titan_b200.ops.sparse_mla import sparse_mla, sparse_mla_forward
+
+    tf_peak, _, tag = peaks()
+    H, dq, dv, K = 16, 576, 512, 2048
+    for S, T in ((4096, 8192), (4096, 32768), (4096, 131072)):
+        g = torch.Generator(device="cuda").manual_seed(0)
+        q = (torch.randn(S, H, dq, device="cuda", generator=g) * 0.3).to(torch.bfloat16)
+        kv = (torch.randn(T, dq, device="cuda", generator=g) * 0.3).to(torch.bfloat16)
+        idx = torch.randint(0, T, (S, K), device="cuda", generator=g, dtype=torch.int32)
+        scale = dq ** -0.5
+        fwd = timeit(lambda: sparse_mla_forward(q, kv, idx, scale, dv), iters)
+        q1, kv1 = q.clone().requires_grad_(), kv.clone().requires_grad_()
+        go = torch.randn(S, H, dv, device="cuda", dtype=torch.bfloat16)
+
+        def fb():
+            q1.grad = kv1.grad = None
+            out, _, _ = sparse_mla(q1, kv1, idx, scale, dv, None, 256)
+            out.backward(go)
+
+        fwdbwd = timeit(fb, max(3, iters // 4))
+        useful = 2.0 * S * H * K * (dq + dv)   # QK^T over the selected keys + PV
+        rec = dict(kernel="sparse_mla_fwd", S=S, T=T, H=H, topk=K, ms=fwd, fwd_bwd_ms=fwdbwd,
+                   useful_tflops=useful / fwd / 1e9, frac_of_peak=useful / fwd / 1e9 / tf_peak, peak=tag,
+                   gathered_gbs=2.0 * S * K * dq * 2 / fwd / 1e6,
+                   note="two passes over the keys: the selected rows are gathered twice per query")
+        if T <= 32768:   # the dense-masked form needs [H, chunk, T] logits: only short streams
+            qh = q.transpose(0, 1).contiguous()
+            v = kv[:, :dv].contiguous()
+
+            def dense():
+                for s0 in range(0, S, 256):
+                    _sparse_chunk(qh[:, s0:s0 + 256], kv, v, idx[s0:s0 + 256], scale, True)
+
+            rec["dense_masked_ms"] = timeit(dense, max(3, iters // 4))
+            rec["speedup_vs_dense_masked"] = rec["dense_masked_ms"] / fwd
+        emit(**rec)
+        del q, kv, idx
+
+
 def profile_case(name: str, launches: int = 3) -> None:
     """One small workload (inputs larger than L2, well under 1 GB on the device), launched a few times: the
     target of a profiler capture.  Prints nothing but the case name; timings come from the bench modes."""
@@ -398,6 +442,13 @@ def profile_case(name: str, launches: int = 3) -> None:
         a, b = torch.randn(8192, 14336, device=dev, dtype=bf), torch.randn(8192, 4096, device=dev, dtype=bf)
         out = torch.empty(14336, 4096, device=dev, dtype=bf)
         fn = lambda: gemm(a, b, a_mn=True, b_mn=True, out=out)  # noqa: E731
+    elif name == "sparse_mla":
+        from titan_b200.ops.sparse_mla import sparse_mla_forward
+
+        q = (torch.randn(1024, 16, 576, device=dev) * 0.3).to(bf)
+        kv = (torch.randn(131072, 576, device=dev) * 0.3).to(bf)      # 151 MB of latent keys: larger than L2
+        idx = torch.randint(0, 131072, (1024, 2048), device=dev, dtype=torch.int32)
+        fn = lambda: sparse_mla_forward(q, kv, idx, 576 ** -0.5, 512)  # noqa: E731
     elif name == "rmsnorm_bwd":
         from titan_b200.ops.norm import rms_norm
 
@@ -489,6 +540,8 @@ def main():
         bench_gemm(args.iters)
     if "gemm_sustained" in which:
         bench_gemm_sustained()
+    if "sparse_mla" in which:
+        bench_sparse_mla(args.iters)
     if "elementwise" in which:
         bench_elementwise(args.iters)
     if "attention" in which:

@@ -349,3 +349,49 @@ def test_fused_chunk_path_matches_dense_oracle_on_gpu(with_idx):
     for a, b, name in zip(leaves, ref_leaves, ("dq", "dkv", "dkvc", "dsink")):
         torch.testing.assert_close(a.grad.float(), b.grad.float(), rtol=8e-2, atol=6e-2,
                                    msg=lambda m, n=name: f"{n}: {m}")
+
+
+@pytest.mark.gpu
+def test_gathered_tile_kernel_path_matches_dense_oracle_on_gpu():
+    """Head dim 128 with a long compressed stream goes to the tensor-core gathered-tile kernel: window keys and selected
+    compressed keys are listed per query in one key buffer.  Outputs, teacher distribution and gradients against the
+    fp32 dense oracle."""
+    from titan_b200.ops import smla
+
+    torch.manual_seed(11)
+    B, S, H, hd, ratio, k, window = 2, 384, 16, 128, 4, 24, 32
+    Tc = S // ratio
+    dev = "cuda"
+    q = torch.randn(B, S, H, hd, device=dev) * 0.5
+    kv = torch.randn(B, S, hd, device=dev) * 0.5
+    kvc = torch.randn(B, Tc, hd, device=dev) * 0.5
+    sink = torch.randn(H, device=dev)
+    idx = torch.full((B, S, k), -1, dtype=torch.long, device=dev)
+    for b in range(B):
+        for s in range(S):
+            vis = (s + 1) // ratio
+            pick = torch.randperm(vis, device=dev)[:k]
+            idx[b, s, : pick.numel()] = pick + S
+    scale = hd ** -0.5
+    ref_leaves = [t.clone().requires_grad_(True) for t in (q, kv, kvc, sink)]
+    ref, probs = sparse_attention_dense(ref_leaves[0], ref_leaves[1], ref_leaves[3], ref_leaves[2], idx, window, ratio,
+                                        scale)
+    leaves = [t.to(torch.bfloat16).requires_grad_(True) for t in (q, kv, kvc)] + [sink.clone().requires_grad_(True)]
+    saved = smla.KERNEL_RATIO
+    smla.KERNEL_RATIO = 0
+    try:
+        assert smla._kernel_takes(leaves[0], leaves[2], idx, window, ratio)
+        out, dist = smla.smla_attention(leaves[0], leaves[1], leaves[3], leaves[2], idx, window, ratio, scale,
+                                        want_dist=True)
+    finally:
+        smla.KERNEL_RATIO = saved
+    torch.testing.assert_close(out.float(), ref, rtol=5e-2, atol=3e-2)
+    cmp = probs[..., S:].detach().sum(dim=1) / H
+    want = torch.gather(cmp, -1, (idx - S).clamp(min=0)).masked_fill(idx < 0, 0.0)
+    torch.testing.assert_close(dist, want, rtol=5e-2, atol=2e-2)
+    g = torch.randn_like(ref)
+    ref.backward(g)
+    out.backward(g.to(out.dtype))
+    for a, b_, name in zip(leaves, ref_leaves, ("dq", "dkv", "dkvc", "dsink")):
+        torch.testing.assert_close(a.grad.float(), b_.grad.float(), rtol=8e-2, atol=6e-2,
+                                   msg=lambda m, n=name: f"{n}: {m}")

@@ -2,7 +2,8 @@
 
 `DSASparseAttention.forward` is replaced by: lightning-indexer top-k (tcgen05 scoring kernel with a fused
 relu·weight·head-sum epilogue + radix-select kernel, no gradient) → sparse attention over the selected rows
-of the shared KV latent → KL indexer loss from the head-summed attention mass and the index scores
+of the shared KV latent (long key streams: the gathered-tile tcgen05 kernel `csrc/attention/sparse_mla_fwd.cu`; short
+ones: one masked GEMM) → KL indexer loss from the head-summed attention mass and the index scores
 re-evaluated at the selected keys only.  Cost drops from O(S²·H) to O(S·k·H) and no [S, S] tensor exists.
 
 Parity: torchtitan_npu/converters/kernels/dsa.py:195-304 (v3.2 only).
@@ -22,8 +23,14 @@ class FusedDSAttention(DSASparseAttention):
         if q_indexer is None or attn_mask is not None:
             return super().forward(q, k, v, attn_mask, scale, q_indexer, k_indexer, weights, index_topk)
         scale = scale if scale is not None else q.shape[-1] ** -0.5
+        prefix = getattr(self, "_values_are_key_prefix", None)
+        if prefix is None and k.shape[1] == 1 and q.is_cuda:
+            from titan_b200.ops.dsa import _values_are_key_prefix
+
+            # MLA absorb: the values are the latent part of the keys; decided once per module (a layout property)
+            prefix = self._values_are_key_prefix = _values_are_key_prefix(k, v)
         return dsa_attention(q, k, v, scale=scale, q_indexer=q_indexer, k_indexer=k_indexer, weights=weights,
-                             index_topk=index_topk or k.shape[2])
+                             index_topk=index_topk or k.shape[2], values_are_key_prefix=prefix)
 
 
 def _swap(old):

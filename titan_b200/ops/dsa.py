@@ -234,9 +234,50 @@ def _sparse_chunk(q, kv, v, idx, scale, want_lse=True):
     return out, p.detach().sum(0), lse
 
 
-def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256, want_lse: bool = True):
-    """q [B,H,S,Dq], k [B,1,T,Dq], v [B,1,T,Dv], idx [B,S,topk] → (out [B,H,S,Dv], teacher [B,S,topk], lse [B,H,S])."""
+KERNEL_RATIO = 4  # key streams longer than this many times top-k go to the gathered-tile tensor-core kernel
+
+
+def _values_are_key_prefix(k: torch.Tensor, v: torch.Tensor) -> bool:
+    """MLA absorb layout: the values are the latent part of the keys (``v == k[..., :Dv]``).  Checked on a few rows
+    (one small device-to-host read; callers cache the answer per module)."""
+    if v.shape[-1] > k.shape[-1] or v.shape[:-1] != k.shape[:-1]:
+        return False
+    dv, t = v.shape[-1], k.shape[2]
+    rows = sorted({0, t // 2, t - 1})
+    return bool(torch.equal(k[0, 0, rows, :dv], v[0, 0, rows]))
+
+
+def _kernel_sparse_attention(q, k, idx, scale, dv):
+    """The tcgen05 sparse kernel per batch row → (out [B,H,S,Dv], teacher [B,S,topk], lse [B,H,S])."""
+    from titan_b200.ops.sparse_mla import sparse_mla
+
+    B, topk = q.shape[0], idx.shape[-1]
+    pad = (-topk) % 128
+    outs, teach, lses = [], [], []
+    for b in range(B):
+        ib = F.pad(idx[b], (0, pad), value=-1) if pad else idx[b]
+        o, t, l = sparse_mla(q[b].transpose(0, 1).contiguous(), k[b, 0], ib, scale, dv)
+        outs.append(o.transpose(0, 1)); teach.append(t[:, :topk]); lses.append(l.t())
+    return torch.stack(outs), torch.stack(teach), torch.stack(lses)
+
+
+def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256, want_lse: bool = True,
+                         values_are_key_prefix: bool | None = None):
+    """q [B,H,S,Dq], k [B,1,T,Dq], v [B,1,T,Dv], idx [B,S,topk] → (out [B,H,S,Dv], teacher [B,S,topk], lse [B,H,S]).
+
+    Long key streams (more than `KERNEL_RATIO` x top-k keys) in the MLA absorb layout run on the gathered-tile
+    tensor-core kernel (`titan_b200.ops.sparse_mla`): work and memory O(S * top-k).  ``values_are_key_prefix`` says
+    that ``v`` is the latent part of ``k`` (None = check a few rows)."""
     B, H, S, _ = q.shape
+    T, dv = k.shape[2], v.shape[-1]
+    if T > KERNEL_RATIO * idx.shape[-1] and q.is_cuda:
+        from titan_b200.ops.sparse_mla import sparse_mla_supported
+
+        if sparse_mla_supported(q[0].transpose(0, 1), k[0, 0], F.pad(idx[0], (0, (-idx.shape[-1]) % 128)), dv):
+            if values_are_key_prefix is None:
+                values_are_key_prefix = _values_are_key_prefix(k, v)
+            if values_are_key_prefix:
+                return _kernel_sparse_attention(q, k, idx, scale, dv)
     outs, teach, lses = [], [], []
     for b in range(B):
         ob, tb, lb = [], [], []
@@ -252,13 +293,15 @@ def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256, want_lse:
     return torch.stack(outs), torch.stack(teach), torch.stack(lses)
 
 
-def dsa_attention(q, k, v, *, scale, q_indexer, k_indexer, weights, index_topk: int, loss_scale: float = 1.0):
+def dsa_attention(q, k, v, *, scale, q_indexer, k_indexer, weights, index_topk: int, loss_scale: float = 1.0,
+                  values_are_key_prefix: bool | None = None):
     """Fused-path equivalent of the eager sparse-attention oracle → (indexer loss, out [B,H,S,Dv])."""
     S, T = q.shape[2], k.shape[2]
     pos_offset = T - S  # with context parallelism the local queries are the tail of the gathered key range
     topk = min(index_topk, T)
     idx, vals = lightning_indexer_topk(q_indexer, weights, k_indexer, topk, pos_offset)
-    out, teacher, _ = sparse_mla_attention(q, k, v, idx, scale, want_lse=False)
+    out, teacher, _ = sparse_mla_attention(q, k, v, idx, scale, want_lse=False,
+                                           values_are_key_prefix=values_are_key_prefix)
     if _scoring_kernels_take(q_indexer) and T % 8 == 0:
         student = indexer_scores_from_selection(q_indexer, weights, k_indexer, idx, vals)
     else:

@@ -31,6 +31,43 @@ __all__ = ["smla_attention", "li_select"]
 from titan_b200.ops.dsa import gather_rows
 
 DENSE_RATIO = 64  # a compressed stream at most this many times longer than k is attended densely with a mask
+KERNEL_RATIO = 4  # compressed streams longer than this many times the selection go to the gathered-tile kernel
+
+
+def _kernel_takes(q, kv_compress, compress_idx, window: int, ratio: int) -> bool:
+    """The gathered-tile tensor-core kernel (`titan_b200.ops.sparse_mla`) serves window + selected compressed keys +
+    sink when the head dim is a multiple of 128 (keys are values here: dq = dv = hd) and the compressed stream is long
+    compared with what a query actually attends to."""
+    hd, H = q.shape[-1], q.shape[2]
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and H % 16 == 0 and hd % 128 == 0 and hd <= 512):
+        return False
+    if kv_compress is None or ratio <= 1:
+        return False
+    k = compress_idx.shape[-1] if compress_idx is not None else kv_compress.shape[1]
+    return compress_idx is not None and kv_compress.shape[1] > KERNEL_RATIO * max(k, 128)
+
+
+def _smla_kernel_row(q, kv, sink, kvc, cidx, koff: int, window: int, scale: float, n_heads_total: int,
+                     want_dist: bool):
+    """One batch row through the sparse kernel.  q [S,H,hd]; kv [Tk,hd] raw keys (local query s sits at key s + koff);
+    kvc [Tc,hd]; cidx [S,k] ids into kvc (-1 = empty).  The keys of a query are listed explicitly: its window of raw
+    keys followed by its selected compressed keys, as rows of ONE buffer [raw keys ; compressed keys]."""
+    from titan_b200.ops.sparse_mla import sparse_mla
+
+    S, H, hd = q.shape
+    Tk, k = kv.shape[0], cidx.shape[1]
+    pos = torch.arange(S, device=q.device).unsqueeze(1) + koff                        # key index of the query itself
+    win = pos - (window - 1) + torch.arange(window, device=q.device).unsqueeze(0)      # [S, window], oldest first
+    win = torch.where(win < 0, torch.full_like(win, -1), win)
+    comp = torch.where(cidx < 0, cidx, cidx + Tk)
+    idx = torch.cat([win, comp], dim=1)
+    pad = (-idx.shape[1]) % 128
+    if pad:
+        idx = F.pad(idx, (0, pad), value=-1)
+    keys = torch.cat([kv, kvc], dim=0)
+    out, teacher, _ = sparse_mla(q.contiguous(), keys, idx.to(torch.int32), scale, hd, sink)
+    dist = teacher[:, window: window + k] / n_heads_total if want_dist else None
+    return out, dist
 
 
 def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, ratio: int, scale: float,
@@ -152,6 +189,16 @@ def smla_attention(q, kv, sink, kv_compress, compress_idx, window: int, ratio: i
         local_idx = torch.where(compress_idx < 0, compress_idx, compress_idx - idx_offset)
     outs, dists = [], []
     need_grad = torch.is_grad_enabled() and (q.requires_grad or kv.requires_grad)
+    if _kernel_takes(q, kv_compress, compress_idx, window, ratio):
+        for b in range(B):
+            o, d = _smla_kernel_row(q[b], kv[b], sink, kv_compress[b], local_idx[b], koff, window, scale,
+                                    n_heads_total, want_dist)
+            outs.append(o)
+            if d is not None:
+                dists.append(d)
+        out = torch.stack(outs)
+        dist = torch.stack(dists).masked_fill(compress_idx < 0, 0.0) if dists else None
+        return out, dist
     for b in range(B):
         ob, db = [], []
         for s0 in range(0, S, chunk):
