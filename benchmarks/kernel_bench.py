@@ -449,6 +449,96 @@ def profile_case(name: str, launches: int = 3) -> None:
         kv = (torch.randn(131072, 576, device=dev) * 0.3).to(bf)      # 151 MB of latent keys: larger than L2
         idx = torch.randint(0, 131072, (1024, 2048), device=dev, dtype=torch.int32)
         fn = lambda: sparse_mla_forward(q, kv, idx, 576 ** -0.5, 512)  # noqa: E731
+    elif name == "sparse_mla_bwd":
+        from titan_b200.ops.sparse_mla import sparse_mla_backward
+
+        q = (torch.randn(1024, 16, 576, device=dev) * 0.3).to(bf)
+        kv = (torch.randn(131072, 576, device=dev) * 0.3).to(bf)
+        idx = torch.randint(0, 131072, (1024, 2048), device=dev, dtype=torch.int32)
+        go = (torch.randn(1024, 16, 512, device=dev) * 0.3).to(bf)
+        lse = torch.full((1024, 16), 8.0, device=dev)
+        delta = torch.zeros(1024, 16, device=dev)
+        fn = lambda: sparse_mla_backward(q, kv, idx, go, lse, delta, 576 ** -0.5, 512)  # noqa: E731
+    elif name == "rope":
+        from titan_b200.models.common import rope as rope_ref
+        from titan_b200.ops.rope import rope_apply
+
+        q = torch.randn(2, 8192, 32, 128, device=dev, dtype=bf)     # 134 MB
+        cache = rope_ref.precompute_freqs_cis(128, 8192, 500000.0).cuda()
+        fn = lambda: rope_apply(q, cache)  # noqa: E731
+    elif name == "swiglu":
+        from titan_b200.ops.swiglu import swiglu
+
+        a = torch.randn(8192, 14336, device=dev, dtype=bf, requires_grad=True)   # 235 MB each
+        b = torch.randn(8192, 14336, device=dev, dtype=bf, requires_grad=True)
+        g = torch.randn(8192, 14336, device=dev, dtype=bf)
+
+        def fn():
+            a.grad = b.grad = None
+            swiglu(a, b).backward(g)
+    elif name == "cross_entropy":
+        from titan_b200.ops.cross_entropy import cross_entropy_sum
+
+        logits = torch.randn(2048, 128256, device=dev, dtype=bf, requires_grad=True)   # 525 MB
+        labels = torch.randint(0, 128256, (2048,), device=dev)
+
+        def fn():
+            logits.grad = None
+            cross_entropy_sum(logits, labels).backward()
+    elif name == "adamw":
+        from titan_b200.optim.fused_adamw import adamw_multi_tensor
+
+        n = 64 * 1024 * 1024
+        p_, gr = torch.randn(n, device=dev, dtype=bf), torch.randn(n, device=dev, dtype=bf)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        fn = lambda: adamw_multi_tensor([p_], [gr], [m], [v], lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8,  # noqa: E731
+                                        weight_decay=0.1, step=3)
+    elif name == "moe_route_permute_combine":
+        from titan_b200.ops.moe import combine, make_plan, permute, router_topk
+
+        T_, D, E, k = 32768, 2048, 64, 6                           # x 134 MB; routed copies 805 MB
+        x = torch.randn(T_, D, device=dev, dtype=bf)
+        logits = torch.randn(T_, E, device=dev)
+
+        def fn():
+            gate, idx, _ = router_topk(logits, k, score_func="softmax")
+            plan = make_plan(idx, E)
+            buf = permute(x, plan)
+            combine(buf, plan, T_, gate.to(bf))
+    elif name == "grouped_gemm":
+        from titan_b200.ops.moe import grouped_linear
+
+        E, rows, D, Hd = 8, 4096, 2048, 1408
+        x = torch.randn(E * rows, D, device=dev, dtype=bf)
+        w = torch.randn(E, Hd, D, device=dev, dtype=bf) * 0.02
+        offs = (torch.arange(1, E + 1, device=dev, dtype=torch.int32) * rows)
+        fn = lambda: grouped_linear(x, w, offs)  # noqa: E731
+    elif name == "mhc":
+        from titan_b200.ops.mhc_cuda import mhc_post, mhc_pre
+
+        T_, D = 8192, 2048                                          # streams [T, 4, D] bf16 = 134 MB
+        x = torch.randn(T_, 4, D, device=dev, dtype=bf, requires_grad=True)
+        hfn = (torch.randn(24, 4 * D, device=dev) * 0.05).requires_grad_()
+        hs = (torch.randn(3, device=dev) * 0.5 + 1.0).requires_grad_()
+        hb = (torch.randn(24, device=dev) * 0.3).requires_grad_()
+        g = torch.randn(T_, 4, D, device=dev, dtype=bf)
+
+        def fn():
+            x.grad = hfn.grad = hs.grad = hb.grad = None
+            y, post, comb = mhc_pre(x, hfn, hs, hb, 20, 1e-6, 1e-6)
+            mhc_post(y, x, post, comb).backward(g)
+    elif name == "compressor_pool":
+        from titan_b200.ops.compressor_pool import compressor_pool
+
+        B_, S_, d = 2, 16384, 512                                   # ratio 4 with overlap: width 1024, 134 MB per input
+        kv = torch.randn(B_, S_, 2 * d, device=dev, requires_grad=True)
+        score = torch.randn(B_, S_, 2 * d, device=dev, requires_grad=True)
+        ape = torch.randn(4, 2 * d, device=dev, requires_grad=True)
+        g = torch.randn(B_, S_ // 4, d, device=dev)
+
+        def fn():
+            kv.grad = score.grad = ape.grad = None
+            compressor_pool(kv, score, ape, 4, d, True).backward(g)
     elif name == "rmsnorm_bwd":
         from titan_b200.ops.norm import rms_norm
 
@@ -530,7 +620,7 @@ def main():
     ap.add_argument("--only", default="gemm,elementwise")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--profile-case", default=None,
-                    help="run one small case a few times and exit (gemm | gemm_wgrad | rmsnorm_bwd | indexer_topk | flash_fwd | mxfp8_gemm | masked_softmax | indexer_relu_bwd)")
+                    help="run one small case a few times and exit (see `profile_case` for the names)")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)

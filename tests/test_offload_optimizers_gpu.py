@@ -68,7 +68,8 @@ def test_virtual_adamw_with_a_budget_smaller_than_the_model(cuda_device):
     model = copy.deepcopy(ref_model)
     kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
     ref = FusedAdamW(list(ref_model.parameters()), **kw)
-    # 6 MB: both moments of the first matrix (2 x 2 MiB) fit, the second matrix (2 x 4 MiB) does not
+    # 6 MB: both moments of the first matrix (2 x 2 MiB) and of the norm fit, the second matrix (params[3], 2 x 4 MiB)
+    # does not
     alloc = VirtualAllocator(6e-3)
     opt = VirtualAdamW(list(model.parameters()), allocator=alloc, **kw)
     _steps(ref_model, ref)
@@ -76,8 +77,8 @@ def test_virtual_adamw_with_a_budget_smaller_than_the_model(cuda_device):
     for a, b in zip(ref_model.parameters(), model.parameters()):
         assert torch.equal(a, b)
     params = list(model.parameters())
-    assert id(params[0]) in opt.virtual_params and id(params[2]) not in opt.virtual_params
+    assert id(params[0]) in opt.virtual_params and id(params[3]) not in opt.virtual_params
     m0 = opt.state[params[0]]["exp_avg"]
     assert not m0.is_cuda and m0.is_pinned()            # read and written in place over the host link
-    assert opt.state[params[2]]["exp_avg"].is_cuda      # beyond the budget: ordinary device state
+    assert opt.state[params[3]]["exp_avg"].is_cuda      # beyond the budget: ordinary device state
     assert torch.equal(m0.float(), ref.state[next(iter(ref_model.parameters()))]["exp_avg"].cpu().float())

@@ -51,17 +51,33 @@ def test_sink_and_fully_empty_rows(cuda_device):
     assert torch.isinf(lse2[3]).all() and float(out2[3].abs().max()) == 0.0
 
 
-def test_backward_matches_autograd_of_the_oracle(cuda_device):
-    from titan_b200.ops.sparse_mla import sparse_mla, sparse_mla_forward_ref
+@pytest.mark.parametrize("kernel_backward", [True, False])
+@pytest.mark.parametrize("S,H,T,K,dq,dv,sink", [(24, 16, 512, 128, 576, 512, False), (20, 32, 900, 256, 576, 512, True),
+                                                (9, 64, 640, 384, 192, 128, False), (16, 16, 300, 128, 512, 512, True)])
+def test_backward_matches_autograd_of_the_oracle(cuda_device, kernel_backward, S, H, T, K, dq, dv, sink):
+    """Both backwards (tensor-core kernel with vector reductions into the latent's rows; chunked PyTorch) against
+    autograd through the fp32 oracle: queries, latent (keys + values share rows), sink logits."""
+    from titan_b200.ops import _lib, sparse_mla as mod
 
-    q, kv, idx = _case(24, 16, 512, 128, empty=0.2)
-    scale = 576 ** -0.5
+    q, kv, idx = _case(S, H, T, K, dq, dv, empty=0.2)
+    scale = dq ** -0.5
+    sk = torch.randn(H, device="cuda") if sink else None
     q1, kv1 = q.clone().requires_grad_(), kv.clone().requires_grad_()
-    out, teacher, lse = sparse_mla(q1, kv1, idx, scale, 512, chunk=16)
-    g = torch.randn_like(out)
-    out.backward(g)
+    sk1 = sk.clone().requires_grad_() if sink else None
+    saved = mod.KERNEL_BACKWARD
+    mod.KERNEL_BACKWARD = kernel_backward
+    try:
+        out, teacher, lse = mod.sparse_mla(q1, kv1, idx, scale, dv, sk1, chunk=16)
+        g = torch.randn_like(out)
+        out.backward(g)
+        _lib.shared_status().raise_if_set("sparse_mla_bwd")
+    finally:
+        mod.KERNEL_BACKWARD = saved
     qr, kr = q.float().requires_grad_(), kv.float().requires_grad_()
-    ro, _, _ = sparse_mla_forward_ref(qr, kr, idx, scale, 512)
+    skr = sk.clone().requires_grad_() if sink else None
+    ro, _, _ = mod.sparse_mla_forward_ref(qr, kr, idx, scale, dv, skr)
     ro.backward(g.float())
     torch.testing.assert_close(q1.grad.float(), qr.grad, rtol=5e-2, atol=2e-2)
     torch.testing.assert_close(kv1.grad.float(), kr.grad, rtol=5e-2, atol=3e-2)
+    if sink:
+        torch.testing.assert_close(sk1.grad, skr.grad, rtol=5e-2, atol=2e-2)

@@ -123,6 +123,10 @@ class CheckpointManager:
         if 0 < self.keep_latest_k < 2:
             raise ValueError("keep_latest_k must be 0 (keep all) or >= 2")
         self.async_mode = AsyncMode(config.async_mode.lower())
+        if self.async_mode == AsyncMode.ASYNC_WITH_PINNED_MEM and not torch.cuda.is_available():
+            # pinned staging needs a device; a host-only run still overlaps the write with training
+            logger.warning("checkpoint.async_mode async_with_pinned_mem needs a GPU; using 'async'")
+            self.async_mode = AsyncMode.ASYNC
         self.export_dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}[
             config.export_dtype
         ]

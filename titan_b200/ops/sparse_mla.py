@@ -30,6 +30,7 @@ def _declare():
     if not _DECLARED:
         P, I, Fl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         _lib.declare("tb_sparse_mla_fwd", [P, P, P, P, P, P, P, I, I, I, I, I, I, Fl, P, P])
+        _lib.declare("tb_sparse_mla_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, Fl, P, P])
         _DECLARED = True
 
 
@@ -91,30 +92,59 @@ class SparseMLAFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g_out, _gt, _gl):
         q, kv, idx, lse, out, sink = ctx.saved_tensors
-        S, H, dq = q.shape
-        dv, scale = ctx.dv, ctx.scale
-        dq_ = torch.empty_like(q)
-        dkv = torch.zeros(kv.shape[0], dq, dtype=torch.float32, device=kv.device)
-        dsink = torch.zeros(H, dtype=torch.float32, device=q.device) if ctx.has_sink else None
+        H = q.shape[1]
         delta = (g_out.float() * out.float()).sum(-1)                    # [S, H]
-        for s0 in range(0, S, ctx.chunk):
-            s1 = min(s0 + ctx.chunk, S)
-            ix = idx[s0:s1]
-            safe = ix.clamp_min(0).long()
-            ksel = kv[safe]                                              # [sc, K, Dq] storage dtype
-            sc = torch.einsum("shd,skd->shk", q[s0:s1], ksel).float() * scale
-            p = torch.exp(sc - lse[s0:s1].unsqueeze(-1)).masked_fill((ix < 0).unsqueeze(1), 0.0)
-            go = g_out[s0:s1]
-            dp = torch.einsum("shd,skd->shk", go, ksel[..., :dv]).float()
-            ds = (p * (dp - delta[s0:s1].unsqueeze(-1)) * scale).to(q.dtype)
-            dq_[s0:s1] = torch.einsum("shk,skd->shd", ds, ksel)
-            dk_rows = torch.einsum("shk,shd->skd", ds, q[s0:s1]).float()  # score path, [sc, K, Dq]
-            dk_rows[..., :dv] += torch.einsum("shk,shd->skd", p.to(q.dtype), go).float()   # value path
-            dkv.index_add_(0, safe.reshape(-1), dk_rows.reshape(-1, dq))
-            if dsink is not None:
-                ps = torch.exp(sink.float().view(1, H) - lse[s0:s1])      # probability mass on the sink
-                dsink -= (ps * delta[s0:s1]).sum(0)
-        return dq_, dkv.to(kv.dtype), None, None, None, (dsink.to(sink.dtype) if dsink is not None else None), None
+        if KERNEL_BACKWARD:
+            dq_, dkv = sparse_mla_backward(q, kv, idx, g_out, lse, delta, ctx.scale, ctx.dv)
+        else:
+            dq_, dkv = sparse_mla_backward_ref(q, kv, idx, g_out, lse, delta, ctx.scale, ctx.dv, ctx.chunk)
+        dsink = None
+        if ctx.has_sink:   # probability mass on the sink times -delta, summed over the queries
+            dsink = -(torch.exp(sink.float().view(1, H) - lse) * delta).sum(0).to(sink.dtype)
+        return dq_, dkv.to(kv.dtype), None, None, None, dsink, None
+
+
+KERNEL_BACKWARD = True  # False: the chunked PyTorch backward below (the oracle of the kernel's test)
+
+
+def sparse_mla_backward(q, kv, idx, g_out, lse, delta, scale: float, dv: int):
+    """Gradients of queries and latent on the tensor cores (`csrc/attention/sparse_mla_bwd.cu`):
+    → (dq [S, H, Dq] bf16, dkv [T, Dq] fp32)."""
+    _declare()
+    S, H, dq = q.shape
+    T, K = kv.shape[0], idx.shape[1]
+    q, kv, g_out = q.contiguous(), kv.contiguous(), g_out.contiguous()
+    idx = idx.to(torch.int32).contiguous()
+    dq_ = torch.empty_like(q)
+    dkv = torch.zeros(T, dq, dtype=torch.float32, device=kv.device)
+    rc = _lib.lib().tb_sparse_mla_bwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), g_out.data_ptr(),
+                                      lse.contiguous().data_ptr(), delta.contiguous().data_ptr(), dq_.data_ptr(),
+                                      dkv.data_ptr(), S, H, T, K, dq, dv, float(scale),
+                                      _lib.shared_status().ptr, _lib.stream_ptr())
+    _lib.check(rc, "sparse_mla_bwd")
+    return dq_, dkv
+
+
+def sparse_mla_backward_ref(q, kv, idx, g_out, lse, delta, scale: float, dv: int, chunk: int = 128):
+    """The same gradients in PyTorch, ``chunk`` queries at a time (memory O(chunk * K * Dq))."""
+    S, H, dq = q.shape
+    dq_ = torch.empty_like(q)
+    dkv = torch.zeros(kv.shape[0], dq, dtype=torch.float32, device=kv.device)
+    for s0 in range(0, S, chunk):
+        s1 = min(s0 + chunk, S)
+        ix = idx[s0:s1]
+        safe = ix.clamp_min(0).long()
+        ksel = kv[safe]                                              # [sc, K, Dq] storage dtype
+        sc = torch.einsum("shd,skd->shk", q[s0:s1], ksel).float() * scale
+        p = torch.exp(sc - lse[s0:s1].unsqueeze(-1)).masked_fill((ix < 0).unsqueeze(1), 0.0)
+        go = g_out[s0:s1]
+        dp = torch.einsum("shd,skd->shk", go, ksel[..., :dv]).float()
+        ds = (p * (dp - delta[s0:s1].unsqueeze(-1)) * scale).to(q.dtype)
+        dq_[s0:s1] = torch.einsum("shk,skd->shd", ds, ksel)
+        dk_rows = torch.einsum("shk,shd->skd", ds, q[s0:s1]).float()  # score path, [sc, K, Dq]
+        dk_rows[..., :dv] += torch.einsum("shk,shd->skd", p.to(q.dtype), go).float()   # value path
+        dkv.index_add_(0, safe.reshape(-1), dk_rows.reshape(-1, dq))
+    return dq_, dkv
 
 
 def sparse_mla(q, kv, idx, scale: float, dv: int, sink: torch.Tensor | None = None, chunk: int = 128):

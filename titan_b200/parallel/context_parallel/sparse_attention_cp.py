@@ -4,7 +4,7 @@ Queries stay sequence-local.  The single-head KV latent ``k, v [B, 1, S/cp, D]``
 ``k_indexer [B, S/cp, 1, 128]`` are all-gathered over the ``cp`` mesh (small: one head), then cut to the
 causal prefix ``[: (rank + 1) · S_local]`` so rank r attends to everything up to its own block; the
 attention core treats the local queries as the tail of that key range.  Backward of the gather is a
-reduce-scatter (functional collective with autograd).  Work grows with the rank; no balancing is applied
+reduce-scatter.  Work grows with the rank; no balancing is applied
 because top-k selection bounds the attention cost and the indexer is cheap.
 
 Parity: torchtitan_npu/distributed/context_parallel/sparse_attention_cp.py:30-90.
@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-from torch.distributed._functional_collectives import all_gather_tensor_autograd
+import torch.distributed as dist
 from torch.distributed.device_mesh import DeviceMesh
 
 from titan_b200.parallel.context_parallel.registry import register_cp_strategy
@@ -28,9 +28,26 @@ def _gather(x: torch.Tensor, dim: int, group, world: int) -> torch.Tensor:
         return x
     if is_fake_process_group(group):
         return torch.cat([x] * world, dim=dim)
-    out = all_gather_tensor_autograd(x.contiguous(), gather_dim=dim, group=group)
-    # wait on the functional tensor (not `.wait()` of the async wrapper) so autograd keeps the edge
-    return torch.ops._c10d_functional.wait_tensor(out)
+    return _AllGatherDim.apply(x, dim, group, world)
+
+
+class _AllGatherDim(torch.autograd.Function):
+    """All-gather along ``dim``; the backward is the matching reduce-scatter (sum) of the gathered gradient."""
+
+    @staticmethod
+    def forward(ctx, x, dim, group, world):
+        ctx.dim, ctx.group, ctx.world = dim, group, world
+        xt = x.movedim(dim, 0).contiguous()
+        out = xt.new_empty((world * xt.shape[0], *xt.shape[1:]))
+        dist.all_gather_into_tensor(out, xt, group=group)
+        return out.movedim(0, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        gt = g.movedim(ctx.dim, 0).contiguous()
+        out = gt.new_empty((gt.shape[0] // ctx.world, *gt.shape[1:]))
+        dist.reduce_scatter_tensor(out, gt, op=dist.ReduceOp.SUM, group=ctx.group)
+        return out.movedim(0, ctx.dim), None, None, None
 
 
 class SparseAttentionCP:

@@ -237,6 +237,8 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         ep=par.expert_parallel_degree, etp=par.expert_tensor_parallel_degree, world_size=world_size)
     spec = get_model_spec(cfg.model.name, cfg.model.flavor)
     mc = spec.model
+    for key, value in cfg.model.overrides.items():
+        setattr(mc, key, value)
     mc.update_from_config(trainer_config=cfg)
     store_dt = _DT[cfg.training.dtype]
     old = torch.get_default_dtype()
