@@ -263,7 +263,7 @@ def bench_attention(iters):
     k = torch.randn(B, S, HK, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
     v = torch.randn(B, S, HK, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
     fl = 4.0 * B * H * S * S * D / 2
-    ours = timeit(lambda: _FlashFn.apply(q, k, v, D ** -0.5), iters)
+    ours = timeit(lambda: _FlashFn.apply(q, k, v, D ** -0.5, None), iters)
     rec = dict(kernel="flash_fwd_tcgen05", shape=[B, H, HK, S, D], ms=ours, tflops=fl / ours / 1e9,
                frac_of_peak=fl / ours / 1e9 / tf_peak, peak=tag)
     for name, be in (("cudnn", SDPBackend.CUDNN_ATTENTION), ("flash2", SDPBackend.FLASH_ATTENTION)):
@@ -274,6 +274,46 @@ def bench_attention(iters):
         except RuntimeError as e:  # backend not available for this shape
             rec[f"{name}_error"] = str(e)[:80]
     emit(**rec)
+
+    # backward: the tcgen05 kernel (dK / dV in tensor memory, dQ by vector reductions) against the library backends
+    from titan_b200.ops.flash_attention import _flash_bwd_launch, _flash_fwd_launch
+
+    g = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+    out, lse = _flash_fwd_launch(q, k, v, D ** -0.5)
+    ours = timeit(lambda: _flash_bwd_launch(q, k, v, out, lse, g, D ** -0.5), iters)
+    rec = dict(kernel="flash_bwd_tcgen05", shape=[B, H, HK, S, D], ms=ours, tflops=2.5 * fl / ours / 1e9,
+               frac_of_peak=2.5 * fl / ours / 1e9 / tf_peak, peak=tag)
+    for name, be in (("cudnn", SDPBackend.CUDNN_ATTENTION), ("flash2", SDPBackend.FLASH_ATTENTION)):
+        try:
+            ql, kl, vl = (t.detach().clone().requires_grad_() for t in (q, k, v))
+            with sdpa_kernel(be):
+                o = F.scaled_dot_product_attention(ql, kl, vl, is_causal=True, enable_gqa=True)
+                ms = timeit(lambda: torch.autograd.grad(o, (ql, kl, vl), g, retain_graph=True), iters)
+            rec[f"{name}_ms"], rec[f"{name}_tflops"] = ms, 2.5 * fl / ms / 1e9
+        except RuntimeError as e:
+            rec[f"{name}_error"] = str(e)[:80]
+    emit(**rec)
+
+    # packed documents (8 documents of 1024 tokens in one 8192-token row): one launch each way against the
+    # per-document loop over the library attention
+    from titan_b200.models.common.varlen_attention import VarlenMetadata
+    from titan_b200.ops.flash_attention import flash_attention
+
+    meta = VarlenMetadata([list(range(0, S + 1, 1024))], 1024)
+    ss = meta.seq_start("cuda")
+
+    def ours_fb():
+        ql, kl, vl = (t.detach().requires_grad_() for t in (q, k, v))
+        flash_attention(ql, kl, vl, seq_start=ss).backward(g)
+
+    def loop_fb():
+        ql, kl, vl = (t.detach().requires_grad_() for t in (q, k, v))
+        docs = [F.scaled_dot_product_attention(ql[:, :, a:a + 1024], kl[:, :, a:a + 1024], vl[:, :, a:a + 1024],
+                                               is_causal=True, enable_gqa=True) for a in range(0, S, 1024)]
+        torch.cat(docs, dim=2).backward(g)
+
+    emit(kernel="flash_packed_docs_fwd_bwd", shape=[B, H, HK, S, D], docs=8, ms=timeit(ours_fb, iters),
+         library_loop_ms=timeit(loop_fb, iters))
 
 
 def bench_lowp(iters):
@@ -562,7 +602,7 @@ def profile_case(name: str, launches: int = 3) -> None:
         q = torch.randn(1, 8192, 32, 128, device=dev, dtype=bf).transpose(1, 2)
         k = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).transpose(1, 2)
         v = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).transpose(1, 2)
-        fn = lambda: _FlashFn.apply(q, k, v, 128 ** -0.5)  # noqa: E731
+        fn = lambda: _FlashFn.apply(q, k, v, 128 ** -0.5, None)  # noqa: E731
     elif name == "mxfp8_gemm":
         from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, pack_scale_atoms
 

@@ -111,3 +111,45 @@ def test_aligned_grouped_mm_autograd_matches_the_loop_over_experts(cuda_device):
     for a, b in zip(got, (y2.detach().float()[:n], x.grad.float()[:n], w.grad.float())):
         a = a[:n] if a.shape[0] == T else a
         assert torch.isfinite(a).all() and (a - b).pow(2).sum() <= 1e-4 * b.pow(2).sum()
+
+
+@pytest.mark.gpu
+def test_expert_weight_quantisation_is_kept_between_optimizer_steps(cuda_device):
+    """With a `weight_key` the grouped MX product quantises the weight once (both views from one dual-axis pass) and
+    reuses it in forward, recomputed forward and input gradient; an invalidation or an in-place update refreshes it."""
+    from titan_b200.lowp import mx_linear
+    from titan_b200.ops import _lib
+
+    torch.manual_seed(3)
+    E, N, K, rows = 2, 256, 256, 256
+    offs = torch.tensor([rows, 2 * rows], device="cuda", dtype=torch.int32)
+    x = torch.randn(2 * rows, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.1).requires_grad_()
+    g = torch.randn(2 * rows, N, device="cuda", dtype=torch.bfloat16)
+
+    def run(key):
+        x.grad = w.grad = None
+        before = _lib.launch_count()
+        y = mx_linear.mx_grouped_mm(x, w, offs, aligned=True, weight_key=key)
+        y.backward(g)
+        return y.detach().clone(), x.grad.clone(), w.grad.clone(), _lib.launch_count() - before
+
+    mx_linear.invalidate_weight_cache()
+    plain = run(None)
+    first = run("w")      # fills the cache: one weight pass instead of two
+    second = run("w")     # reuses it: no weight pass at all
+    for a, b in zip(plain[:3], first[:3]):
+        assert torch.equal(a, b)
+    for a, b in zip(first[:3], second[:3]):
+        assert torch.equal(a, b)
+    assert first[3] == plain[3] - 1 and second[3] == plain[3] - 2
+    with torch.no_grad():
+        w.mul_(2.0)       # in-place update: the version counter moves, the views are rebuilt
+    third = run("w")
+    assert third[3] == first[3]
+    torch.testing.assert_close(third[0].float(), 2 * first[0].float(), rtol=2e-2, atol=2e-2)
+    # a raw-pointer update (what the fused optimizer kernels do) is invisible to the counter: the trainer invalidates
+    w.data = w.data * 0.5
+    mx_linear.invalidate_weight_cache()
+    fourth = run("w")
+    torch.testing.assert_close(fourth[0].float(), first[0].float(), rtol=2e-2, atol=2e-2)

@@ -44,14 +44,29 @@ class FusedGroupedExperts(Module):
     def _local(p):
         return p.to_local() if hasattr(p, "to_local") else p
 
+    def _weights_resident(self) -> bool:
+        """False when FSDP shards this module's weights over more than one rank: the gathered copy is transient there,
+        and a cache of its quantised views would pin the unsharded bytes."""
+        if not hasattr(self, "_get_fsdp_state"):
+            return True
+        try:
+            group = self._get_fsdp_state()._fsdp_param_group
+            return group is None or group.mesh_info.shard_mesh_size <= 1
+        except Exception:  # noqa: BLE001
+            return False
+
     def forward_padded(self, xp: torch.Tensor, offs: torch.Tensor, scores: torch.Tensor | None = None):
         """xp: padded expert-major rows [cap, D]; offs: cumulative padded ends of the LOCAL experts."""
         w13, w2 = self._local(self.w13), self._local(self.w2)
         mx = getattr(self, "mx_round_mode", None)
         if mx is not None:  # MXFP8 experts: both GEMMs block-quantised along their contraction dims
-            h13 = self.mx_grouped_mm(xp, w13.to(xp.dtype), offs, mx, aligned=True)  # groups are 128-row multiples
+            # a weight that stays whole on this rank keeps its quantised views between optimizer steps
+            k13, k2 = ((id(self), "w13"), (id(self), "w2")) if self._weights_resident() else (None, None)
+            kw = {"weight_key": k13} if k13 is not None else {}
+            h13 = self.mx_grouped_mm(xp, w13.to(xp.dtype), offs, mx, aligned=True, **kw)  # groups: 128-row multiples
             h = swiglu_fused(h13, scores, self.swiglu_limit)
-            return self.mx_grouped_mm(h, w2.to(xp.dtype), offs, mx, aligned=True)
+            kw = {"weight_key": k2} if k2 is not None else {}
+            return self.mx_grouped_mm(h, w2.to(xp.dtype), offs, mx, aligned=True, **kw)
         h13 = grouped_linear(xp, w13.to(xp.dtype), offs)
         h = swiglu_fused(h13, scores, self.swiglu_limit)
         return grouped_linear(h, w2.to(xp.dtype), offs)

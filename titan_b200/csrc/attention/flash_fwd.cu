@@ -38,6 +38,7 @@ struct FaParams {
   float scale_log2;  // softmax scale * log2(e)
   __nv_bfloat16* O;
   float* LSE;
+  const int* seq_start;  // [B * S] first position of each token's document (packed sequences), or null
   int* status;
 };
 
@@ -57,6 +58,8 @@ __device__ __forceinline__ void fail(Bars* b, int* status, int code) {
   }
 }
 
+// VARLEN: packed documents (`seq_start` given).  The dense instance carries none of the extra masking code.
+template <bool VARLEN>
 __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_k,
                                                                 const __grid_constant__ CUtensorMap tm_v,
@@ -81,8 +84,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
   const int qb = nq - 1 - (int)blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
-  const int nblk = qb + 1;  // causal: key blocks 0..qb
   const int q_row0 = b * p.S + qb * BQ;
+  // causal: key blocks j0 .. qb.  With packed documents the block's first query belongs to the earliest document of
+  // the block (documents start at non-decreasing positions), so no row needs a key block before that document.
+  const int j0 = VARLEN ? p.seq_start[q_row0] / BK : 0;
+  const int nblk = qb + 1 - j0;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -116,7 +122,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       for (int j = 0; j < nblk; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int k_row0 = b * p.S + j * BK;
+        const int k_row0 = b * p.S + (j0 + j) * BK;
         if (!mbar_wait(&bars->k_empty[st], ph ^ 1, abort_flag)) { fail(bars, p.status, TB_ERR_WAIT_EMPTY); break; }
         mbar_expect_tx(&bars->k_full[st], TILE);
         tma_load_2d(sK + st * TILE, &tm_k, &bars->k_full[st], hk * D, k_row0);
@@ -204,6 +210,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       group_sync();
       return acc;
     };
+    // keys before the start of this row's document are masked: key column c of block j is allowed from `lo` on
+    const int row_start = VARLEN ? p.seq_start[q_row0 + row] : 0;
     float m_run = -INFINITY, l_run = 0.f;
     float o[HC];
 #pragma unroll
@@ -218,6 +226,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       tc_fence_after();
       const uint32_t s_addr = lane_base + st * BK + part * HC;
       const bool diag = j == nblk - 1;
+      const int lo = VARLEN ? row_start - (j0 + j) * BK : 0;   // first allowed column of this block (<= 0: all)
+      const bool edge = diag || (VARLEN && lo > 0);
       uint32_t r[32];
       float mx = -INFINITY;
       if (ok) {
@@ -225,13 +235,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (!diag || part * HC + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
+          if (!edge || ((!diag || part * HC + i <= row) && (!VARLEN || part * HC + i >= lo)))
+            mx = fmaxf(mx, __uint_as_float(r[i]));
       }
       bool all_ok = true;
       const float row_max = exchange(ok ? mx : NAN, true, all_ok);
       if (!ok || !all_ok) { ok = false; break; }
       const float m_new = fmaxf(m_run, row_max * p.scale_log2);
-      const float alpha = ex2(m_run - m_new);
+      // a row whose document starts after this block has seen no key yet: keep its state untouched
+      const float alpha = (VARLEN && m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
       // P = 2^(s' - m), row sum, bf16 into the swizzled K-major A-operand layout: this thread's 32 keys are 4 of the
       // 8 sixteen-byte chunks of its row in one 64-key box
       float sum = 0.f;
@@ -241,9 +253,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       for (int i = 0; i < 16; ++i) {
         float p0 = ex2(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_new));
         float p1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_new));
-        if (diag) {
-          if (part * HC + 2 * i > row) p0 = 0.f;
-          if (part * HC + 2 * i + 1 > row) p1 = 0.f;
+        if (edge) {
+          if ((diag && part * HC + 2 * i > row) || (VARLEN && part * HC + 2 * i < lo)) p0 = 0.f;
+          if ((diag && part * HC + 2 * i + 1 > row) || (VARLEN && part * HC + 2 * i + 1 < lo)) p1 = 0.f;
         }
         sum += p0 + p1;
         pk[i] = pack_bf16x2(p0, p1);
@@ -326,9 +338,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
 }  // namespace
 
 // q: [B, S, H, 128] bf16, k / v: [B, S, Hkv, 128] bf16 (contiguous), out: [B, S, H, 128] bf16, lse: [B, H, S] fp32 or
-// nullptr.  S must be a multiple of 128.
-TB_API int tb_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H,
-                             int Hkv, int head_dim, float scale, int* status, cudaStream_t st) {
+// nullptr; seq_start: [B * S] int32 (position of the first token of each token's document, non-decreasing along a
+// sequence) for packed documents, or nullptr.  S must be a multiple of 128.
+TB_API int tb_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* seq_start,
+                             int B, int S, int H, int Hkv, int head_dim, float scale, int* status, cudaStream_t st) {
   if (B <= 0 || S <= 0) return 0;
   if (head_dim != D || S % BQ != 0 || Hkv < 1 || H % Hkv != 0 || (long long)B * S > 0x7fffffffLL) return TB_ERR_ARG;
   CUtensorMap tq, tk, tv;
@@ -339,11 +352,16 @@ TB_API int tb_flash_attn_fwd(const void* q, const void* k, const void* v, void* 
   FaParams p;
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.O = (__nv_bfloat16*)out; p.LSE = lse; p.status = status;
+  p.O = (__nv_bfloat16*)out; p.LSE = lse; p.seq_start = seq_start; p.status = status;
   const size_t smem = 7 * TILE + sizeof(Bars);
-  TB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(S / BQ, H, B);
-  flash_fwd_kernel<<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
+  if (seq_start != nullptr) {
+    TB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    flash_fwd_kernel<true><<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
+  } else {
+    TB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    flash_fwd_kernel<false><<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
+  }
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

@@ -270,12 +270,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
         {
           const int row = ctl->valid[r];
           const int hw = w >> 1;                                 // columns per warp set (multiple of 32)
-          if (row >= 0) {
-            float* dst = p.dkv + (long long)row * p.dq + c0 + half * hw;
-            for (int c = 0; c < hw; c += 32) {
-              uint32_t v[32];
-              tmem_ld_32x32(tmem_kv + lane_off + half * hw + c, v);
-              tmem_ld_wait();
+          // the tensor-memory load is a warp-wide instruction: every lane takes part, empty slots only skip the adds
+          float* dst = p.dkv + (long long)(row >= 0 ? row : 0) * p.dq + c0 + half * hw;
+          for (int c = 0; c < hw; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_kv + lane_off + half * hw + c, v);
+            tmem_ld_wait();
+            if (row >= 0) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
                 asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c + i),
@@ -319,8 +320,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
 template <int HG>
 int launch(const BwdParams& p, cudaStream_t st) {
   const int qchunks = p.dq / 64, vchunks = p.dv / 64;
-  // one spare chunk behind the tile keeps the padded last dQ^T block inside the allocation for every dq
-  const int smem = qchunks * CHUNK_BYTES + (qchunks + vchunks + 4) * HG * 128 + (int)sizeof(Ctl) + CHUNK_BYTES + 1024;
+  // the padded last dQ^T block (dq not a multiple of 128) reads one chunk past the tile: the Q / dO / P / dS buffers
+  // that follow are at least that long for every accepted shape (dq >= 128 here; dq = 64 gets a spare chunk)
+  const int spare = qchunks == 1 ? CHUNK_BYTES : 0;
+  const int smem = qchunks * CHUNK_BYTES + (qchunks + vchunks + 4) * HG * 128 + (int)sizeof(Ctl) + spare + 1024;
   TB_CUDA_CHECK(cudaFuncSetAttribute(sparse_mla_bwd_kernel<HG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -353,5 +356,6 @@ TB_API int tb_sparse_mla_bwd(const void* q, const void* kv, const int* idx, cons
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  return (H % 32 == 0) ? launch<32>(p, st) : launch<16>(p, st);
+  // 16 heads per CTA: with 32 the tile, Q, dO and the two operand buffers exceed the shared memory of an SM at dq 576
+  return launch<16>(p, st);
 }

@@ -106,10 +106,37 @@ __device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t da, uint64_t
       : "memory");
 }
 
+// The same instruction with the two descriptors given as (low, high) words: the issuing thread keeps the layout
+// halves in registers and only adds stage / k offsets to the start-address field.
+__device__ __forceinline__ void umma_mxf8_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %8, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %5, [%6], [%7], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
 // 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, replicated into the four lane quarters
 __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint32_t smem_addr) {
   const uint64_t desc = make_smem_desc(smem_addr, 16, 128, 0);  // no swizzle; 8-row groups 128 B apart
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_lohi(uint32_t taddr, uint32_t lo, uint32_t hi) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 d;\n"
+      "mov.b64 d, {%1, %2};\n"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n"
+      "}\n" ::"r"(taddr), "r"(lo), "r"(hi)
+      : "memory");
 }
 
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -215,6 +242,16 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t acc_phase = 0;
+      // Descriptors of stage 0: K-major, 128-byte swizzled rows (128 fp8 each), 8-row atoms 1024 B apart; a K step of
+      // 32 elements = +32 B.  The loop adds stage / k offsets to the start-address words only.
+      const uint64_t da0 = make_smem_desc(smem_u32(smem_a), 16, 1024, 2);
+      const uint64_t db0 = make_smem_desc(smem_u32(smem_b), 16, 1024, 2);
+      const uint64_t ds0 = make_smem_desc(smem_u32(smem_sf), 16, 128, 0);  // scale atoms: no swizzle, 8-row groups 128 B apart
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32), s_hi = (uint32_t)(ds0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0, s_lo0 = (uint32_t)ds0;
+      const uint32_t id0 = idesc_mxf8(BM, XBN, 0), id1 = idesc_mxf8(BM, XBN, 1), id2 = idesc_mxf8(BM, XBN, 2),
+                     id3 = idesc_mxf8(BM, XBN, 3);
+      static_assert(XBK / 32 == 4, "four scale blocks per stage");
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const XTile ti = tile_of(t);
         if (ti.ks0 >= ti.ks1) continue;  // nothing to contract: the epilogue writes zeros without an accumulator
@@ -223,28 +260,27 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           break;
         }
         tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * XBN;
+        uint32_t accum = 0;  // the first MMA of a tile overwrites the accumulator
         for (int ks = ti.ks0; ks < ti.ks1; ++ks) {
           if (!wait_bounded(&full_bar[stage], phase, abort_flag)) {
             if (*abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMA); }
             ok = false; break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem_a + stage * XA_STAGE);
-          const uint32_t sb = smem_u32(smem_b + stage * XB_STAGE);
-          const uint32_t sf = smem_u32(smem_sf + stage * XSF_STAGE);
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * (XA_STAGE >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)stage * (XB_STAGE >> 4);
+          const uint32_t s_lo = s_lo0 + (uint32_t)stage * (XSF_STAGE >> 4);
           const uint32_t sfa_t = tmem_base + SF_TMEM_BASE + stage * SF_TMEM_PER_STAGE;
           const uint32_t sfb_t = sfa_t + 4;
-          tmem_cp_sf(sfa_t, sf);
-          tmem_cp_sf(sfb_t, sf + SF_ATOM);
-          if (C::B_ATOMS == 2) tmem_cp_sf(sfb_t + 4, sf + 2 * SF_ATOM);
-#pragma unroll
-          for (int k = 0; k < XBK / 32; ++k) {
-            // K-major, 128-byte swizzled rows (128 fp8 each), 8-row atoms 1024 B apart; a K step of 32 elements = +32 B
-            const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, 2);
-            const uint64_t db = make_smem_desc(sb + k * 32, 16, 1024, 2);
-            umma_mxf8(tmem_base + acc * XBN, da, db, idesc_mxf8(BM, XBN, (uint32_t)k), sfa_t, sfb_t,
-                      (ks > ti.ks0 || k > 0) ? 1u : 0u);
-          }
+          tmem_cp_sf_lohi(sfa_t, s_lo, s_hi);
+          tmem_cp_sf_lohi(sfb_t, s_lo + (SF_ATOM >> 4), s_hi);
+          if (C::B_ATOMS == 2) tmem_cp_sf_lohi(sfb_t + 4, s_lo + 2 * (SF_ATOM >> 4), s_hi);
+          umma_mxf8_lohi(d_tmem, a_lo, a_hi, b_lo, b_hi, id0, sfa_t, sfb_t, accum);
+          umma_mxf8_lohi(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u);
+          umma_mxf8_lohi(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t, sfb_t, 1u);
+          umma_mxf8_lohi(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t, sfb_t, 1u);
+          accum = 1u;
           umma_commit(&empty_bar[stage]);
           if (++stage == XSTAGES) { stage = 0; phase ^= 1; }
         }

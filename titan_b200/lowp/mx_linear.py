@@ -140,6 +140,34 @@ def mx_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None =
     return y if bias is None else y + bias
 
 
+# ---- quantised expert weights, kept between the optimizer steps
+# Expert weights change once per optimizer step but are multiplied several times in between (forward, recomputed
+# forward under activation checkpointing, input gradient; every micro-batch of a gradient-accumulation step).  A module
+# that passes a `weight_key` gets both quantised views of its weight (row-blocked for the forward, transposed for the
+# input gradient) from ONE dual-axis pass, kept until `invalidate_weight_cache()` (the optimizer containers call it
+# after every step) or until the tensor's version counter moves (in-place loads).  Modules whose weight is resharded
+# between uses (FSDP) must not pass a key: the cache would pin the unsharded bytes.
+_WEIGHT_CACHE: dict = {}
+
+
+def invalidate_weight_cache() -> None:
+    _WEIGHT_CACHE.clear()
+
+
+def _quantized_weight(w2d: torch.Tensor, round_mode: str, weight_key):
+    """→ (wq, ws, wq_t, ws_t): row-blocked and transposed MX views of ``w2d`` [E*N, K], atom-ordered scales."""
+    if weight_key is None:
+        return None
+    tag = (w2d._version, tuple(w2d.shape), w2d.data_ptr(), round_mode)
+    hit = _WEIGHT_CACHE.get(weight_key)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    with torch.no_grad():
+        views = mx_quantize_dual(w2d.contiguous(), round_mode, rows=True, transposed=True, atoms=True)
+    _WEIGHT_CACHE[weight_key] = (tag, views)
+    return views
+
+
 class _MXGroupedMMAligned(torch.autograd.Function):
     """Grouped MXFP8 product over rows whose groups are multiples of 128 (the padded expert-major layout): three
     launches of the grouped block-scaled GEMM, operands quantised once each by the dual-axis kernel, no host sync.
@@ -148,7 +176,7 @@ class _MXGroupedMMAligned(torch.autograd.Function):
     those rows are never routed to and only need a defined value."""
 
     @staticmethod
-    def forward(ctx, x, w, offs, round_mode):
+    def forward(ctx, x, w, offs, round_mode, weight_key=None):
         from titan_b200.ops.mxfp8_gemm import GROUP_B_ROWS, mxfp8_grouped_gemm
 
         E, N, K = w.shape
@@ -156,9 +184,14 @@ class _MXGroupedMMAligned(torch.autograd.Function):
         used = T // 128 * 128
         xq1, xs1, xq2t, xs2t = mx_quantize_dual(x[:used].contiguous(), round_mode, transposed=ctx.needs_input_grad[1],
                                                 atoms=True)
-        wq1, ws1, _, _ = mx_quantize_dual(w.reshape(E * N, K).contiguous(), round_mode, transposed=False, atoms=True)
+        cached = _quantized_weight(w.reshape(E * N, K), round_mode, weight_key)
+        if cached is not None:
+            wq1, ws1 = cached[0], cached[1]
+        else:
+            wq1, ws1, _, _ = mx_quantize_dual(w.reshape(E * N, K).contiguous(), round_mode, transposed=False,
+                                              atoms=True)
         ctx.save_for_backward(xq2t, xs2t, w, offs)
-        ctx.round_mode, ctx.rows = round_mode, T
+        ctx.round_mode, ctx.rows, ctx.weight_key = round_mode, T, weight_key
         y = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
         if used < T:
             y[used:].zero_()
@@ -177,15 +210,19 @@ class _MXGroupedMMAligned(torch.autograd.Function):
                                                 transposed=need_dw, atoms=True)
         dx = dw = None
         if need_dx:  # every expert's weight blocked down its N rows, transposed in the same pass: [K, E*N]
-            _, _, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K).contiguous(), ctx.round_mode, rows=False,
-                                                atoms=True)
+            cached = _quantized_weight(w.reshape(E * N, K), ctx.round_mode, ctx.weight_key)
+            if cached is not None:
+                wq2t, ws2t = cached[2], cached[3]
+            else:
+                _, _, wq2t, ws2t = mx_quantize_dual(w.reshape(E * N, K).contiguous(), ctx.round_mode, rows=False,
+                                                    atoms=True)
             dx = torch.empty(T, K, dtype=torch.bfloat16, device=g.device)
             if used < T:
                 dx[used:].zero_()
             mxfp8_grouped_gemm(gq1, gs1, wq2t, ws2t, offs, GROUP_B_SLICE, out=dx, packed=True)
         if need_dw:  # gᵀ [N, T] · xᵀ [K, T]ᵀ over each expert's own rows → [E*N, K]
             dw = mxfp8_grouped_gemm(gq2t, gs2t, xq2t, xs2t, offs, GROUP_K, packed=True).view(E, N, K).to(w.dtype)
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
 def _aligned_ok(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor) -> bool:
@@ -230,10 +267,11 @@ class _MXGroupedMM(torch.autograd.Function):
 
 
 def mx_grouped_mm(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, round_mode: str = "rceil", *,
-                  aligned: bool = False) -> torch.Tensor:
+                  aligned: bool = False, weight_key=None) -> torch.Tensor:
     """Grouped MXFP8 GEMM: rows ``[offs[e-1], offs[e])`` of ``x`` go through ``w[e]ᵀ``.  ``aligned=True`` is the
     caller's promise that every group is a multiple of 128 rows (the padded expert-major layout): on CUDA that form runs
-    as one grouped tensor-core launch per product instead of a loop over experts."""
+    as one grouped tensor-core launch per product instead of a loop over experts.  ``weight_key`` (any hashable that
+    names the weight) keeps the weight's quantised views between optimizer steps (see `invalidate_weight_cache`)."""
     if aligned and _aligned_ok(x, w, offs):
-        return _MXGroupedMMAligned.apply(x, w, offs.to(torch.int32), round_mode)
+        return _MXGroupedMMAligned.apply(x, w, offs.to(torch.int32), round_mode, weight_key)
     return _MXGroupedMM.apply(x, w, offs, round_mode)

@@ -2,9 +2,10 @@
 
 The trainer hands a batch of packed sequences with position ids that restart at every document.  `VarlenMetadata`
 turns them into cumulative document boundaries once per step; `VarlenAttention` then runs causal attention per
-document (one flash-attention call per document through the library SDPA, which sees a plain causal problem and
-needs no ``S × S`` mask).  Under Ulysses context parallelism the core sees the full sequence with a slice of the
-heads, so the same metadata applies unchanged.
+document.  On a B200 (bf16, head dim 128, sequence a multiple of 128) that is ONE launch of the tcgen05 flash kernels
+with the per-token document start as the mask (`titan_b200.ops.flash_attention`, forward and backward); elsewhere one
+library SDPA call per document, which sees a plain causal problem and needs no ``S × S`` mask.  Under Ulysses context
+parallelism the core sees the full sequence with a slice of the heads, so the same metadata applies unchanged.
 
 Parity: `NPUVarlenAttention` (torchtitan_npu/models/common/npu_varlen_attention.py) used by the Qwen3 TND recipe
 (models/qwen3/tnd_config.py:20-45).
@@ -29,6 +30,18 @@ class VarlenMetadata:
 
     def to(self, *args, **kwargs):  # moves with the batch like a tensor would
         return self
+
+    def seq_start(self, device) -> torch.Tensor:
+        """[B, S] int32: the position of the first token of each token's document (built once per step)."""
+        cached = self.__dict__.get("_seq_start")
+        if cached is None or cached.device != torch.device(device):
+            rows = []
+            for bounds in self.cu_seqlens:
+                b = torch.tensor(bounds, dtype=torch.int64)
+                rows.append(torch.repeat_interleave(b[:-1], b[1:] - b[:-1]))
+            cached = torch.stack(rows).to(torch.int32).to(device)
+            self.__dict__["_seq_start"] = cached
+        return cached
 
 
 def build_varlen_metadata(positions: torch.Tensor) -> VarlenMetadata:
@@ -60,6 +73,10 @@ class VarlenAttention(Module):
             return F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=gqa)
         if not isinstance(attn_mask, VarlenMetadata):
             return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, scale=scale, enable_gqa=gqa)
+        from titan_b200.ops.flash_attention import flash_attention, flash_attention_supported
+
+        if q.is_cuda and flash_attention_supported(q, k) and v.shape[-1] == q.shape[-1]:
+            return flash_attention(q, k, v, scale=scale, seq_start=attn_mask.seq_start(q.device))
         rows = []
         for b, bounds in enumerate(attn_mask.cu_seqlens):
             docs = []

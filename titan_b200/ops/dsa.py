@@ -244,7 +244,9 @@ def _values_are_key_prefix(k: torch.Tensor, v: torch.Tensor) -> bool:
         return False
     dv, t = v.shape[-1], k.shape[2]
     rows = sorted({0, t // 2, t - 1})
-    return bool(torch.equal(k[0, 0, rows, :dv], v[0, 0, rows]))
+    with torch.no_grad():   # a probe, not part of the graph (under activation checkpointing it runs only once)
+        kd, vd = k.detach(), v.detach()
+        return bool(torch.equal(kd[0, 0, rows, :dv], vd[0, 0, rows]))
 
 
 def _kernel_sparse_attention(q, k, idx, scale, dv):

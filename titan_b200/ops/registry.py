@@ -199,19 +199,37 @@ _define("cross_entropy_bwd_(Tensor(a!) x, Tensor labels, Tensor lse, Tensor gsca
 
 
 # ---------------------------------------------------------------------------------------------- flash attention
-def _flash_fwd_cuda(q, k, v, scale):
+def _flash_fwd_cuda(q, k, v, scale, seq_start=None):
     from titan_b200.ops.flash_attention import _flash_fwd_launch
 
-    return _flash_fwd_launch(q, k, v, scale)
+    return _flash_fwd_launch(q, k, v, scale, seq_start)
 
 
-def _flash_fwd_fake(q, k, v, scale):
+def _flash_fwd_fake(q, k, v, scale, seq_start=None):
     b, h, s, d = q.shape
     return q.new_empty((b, s, h, v.shape[-1])).transpose(1, 2), q.new_empty((b, h, s), dtype=torch.float32)
 
 
-_define("flash_attention_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)", _flash_fwd_cuda,
-        _flash_fwd_fake)
+_define("flash_attention_fwd(Tensor q, Tensor k, Tensor v, float scale, Tensor? seq_start=None) -> (Tensor, Tensor)",
+        _flash_fwd_cuda, _flash_fwd_fake)
+
+
+def _flash_bwd_cuda(q, k, v, out, lse, g, scale, seq_start=None):
+    from titan_b200.ops.flash_attention import _flash_bwd_launch
+
+    return _flash_bwd_launch(q, k, v, out, lse, g, scale, seq_start)
+
+
+def _flash_bwd_fake(q, k, v, out, lse, g, scale, seq_start=None):
+    def like(t):
+        b, h, s, d = t.shape
+        return t.new_empty((b, s, h, d)).transpose(1, 2)
+
+    return like(q), like(k), like(v)
+
+
+_define("flash_attention_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor grad, float scale, "
+        "Tensor? seq_start=None) -> (Tensor, Tensor, Tensor)", _flash_bwd_cuda, _flash_bwd_fake)
 
 
 # Ops whose outputs selective activation checkpointing keeps (contractions: recomputing them costs real FLOPs).

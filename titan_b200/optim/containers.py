@@ -75,7 +75,6 @@ class OptimizersContainer(Optimizer, Stateful):
     def step(self, *args, **kwargs) -> None:
         for opt in self.optimizers:
             opt.step(*args, **kwargs)
-
     def zero_grad(self, *args, **kwargs) -> None:
         for opt in self.optimizers:
             opt.zero_grad(*args, **kwargs)

@@ -30,6 +30,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from titan_b200.lowp.mx_linear import invalidate_weight_cache
 from titan_b200.checkpoint.manager import CheckpointManager
 from titan_b200.data.synthetic import build_dataloader
 from titan_b200.optim.containers import build_lr_schedulers, build_optimizers
@@ -375,6 +376,9 @@ class Trainer:
             defer_scale_to=fused_clip,  # optimizers that apply the clip coefficient inside their update kernel
         )
         self.optimizers.step()
+        # the fused optimizer kernels write weights through raw pointers (no version bump): quantised copies kept by
+        # the low-precision expert path are stale from here on
+        invalidate_weight_cache()
         self.lr_schedulers.step()
         loss = torch.sum(torch.stack(losses))
         self._last_loss = loss
