@@ -206,6 +206,7 @@ def run_arm(args, impl: str, *, ac_override: str | None = None, with_e2e: bool =
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    barrier()  # creates the communicator now: after warm-up the caching allocator may hold all free memory
     tokens_per_step_rank = cfg.training.local_batch_size * cfg.training.seq_len
     dp = trainer.dp_degree
     tokens_per_step = tokens_per_step_rank * dp

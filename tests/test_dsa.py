@@ -168,3 +168,36 @@ def test_indexer_scores_from_selection_match_recomputed_scores(cuda_device):
     ref.masked_fill(~m, 0.0).mul(g).sum().backward()
     for x, y, name in zip(a, b, ("dq", "dw", "dk")):
         torch.testing.assert_close(x.grad.float(), y.grad.float(), rtol=5e-2, atol=5e-2, msg=lambda s, n=name: f"{n}: {s}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("S,H,T,k", [(70, 64, 1024, 256), (33, 16, 400, 100), (16, 32, 2048, 384)])
+def test_selected_key_indexer_backward_kernel(cuda_device, S, H, T, k):
+    """The tensor-core backward through the selected keys only (head dim 128; 16 / 32 / 64 index heads; top-k that is
+    and is not a multiple of 128; empty slots) against fp32 autograd of the scores recomputed at the selected keys."""
+    from titan_b200.ops import _lib, dsa
+
+    torch.manual_seed(5)
+    B, D = 2, 128
+    q = (torch.randn(B, S, H, D, device="cuda") * 0.3).to(torch.bfloat16)
+    kk = (torch.randn(B, T, 1, D, device="cuda") * 0.3).to(torch.bfloat16)
+    w = torch.rand(B, S, H, device="cuda")
+    idx = torch.stack([torch.stack([torch.randperm(T, device="cuda")[:k] for _ in range(S)]) for _ in range(B)])
+    idx = torch.where(torch.rand(B, S, k, device="cuda") < 0.15, torch.full_like(idx, -1), idx).to(torch.int32)
+    assert dsa._selected_backward_takes(q, kk)
+    # fp32 oracle: scores at the selected keys
+    qr, wr, kr = q.float().requires_grad_(), w.clone().requires_grad_(), kk.float().requires_grad_()
+    ksel = torch.stack([kr[b, :, 0][idx[b].clamp_min(0).long()] for b in range(B)])          # [B,S,k,D]
+    x = torch.einsum("bshd,bskd->bshk", qr, ksel)
+    ref = (torch.relu(x) * wr.unsqueeze(-1)).sum(2)
+    vals = ref.detach().masked_fill(idx < 0, float("-inf"))
+    a = [t.clone().requires_grad_(True) for t in (q, w, kk)]
+    got = dsa.indexer_scores_from_selection(a[0], a[1], a[2], idx, vals)
+    m = idx >= 0
+    g = torch.randn_like(ref).masked_fill(~m, 0.0)
+    got.masked_fill(~m, 0.0).mul(g).sum().backward()
+    _lib.shared_status().raise_if_set("indexer_sel_bwd")
+    ref.masked_fill(~m, 0.0).mul(g).sum().backward()
+    for xg, y, name in zip(a, (qr, wr, kr), ("dq", "dw", "dk")):
+        torch.testing.assert_close(xg.grad.float(), y.grad.float(), rtol=5e-2, atol=5e-2,
+                                   msg=lambda s_, n=name: f"{n}: {s_}")

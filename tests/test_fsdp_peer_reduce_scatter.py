@@ -48,7 +48,8 @@ def test_two_gpus_peer_memory_matches_nccl(tmp_path):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
                "127.0.0.1", "--master-port", str(port), "-m", "titan_b200.entry", "--module", "llama3", "--config",
                "llama3_debugmodel_b200", "--training.steps", "4", "--debug.seed", "3", "--job.dump_folder",
-               str(tmp_path / mode), "--parallelism.fsdp_reduce_scatter", mode, "--parallelism.fsdp_all_gather", mode]
+               str(tmp_path / mode), "--parallelism.fsdp_reduce_scatter", mode, "--parallelism.fsdp_all_gather",
+               "peer_memory" if mode == "nvls" else mode]
         res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
         assert res.returncode == 0, (res.stdout + res.stderr)[-4000:]
         return losses(res.stdout + res.stderr)
@@ -57,3 +58,7 @@ def test_two_gpus_peer_memory_matches_nccl(tmp_path):
     assert len(ref) == 4 and len(got) == 4
     for a, b in zip(got, ref):
         assert abs(a - b) < 2e-2, (got, ref)   # same bf16 inputs, fp32 sums in a different order
+    # the in-switch sum (multimem.ld_reduce; peer loads where the fabric has no multicast) gives the same losses
+    nvls = run("nvls", 29694)
+    for a, b in zip(nvls, ref):
+        assert abs(a - b) < 2e-2, (nvls, ref)

@@ -200,10 +200,11 @@ class ParallelismConfig:
     """Parameter all-gather of FSDP2: `nccl` = stock, `peer_memory` = copy-engine pulls from the peers' symmetric
     buffers (no SMs taken from the overlapping GEMMs), `auto` = `peer_memory` under the conditions of
     `fsdp_reduce_scatter`."""
-    fsdp_reduce_scatter: Literal["auto", "nccl", "peer_memory"] = "auto"
+    fsdp_reduce_scatter: Literal["auto", "nccl", "peer_memory", "nvls"] = "auto"
     """Gradient reduce-scatter of FSDP2: `nccl` = stock (fp32 bucket through NCCL), `peer_memory` = bf16 bucket in
-    symmetric memory reduced by one kernel over NVLink peer loads, `auto` = `peer_memory` for CUDA jobs whose FSDP
-    group is 2..8 GPUs of one node."""
+    symmetric memory reduced by one kernel over NVLink peer loads, `nvls` = the same bucket summed inside the NVSwitch
+    (`multimem.ld_reduce` through the slot's multicast address; falls back to peer loads where the fabric has no
+    multicast), `auto` = `peer_memory` for CUDA jobs whose FSDP group is 2..8 GPUs of one node."""
     dedicated_ep_group: bool = True
     """Give EP its own communicator so FSDP and EP traffic overlap (reference train.py:136-175)."""
 

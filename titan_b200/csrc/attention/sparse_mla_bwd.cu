@@ -17,8 +17,9 @@
 //                                           B = Q / dO read MN-major
 //
 // dQ^T stays in tensor memory over all key blocks of the query.  dKV is produced per block in column groups of 192
-// and added to the rows the block gathered from with 16-byte vector reductions (different queries select the same
-// rows).  When DQ is not a multiple of 128 the last 128-row block of dQ^T reads 64 columns past the tile; those
+// and added to the rows the block gathered from (different queries select the same rows): the group is staged as
+// fp32 rows in the shared memory of the tile, which is dead by then, and every row leaves as ONE bulk reduction
+// (`cp.reduce.async.bulk ... add.f32`, up to 768 contiguous bytes) instead of 48 vector atomics per thread.  When DQ is not a multiple of 128 the last 128-row block of dQ^T reads 64 columns past the tile; those
 // accumulator lanes are never read.
 //
 // Every wait is bounded; a failure sets the status word and the CTA drains to the common exit.
@@ -86,14 +87,21 @@ __device__ __forceinline__ void st_shared_b16(uint32_t addr, float v) {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const uint16_t*>(&b)) : "memory");
 }
 
+// fp32 staging of one dKV column group: [128 keys][w + 4] (the pad spreads the rows over the banks)
+__host__ __device__ inline int stage_ld(int dq) { return (dq < GROUP_COLS ? dq : GROUP_COLS) + 4; }
+__host__ __device__ inline int region0_bytes(int dq) {
+  const int tile = (dq / 64) * CHUNK_BYTES, stage = BKEYS * stage_ld(dq) * 4;
+  return ((tile > stage ? tile : stage) + 1023) & ~1023;
+}
+
 template <int HG>
 __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int qchunks = p.dq / 64, vchunks = p.dv / 64;
   constexpr int HROW = HG * 128;                 // bytes of one [HG x 64] chunk
-  uint8_t* sK = smem;                            // qchunks x 16 KB: gathered tile [128 keys x dq]
-  uint8_t* sQ = sK + qchunks * CHUNK_BYTES;      // qchunks x [HG x 64]
+  uint8_t* sK = smem;                            // qchunks x 16 KB: gathered tile [128 keys x dq]; later the dKV staging
+  uint8_t* sQ = sK + region0_bytes(p.dq);        // qchunks x [HG x 64]
   uint8_t* sDO = sQ + qchunks * HROW;            // vchunks x [HG x 64]
   uint8_t* sP = sDO + vchunks * HROW;            // 2 x [HG x 64 keys]
   uint8_t* sDS = sP + 2 * HROW;                  // 2 x [HG x 64 keys]
@@ -266,28 +274,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
         __syncthreads();
         if (*abort_flag) break;
 
-        // ---- add the group to the gathered rows (all 256 threads: two warp sets split the columns)
+        // ---- stage the group as fp32 rows (all 256 threads: two warp sets split the columns), then one bulk
+        //      reduction per gathered row
         {
           const int row = ctl->valid[r];
           const int hw = w >> 1;                                 // columns per warp set (multiple of 32)
-          // the tensor-memory load is a warp-wide instruction: every lane takes part, empty slots only skip the adds
-          float* dst = p.dkv + (long long)(row >= 0 ? row : 0) * p.dq + c0 + half * hw;
+          const int ld = stage_ld(p.dq);
+          const uint32_t srow = smem_u32(sK) + (uint32_t)(r * ld + half * hw) * 4;
           for (int c = 0; c < hw; c += 32) {
             uint32_t v[32];
             tmem_ld_32x32(tmem_kv + lane_off + half * hw + c, v);
             tmem_ld_wait();
-            if (row >= 0) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c + i),
-                             "f"(__uint_as_float(v[i])), "f"(__uint_as_float(v[i + 1])),
-                             "f"(__uint_as_float(v[i + 2])), "f"(__uint_as_float(v[i + 3]))
-                             : "memory");
-            }
+            for (int i = 0; i < 32; i += 4)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + (uint32_t)(c + i) * 4), "r"(v[i]),
+                           "r"(v[i + 1]), "r"(v[i + 2]), "r"(v[i + 3])
+                           : "memory");
           }
           tc_fence_before();
+          fence_proxy_async();   // the bulk engine reads what ordinary stores wrote
+          __syncthreads();
+          if (tid < BKEYS) {     // warps 0..3: r == tid
+            if (row >= 0) {
+              const float* dst = p.dkv + (long long)row * p.dq + c0;
+              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst),
+                           "r"(smem_u32(sK) + (uint32_t)(r * ld) * 4), "r"(w * 4)
+                           : "memory");
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the staging rows may be overwritten
+          }
         }
-        __syncthreads();   // the group accumulator is free again
+        __syncthreads();   // the group accumulator and the staging area are free again
       }
       if (*abort_flag) break;
     }
@@ -309,6 +327,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
     __syncthreads();
   }
 
+  // The per-group waits above only cover the bulk engine's READS of the staging rows.  Before this CTA ends, wait for
+  // the reductions themselves: a launch that completed while row updates were still on their way let the next
+  // kernels of the stream read (and the allocator reuse) the gradient buffer too early.
+  if (tid < BKEYS) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -323,7 +345,7 @@ int launch(const BwdParams& p, cudaStream_t st) {
   // the padded last dQ^T block (dq not a multiple of 128) reads one chunk past the tile: the Q / dO / P / dS buffers
   // that follow are at least that long for every accepted shape (dq >= 128 here; dq = 64 gets a spare chunk)
   const int spare = qchunks == 1 ? CHUNK_BYTES : 0;
-  const int smem = qchunks * CHUNK_BYTES + (qchunks + vchunks + 4) * HG * 128 + (int)sizeof(Ctl) + spare + 1024;
+  const int smem = region0_bytes(p.dq) + (qchunks + vchunks + 4) * HG * 128 + (int)sizeof(Ctl) + spare + 1024;
   TB_CUDA_CHECK(cudaFuncSetAttribute(sparse_mla_bwd_kernel<HG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -84,6 +84,49 @@ __global__ void __launch_bounds__(512) castscale_rs_kernel(PeerPtrs in, TOut* __
   }
 }
 
+// The same reduction done INSIDE the NVSwitch: `mc` is the multicast address of the symmetric slot (all ranks'
+// buckets bound to one multicast object), and one `multimem.ld_reduce` returns the sum over the ranks of 16 bytes,
+// accumulated in fp32 for bf16 data.  Each rank asks for its own chunk only, so every byte crosses its link once.
+template <typename TOut>
+__global__ void __launch_bounds__(512) castscale_rs_nvls_bf16_kernel(const __nv_bfloat16* __restrict__ mc,
+                                                                      TOut* __restrict__ out, long long chunk,
+                                                                      float scale) {
+  const long long nvec = chunk / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    uint32_t r0, r1, r2, r3;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "l"(mc + i * 8)
+                 : "memory");
+    const uint32_t r[4] = {r0, r1, r2, r3};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16x2(r[k]);
+      out[i * 8 + 2 * k] = from_f<TOut>(f.x * scale);
+      out[i * 8 + 2 * k + 1] = from_f<TOut>(f.y * scale);
+    }
+  }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(512) castscale_rs_nvls_f32_kernel(const float* __restrict__ mc, TOut* __restrict__ out,
+                                                                     long long chunk, float scale) {
+  const long long nvec = chunk / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float a, b, c, d;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+                 : "l"(mc + i * 4)
+                 : "memory");
+    out[i * 4] = from_f<TOut>(a * scale);
+    out[i * 4 + 1] = from_f<TOut>(b * scale);
+    out[i * 4 + 2] = from_f<TOut>(c * scale);
+    out[i * 4 + 3] = from_f<TOut>(d * scale);
+  }
+}
+
 // out[row, :] = Σ_src stage[src][row, :]; each block first makes sure all sources have published
 template <typename T>
 __global__ void __launch_bounds__(256) rs_reduce_kernel(const T* __restrict__ stage, const unsigned int* flags,
@@ -270,6 +313,30 @@ TB_API int tb_castscale_rs(void* const* in_ptrs, void* out, long long chunk, int
   else if (in_dtype == 0 && out_dtype == 1) TB_RS(float, __nv_bfloat16);
   else return TB_ERR_ARG;
 #undef TB_RS
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+// In-switch variant of tb_castscale_rs: `mc_chunk` is the MULTICAST address of this rank's chunk inside the symmetric
+// slot (multicast base + the slot's offset + rank * chunk elements); `chunk` elements, a multiple of 8 (bf16) or 4
+// (fp32), 16-byte aligned.  Callers order it after the same flag exchange.
+TB_API int tb_castscale_rs_nvls(const void* mc_chunk, void* out, long long chunk, float scale, int in_dtype,
+                                int out_dtype, cudaStream_t st) {
+  if (mc_chunk == nullptr || chunk <= 0 || (reinterpret_cast<uintptr_t>(mc_chunk) & 15) != 0) return TB_ERR_ARG;
+  if (chunk % (in_dtype == 1 ? 8 : 4) != 0) return TB_ERR_ARG;
+  long long grid = (chunk / 8 + 511) / 512;
+  if (grid > 148 * 4) grid = 148 * 4;
+  if (grid < 1) grid = 1;
+  if (in_dtype == 1 && out_dtype == 0)
+    castscale_rs_nvls_bf16_kernel<float><<<(int)grid, 512, 0, st>>>((const __nv_bfloat16*)mc_chunk, (float*)out, chunk, scale);
+  else if (in_dtype == 1 && out_dtype == 1)
+    castscale_rs_nvls_bf16_kernel<__nv_bfloat16><<<(int)grid, 512, 0, st>>>((const __nv_bfloat16*)mc_chunk, (__nv_bfloat16*)out, chunk, scale);
+  else if (in_dtype == 0 && out_dtype == 0)
+    castscale_rs_nvls_f32_kernel<float><<<(int)grid, 512, 0, st>>>((const float*)mc_chunk, (float*)out, chunk, scale);
+  else if (in_dtype == 0 && out_dtype == 1)
+    castscale_rs_nvls_f32_kernel<__nv_bfloat16><<<(int)grid, 512, 0, st>>>((const float*)mc_chunk, (__nv_bfloat16*)out, chunk, scale);
+  else return TB_ERR_ARG;
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

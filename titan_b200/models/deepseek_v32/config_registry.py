@@ -75,7 +75,7 @@ def deepseek_v32_671b_61layers_32k() -> TrainerConfig:
 
 def deepseek_v32_sparse_cp8() -> TrainerConfig:
     """12-layer sparse-attention model at seq 131072 on 8 GPUs: CP=8 (DSA all-gather of the shared KV latent),
-    fp8 indexer, top-2048 keys per query."""
+    lightning indexer scored in bf16 on the tensor cores, top-2048 keys per query."""
     return TrainerConfig(
         model=ModelConfigRef(name="deepseek_v32", flavor="sparse_12l"),
         metrics=MetricsConfig(log_freq=1),
@@ -84,6 +84,8 @@ def deepseek_v32_sparse_cp8() -> TrainerConfig:
         training=TrainingConfig(local_batch_size=1, seq_len=131072, steps=100, dtype="bfloat16"),
         dataloader=SyntheticDataLoaderConfig(seed=0),
         parallelism=ParallelismConfig(context_parallel_degree=8, data_parallel_shard_degree=1),
-        activation_checkpoint=ActivationCheckpointConfig(mode="full"),
+        # keep what is expensive to recompute and small to store (contraction outputs, the indexer's selection, the
+        # sparse-attention output); recompute the elementwise rest
+        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op_save_all_mm"),
         model_converters=_converters(*_FUSED),
     )

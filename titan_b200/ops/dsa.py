@@ -63,6 +63,13 @@ def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0
     ``(pos_offset + s + 1) // ratio`` of them."""
     if not _scoring_kernels_take(q_idx):
         return lightning_indexer_topk_ref(q_idx, weights, k_idx, topk, pos_offset, ratio)
+    from titan_b200.ops.registry import ops
+
+    # a dispatcher op: selective activation checkpointing keeps the selection instead of scoring every key again
+    return ops.indexer_topk(q_idx.detach(), weights.detach(), k_idx.detach(), topk, pos_offset, ratio)
+
+
+def _indexer_topk_launch(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, ratio: int = 1):
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]
     L = _lib.lib()
@@ -149,9 +156,9 @@ def indexer_scores_selected(q_idx, weights, k_idx, idx, chunk: int = 512):
 
 class _IndexScoresAtSelected(torch.autograd.Function):
     """Index scores at the selected keys whose forward costs nothing (the scoring kernel already produced the values
-    while selecting) and whose backward never builds fp32 [queries, heads, keys] tensors: per query chunk it recomputes
-    ``x = q·kᵀ`` in the storage dtype, runs one kernel for ``dx`` and ``dw`` (`csrc/attention/indexer_bwd.cu`) and two
-    GEMMs for ``dq`` and ``dk``."""
+    while selecting).  The gradient only flows through the selected keys, so the backward gathers those key rows and
+    runs on the tensor cores in O(S * top-k) (`csrc/attention/indexer_sel_bwd.cu`); other shapes take a dense pass
+    over all keys in query chunks."""
 
     @staticmethod
     def forward(ctx, q_idx, weights, k_idx, idx, vals, chunk):
@@ -161,38 +168,85 @@ class _IndexScoresAtSelected(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        import ctypes
-
         q_idx, weights, k_idx, idx = ctx.saved_tensors
-        B, S, H, D = q_idx.shape
-        T = k_idx.shape[1]
-        P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        _lib.declare("tb_indexer_relu_bwd", [P, P, P, P, P, LL, I, I, I, P])
-        safe = idx.clamp_min(0).long()
         g = g.float().masked_fill(idx < 0, 0.0)
-        dq = torch.empty_like(q_idx)
-        dw = torch.empty(B, S, H, dtype=torch.float32, device=q_idx.device)
-        dk = torch.zeros(B, T, D, dtype=torch.float32, device=q_idx.device)
-        for b in range(B):
-            kb = k_idx[b, :, 0].contiguous()
-            for s0 in range(0, S, ctx.chunk):
-                s1 = min(s0 + ctx.chunk, S)
-                sc = s1 - s0
-                qc = q_idx[b, s0:s1].reshape(sc * H, D)
-                dense_g = torch.zeros(sc, T, dtype=torch.float32, device=g.device).scatter_add_(1, safe[b, s0:s1],
-                                                                                            g[b, s0:s1])
-                x = torch.matmul(qc, kb.t())  # [sc*H, T], storage dtype
-                dx = torch.empty_like(x)
-                dwc = torch.empty(sc * H, dtype=torch.float32, device=x.device)
-                wc = weights[b, s0:s1].float().contiguous()
-                rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dense_g.data_ptr(), wc.data_ptr(), dx.data_ptr(),
-                                                    dwc.data_ptr(), sc * H, H, T, _lib.dtype_code(x.dtype),
-                                                    _lib.stream_ptr())
-                _lib.check(rc, "indexer_relu_bwd")
-                dq[b, s0:s1] = torch.matmul(dx, kb).view(sc, H, D)
-                dk[b] += torch.matmul(dx.t(), qc).float()
-                dw[b, s0:s1] = dwc.view(sc, H)
+        if SELECTED_BACKWARD and _selected_backward_takes(q_idx, k_idx):
+            dq, dw, dk = _indexer_selected_backward(q_idx, weights, k_idx, idx, g)
+        else:
+            dq, dw, dk = _indexer_dense_backward(q_idx, weights, k_idx, idx, g, ctx.chunk)
         return dq, dw.to(weights.dtype), dk.to(k_idx.dtype).unsqueeze(2), None, None, None
+
+
+SELECTED_BACKWARD = True  # False: the dense chunked backward below (the oracle of the sparse kernel's test)
+
+
+def _selected_backward_takes(q_idx, k_idx) -> bool:
+    return (q_idx.is_cuda and q_idx.dtype == torch.bfloat16 and q_idx.shape[-1] == 128
+            and q_idx.shape[2] in (16, 32, 64))
+
+
+def _indexer_selected_backward(q_idx, weights, k_idx, idx, g):
+    """Gradients through the selected keys only (`csrc/attention/indexer_sel_bwd.cu`): O(S * top-k) work.
+    → (dq like q_idx, dw [B,S,H] fp32, dk [B,T,D] fp32)."""
+    import ctypes
+
+    B, S, H, D = q_idx.shape
+    T, kk = k_idx.shape[1], idx.shape[-1]
+    P, I = ctypes.c_void_p, ctypes.c_int
+    _lib.declare("tb_indexer_sel_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, P, P])
+    pad = (-kk) % 128
+    if pad:
+        idx, g = F.pad(idx, (0, pad), value=-1), F.pad(g, (0, pad))
+    idx = idx.to(torch.int32).contiguous()
+    g = g.contiguous()
+    dq = torch.empty_like(q_idx, memory_format=torch.contiguous_format)
+    dw = torch.empty(B, S, H, dtype=torch.float32, device=q_idx.device)
+    dk = torch.zeros(B, T, D, dtype=torch.float32, device=q_idx.device)
+    for b in range(B):
+        qb = q_idx[b].contiguous()
+        kb = k_idx[b, :, 0].contiguous().to(qb.dtype)
+        wb = weights[b].float().contiguous()
+        rc = _lib.lib().tb_indexer_sel_bwd(qb.data_ptr(), kb.data_ptr(), idx[b].data_ptr(), g[b].data_ptr(),
+                                           wb.data_ptr(), dq[b].data_ptr(), dw[b].data_ptr(), dk[b].data_ptr(),
+                                           S, H, T, kk + pad, D, _lib.shared_status().ptr, _lib.stream_ptr())
+        _lib.check(rc, "indexer_sel_bwd")
+    return dq, dw, dk
+
+
+def _indexer_dense_backward(q_idx, weights, k_idx, idx, g, chunk):
+    """The same gradients through a dense pass over all keys, ``chunk`` queries at a time: recompute ``x = q·kᵀ`` in
+    the storage dtype, one kernel for ``dx`` and ``dw`` (`csrc/attention/indexer_bwd.cu`), two GEMMs for ``dq`` /
+    ``dk``.  Never builds fp32 [queries, heads, keys] tensors."""
+    import ctypes
+
+    B, S, H, D = q_idx.shape
+    T = k_idx.shape[1]
+    P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    _lib.declare("tb_indexer_relu_bwd", [P, P, P, P, P, LL, I, I, I, P])
+    safe = idx.clamp_min(0).long()
+    dq = torch.empty_like(q_idx)
+    dw = torch.empty(B, S, H, dtype=torch.float32, device=q_idx.device)
+    dk = torch.zeros(B, T, D, dtype=torch.float32, device=q_idx.device)
+    for b in range(B):
+        kb = k_idx[b, :, 0].contiguous()
+        for s0 in range(0, S, chunk):
+            s1 = min(s0 + chunk, S)
+            sc = s1 - s0
+            qc = q_idx[b, s0:s1].reshape(sc * H, D)
+            dense_g = torch.zeros(sc, T, dtype=torch.float32, device=g.device).scatter_add_(1, safe[b, s0:s1],
+                                                                                        g[b, s0:s1])
+            x = torch.matmul(qc, kb.t())  # [sc*H, T], storage dtype
+            dx = torch.empty_like(x)
+            dwc = torch.empty(sc * H, dtype=torch.float32, device=x.device)
+            wc = weights[b, s0:s1].float().contiguous()
+            rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dense_g.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+                                                dwc.data_ptr(), sc * H, H, T, _lib.dtype_code(x.dtype),
+                                                _lib.stream_ptr())
+            _lib.check(rc, "indexer_relu_bwd")
+            dq[b, s0:s1] = torch.matmul(dx, kb).view(sc, H, D)
+            dk[b] += torch.matmul(dx.t(), qc).float()
+            dw[b, s0:s1] = dwc.view(sc, H)
+    return dq, dw, dk
 
 
 def indexer_scores_from_selection(q_idx, weights, k_idx, idx, vals, chunk: int = 256):
@@ -234,7 +288,7 @@ def _sparse_chunk(q, kv, v, idx, scale, want_lse=True):
     return out, p.detach().sum(0), lse
 
 
-KERNEL_RATIO = 4  # key streams longer than this many times top-k go to the gathered-tile tensor-core kernel
+KERNEL_RATIO = 4  # key streams at least this many times top-k go to the gathered-tile tensor-core kernel
 
 
 def _values_are_key_prefix(k: torch.Tensor, v: torch.Tensor) -> bool:
@@ -267,12 +321,12 @@ def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256, want_lse:
                          values_are_key_prefix: bool | None = None):
     """q [B,H,S,Dq], k [B,1,T,Dq], v [B,1,T,Dv], idx [B,S,topk] → (out [B,H,S,Dv], teacher [B,S,topk], lse [B,H,S]).
 
-    Long key streams (more than `KERNEL_RATIO` x top-k keys) in the MLA absorb layout run on the gathered-tile
+    Long key streams (at least `KERNEL_RATIO` x top-k keys) in the MLA absorb layout run on the gathered-tile
     tensor-core kernel (`titan_b200.ops.sparse_mla`): work and memory O(S * top-k).  ``values_are_key_prefix`` says
     that ``v`` is the latent part of ``k`` (None = check a few rows)."""
     B, H, S, _ = q.shape
     T, dv = k.shape[2], v.shape[-1]
-    if T > KERNEL_RATIO * idx.shape[-1] and q.is_cuda:
+    if T >= KERNEL_RATIO * idx.shape[-1] and q.is_cuda:
         from titan_b200.ops.sparse_mla import sparse_mla_supported
 
         if sparse_mla_supported(q[0].transpose(0, 1), k[0, 0], F.pad(idx[0], (0, (-idx.shape[-1]) % 128)), dv):

@@ -227,20 +227,45 @@ def grad_slots(group, nbytes: int) -> _Slots:
     return _slots(group, "grad", nbytes, CH_GRAD_READY, CH_GRAD_DONE)
 
 
-def reduce_scatter_slot(slot, numel: int, in_dtype: torch.dtype, out: torch.Tensor, scale: float) -> None:
+def reduce_scatter_slot(slot, numel: int, in_dtype: torch.dtype, out: torch.Tensor, scale: float,
+                        nvls: bool = False) -> None:
     """Reduce-scatter a bucket that already sits in a slot from `grad_slots().acquire()`: ``slot`` is
     ``(slots, index, byte offset)``.  Runs on the current stream: publish "my bucket is complete", wait for every
-    peer's, reduce this rank's chunk from all buckets into ``out``, then mark the slot as read."""
+    peer's, reduce this rank's chunk from all buckets into ``out``, then mark the slot as read.  ``nvls``: let the
+    NVSwitch add the ranks' buckets (`multimem.ld_reduce` through the multicast address) when the fabric offers it."""
     slots, index, off = slot
     ws = slots.ws
     epoch = ws.next_epoch(CH_GRAD_READY)
     ws.signal(CH_GRAD_READY, epoch)
     ws.wait(CH_GRAD_READY, epoch)
-    rc = _lib.lib().tb_castscale_rs(ws.ptr_array(off), out.data_ptr(), numel // ws.world, ws.rank, ws.world,
-                                    float(scale), _lib.dtype_code(in_dtype), _lib.dtype_code(out.dtype),
-                                    _lib.stream_ptr())
-    _lib.check(rc, "castscale_rs")
+    chunk = numel // ws.world
+    esz = torch.empty((), dtype=in_dtype).element_size()
+    mc = ws.multicast_ptr(off) if nvls else 0
+    if mc and chunk % (16 // esz) == 0:
+        _declare_nvls()
+        rc = _lib.lib().tb_castscale_rs_nvls(mc + ws.rank * chunk * esz, out.data_ptr(), chunk, float(scale),
+                                             _lib.dtype_code(in_dtype), _lib.dtype_code(out.dtype),
+                                             _lib.stream_ptr())
+        _lib.check(rc, "castscale_rs_nvls")
+    else:
+        rc = _lib.lib().tb_castscale_rs(ws.ptr_array(off), out.data_ptr(), chunk, ws.rank, ws.world,
+                                        float(scale), _lib.dtype_code(in_dtype), _lib.dtype_code(out.dtype),
+                                        _lib.stream_ptr())
+        _lib.check(rc, "castscale_rs")
     slots.release(index)
+
+
+_NVLS_DECLARED = False
+
+
+def _declare_nvls() -> None:
+    global _NVLS_DECLARED
+    if not _NVLS_DECLARED:
+        import ctypes
+
+        P, LL, I, Fl = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+        _lib.declare("tb_castscale_rs_nvls", [P, P, LL, Fl, I, I, P])
+        _NVLS_DECLARED = True
 
 
 def castscale_reduce_scatter(bucket: torch.Tensor, scale: float, out_dtype: torch.dtype = torch.float32,

@@ -232,9 +232,42 @@ _define("flash_attention_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor ls
         "Tensor? seq_start=None) -> (Tensor, Tensor, Tensor)", _flash_bwd_cuda, _flash_bwd_fake)
 
 
-# Ops whose outputs selective activation checkpointing keeps (contractions: recomputing them costs real FLOPs).
+# ---------------------------------------------------------------------------------------------- sparse attention
+def _sparse_mla_fwd_cuda(q, kv, idx, scale, dv, sink=None):
+    from titan_b200.ops.sparse_mla import sparse_mla_forward
+
+    return sparse_mla_forward(q, kv, idx, scale, dv, sink)
+
+
+def _sparse_mla_fwd_fake(q, kv, idx, scale, dv, sink=None):
+    s, h, _ = q.shape
+    return (q.new_empty((s, h, dv)), q.new_empty((s, h), dtype=torch.float32),
+            q.new_empty((s, idx.shape[1]), dtype=torch.float32))
+
+
+_define("sparse_mla_fwd(Tensor q, Tensor kv, Tensor idx, float scale, int dv, Tensor? sink=None) -> "
+        "(Tensor, Tensor, Tensor)", _sparse_mla_fwd_cuda, _sparse_mla_fwd_fake)
+
+
+def _indexer_topk_cuda(q_idx, weights, k_idx, topk, pos_offset=0, ratio=1):
+    from titan_b200.ops.dsa import _indexer_topk_launch
+
+    return _indexer_topk_launch(q_idx, weights, k_idx, topk, pos_offset, ratio)
+
+
+def _indexer_topk_fake(q_idx, weights, k_idx, topk, pos_offset=0, ratio=1):
+    b, s = q_idx.shape[0], q_idx.shape[1]
+    return q_idx.new_empty((b, s, topk), dtype=torch.int32), q_idx.new_empty((b, s, topk), dtype=torch.float32)
+
+
+_define("indexer_topk(Tensor q_idx, Tensor weights, Tensor k_idx, int topk, int pos_offset=0, int ratio=1) -> "
+        "(Tensor, Tensor)", _indexer_topk_cuda, _indexer_topk_fake)
+
+
+# Ops whose outputs selective activation checkpointing keeps (contractions and the sparse-attention selection:
+# recomputing them costs real FLOPs, their outputs are small next to what they read).
 CONTRACTION_OPS = (ops.gemm.default, ops.grouped_gemm_m.default, ops.grouped_gemm_k.default,
-                   ops.flash_attention_fwd.default)
+                   ops.flash_attention_fwd.default, ops.sparse_mla_fwd.default, ops.indexer_topk.default)
 
 
 def _register_with_sac() -> None:

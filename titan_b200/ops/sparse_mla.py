@@ -83,7 +83,9 @@ class SparseMLAFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, kv, idx, scale, dv, sink, chunk):
-        out, lse, teacher = sparse_mla_forward(q, kv, idx, scale, dv, sink)
+        from titan_b200.ops.registry import ops
+
+        out, lse, teacher = ops.sparse_mla_fwd(q, kv, idx.to(torch.int32), float(scale), dv, sink)
         ctx.save_for_backward(q, kv, idx, lse, out, sink if sink is not None else torch.empty(0, device=q.device))
         ctx.scale, ctx.dv, ctx.chunk, ctx.has_sink = scale, dv, chunk, sink is not None
         ctx.mark_non_differentiable(teacher, lse)

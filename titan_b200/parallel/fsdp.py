@@ -127,7 +127,8 @@ def apply_fsdp(
         from titan_b200.parallel.fsdp_comm import install_peer_all_gather
 
         if peer_reduce_scatter_wanted(reduce_scatter, dp_mesh, dp_mesh.device_type):
-            model._peer_reduce_scatter = install_peer_reduce_scatter(model, dp_mesh, wire_dtype=param_dtype)
+            model._peer_reduce_scatter = install_peer_reduce_scatter(model, dp_mesh, wire_dtype=param_dtype,
+                                                                     nvls=reduce_scatter == "nvls")
         if peer_reduce_scatter_wanted(all_gather, dp_mesh, dp_mesh.device_type):
             model._peer_all_gather = install_peer_all_gather(model, dp_mesh, param_dtype=param_dtype)
     return model

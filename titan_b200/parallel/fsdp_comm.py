@@ -44,10 +44,11 @@ __all__ = ["PeerMemoryReduceScatter", "PeerMemoryAllGather", "install_peer_reduc
 
 
 class PeerMemoryReduceScatter(ReduceScatter):
-    def __init__(self, group, wire_dtype: torch.dtype = torch.bfloat16, reserve_numel: int = 0):
+    def __init__(self, group, wire_dtype: torch.dtype = torch.bfloat16, reserve_numel: int = 0, nvls: bool = False):
         self.group = group
         self.world = dist.get_world_size(group)
         self.wire_dtype = wire_dtype
+        self.nvls = nvls               # sum inside the NVSwitch (multimem.ld_reduce) instead of one load per peer
         self._bucket_next = True       # FSDP2 allocates the bucket first, then the output, per reduction
         self._slot = None              # (slots, slot index, byte offset) of the bucket handed out last
         self.calls = 0                 # reductions done by the peer-memory kernel (tests, bench records)
@@ -95,7 +96,8 @@ class PeerMemoryReduceScatter(ReduceScatter):
         if kernel_ok:
             from titan_b200.ops import fused_comm
 
-            fused_comm.reduce_scatter_slot(slot, input_tensor.numel(), input_tensor.dtype, output_tensor, scale)
+            fused_comm.reduce_scatter_slot(slot, input_tensor.numel(), input_tensor.dtype, output_tensor, scale,
+                                           nvls=self.nvls)
             self.calls += 1
             return None
         if slot is not None:
@@ -208,9 +210,9 @@ def peer_reduce_scatter_wanted(setting: str, dp_mesh, device_type: str) -> bool:
     one_node = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1"))) == \
         int(os.environ.get("WORLD_SIZE", "1"))
     ok = device_type == "cuda" and 2 <= n <= 8 and one_node
-    if setting == "peer_memory" and not ok and device_type == "cuda":
-        raise ValueError("fsdp_reduce_scatter=peer_memory needs an FSDP group of 2..8 GPUs on one node")
-    return ok or setting == "peer_memory"
+    if setting in ("peer_memory", "nvls") and not ok and device_type == "cuda":
+        raise ValueError(f"fsdp_reduce_scatter={setting} needs an FSDP group of 2..8 GPUs on one node")
+    return ok or setting in ("peer_memory", "nvls")
 
 
 def install_peer_all_gather(model: nn.Module, dp_mesh, param_dtype: torch.dtype) -> PeerMemoryAllGather | None:
@@ -235,7 +237,8 @@ def install_peer_all_gather(model: nn.Module, dp_mesh, param_dtype: torch.dtype)
     return comm
 
 
-def install_peer_reduce_scatter(model: nn.Module, dp_mesh, wire_dtype: torch.dtype) -> PeerMemoryReduceScatter | None:
+def install_peer_reduce_scatter(model: nn.Module, dp_mesh, wire_dtype: torch.dtype,
+                                nvls: bool = False) -> PeerMemoryReduceScatter | None:
     """Give every FSDP module of `model` whose shard group is ``dp_mesh``'s shard axis the peer-memory hook."""
     from torch.distributed.fsdp import FSDPModule
 
@@ -244,7 +247,7 @@ def install_peer_reduce_scatter(model: nn.Module, dp_mesh, wire_dtype: torch.dty
     world = shard_mesh.size()
     if world < 2:
         return None
-    comm = PeerMemoryReduceScatter(group, wire_dtype, reserve_numel=max_bucket_numel(model, world))
+    comm = PeerMemoryReduceScatter(group, wire_dtype, reserve_numel=max_bucket_numel(model, world), nvls=nvls)
     for m in model.modules():
         if not isinstance(m, FSDPModule):
             continue

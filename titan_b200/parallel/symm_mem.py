@@ -52,6 +52,10 @@ class SymmWorkspace:
         if off < 0 or off + self.nbytes > int(self.handle.buffer_size):
             raise RuntimeError("symmetric buffer does not lie inside the rendezvoused allocation")
         self.ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
+        # multicast address of the same bytes on every rank (0 when the fabric has no NVLink multicast): loads through
+        # it with `multimem.ld_reduce` return the sum over the ranks, computed inside the switch
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_base = mc + off if mc else 0
         self.flags = self.buf[:FLAG_BYTES].view(torch.int32)
         self._epochs: dict[int, int] = {}
         dist.barrier(group=group)
@@ -59,6 +63,10 @@ class SymmWorkspace:
     # ---- addressing
     def data_ptr(self, rank: int, byte_offset: int = 0) -> int:
         return self.ptrs[rank] + FLAG_BYTES + byte_offset
+
+    def multicast_ptr(self, byte_offset: int = 0) -> int:
+        """Multicast address of data byte ``byte_offset`` (0 = no multicast support)."""
+        return self.mc_base + FLAG_BYTES + byte_offset if self.mc_base else 0
 
     def ptr_array(self, byte_offset: int = 0):
         return (ctypes.c_void_p * self.world)(*[self.data_ptr(r, byte_offset) for r in range(self.world)])
