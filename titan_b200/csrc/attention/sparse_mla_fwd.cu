@@ -21,7 +21,10 @@
 //
 // Two passes over the key blocks: the first finds the exact row maxima and sums, the second computes the
 // probabilities against them, so the head-summed probabilities (the indexer's teacher) are exact and O^T never needs
-// rescaling.  The gather is repeated in the second pass.
+// rescaling.  When the logits of all blocks fit in tensor memory next to O^T (K / 128 + DV / 128 blocks of HG columns
+// <= 512 columns: top-2048 with 16 heads does) the first pass leaves them there, and the second pass only gathers the
+// value columns again: its softmax runs on the stashed logits WHILE the copies are in flight and no logit is computed
+// twice.  Otherwise the second pass repeats gather and logits.
 //
 // Every wait is bounded; a failure sets the status word and the CTA drains to the common exit.
 //
@@ -36,7 +39,7 @@ constexpr int BKEYS = 128;          // keys per block = M of both MMAs
 constexpr int CHUNK_BYTES = 16384;  // one [128 rows x 64 columns] bf16 chunk of the gathered tile
 constexpr int NTHREADS = 256;
 constexpr int MAX_HG = 32;          // heads per CTA
-constexpr uint32_t TMEM_COLS = 256; // S^T (HG) + O^T (DV/128 * HG) <= 5 * 32
+constexpr uint32_t TMEM_COLS = 512; // O^T (DV/128 * HG) + S^T (HG, or K/128 * HG when the logits are stashed)
 
 struct SmlaParams {
   const __nv_bfloat16* q;
@@ -51,6 +54,7 @@ struct SmlaParams {
   int hg;              // heads per CTA (16 or 32), H % hg == 0
   float scale_log2;    // softmax scale * log2(e)
   int teacher_atomic;  // several head groups add into teacher
+  int stash;           // the logits of all key blocks stay in tensor memory between the passes
   int* status;
 };
 
@@ -113,8 +117,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t tmem_s = tmem;                  // S^T: HG columns
-  const uint32_t tmem_o = tmem + HG;             // O^T: dvb x HG columns
+  const uint32_t tmem_o = tmem;                  // O^T: dvb x HG columns
+  const uint32_t tmem_s0 = tmem + dvb * HG;      // S^T: HG columns per key block (one block unless stashed)
+  const int vchunks = p.dv / 64;
   const uint32_t idesc_s = make_idesc_f16(128, HG, true, false, false);   // K tile K-major, Q K-major
   const uint32_t idesc_o = make_idesc_f16(128, HG, true, true, false);    // V tile MN-major, P K-major
   uint32_t mma_phase = 0;
@@ -141,44 +146,51 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
 
     for (int pass = 0; pass < 2; ++pass) {
       for (int jb = 0; jb < nblocks; ++jb) {
-        // ---- gather the selected rows of this block (all threads)
+        const bool reuse = pass == 1 && p.stash;     // logits of this block are in tensor memory already
+        const uint32_t tmem_s = tmem_s0 + (p.stash ? jb * HG : 0);
+        // ---- gather the selected rows of this block (all threads); with stashed logits only the value columns
         if (tid < BKEYS) {
           const int row = irow[jb * BKEYS + tid];
           ctl->valid[tid] = (row >= 0 && row < p.T) ? row : -1;
         }
         __syncthreads();   // valid[] visible; the previous block's MMAs have finished with sK / sP (waited below)
-        for (int i = tid; i < BKEYS * qchunks * 8; i += NTHREADS) {
-          const int kr = i / (qchunks * 8), c = i - kr * (qchunks * 8);
-          const int row = ctl->valid[kr];
-          const uint32_t dst = smem_u32(sK) + (c >> 3) * CHUNK_BYTES + kr * 128 + (((c & 7) ^ (kr & 7)) << 4);
-          const __nv_bfloat16* src = row >= 0 ? p.kv + (long long)row * p.dq + c * 8 : p.kv;
-          cp_async16(dst, src, row >= 0 ? 16 : 0);   // an empty slot becomes a zero row
-        }
-        cp_async_wait_all();
-        fence_proxy_async();   // generic-proxy writes -> visible to the tensor cores (async proxy)
-        __syncthreads();
-
-        // ---- S^T = K_tile * Q^T
-        if (tid == 0) {
-          tc_fence_after();
-          const uint32_t ka = smem_u32(sK), qa = smem_u32(sQ);
-          for (int c = 0; c < qchunks; ++c) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint64_t da = make_smem_desc(ka + c * CHUNK_BYTES + k * 32, 16, 1024, 2);
-              const uint64_t db = make_smem_desc(qa + c * (HG * 128) + k * 32, 16, 1024, 2);
-              umma_f16(tmem_s, da, db, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
-            }
+        {
+          const int nch = reuse ? vchunks : qchunks;
+          for (int i = tid; i < BKEYS * nch * 8; i += NTHREADS) {
+            const int kr = i / (nch * 8), c = i - kr * (nch * 8);
+            const int row = ctl->valid[kr];
+            const uint32_t dst = smem_u32(sK) + (c >> 3) * CHUNK_BYTES + kr * 128 + (((c & 7) ^ (kr & 7)) << 4);
+            const __nv_bfloat16* src = row >= 0 ? p.kv + (long long)row * p.dq + c * 8 : p.kv;
+            cp_async16(dst, src, row >= 0 ? 16 : 0);   // an empty slot becomes a zero row
           }
-          umma_commit(&ctl->mma_bar);
         }
-        if (!mbar_wait(&ctl->mma_bar, mma_phase, abort_flag)) {
-          if (tid == 0 && *abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL); }
+        if (!reuse) {
+          cp_async_wait_all();
+          fence_proxy_async();   // generic-proxy writes -> visible to the tensor cores (async proxy)
+          __syncthreads();
+
+          // ---- S^T = K_tile * Q^T
+          if (tid == 0) {
+            tc_fence_after();
+            const uint32_t ka = smem_u32(sK), qa = smem_u32(sQ);
+            for (int c = 0; c < qchunks; ++c) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t da = make_smem_desc(ka + c * CHUNK_BYTES + k * 32, 16, 1024, 2);
+                const uint64_t db = make_smem_desc(qa + c * (HG * 128) + k * 32, 16, 1024, 2);
+                umma_f16(tmem_s, da, db, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+              }
+            }
+            umma_commit(&ctl->mma_bar);
+          }
+          if (!mbar_wait(&ctl->mma_bar, mma_phase, abort_flag)) {
+            if (tid == 0 && *abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL); }
+          }
+          mma_phase ^= 1;
+          tc_fence_after();
+          __syncthreads();
+          if (*abort_flag) break;
         }
-        mma_phase ^= 1;
-        tc_fence_after();
-        __syncthreads();
-        if (*abort_flag) break;
 
         // ---- softmax along the lanes (threads 0..127, one key each)
         float x[HG];
@@ -239,6 +251,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
               if (p.teacher_atomic) atomicAdd(dst, t); else *dst = t;
             }
           }
+          cp_async_wait_all();   // with stashed logits the value tile was travelling during the softmax above
           fence_proxy_async();
           tc_fence_before();
           __syncthreads();
@@ -337,6 +350,7 @@ TB_API int tb_sparse_mla_fwd(const void* q, const void* kv, const int* idx, void
   p.hg = (H % 32 == 0) ? 32 : 16;
   p.teacher_atomic = (H / p.hg) > 1;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.stash = ((K / BKEYS) + dv / 128) * p.hg <= (int)TMEM_COLS ? 1 : 0;
   p.status = status;
   return p.hg == 32 ? launch<32>(p, st) : launch<16>(p, st);
 }
