@@ -44,7 +44,7 @@ def test_scatter_places_valid_patches_in_order_and_validates_count():
     out = scatter_visual_embeddings(h, tok, vis, mask, 9)
     assert out[0, 1].tolist() == [1, 2] and out[0, 2].tolist() == [3, 4] and out[0, 4].tolist() == [5, 6]
     assert out[0, 0].abs().sum() == 0
-    with pytest.raises(ValueError, match="Different number"):
+    with pytest.raises(ValueError, match="image placeholder tokens"):
         scatter_visual_embeddings(h, tok, vis, torch.ones(2, 2, dtype=torch.bool), 9)
 
 

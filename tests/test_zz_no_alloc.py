@@ -7,6 +7,9 @@ whose partial-sum scratch is a fixed array inside the library image.  This test 
 its exported C symbol (plain ctypes, as such a host would) and checks it against the regular entry point,
 which uses a caller-provided scratch buffer, on two consecutive calls: the second call sees the scratch
 contents left by the first and must still be right.
+
+The oracle here is the regular entry point on purpose (both must agree bit for bit); the regular entry point itself is
+pinned against an fp32 PyTorch statement of RMSNorm backward in `tests/test_kernels_elementwise_gpu.py`.
 """
 
 import ctypes
