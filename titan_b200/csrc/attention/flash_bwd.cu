@@ -52,18 +52,27 @@ struct FbParams {
   int* status;
 };
 
-struct __align__(8) Ctl {
+struct __align__(16) Ctl {
+  float lse2[BLK], delta[BLK];   // 16-byte aligned: read four at a time
+  int qstart[BLK];
   uint64_t kv_bar, q_bar, mma_bar;
   uint32_t tmem_slot;
   int abort_flag;
-  float lse2[BLK], delta[BLK];
-  int qstart[BLK];
 };
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float4 ld_shared_f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+// VARLEN: packed documents (`seq_start` given); the dense instance carries no document-mask code.
+template <bool VARLEN>
 __global__ void __launch_bounds__(NTHREADS, 1) flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_do,
                                                                 const __grid_constant__ CUtensorMap tm_k,
@@ -110,7 +119,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_bwd_kernel(const __grid_con
   // the query blocks this key block takes part in: i = j .. i_end - 1 (documents start at non-decreasing positions,
   // so the first block whose first query's document starts after the last key of this block ends the walk)
   int i_end = nblk;
-  if (p.seq_start != nullptr) {
+  if (VARLEN) {
     for (int i = j + 1; i < nblk; ++i)
       if (p.seq_start[(long long)b * p.S + i * BLK] > j * BLK + BLK - 1) { i_end = i; break; }
   }
@@ -131,7 +140,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_bwd_kernel(const __grid_con
     const long long o = ((long long)b * p.H + h) * p.S + i * BLK + tid;
     ctl->lse2[tid] = p.lse[o] * 1.4426950408889634f;
     ctl->delta[tid] = p.delta[o];
-    ctl->qstart[tid] = p.seq_start != nullptr ? p.seq_start[(long long)b * p.S + i * BLK + tid] : 0;
+    if (VARLEN) ctl->qstart[tid] = p.seq_start[(long long)b * p.S + i * BLK + tid];
   };
 
   if (tid == 0) {
@@ -187,10 +196,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_bwd_kernel(const __grid_con
     __syncthreads();   // also: the statistics of this iteration are visible
     if (*abort_flag) break;
 
-    // ---- P^T and dS^T: thread = (key r, 64 queries of its half), 32 queries per pass
+    // ---- P^T and dS^T: thread = (key r, 64 queries of its half), 32 queries per pass.  Masks only where they can
+    //      bite: the causal one on the diagonal block, the document one when the batch is packed.
     {
       const int kpos = j * BLK + r;
       const int qpos0 = i * BLK;
+      const bool diag = i == j;
 #pragma unroll 1
       for (int pass = 0; pass < 2; ++pass) {
         const int c0 = half * 64 + pass * 32;          // first query column of this pass
@@ -200,18 +211,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_bwd_kernel(const __grid_con
         tmem_ld_wait();
         uint32_t pp[16], ds[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float pv[2], dsv[2];
+        for (int e4 = 0; e4 < 8; ++e4) {               // four queries per step: statistics read as float4
+          const float4 l4 = ld_shared_f4(&ctl->lse2[c0 + 4 * e4]);
+          const float4 d4 = ld_shared_f4(&ctl->delta[c0 + 4 * e4]);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dsv[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int qc = c0 + 2 * e + u;
-            const bool ok = (qpos0 + qc >= kpos) && (kpos >= ctl->qstart[qc]);
-            const float pr = ok ? exp2f(fmaf(__uint_as_float(sv[2 * e + u]), p.scale_log2, -ctl->lse2[qc])) : 0.f;
+          for (int u = 0; u < 4; ++u) {
+            const int qc = c0 + 4 * e4 + u;
+            float pr = ex2_approx(fmaf(__uint_as_float(sv[4 * e4 + u]), p.scale_log2, -lv[u]));
+            if (diag && qpos0 + qc < kpos) pr = 0.f;
+            if (VARLEN && kpos < ctl->qstart[qc]) pr = 0.f;
             pv[u] = pr;
-            dsv[u] = pr * (__uint_as_float(dv[2 * e + u]) - ctl->delta[qc]) * p.scale;
+            dsv[u] = pr * (__uint_as_float(dv[4 * e4 + u]) - dl[u]) * p.scale;
           }
-          pp[e] = pack_bf16x2(pv[0], pv[1]);
-          ds[e] = pack_bf16x2(dsv[0], dsv[1]);
+          pp[2 * e4] = pack_bf16x2(pv[0], pv[1]);
+          pp[2 * e4 + 1] = pack_bf16x2(pv[2], pv[3]);
+          ds[2 * e4] = pack_bf16x2(dsv[0], dsv[1]);
+          ds[2 * e4 + 1] = pack_bf16x2(dsv[2], dsv[3]);
         }
         // row r of the [keys x queries] operand tile: box c0 / 64, 16-byte slots ((c0 % 64) / 8 + s) ^ (r & 7)
         const uint32_t rowoff = (uint32_t)(c0 >> 6) * BOX + (uint32_t)r * 128;
@@ -336,9 +353,14 @@ TB_API int tb_flash_attn_bwd(const void* q, const void* k, const void* v, const 
   p.dQ = dq32;
   p.status = status;
   const int smem = 6 * TILE + (int)sizeof(Ctl) + 1024;
-  TB_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(S / BLK, Hkv, B);
-  flash_bwd_kernel<<<grid, NTHREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  if (seq_start != nullptr) {
+    TB_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    flash_bwd_kernel<true><<<grid, NTHREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  } else {
+    TB_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    flash_bwd_kernel<false><<<grid, NTHREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  }
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

@@ -7,10 +7,10 @@
 //   warp 1      MMA issuer (one thread): S_j = Q K_j^T  (M128 N128 K128, both operands K-major)
 //                                        PV_j = P_j V_j (A = P_j from shared memory, B = V_j MN-major)
 //               S_{j+1} is issued before PV_j so the tensor cores work while the softmax warps handle block j
-//   warps 2..17 softmax, FOUR threads per query row (TMEM lane = row; warps w, w+4, w+8, w+12 share a lane quarter and
-//               take 32 of the 128 columns each): one read of S_j from tensor memory into registers, row maximum
-//               (parts exchanged through shared memory), exp2 / row sum / bf16 P_j into the swizzled A-operand
-//               layout, then fold PV_{j-1} into the running output kept in REGISTERS (32 fp32 per thread):
+//   warps 2..9  softmax, TWO threads per query row (TMEM lane = row; warps w and w+4 share a lane quarter and take
+//               64 of the 128 columns each): one read of S_j from tensor memory into registers, row maximum
+//               (halves exchanged through shared memory), exp2 / row sum / bf16 P_j into the swizzled A-operand
+//               layout, then fold PV_{j-1} into the running output kept in REGISTERS (64 fp32 per thread):
 //               O <- (O + PV_{j-1}) * 2^(m_{j-1}-m_j)
 // Tensor memory: S double-buffered (2 x 128 columns) + PV double-buffered (2 x 128 columns) = all 512 columns.
 // Shared memory: Q 32 KB + K 2 x 32 KB + V 2 x 32 KB + P 2 x 32 KB = 224 KB, + 2 KB exchange area and barriers.
@@ -29,8 +29,7 @@ constexpr int D = 128;        // head dim
 constexpr int BQ = 128;       // query rows per CTA
 constexpr int BK = 128;       // keys per block
 constexpr int TILE = 32768;   // bytes of a [128 x 128] bf16 tile (two 16 KB boxes of 64 columns)
-constexpr int NSPLIT = 4;                      // softmax threads per query row (each takes BK / NSPLIT columns)
-constexpr int NTHREADS = 32 * (2 + 4 * NSPLIT);  // TMA warp, MMA warp, 4 * NSPLIT softmax warps
+constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 softmax warps
 constexpr uint32_t TMEM_COLS = 512;
 
 struct FaParams {
@@ -48,7 +47,7 @@ struct __align__(8) Bars {
   uint64_t s_full[2], s_empty[2], p_ready[2], o_full[2], o_empty[2];
   uint32_t tmem_slot;
   int abort_flag;
-  float xchg[NSPLIT][BQ];  // [column part][row]: row maxima (and, at the end, row sums) of the parts of a row
+  float xchg[2][2][BQ];  // [parity][column half][row]: row maxima (and, at the end, row sums) of the two halves
 };
 
 __device__ __forceinline__ void fail(Bars* b, int* status, int code) {
@@ -95,9 +94,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1);
       mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 4 * NSPLIT);
-      mbar_init(&bars->p_ready[i], 4 * NSPLIT);
-      mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4 * NSPLIT);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 8);
+      mbar_init(&bars->p_ready[i], 8);
+      mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 8);
     }
     bars->abort_flag = 0;
     fence_barrier_init();
@@ -185,87 +184,78 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax + output (warps 2 .. 2 + 4*NSPLIT)
-    constexpr int HC = BK / NSPLIT;       // columns per thread (32)
-    static_assert(HC == 32, "one tcgen05.ld of 32 columns per thread and block");
+    // ---------------------------------------------------------------- softmax + output (warps 2..9)
+    constexpr int HC = BK / 2;            // columns per thread
     const int quarter = warp & 3;         // TMEM lane quarter this warp may read
-    const int part = (warp - 2) >> 2;     // which HC columns of S / PV / O
+    const int half = (warp - 2) >> 2;     // which 64 columns of S / PV / O
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    const int group_bar = 2 + quarter;    // named barrier of the NSPLIT warps that share this lane quarter
-    auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(group_bar), "n"(32 * NSPLIT) : "memory"); };
+    const int pair_bar = 2 + quarter;     // named barrier of the two warps that share this lane quarter
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
     auto ex2 = [](float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; };
-    // exchange of one value per part of a row: write, barrier, read all parts, barrier (the second barrier lets the
-    // area be reused by the next exchange).  NaN marks a thread that gave up; then the whole group leaves together.
-    auto exchange = [&](float mine, bool combine_max, bool& all_ok) {
-      bars->xchg[part][row] = mine;
-      group_sync();
-      float acc = combine_max ? -INFINITY : 0.f;
-#pragma unroll
-      for (int q = 0; q < NSPLIT; ++q) {
-        const float v = bars->xchg[q][row];
-        if (v != v) all_ok = false;
-        acc = combine_max ? fmaxf(acc, v) : acc + v;
-      }
-      group_sync();
-      return acc;
-    };
-    // keys before the start of this row's document are masked: key column c of block j is allowed from `lo` on
-    const int row_start = VARLEN ? p.seq_start[q_row0 + row] : 0;
     float m_run = -INFINITY, l_run = 0.f;
     float o[HC];
 #pragma unroll
     for (int i = 0; i < HC; ++i) o[i] = 0.f;
-    // A thread that gives up (a bounded wait ran out) must not leave its partners alone at the group barrier: it
-    // keeps walking to the next exchange, publishes NaN there, and all of them leave right after it.
+    // A thread that gives up (a bounded wait ran out) must not leave its partner alone at the pair barrier: it keeps
+    // walking to the next exchange, publishes NaN there, and both leave together right after that barrier.
     bool ok = true;
+    // keys before the start of this row's document are masked: key column c of block j is allowed from `lo` on
+    const int row_start = VARLEN ? p.seq_start[q_row0 + row] : 0;
     for (int j = 0; j < nblk; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       if (ok && !mbar_wait(&bars->s_full[st], ph, abort_flag)) { fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL); ok = false; }
       tc_fence_after();
-      const uint32_t s_addr = lane_base + st * BK + part * HC;
+      const uint32_t s_addr = lane_base + st * BK + half * HC;
       const bool diag = j == nblk - 1;
       const int lo = VARLEN ? row_start - (j0 + j) * BK : 0;   // first allowed column of this block (<= 0: all)
       const bool edge = diag || (VARLEN && lo > 0);
-      uint32_t r[32];
+      uint32_t r[2][32];
       float mx = -INFINITY;
       if (ok) {
-        tmem_ld_32x32(s_addr, r);
+        tmem_ld_32x32(s_addr, r[0]);
+        tmem_ld_32x32(s_addr + 32, r[1]);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (!edge || ((!diag || part * HC + i <= row) && (!VARLEN || part * HC + i >= lo)))
-            mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!edge || ((!diag || half * HC + c * 32 + i <= row) && (!VARLEN || half * HC + c * 32 + i >= lo)))
+              mx = fmaxf(mx, __uint_as_float(r[c][i]));
       }
-      bool all_ok = true;
-      const float row_max = exchange(ok ? mx : NAN, true, all_ok);
-      if (!ok || !all_ok) { ok = false; break; }
-      const float m_new = fmaxf(m_run, row_max * p.scale_log2);
+      bars->xchg[st][half][row] = ok ? mx : NAN;
+      pair_sync();
+      const float other = bars->xchg[st][half ^ 1][row];
+      if (!ok || other != other) { ok = false; break; }
+      const float m_new = fmaxf(m_run, fmaxf(mx, other) * p.scale_log2);
       // a row whose document starts after this block has seen no key yet: keep its state untouched
       const float alpha = (VARLEN && m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
-      // P = 2^(s' - m), row sum, bf16 into the swizzled K-major A-operand layout: this thread's 32 keys are 4 of the
-      // 8 sixteen-byte chunks of its row in one 64-key box
+      // P = 2^(s' - m), row sum, bf16 into the swizzled K-major A-operand layout (this thread's 64 keys = one box)
       float sum = 0.f;
-      const uint32_t prow = smem_u32(sP + st * TILE) + row * 128 + (part >> 1) * 16384;
-      uint32_t pk[16];
+      const uint32_t prow = smem_u32(sP + st * TILE) + row * 128 + half * 16384;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float p0 = ex2(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_new));
-        float p1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_new));
-        if (edge) {
-          if ((diag && part * HC + 2 * i > row) || (VARLEN && part * HC + 2 * i < lo)) p0 = 0.f;
-          if ((diag && part * HC + 2 * i + 1 > row) || (VARLEN && part * HC + 2 * i + 1 < lo)) p1 = 0.f;
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2(fmaf(__uint_as_float(r[c][2 * i]), p.scale_log2, -m_new));
+          float p1 = ex2(fmaf(__uint_as_float(r[c][2 * i + 1]), p.scale_log2, -m_new));
+          if (edge) {
+            const int col = half * HC + c * 32 + 2 * i;
+            if ((diag && col > row) || (VARLEN && col < lo)) p0 = 0.f;
+            if ((diag && col + 1 > row) || (VARLEN && col + 1 < lo)) p1 = 0.f;
+          }
+          sum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
         }
-        sum += p0 + p1;
-        pk[i] = pack_bf16x2(p0, p1);
-      }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t chunk = (uint32_t)((part & 1) * 4 + i) ^ (uint32_t)(row & 7);  // 128B swizzle
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16), "r"(pk[4 * i]),
-                     "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
-                     : "memory");
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t chunk = (uint32_t)(c * 4 + i) ^ (uint32_t)(row & 7);  // 128B swizzle
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16), "r"(pk[4 * i]),
+                       "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                       : "memory");
+        }
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
@@ -278,52 +268,65 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_fwd_kernel(const __grid_con
         if (!mbar_wait(&bars->o_full[ps], ((j - 1) >> 1) & 1, abort_flag)) {
           fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL);
           ok = false;
-          continue;  // to the next exchange (or the final one), where the group leaves together
+          continue;  // to the next exchange (or the final one), where the pair leaves together
         }
         tc_fence_after();
-        uint32_t pv[32];
-        tmem_ld_32x32(lane_base + 2 * BK + ps * D + part * HC, pv);
-        tmem_ld_wait();
+        const uint32_t o_addr = lane_base + 2 * BK + ps * D + half * HC;
+        const bool rescale = alpha != 1.f;  // the running maximum moved
+#pragma unroll
+        for (int c = 0; c < HC / 32; ++c) {
+          uint32_t pv[32];
+          tmem_ld_32x32(o_addr + c * 32, pv);
+          tmem_ld_wait();
+          if (rescale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(pv[i])) * alpha;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(pv[i]);
+          }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->o_empty[ps]);
-        if (alpha != 1.f) {  // the running maximum moved
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = (o[i] + __uint_as_float(pv[i])) * alpha;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] += __uint_as_float(pv[i]);
-        }
       }
     }
     {
-      // final exchange: partial row sums (all parts were scaled by the same factors, so they simply add up)
+      // final exchange: partial row sums (NaN = this half gave up)
+      const int xs = nblk & 1;
       const int ps = (nblk - 1) & 1;
       if (ok && !mbar_wait(&bars->o_full[ps], ((nblk - 1) >> 1) & 1, abort_flag)) {
         fail(bars, p.status, TB_ERR_WAIT_TMEM_FULL);
         ok = false;
       }
-      bool all_ok = true;
-      const float l_tot = exchange(ok ? l_run : NAN, false, all_ok);
-      if (ok && all_ok) {
+      bars->xchg[xs][half][row] = ok ? l_run : NAN;
+      pair_sync();
+      const float l_other = bars->xchg[xs][half ^ 1][row];
+      if (ok && l_other == l_other) {
         tc_fence_after();
+        const float l_tot = l_run + l_other;
+        const uint32_t o_addr = lane_base + 2 * BK + ps * D + half * HC;
         const float inv = 1.f / l_tot;
-        __nv_bfloat16* dst = p.O + ((size_t)(q_row0 + row) * p.H + h) * D + part * HC;
-        uint32_t r[32];
-        tmem_ld_32x32(lane_base + 2 * BK + ps * D + part * HC, r);
-        tmem_ld_wait();
+        __nv_bfloat16* dst = p.O + ((size_t)(q_row0 + row) * p.H + h) * D + half * HC;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 v;
-          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+        for (int c = 0; c < HC / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = i * 8 + e * 2;
-            w[e] = pack_bf16x2((o[col] + __uint_as_float(r[col])) * inv, (o[col + 1] + __uint_as_float(r[col + 1])) * inv);
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int col = c * 32 + i * 8 + e * 2;
+              w[e] = pack_bf16x2((o[col] + __uint_as_float(r[i * 8 + e * 2])) * inv,
+                                 (o[col + 1] + __uint_as_float(r[i * 8 + e * 2 + 1])) * inv);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = v;
           }
-          *reinterpret_cast<uint4*>(dst + i * 8) = v;
         }
-        if (p.LSE != nullptr && part == 0)
+        if (p.LSE != nullptr && half == 0)
           p.LSE[((size_t)b * p.H + h) * p.S + qb * BQ + row] = (m_run + log2f(l_tot)) * 0.6931471805599453f;
         tc_fence_before();
       }
@@ -354,14 +357,14 @@ TB_API int tb_flash_attn_fwd(const void* q, const void* k, const void* v, void* 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.O = (__nv_bfloat16*)out; p.LSE = lse; p.seq_start = seq_start; p.status = status;
   const size_t smem = 7 * TILE + sizeof(Bars);
-  dim3 grid(S / BQ, H, B);
   if (seq_start != nullptr) {
     TB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    flash_fwd_kernel<true><<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
   } else {
     TB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    flash_fwd_kernel<false><<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
   }
+  dim3 grid(S / BQ, H, B);
+  if (seq_start != nullptr) flash_fwd_kernel<true><<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
+  else flash_fwd_kernel<false><<<grid, NTHREADS, smem, st>>>(tq, tk, tv, p);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;

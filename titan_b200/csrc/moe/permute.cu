@@ -175,6 +175,30 @@ __global__ void __launch_bounds__(256) zero_pad_kernel(T* __restrict__ buf, cons
   }
 }
 
+// dst[row] = src[row] for the rows an expert received, 0 for its alignment padding; rows past the last expert's end
+// are not touched (nobody reads them).  One pass over the USED part of a capacity-sized buffer: the copy out of (or
+// into) a staging buffer and the padding fill in one launch, independent of the capacity factor.
+template <typename T>
+__global__ void __launch_bounds__(256) take_kernel(const T* __restrict__ src, T* __restrict__ dst,
+                                                   const int* __restrict__ starts, const int* __restrict__ totals,
+                                                   const int* __restrict__ offs, int dim, long long buf_rows) {
+  constexpr int V = Vec16<T>::N;
+  const int e = blockIdx.y;
+  const int r_begin = e > 0 ? offs[e - 1] : 0, r_end = offs[e];
+  const int v_begin = starts[e], v_end = starts[e] + totals[e];
+  const int per_row = dim / V;
+  Vec16<T> z;
+#pragma unroll
+  for (int i = 0; i < V; ++i) z.v[i] = from_f<T>(0.f);
+  const long long n = (long long)(r_end - r_begin) * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = r_begin + i / per_row;
+    if (row >= buf_rows) continue;
+    const long long o = row * dim + (i % per_row) * V;
+    st16(dst + o, (row >= v_begin && row < v_end) ? ld16(src + o) : z);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) combine_kernel(MoeBufs bufs, int nown, const int* __restrict__ dest,
                                                       const float* __restrict__ w, const T* __restrict__ base,
@@ -305,6 +329,21 @@ TB_API int tb_moe_zero_pad(void* buf, const int* starts, const int* totals, cons
   TB_MOE_DT(dtype, {
     if (dim % Vec16<T>::N) return TB_ERR_ARG;
     zero_pad_kernel<T><<<E, 256, 0, st>>>((T*)buf, starts, totals, offs, dim, buf_rows);
+  });
+  TB_CUDA_CHECK(cudaGetLastError());
+  tb_note_launch(1);
+  return 0;
+}
+
+// Copy the received rows of experts e in [0, E) from `src` to `dst` (both [buf_rows, dim]) and zero their alignment
+// padding [starts[e] + totals[e], offs[e]); see take_kernel.
+TB_API int tb_moe_take(const void* src, void* dst, const int* starts, const int* totals, const int* offs, int E,
+                       int dim, long long buf_rows, int dtype, cudaStream_t st) {
+  if (E <= 0) return 0;
+  TB_MOE_DT(dtype, {
+    if (dim % Vec16<T>::N) return TB_ERR_ARG;
+    take_kernel<T><<<dim3(148 * 2 / (E < 148 ? E : 148) + 1, E), 256, 0, st>>>((const T*)src, (T*)dst, starts, totals,
+                                                                              offs, dim, buf_rows);
   });
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);

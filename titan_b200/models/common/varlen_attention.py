@@ -2,9 +2,9 @@
 
 The trainer hands a batch of packed sequences with position ids that restart at every document.  `VarlenMetadata`
 turns them into cumulative document boundaries once per step; `VarlenAttention` then runs causal attention per
-document.  On a B200 (bf16, head dim 128, sequence a multiple of 128) that is ONE launch of the tcgen05 flash kernels
-with the per-token document start as the mask (`titan_b200.ops.flash_attention`, forward and backward); elsewhere one
-library SDPA call per document, which sees a plain causal problem and needs no ``S × S`` mask.  Under Ulysses context
+document.  On a B200 (bf16, head dim 128, sequence a multiple of 128, documents up to `KERNEL_MAX_DOCUMENT` tokens)
+that is ONE launch of the tcgen05 flash kernels with the per-token document start as the mask
+(`titan_b200.ops.flash_attention`, forward and backward); elsewhere one library SDPA call per document, which sees a plain causal problem and needs no ``S × S`` mask.  Under Ulysses context
 parallelism the core sees the full sequence with a slice of the heads, so the same metadata applies unchanged.
 
 Parity: `NPUVarlenAttention` (torchtitan_npu/models/common/npu_varlen_attention.py) used by the Qwen3 TND recipe
@@ -21,6 +21,11 @@ import torch.nn.functional as F
 from titan_b200.protocols.module import Module
 
 __all__ = ["VarlenMetadata", "VarlenAttention", "build_varlen_metadata"]
+
+# Packed batches of short documents go through ONE launch of the tcgen05 flash kernels (document masks inside); with
+# long documents the per-document library calls win (fewer launches to save, and the library's dense kernel is faster
+# per FLOP), so rows whose longest document exceeds this many tokens take the per-document path.
+KERNEL_MAX_DOCUMENT = 2048
 
 
 @dataclass
@@ -75,7 +80,8 @@ class VarlenAttention(Module):
             return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, scale=scale, enable_gqa=gqa)
         from titan_b200.ops.flash_attention import flash_attention, flash_attention_supported
 
-        if q.is_cuda and flash_attention_supported(q, k) and v.shape[-1] == q.shape[-1]:
+        if (q.is_cuda and flash_attention_supported(q, k) and v.shape[-1] == q.shape[-1]
+                and attn_mask.max_seqlen <= KERNEL_MAX_DOCUMENT):
             return flash_attention(q, k, v, scale=scale, seq_start=attn_mask.seq_start(q.device))
         rows = []
         for b, bounds in enumerate(attn_mask.cu_seqlens):

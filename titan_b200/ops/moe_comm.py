@@ -138,14 +138,35 @@ class EPContext:
         _lib.check(rc, "moe_pair_dot(ep)")
         return d
 
+    def _take(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        _declare_take()
+        rc = _lib.lib().tb_moe_take(src.data_ptr(), dst.data_ptr(), self.starts_local.data_ptr(),
+                                    self.totals_local.data_ptr(), self.offs_local.data_ptr(), self.e_local, self.D,
+                                    self.cap, _lib.dtype_code(self.dtype), _lib.stream_ptr())
+        _lib.check(rc, "moe_take(ep)")
+
     def take_local(self, view: torch.Tensor) -> torch.Tensor:
-        """Copy the received rows out of the staging buffer and zero the alignment padding."""
-        xp = view.clone()
-        rc = _lib.lib().tb_moe_zero_pad(xp.data_ptr(), self.starts_local.data_ptr(), self.totals_local.data_ptr(),
-                                        self.offs_local.data_ptr(), self.e_local, self.D, self.cap,
-                                        _lib.dtype_code(self.dtype), _lib.stream_ptr())
-        _lib.check(rc, "moe_zero_pad(ep)")
+        """The received rows out of the staging buffer, alignment padding zeroed, in ONE pass over the rows in use
+        (the buffer is sized for `capacity_factor` times the balanced load; rows past the last expert stay unwritten
+        and are never read)."""
+        xp = torch.empty_like(view)
+        self._take(view, xp)
         return xp
+
+    def publish(self, rows: torch.Tensor, view: torch.Tensor) -> None:
+        """Rows in use of a local expert-major tensor → the staging buffer the peers read from."""
+        self._take(rows.contiguous(), view)
+
+
+_TAKE_DECLARED = False
+
+
+def _declare_take() -> None:
+    global _TAKE_DECLARED
+    if not _TAKE_DECLARED:
+        P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        _lib.declare("tb_moe_take", [P, P, P, P, P, I, I, LL, I, P])
+        _TAKE_DECLARED = True
 
 
 class _EPDispatch(torch.autograd.Function):
@@ -166,7 +187,7 @@ class _EPDispatch(torch.autograd.Function):
         ep = ctx.ep
         x, s32 = ctx.saved_tensors
         # owners publish the gradient rows, sources pull their tokens' contributions
-        ep.in_view().copy_(g)
+        ep.publish(g, ep.in_view())
         ep.sync(CH_BWD_A)
         dx = ep.pull(ep.in_ptrs(), s32 if ctx.has_scale else None, None)
         ds = ep.pair_dot(ep.in_ptrs(), x).view(ctx.scale_shape) if ctx.has_scale else None
@@ -178,7 +199,7 @@ class _EPCombine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, yp, w, base, ep: EPContext):
         w32 = w.reshape(-1).float().contiguous() if w is not None else None
-        ep.out_view().copy_(yp)
+        ep.publish(yp, ep.out_view())
         ep.sync(CH_OUT)
         out = ep.pull(ep.out_ptrs(), w32, base.contiguous() if base is not None else None)
         ep.sync(CH_DONE)
@@ -195,7 +216,7 @@ class _EPCombine(torch.autograd.Function):
         dw = None
         if ctx.has_w:
             # the weights' gradient needs this layer's expert outputs, which owners still hold
-            ep.out_view().copy_(yp)
+            ep.publish(yp, ep.out_view())
             ep.sync(CH_BWD_B)
             dw = ep.pair_dot(ep.out_ptrs(), g).view(ctx.w_shape)
         ep.push(g, w32 if ctx.has_w else None, ep.in_ptrs())
