@@ -59,7 +59,8 @@ CASES: tuple[Case, ...] = (
     _c("llama3_cp_ulysses", "llama3", "llama3_debugmodel", ("--parallelism.context_parallel_degree", "2"),
        cpu_ok=True),
     _c("llama3_async_tp", "llama3", "llama3_debugmodel",
-       ("--parallelism.tensor_parallel_degree", "2", "--parallelism.enable_async_tensor_parallel"),
+       ("--parallelism.tensor_parallel_degree", "2", "--parallelism.enable_async_tensor_parallel",
+        "--training.local_batch_size", "1"),
        note="fused all-gather→GEMM / GEMM→reduce-scatter kernels over peer memory"),
     _c("llama3_fused_kernels", "llama3", "llama3_debugmodel",
        ("--model_converters.converters", "b200_rms_norm,b200_rope,b200_swiglu,b200_cross_entropy,b200_linear"),
