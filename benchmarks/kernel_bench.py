@@ -501,6 +501,15 @@ def profile_case(name: str, launches: int = 3) -> None:
         lse = torch.full((1024, 16), 8.0, device=dev)
         delta = torch.zeros(1024, 16, device=dev)
         fn = lambda: sparse_mla_backward(q, kv, idx, go, lse, delta, 576 ** -0.5, 512)  # noqa: E731
+    elif name == "indexer_sel_bwd":
+        from titan_b200.ops.dsa import _indexer_selected_backward
+
+        q = (torch.randn(1, 2048, 64, 128, device=dev) * 0.3).to(bf)
+        k = (torch.randn(1, 131072, 1, 128, device=dev) * 0.3).to(bf)
+        w = torch.rand(1, 2048, 64, device=dev)
+        idx = torch.randint(0, 131072, (1, 2048, 2048), device=dev, dtype=torch.int32)
+        g = torch.randn(1, 2048, 2048, device=dev)
+        fn = lambda: _indexer_selected_backward(q, w, k, idx, g)  # noqa: E731
     elif name == "rope":
         from titan_b200.models.common import rope as rope_ref
         from titan_b200.ops.rope import rope_apply

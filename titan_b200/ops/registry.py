@@ -21,10 +21,11 @@ from __future__ import annotations
 
 import torch
 
-__all__ = ["ops", "CONTRACTION_OPS"]
+__all__ = ["ops", "dispatcher_ops", "CONTRACTION_OPS"]
 
 _LIB = torch.library.Library("titan_b200", "DEF")
-ops = torch.ops.titan_b200
+dispatcher_ops = torch.ops.titan_b200
+_CUDA_IMPLS: dict = {}
 
 
 def _define(schema: str, cuda_impl, fake_impl) -> None:
@@ -32,6 +33,42 @@ def _define(schema: str, cuda_impl, fake_impl) -> None:
     _LIB.define(schema)
     _LIB.impl(name, cuda_impl, "CUDA")
     torch.library.register_fake(f"titan_b200::{name}", fake_impl, lib=_LIB)
+    _CUDA_IMPLS[name] = cuda_impl
+
+
+def _nobody_watches(args) -> bool:
+    """True when a call can go straight to the launcher: no dispatch mode on the stack (selective checkpointing,
+    fake tensors, the memory tracker), no compiler tracing, and a real CUDA tensor in front."""
+    if torch._C._len_torch_dispatch_stack() > 0 or torch.compiler.is_compiling():
+        return False
+    for a in args:
+        if isinstance(a, torch.Tensor):
+            return a.is_cuda
+    return False
+
+
+class _Ops:
+    """``ops.<name>(...)``: the dispatcher operator when somebody needs to see the call, the launcher itself otherwise.
+    A Python operator call through the dispatcher costs tens of microseconds of host time; launch-bound models (small
+    MoE blocks, hyper-connection kernels) feel that, so eager steps without an observer skip it.  ``ops.<name>.op`` is
+    the `torch.ops` overload packet (`.default` for save lists and tests)."""
+
+    def __getattr__(self, name: str):
+        op, impl = getattr(dispatcher_ops, name), _CUDA_IMPLS[name]
+
+        def call(*args, **kwargs):
+            if _nobody_watches(args):
+                return impl(*args, **kwargs)
+            return op(*args, **kwargs)
+
+        call.op = op
+        call.default = op.default
+        call.__name__ = name
+        setattr(self, name, call)
+        return call
+
+
+ops = _Ops()
 
 
 # ---------------------------------------------------------------------------------------------- GEMM
