@@ -395,3 +395,35 @@ def test_gathered_tile_kernel_path_matches_dense_oracle_on_gpu():
     for a, b_, name in zip(leaves, ref_leaves, ("dq", "dkv", "dkvc", "dsink")):
         torch.testing.assert_close(a.grad.float(), b_.grad.float(), rtol=8e-2, atol=6e-2,
                                    msg=lambda m, n=name: f"{n}: {m}")
+
+
+def test_kernel_path_key_lists_match_the_dense_oracle_on_cpu(monkeypatch):
+    """The key lists handed to the gathered-tile kernel (window of raw keys, then the selected compressed keys, as rows
+    of one buffer, padded to 128) with the kernel replaced by its fp32 gather oracle: same output and teacher
+    distribution as the dense statement of the attention."""
+    from titan_b200.ops import smla, sparse_mla as sm
+
+    def oracle(q, kv, idx, scale, dv, sink=None, chunk=128):
+        out, lse, teacher = sm.sparse_mla_forward_ref(q, kv, idx, scale, dv, sink)
+        return out, teacher, lse
+
+    monkeypatch.setattr(sm, "sparse_mla", oracle)
+    monkeypatch.setattr(smla, "_kernel_takes", lambda *a, **k: True)
+    torch.manual_seed(2)
+    B, S, H, hd, ratio, k, window = 2, 96, 4, 32, 4, 8, 16
+    Tc = S // ratio
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64) * 0.5  # noqa: E731
+    q, kv, kvc, sink = mk(B, S, H, hd), mk(B, S, hd), mk(B, Tc, hd), mk(H)
+    idx = torch.full((B, S, k), -1, dtype=torch.long)
+    for b in range(B):
+        for s in range(S):
+            vis = (s + 1) // ratio
+            pick = torch.randperm(vis)[:k]
+            idx[b, s, : pick.numel()] = pick + S
+    scale = hd ** -0.5
+    ref, probs = sparse_attention_dense(q, kv, sink, kvc, idx, window, ratio, scale)
+    out, dist = smla.smla_attention(q, kv, sink, kvc, idx, window, ratio, scale, want_dist=True)
+    torch.testing.assert_close(out, ref.to(out.dtype), rtol=1e-4, atol=1e-6)   # the oracle works in fp32
+    cmp = probs[..., S:].sum(dim=1) / H
+    want = torch.gather(cmp, -1, (idx - S).clamp(min=0)).masked_fill(idx < 0, 0.0)
+    torch.testing.assert_close(dist, want.to(dist.dtype), rtol=1e-4, atol=1e-6)

@@ -307,10 +307,15 @@ CONTRACTION_OPS = (ops.gemm.default, ops.grouped_gemm_m.default, ops.grouped_gem
                    ops.flash_attention_fwd.default, ops.sparse_mla_fwd.default, ops.indexer_topk.default)
 
 
+# The SwiGLU output is the input of the down projection (needed again for its weight gradient) and the largest tensor
+# a checkpointed block would otherwise rebuild: keeping it costs hidden_dim * 2 bytes per token and layer.
+KEPT_ELEMENTWISE_OPS = (ops.swiglu_fwd.default,)
+
+
 def _register_with_sac() -> None:
     from titan_b200.parallel.activation_checkpoint import register_sac_save_op
 
-    for op in CONTRACTION_OPS:
+    for op in (*CONTRACTION_OPS, *KEPT_ELEMENTWISE_OPS):
         register_sac_save_op(op)
 
 
