@@ -240,6 +240,9 @@ class ActivationCheckpointConfig:
     mode: Literal["none", "selective", "full"] = "selective"
     selective_ac_option: str = "op"
     """'op' = op-level policy, or an integer string N = checkpoint every Nth block."""
+    selective_keep_swiglu: bool = False
+    """Op-level policy: also keep the fused SwiGLU output (the down projection's input; hidden_dim * 2 bytes per token
+    and layer).  Worth it for dense feed-forward blocks; MoE blocks would keep capacity-sized expert buffers."""
     per_op_sac_force_recompute_mm_shapes_by_fqns: list[str] = field(default_factory=lambda: ["moe.router.gate"])
     early_stop: bool = False
     preserve_rng_state: bool = False

@@ -64,7 +64,7 @@ struct __align__(8) Ctl {
   int abort_flag;
   float m[MAX_HG], l[MAX_HG], inv_l[MAX_HG];
   float red[4][MAX_HG];
-  int valid[BKEYS];
+  int valid[2][BKEYS];   // row ids of the current and of the next key block
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -144,26 +144,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
       ctl->l[tid] = p.sink != nullptr ? 1.f : 0.f;
     }
 
+    // Steps t = pass * nblocks + jb.  The gather of step t + 1 is issued as soon as step t no longer needs the tile
+    // (after its logits in the first pass, after its value product in the second), so the copies travel under the
+    // softmax work; row ids alternate between two small buffers.
+    auto issue_gather = [&](int t) {
+      const int tpass = t >= nblocks ? 1 : 0, tjb = t - tpass * nblocks;
+      const int nch = (tpass == 1 && p.stash) ? vchunks : qchunks;   // stashed logits: only the value columns
+      int* valid = ctl->valid[t & 1];
+      if (tid < BKEYS) {
+        const int row = irow[tjb * BKEYS + tid];
+        valid[tid] = (row >= 0 && row < p.T) ? row : -1;
+      }
+      __syncthreads();   // row ids first (one global read each), then the copies look them up in shared memory
+      for (int i = tid; i < BKEYS * nch * 8; i += NTHREADS) {
+        const int kr = i / (nch * 8), c = i - kr * (nch * 8);
+        const int row = valid[kr];
+        const uint32_t dst = smem_u32(sK) + (c >> 3) * CHUNK_BYTES + kr * 128 + (((c & 7) ^ (kr & 7)) << 4);
+        const __nv_bfloat16* src = row >= 0 ? p.kv + (long long)row * p.dq + c * 8 : p.kv;
+        cp_async16(dst, src, row >= 0 ? 16 : 0);   // an empty slot becomes a zero row
+      }
+    };
+    issue_gather(0);
+
     for (int pass = 0; pass < 2; ++pass) {
       for (int jb = 0; jb < nblocks; ++jb) {
+        const int t = pass * nblocks + jb;
         const bool reuse = pass == 1 && p.stash;     // logits of this block are in tensor memory already
         const uint32_t tmem_s = tmem_s0 + (p.stash ? jb * HG : 0);
-        // ---- gather the selected rows of this block (all threads); with stashed logits only the value columns
-        if (tid < BKEYS) {
-          const int row = irow[jb * BKEYS + tid];
-          ctl->valid[tid] = (row >= 0 && row < p.T) ? row : -1;
-        }
-        __syncthreads();   // valid[] visible; the previous block's MMAs have finished with sK / sP (waited below)
-        {
-          const int nch = reuse ? vchunks : qchunks;
-          for (int i = tid; i < BKEYS * nch * 8; i += NTHREADS) {
-            const int kr = i / (nch * 8), c = i - kr * (nch * 8);
-            const int row = ctl->valid[kr];
-            const uint32_t dst = smem_u32(sK) + (c >> 3) * CHUNK_BYTES + kr * 128 + (((c & 7) ^ (kr & 7)) << 4);
-            const __nv_bfloat16* src = row >= 0 ? p.kv + (long long)row * p.dq + c * 8 : p.kv;
-            cp_async16(dst, src, row >= 0 ? 16 : 0);   // an empty slot becomes a zero row
-          }
-        }
+        const int* valid = ctl->valid[t & 1];
         if (!reuse) {
           cp_async_wait_all();
           fence_proxy_async();   // generic-proxy writes -> visible to the tensor cores (async proxy)
@@ -190,13 +198,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
           tc_fence_after();
           __syncthreads();
           if (*abort_flag) break;
+          if (pass == 0) issue_gather(t + 1);   // the tile is free: the next block (or the second pass) travels now
         }
 
         // ---- softmax along the lanes (threads 0..127, one key each)
         float x[HG];
         if (tid < BKEYS) {
           tmem_ld_row(tmem_s + lane_off, x, HG);
-          const bool ok = ctl->valid[r] >= 0;
+          const bool ok = valid[r] >= 0;
 #pragma unroll
           for (int h = 0; h < HG; ++h) x[h] = ok ? x[h] * p.scale_log2 : -INFINITY;
           tc_fence_before();   // the next MMA into S^T is ordered after these reads
@@ -275,6 +284,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
           tc_fence_after();
           __syncthreads();
           if (*abort_flag) break;
+          if (t + 1 < 2 * nblocks) issue_gather(t + 1);   // the tile is free again
         }
       }
       if (*abort_flag) break;
@@ -306,6 +316,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_fwd_kernel(const SmlaP
     __syncthreads();   // TMEM and the control block are free for the next item
   }
 
+  cp_async_wait_all();   // a CTA that gave up may still have copies in flight
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -66,7 +66,8 @@ def llama3_8b() -> TrainerConfig:
         # selective checkpointing with the rule that keeps every contraction (GEMM, attention) and recomputes norms,
         # rotary embedding, SwiGLU and residual adds: about 2 % of the step for 9 GB.  `llama3_8b_noac` drops it (an 8B
         # model at seq 8192 peaks at 112 GB on ONE 180 GB GPU, 96 GB of it weights, gradients and fp32 AdamW state).
-        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op_save_all_mm"),
+        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op_save_all_mm",
+                                                         selective_keep_swiglu=True),
         # every operator of the block that this framework owns: norms, rotary embedding, SwiGLU, the loss and all
         # projections (tcgen05 GEMMs); attention stays on the fused library kernel
         model_converters=ModelConvertersConfig(

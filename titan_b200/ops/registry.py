@@ -308,14 +308,15 @@ CONTRACTION_OPS = (ops.gemm.default, ops.grouped_gemm_m.default, ops.grouped_gem
 
 
 # The SwiGLU output is the input of the down projection (needed again for its weight gradient) and the largest tensor
-# a checkpointed block would otherwise rebuild: keeping it costs hidden_dim * 2 bytes per token and layer.
-KEPT_ELEMENTWISE_OPS = (ops.swiglu_fwd.default,)
+# a checkpointed block would otherwise rebuild: keeping it costs hidden_dim * 2 bytes per token and layer.  Recipes
+# opt in (`activation_checkpoint.selective_keep_swiglu`): MoE blocks would keep capacity-sized expert buffers.
+SWIGLU_OPS = (ops.swiglu_fwd.default,)
 
 
 def _register_with_sac() -> None:
     from titan_b200.parallel.activation_checkpoint import register_sac_save_op
 
-    for op in (*CONTRACTION_OPS, *KEPT_ELEMENTWISE_OPS):
+    for op in CONTRACTION_OPS:
         register_sac_save_op(op)
 
 

@@ -61,11 +61,11 @@ def extend_sac_save_ops(*ops):
             _SAVE_OPS.discard(op)
 
 
-def _op_policy(force_recompute_mm_shapes: set[tuple[int, ...]], save_every_mm: bool = False):
+def _op_policy(force_recompute_mm_shapes: set[tuple[int, ...]], save_every_mm: bool = False, extra_save_ops=()):
     """Per-op policy: attention, collectives and matmuls are saved, the rest is recomputed.  By default every
     SECOND matmul is recomputed (the memory-lean upstream rule); ``save_every_mm`` keeps them all: on a 180 GB part
     the extra ~0.75 GB per Llama-8B layer buys back one sixth of the step's GEMM work."""
-    save_ops = set(_SAVE_OPS)
+    save_ops = set(_SAVE_OPS) | set(extra_save_ops)
 
     def make():
         meta = defaultdict(int)
@@ -99,8 +99,13 @@ def _wrap(module: nn.Module, ac_config, *, block_index: int, force_shapes: set) 
         return checkpoint_wrapper(module, **kw)
     opt = str(ac_config.selective_ac_option)
     if opt in ("op", "op_save_all_mm"):
-        return checkpoint_wrapper(module, context_fn=_op_policy(force_shapes, save_every_mm=opt == "op_save_all_mm"),
-                                  **kw)
+        extra = ()
+        if getattr(ac_config, "selective_keep_swiglu", False):
+            from titan_b200.ops.registry import SWIGLU_OPS
+
+            extra = SWIGLU_OPS
+        return checkpoint_wrapper(module, context_fn=_op_policy(force_shapes, save_every_mm=opt == "op_save_all_mm",
+                                                                extra_save_ops=extra), **kw)
     if opt.isdigit():
         n = int(opt)
         if n <= 0:
