@@ -82,3 +82,36 @@ def test_virtual_adamw_with_a_budget_smaller_than_the_model(cuda_device):
     assert not m0.is_cuda and m0.is_pinned()            # read and written in place over the host link
     assert opt.state[params[3]]["exp_avg"].is_cuda      # beyond the budget: ordinary device state
     assert torch.equal(m0.float(), ref.state[next(iter(ref_model.parameters()))]["exp_avg"].cpu().float())
+
+
+def test_graphed_fused_adamw_matches_the_eager_step(cuda_device):
+    """The fused AdamW step replayed from a CUDA graph: bit-identical parameters to the eager launches over steps with a
+    changing learning rate and a clip coefficient, re-recorded when a gradient moves to another address."""
+    from titan_b200.optim.fused_adamw import FusedAdamW
+
+    ref_model = _model(cuda_device)
+    model = copy.deepcopy(ref_model)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ref = FusedAdamW(list(ref_model.parameters()), **kw)
+    opt = FusedAdamW(list(model.parameters()), cuda_graph=True, **kw)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    hold = []
+    for step in range(6):
+        for o in (ref, opt):
+            for grp in o.param_groups:
+                grp["lr"] = 1e-2 * (1.0 - 0.1 * step)
+        scale = torch.tensor(0.5 + 0.1 * step, device="cuda")
+        ref.grad_scale, opt.grad_scale = scale, scale.clone()
+        x = torch.randn(64, 512, device="cuda", dtype=torch.bfloat16, generator=g)
+        for m, o in ((ref_model, ref), (model, opt)):
+            o.zero_grad()
+            m(x).float().pow(2).mean().backward()
+        if step == 3:
+            hold = [p.grad for p in model.parameters()]          # keep these alive: the next gradients land elsewhere
+        ref.step()
+        opt.step()
+    torch.cuda.synchronize()
+    for a, b in zip(ref_model.parameters(), model.parameters()):
+        assert torch.equal(a, b)
+    assert opt.graph_replays == 6 and 1 <= opt.graph_captures <= 5, (opt.graph_captures, opt.graph_replays)
+    del hold

@@ -66,8 +66,12 @@ __device__ __forceinline__ void store4(__half* ptr, const float (&o)[4]) {
 template <typename PT, typename GT, typename ST>
 __global__ void __launch_bounds__(512) adamw_kernel(const __grid_constant__ TbAdamArgs a, float lr, float beta1,
                                                     float beta2, float eps, float wd, float bc1, float rsqrt_bc2,
-                                                    const float* __restrict__ grad_scale, int decoupled,
-                                                    int amsgrad, int maximize) {
+                                                    const float* __restrict__ grad_scale,
+                                                    const float* __restrict__ dyn, int decoupled, int amsgrad,
+                                                    int maximize) {
+  // A launch recorded in a CUDA graph reads what changes from step to step (learning rate, bias corrections) from
+  // device memory instead of its baked-in arguments.
+  if (dyn != nullptr) { lr = dyn[0]; bc1 = dyn[1]; rsqrt_bc2 = dyn[2]; }
   const int t = a.block_tensor[blockIdx.x];
   const long long start = a.base[t] + (long long)a.block_chunk[blockIdx.x] * TB_ADAM_CHUNK;
   const long long n = a.n[t];
@@ -140,9 +144,10 @@ __global__ void __launch_bounds__(512) adamw_kernel(const __grid_constant__ TbAd
 
 template <typename PT, typename GT, typename ST>
 int launch(const TbAdamArgs& a, int nblocks, float lr, float b1, float b2, float eps, float wd, float bc1,
-           float rsqrt_bc2, const float* gs, int decoupled, int amsgrad, int maximize, cudaStream_t st) {
-  adamw_kernel<PT, GT, ST><<<nblocks, 512, 0, st>>>(a, lr, b1, b2, eps, wd, bc1, rsqrt_bc2, gs, decoupled, amsgrad,
-                                                    maximize);
+           float rsqrt_bc2, const float* gs, const float* dyn, int decoupled, int amsgrad, int maximize,
+           cudaStream_t st) {
+  adamw_kernel<PT, GT, ST><<<nblocks, 512, 0, st>>>(a, lr, b1, b2, eps, wd, bc1, rsqrt_bc2, gs, dyn, decoupled,
+                                                    amsgrad, maximize);
   TB_CUDA_CHECK(cudaGetLastError());
   tb_note_launch(1);
   return 0;
@@ -158,10 +163,10 @@ TB_API int tb_adam_limits(int* max_tensors, int* max_blocks, int* chunk) {
 
 // Host entry: arrays of `count` tensors (any count; launches are split as needed).
 // p_dtype / g_dtype: 0 fp32, 1 bf16, 2 fp16;  s_dtype (moments): 0 fp32, 1 bf16.  step >= 1.
-TB_API int tb_adamw_multi(void* const* p, const void* const* g, void* const* m, void* const* v, void* const* vmax,
-                          const long long* numel, int count, float lr, float beta1, float beta2, float eps, float wd,
-                          long long step, const float* grad_scale, int decoupled, int amsgrad, int maximize,
-                          int p_dtype, int g_dtype, int s_dtype, cudaStream_t st) {
+static int adamw_multi_impl(void* const* p, const void* const* g, void* const* m, void* const* v, void* const* vmax,
+                            const long long* numel, int count, float lr, float beta1, float beta2, float eps, float wd,
+                            long long step, const float* grad_scale, const float* dyn, int decoupled, int amsgrad,
+                            int maximize, int p_dtype, int g_dtype, int s_dtype, cudaStream_t st) {
   if (step < 1 || count < 0) return TB_ERR_ARG;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2 = 1.f - powf(beta2, (float)step);
@@ -171,7 +176,7 @@ TB_API int tb_adamw_multi(void* const* p, const void* const* g, void* const* m, 
   auto flush = [&]() -> int {
     if (nb == 0) { nt = 0; return 0; }
     int rc = TB_ERR_ARG;
-#define TB_GO(PT, GT, ST) rc = launch<PT, GT, ST>(a, nb, lr, beta1, beta2, eps, wd, bc1, rsqrt_bc2, grad_scale, decoupled, amsgrad, maximize, st)
+#define TB_GO(PT, GT, ST) rc = launch<PT, GT, ST>(a, nb, lr, beta1, beta2, eps, wd, bc1, rsqrt_bc2, grad_scale, dyn, decoupled, amsgrad, maximize, st)
     const int key = p_dtype * 100 + g_dtype * 10 + s_dtype;
     switch (key) {
       case 0: TB_GO(float, float, float); break;
@@ -207,6 +212,34 @@ TB_API int tb_adamw_multi(void* const* p, const void* const* g, void* const* m, 
     }
   }
   return flush();
+}
+
+TB_API int tb_adamw_multi(void* const* p, const void* const* g, void* const* m, void* const* v, void* const* vmax,
+                          const long long* numel, int count, float lr, float beta1, float beta2, float eps, float wd,
+                          long long step, const float* grad_scale, int decoupled, int amsgrad, int maximize,
+                          int p_dtype, int g_dtype, int s_dtype, cudaStream_t st) {
+  return adamw_multi_impl(p, g, m, v, vmax, numel, count, lr, beta1, beta2, eps, wd, step, grad_scale, nullptr,
+                          decoupled, amsgrad, maximize, p_dtype, g_dtype, s_dtype, st);
+}
+
+// The bias corrections exactly as tb_adamw_multi computes them on the host (fp32): out = {1 - beta1^step,
+// 1 / sqrt(1 - beta2^step)}.  The graph form fills its device buffer from these, so both forms agree bit for bit.
+TB_API int tb_adamw_bias_corrections(float beta1, float beta2, long long step, float* out) {
+  if (step < 1 || out == nullptr) return TB_ERR_ARG;
+  out[0] = 1.f - powf(beta1, (float)step);
+  out[1] = 1.f / sqrtf(1.f - powf(beta2, (float)step));
+  return 0;
+}
+
+// The same update with the per-step scalars read from device memory: `dyn` = {lr, 1 - beta1^step,
+// 1 / sqrt(1 - beta2^step)}.  For launches recorded in a CUDA graph, which are replayed with new scalars every step.
+TB_API int tb_adamw_multi_dyn(void* const* p, const void* const* g, void* const* m, void* const* v, void* const* vmax,
+                              const long long* numel, int count, const float* dyn, float beta1, float beta2, float eps,
+                              float wd, const float* grad_scale, int decoupled, int amsgrad, int maximize, int p_dtype,
+                              int g_dtype, int s_dtype, cudaStream_t st) {
+  if (dyn == nullptr) return TB_ERR_ARG;
+  return adamw_multi_impl(p, g, m, v, vmax, numel, count, 0.f, beta1, beta2, eps, wd, 1, grad_scale, dyn, decoupled,
+                          amsgrad, maximize, p_dtype, g_dtype, s_dtype, st);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

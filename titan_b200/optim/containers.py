@@ -156,8 +156,10 @@ def build_lr_schedulers(optimizers, lr_cfg, training_steps: int):
     return LRSchedulersContainer(targets, fn)
 
 
-def build_optimizers(model_parts: list[nn.Module], opt_cfg, parallel_dims=None, ft_manager=None):
-    """Dispatch on the optimizer config (see module docstring)."""
+def build_optimizers(model_parts: list[nn.Module], opt_cfg, parallel_dims=None, ft_manager=None, *,
+                     cuda_graph: bool = False):
+    """Dispatch on the optimizer config (see module docstring).  ``cuda_graph`` (`--compile.cuda_graphs`) records the
+    step of the fused AdamW as a CUDA graph."""
     if opt_cfg.virtual_optimizer and opt_cfg.swap_optimizer:
         raise ValueError("virtual_optimizer and swap_optimizer cannot be enabled together")
     name = opt_cfg.name
@@ -179,7 +181,7 @@ def build_optimizers(model_parts: list[nn.Module], opt_cfg, parallel_dims=None, 
         from titan_b200.optim.fused_adamw import FusedAdamW
 
         kw = dict(lr=opt_cfg.lr, betas=(opt_cfg.beta1, opt_cfg.beta2), eps=opt_cfg.eps,
-                  weight_decay=opt_cfg.weight_decay, decoupled=(name == "AdamW"))
+                  weight_decay=opt_cfg.weight_decay, decoupled=(name == "AdamW"), cuda_graph=cuda_graph)
         return OptimizersContainer(model_parts, FusedAdamW, kw)
     cls = torch.optim.AdamW if name == "AdamW" else torch.optim.Adam
     return OptimizersContainer(model_parts, cls, _adam_kwargs(opt_cfg))

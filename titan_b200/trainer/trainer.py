@@ -187,7 +187,7 @@ class Trainer:
         _disable_fsdp_gradient_division(self.model_parts)
 
         # ---- optimizer, schedule, hooks
-        self.optimizers = build_optimizers(self.model_parts, cfg.optimizer, pd)
+        self.optimizers = build_optimizers(self.model_parts, cfg.optimizer, pd, cuda_graph=cfg.compile.cuda_graphs)
         if self.model_spec.post_optimizer_build_fn is not None:
             self.model_spec.post_optimizer_build_fn(self.optimizers, self.model_parts, pd)
         self.lr_schedulers = build_lr_schedulers(self.optimizers, cfg.lr_scheduler, cfg.training.steps)
