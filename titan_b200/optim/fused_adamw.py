@@ -179,6 +179,11 @@ class FusedAdamW(Optimizer):
                 self.launches += 1
         return loss
 
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        # a recorded step addresses the gradients it saw: keep them in place (zeroed, then accumulated into) instead
+        # of freeing them, or their addresses move every step and every step records anew
+        super().zero_grad(set_to_none=set_to_none and not self.cuda_graph)
+
     # ---- CUDA-graph form of the step
     @staticmethod
     def _graph_ok(all_buckets) -> bool:
@@ -214,6 +219,10 @@ class FusedAdamW(Optimizer):
                 self._graphs.pop(next(iter(self._graphs)))   # oldest recording
             entry = self._graphs[sig] = (graph, dyn, scale)
             self.graph_captures += 1
+            from titan_b200.utils.logging import logger
+
+            logger.info("fused AdamW: recorded the step as a CUDA graph (%d launches; recording %d after %d replays)",
+                        len(flat), self.graph_captures, self.graph_replays)
             # recording does not execute: the replay below is this step's update
         graph, dyn, scale = entry
         dyn.copy_(host, non_blocking=True)
