@@ -250,6 +250,30 @@ def bench_elementwise(iters):
          frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
 
 
+def bench_moe(iters):
+    """Router top-k, routing plan, permute and combine at DeepSeek-16B-like sizes (32768 tokens, dim 2048, 64 experts,
+    top-6): CUDA-event time and achieved bytes per kernel."""
+    from titan_b200.ops.moe import combine, make_plan, permute, router_topk
+
+    _, bw_peak, tag = peaks()
+    T_, D, E, k = 32768, 2048, 64, 6
+    x = torch.randn(T_, D, device="cuda", dtype=torch.bfloat16)
+    logits = torch.randn(T_, E, device="cuda")
+    gate, idx, _ = router_topk(logits, k, score_func="softmax")
+    plan = make_plan(idx, E)
+    buf = permute(x, plan)
+    gw = gate.to(torch.bfloat16)
+    ms = timeit(lambda: router_topk(logits, k, score_func="softmax"), iters)
+    emit(kernel="router_topk", shape=[T_, E, k], ms=ms)
+    ms = timeit(lambda: make_plan(idx, E), iters)
+    emit(kernel="moe_plan", pairs=T_ * k, ms=ms)
+    byt = x.numel() * 2 * (1 + k)
+    ms = timeit(lambda: permute(x, plan), iters)
+    emit(kernel="moe_permute", shape=[T_, D, k], ms=ms, gbs=byt / ms / 1e6, frac_of_peak=byt / ms / 1e6 / bw_peak, peak=tag)
+    ms = timeit(lambda: combine(buf, plan, T_, gw), iters)
+    emit(kernel="moe_combine", shape=[T_, D, k], ms=ms, gbs=byt / ms / 1e6, frac_of_peak=byt / ms / 1e6 / bw_peak, peak=tag)
+
+
 def bench_attention(iters):
     """Causal GQA attention forward, Llama-3 8B shape: the tcgen05 kernel against the library backends."""
     import torch.nn.functional as F
@@ -692,6 +716,8 @@ def main():
         bench_gemm_sustained()
     if "sparse_mla" in which:
         bench_sparse_mla(args.iters)
+    if "moe" in which:
+        bench_moe(args.iters)
     if "elementwise" in which:
         bench_elementwise(args.iters)
     if "attention" in which:

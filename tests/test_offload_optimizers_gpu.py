@@ -115,3 +115,28 @@ def test_graphed_fused_adamw_matches_the_eager_step(cuda_device):
         assert torch.equal(a, b)
     assert opt.graph_replays == 6 and 1 <= opt.graph_captures <= 5, (opt.graph_captures, opt.graph_replays)
     del hold
+
+
+@pytest.mark.parametrize("shape", [(512, 1024), (1024, 512), (2, 256, 768)])
+def test_newton_schulz_on_tensor_cores_matches_the_batched_library_form(cuda_device, shape):
+    """Muon's Newton-Schulz iteration with its three products per step on the tcgen05 GEMM against the same iteration
+    on batched library products: same bf16 inputs, fp32 accumulation in both."""
+    from titan_b200.ops import _lib
+    from titan_b200.optim import muon
+
+    torch.manual_seed(0)
+    g = torch.randn(*shape, device="cuda", dtype=torch.bfloat16)
+    before = _lib.launch_count()
+    got = muon.zeropower_via_newtonschulz5(g, steps=5)
+    assert _lib.launch_count() - before >= 15          # 3 products x 5 steps (x batch)
+    saved = muon.TC_MIN_DIM
+    muon.TC_MIN_DIM = 1 << 30
+    try:
+        ref = muon.zeropower_via_newtonschulz5(g, steps=5)
+    finally:
+        muon.TC_MIN_DIM = saved
+    torch.testing.assert_close(got.float(), ref.float(), rtol=3e-2, atol=3e-2)
+    u = got.float() if got.dim() == 2 else got[0].float()
+    small, big = sorted(u.shape)
+    gram = u @ u.t() if u.shape[0] <= u.shape[1] else u.t() @ u
+    assert (gram.diagonal().mean() - 1).abs() < 0.3     # singular values pulled towards 1

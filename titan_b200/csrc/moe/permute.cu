@@ -208,7 +208,52 @@ __global__ void __launch_bounds__(256) combine_kernel(MoeBufs bufs, int nown, co
   const int lane = threadIdx.x & 31;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  constexpr int KMAX = 8;   // slots whose row pointers and weights are kept in registers (top-k of every model here)
   for (long long t = warp0; t < Tn; t += nwarps) {
+    if (k <= KMAX) {
+      // the k expert rows of this token: resolve the indices once, then issue all row loads of a column chunk
+      // back to back before the first use (the slot order of the sum stays fixed: reproducible)
+      const T* rows[KMAX];
+      float ws[KMAX];
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j) {
+        rows[j] = nullptr;
+        ws[j] = 0.f;
+        if (j < k) {
+          const int d = dest[t * k + j];
+          if (d >= 0 && d < buf_rows * nown) {
+            rows[j] = reinterpret_cast<const T*>(bufs.p[d / buf_rows]) + (long long)(d % buf_rows) * dim;
+            ws[j] = w != nullptr ? w[t * k + j] : 1.f;
+          }
+        }
+      }
+      for (int c = lane * V; c < dim; c += 32 * V) {
+        Vec16<T> v[KMAX];
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j)
+          if (rows[j] != nullptr) v[j] = ld16(rows[j] + c);
+        float acc[V];
+        if (base != nullptr) {
+          const Vec16<T> b = ld16(base + t * dim + c);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = to_f(b.v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j)
+          if (rows[j] != nullptr) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] += to_f(v[j].v[i]) * ws[j];
+          }
+        Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.v[i] = from_f<T>(acc[i]);
+        st16(out + t * dim + c, o);
+      }
+      continue;
+    }
     for (int c = lane * V; c < dim; c += 32 * V) {
       float acc[V];
       if (base != nullptr) {

@@ -69,12 +69,40 @@ def zeropower_via_newtonschulz5(grad: torch.Tensor, steps: int = 5, eps: float =
     for i in range(total):
         if hybrid_ns and i >= 8:
             a, b, c = COEFF_SECONDARY
+        if _tc_takes(x):
+            x = _ns_step_tc(x, a, b, c)
+            continue
         gram = torch.bmm(x, x.transpose(1, 2))
         poly = b * gram + c * torch.bmm(gram, gram)
         x = a * x + torch.bmm(poly, x)
     if transposed:
         x = x.transpose(1, 2)
     return (x.squeeze(0) if two_d else x).to(grad.dtype)
+
+
+TC_MIN_DIM = 256   # below this a matrix does not fill the tensor-core tiles: the batched library product stays
+TC_MAX_BATCH = 16  # one launch per matrix and product: large batches of small experts stay batched
+
+
+def _tc_takes(x: torch.Tensor) -> bool:
+    """x [batch, m, n] (m <= n) contiguous bf16 on a B200 with tile-friendly sizes: the three products of a
+    Newton-Schulz step run on the tcgen05 GEMM (`titan_b200.ops.gemm`)."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] <= TC_MAX_BATCH and x.shape[1] >= TC_MIN_DIM
+            and x.shape[1] % 8 == 0 and x.shape[2] % 8 == 0)
+
+
+def _ns_step_tc(x: torch.Tensor, a: float, b: float, c: float) -> torch.Tensor:
+    """One quintic step X <- aX + (bA + cA^2) X with A = X X^T: no operand is transposed in memory.  A = X X^T is
+    `gemm(X, X)` (both K-major), A^2 = `gemm(A, A)` (A is symmetric), and (.) X reads X as the [K, N] operand."""
+    from titan_b200.ops.gemm import gemm
+
+    out = torch.empty_like(x)
+    for i in range(x.shape[0]):
+        xi = x[i].contiguous()
+        gram = gemm(xi, xi)
+        poly = torch.add(b * gram, gemm(gram, gram), alpha=c)
+        out[i] = torch.add(gemm(poly, xi, b_mn=True), xi, alpha=a)
+    return out
 
 
 def normalise_update(u: torch.Tensor, adjust_lr_fn: str | None = "original") -> torch.Tensor:
