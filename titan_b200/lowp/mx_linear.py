@@ -88,6 +88,19 @@ def _atoms_ok(t: torch.Tensor, *dims: int) -> bool:
     return t.is_cuda and t.dtype in (torch.bfloat16, torch.float16) and all(d % 128 == 0 for d in dims)
 
 
+def _mx_linear_fwd(x2, w, round_mode: str, need_wgrad: bool, atoms: bool):
+    """x2 [M, K], w [N, K] (16-bit, block-aligned) → (y [M, N], fp8 copy of x blocked down the token rows and its
+    scales, kept for the weight gradient; empty when not needed).  One dispatcher operator
+    (`titan_b200::mx_linear_fwd`), so selective checkpointing keeps its outputs instead of quantising and multiplying
+    again in backward."""
+    xq1, xs1, xq2t, xs2t = mx_quantize_dual(x2.contiguous(), round_mode, transposed=need_wgrad, atoms=atoms)
+    wq1, ws1, _, _ = mx_quantize_dual(w.contiguous(), round_mode, transposed=False, atoms=atoms)
+    y = _gemm_q(xq1, xs1, wq1, ws1, x2.dtype)
+    if not need_wgrad:
+        return y, x2.new_empty((0,), dtype=torch.float8_e4m3fn), x2.new_empty((0,), dtype=torch.uint8)
+    return y, xq2t, xs2t
+
+
 class MXFP8MM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, round_mode: str = "rceil"):
@@ -99,10 +112,12 @@ class MXFP8MM(torch.autograd.Function):
         ctx.once = _once_ok(x2.shape[0], x2.shape[1], w.shape[0])
         if ctx.once:
             ctx.atoms = at = _atoms_ok(x2, x2.shape[0], x2.shape[1], w.shape[0])
-            xq1, xs1, xq2t, xs2t = mx_quantize_dual(x2.contiguous(), round_mode, transposed=ctx.needs_input_grad[1],
-                                                    atoms=at)
-            wq1, ws1, _, _ = mx_quantize_dual(wq.contiguous(), round_mode, transposed=False, atoms=at)
-            y = _gemm_q(xq1, xs1, wq1, ws1, x2.dtype)
+            if x2.is_cuda or x2.is_meta:
+                from titan_b200.ops.registry import ops
+
+                y, xq2t, xs2t = ops.mx_linear_fwd(x2, wq, round_mode, bool(ctx.needs_input_grad[1]), at)
+            else:
+                y, xq2t, xs2t = _mx_linear_fwd(x2, wq, round_mode, bool(ctx.needs_input_grad[1]), at)
             ctx.compute_dtype = x2.dtype
             ctx.save_for_backward(xq2t, xs2t, wq)
         else:

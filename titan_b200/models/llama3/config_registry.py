@@ -89,8 +89,9 @@ def llama3_8b_mxfp8() -> TrainerConfig:
     from titan_b200.lowp.mx_converter import MXFP8Converter
 
     cfg = llama3_8b()
-    # the block-scaled GEMMs are not on the selective-checkpointing save list (their fp8 inputs are what the op keeps),
-    # so a checkpointed block would run them twice: this recipe stores activations instead (111 GB on one GPU)
+    # measured without recomputation (111 GB on one GPU): the fp8 copies the MX linears keep are half the size of the
+    # bf16 activations they replace.  Selective checkpointing works too (`titan_b200::mx_linear_fwd` is on its save
+    # list, so a checkpointed block does not quantise and multiply twice).
     cfg.activation_checkpoint.mode = "none"
     cfg.model_converters.converters.append(
         MXFP8Converter.Config(recipe_name="mxfp8_rceil", fqns=["attention.w", "feed_forward.w"]))

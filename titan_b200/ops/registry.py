@@ -301,10 +301,31 @@ _define("indexer_topk(Tensor q_idx, Tensor weights, Tensor k_idx, int topk, int 
         "(Tensor, Tensor)", _indexer_topk_cuda, _indexer_topk_fake)
 
 
+# ---------------------------------------------------------------------------------------------- MXFP8 linear
+def _mx_linear_fwd_cuda(x2, w, round_mode, need_wgrad, atoms):
+    from titan_b200.lowp.mx_linear import _mx_linear_fwd
+
+    return _mx_linear_fwd(x2, w, round_mode, need_wgrad, atoms)
+
+
+def _mx_linear_fwd_fake(x2, w, round_mode, need_wgrad, atoms):
+    m, k = x2.shape
+    y = x2.new_empty((m, w.shape[0]))
+    if not need_wgrad:
+        return y, x2.new_empty((0,), dtype=torch.float8_e4m3fn), x2.new_empty((0,), dtype=torch.uint8)
+    return (y, x2.new_empty((k, m), dtype=torch.float8_e4m3fn),
+            x2.new_empty((k * m // 32,), dtype=torch.uint8))
+
+
+_define("mx_linear_fwd(Tensor x, Tensor w, str round_mode, bool need_wgrad, bool atoms) -> (Tensor, Tensor, Tensor)",
+        _mx_linear_fwd_cuda, _mx_linear_fwd_fake)
+
+
 # Ops whose outputs selective activation checkpointing keeps (contractions and the sparse-attention selection:
 # recomputing them costs real FLOPs, their outputs are small next to what they read).
 CONTRACTION_OPS = (ops.gemm.default, ops.grouped_gemm_m.default, ops.grouped_gemm_k.default,
-                   ops.flash_attention_fwd.default, ops.sparse_mla_fwd.default, ops.indexer_topk.default)
+                   ops.flash_attention_fwd.default, ops.sparse_mla_fwd.default, ops.indexer_topk.default,
+                   ops.mx_linear_fwd.default)
 
 
 # The SwiGLU output is the input of the down projection (needed again for its weight gradient) and the largest tensor
