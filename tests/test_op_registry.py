@@ -99,3 +99,37 @@ def test_converted_ops_compile_fullgraph(cuda_device):
     torch.testing.assert_close(compiled.float(), eager.float(), rtol=2e-2, atol=2e-2)
     compiled.float().sum().backward()
     assert x.grad is not None and w1.grad is not None and torch.isfinite(x.grad.float()).all()
+
+
+def test_ops_go_through_the_dispatcher_only_when_somebody_watches():
+    """`ops.<name>` calls the launcher directly for eager CUDA tensors and the dispatcher operator under a dispatch
+    mode (selective checkpointing, fake tensors) or for meta tensors."""
+    import torch
+    from torch.utils._python_dispatch import TorchDispatchMode
+
+    from titan_b200.ops import registry
+
+    class Watch(TorchDispatchMode):
+        def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+            return func(*args, **(kwargs or {}))
+
+    meta = torch.empty(4, 8, device="meta")
+    assert registry._nobody_watches((meta,)) is False          # meta tensors need the fake kernel
+    assert registry._nobody_watches((3, None)) is False        # no tensor in front: nothing to launch on
+    with Watch():
+        assert registry._nobody_watches((meta,)) is False
+    assert registry.ops.gemm.default is torch.ops.titan_b200.gemm.default
+    assert registry.ops.swiglu_fwd.op is torch.ops.titan_b200.swiglu_fwd
+
+
+def test_selective_checkpointing_keeps_swiglu_only_where_a_recipe_asks():
+    from titan_b200.config.manager import resolve_recipe
+    from titan_b200.ops import registry
+    from titan_b200.parallel.activation_checkpoint import sac_save_ops
+
+    assert registry.SWIGLU_OPS[0] not in sac_save_ops()        # not global: MoE blocks hold capacity-sized buffers
+    assert resolve_recipe("llama3", "llama3_8b").activation_checkpoint.selective_keep_swiglu
+    assert not resolve_recipe("deepseek_v32", "deepseek_v32_sparse_cp8").activation_checkpoint.selective_keep_swiglu
+    for op in (registry.ops.gemm.default, registry.ops.sparse_mla_fwd.default, registry.ops.indexer_topk.default,
+               registry.ops.mx_linear_fwd.default):
+        assert op in sac_save_ops()
