@@ -5,8 +5,10 @@ only: the kernel gathers 128 selected rows at a time into shared memory and runs
 cores, so memory and work are O(S * top-k) however long the key stream is.  It returns the output, the log-sum-exp and
 the head-summed probabilities (the teacher of the lightning indexer's KL loss), all exact (two passes over the keys).
 
-`SparseMLAFunction` adds autograd: the backward recomputes the probabilities from the saved log-sum-exp in query
-chunks (row gather, scatter-add of the latent gradient), so nothing of size [S, T] exists in either direction.
+`SparseMLAFunction` adds autograd: the backward kernel (`csrc/attention/sparse_mla_bwd.cu`) recomputes the
+probabilities from the saved log-sum-exp on the same gathered tiles, keeps dQ in tensor memory and adds the latent's
+gradient row by row with bulk reductions, so nothing of size [S, T] exists in either direction.  A chunked PyTorch
+backward (`sparse_mla_backward_ref`) is the oracle of its test.
 
 Parity: `npu_sparse_flash_attention` with `softmax_lse` output (torchtitan_npu/converters/kernels/dsa.py:195-277) and
 `sparse_flash_mla` / `sparse_flash_mla_grad` (converters/kernels/npu_smla.py:59-1348).
@@ -20,7 +22,8 @@ import torch
 
 from titan_b200.ops import _lib
 
-__all__ = ["sparse_mla_supported", "sparse_mla_forward", "sparse_mla_forward_ref", "sparse_mla"]
+__all__ = ["sparse_mla_supported", "sparse_mla_forward", "sparse_mla_forward_ref", "sparse_mla_backward",
+           "sparse_mla_backward_ref", "sparse_mla"]
 
 _DECLARED = False
 
