@@ -130,7 +130,7 @@ def compare(base: dict[int, dict[str, float]], cand: dict[int, dict[str, float]]
 def compare_markdown(res: dict, base_path: str, cand_path: str, max_rows: int = 40) -> str:
     out = ["# Training-log comparison", "", f"* baseline: `{base_path}`", f"* candidate: `{cand_path}`",
            f"* steps compared: {res['steps_compared']}   tolerance: {res['tolerance']:g}",
-           f"* verdict: **{'PASS' if res['passed'] else 'FAIL'}**", ""]
+           f"* result: **{'PASS' if res['passed'] else 'FAIL'}**", ""]
     if res["only_in_baseline"] or res["only_in_candidate"]:
         out += [f"Steps only in the baseline: {res['only_in_baseline'][:20]}; only in the candidate: "
                 f"{res['only_in_candidate'][:20]}", ""]

@@ -1,5 +1,5 @@
 """End-to-end feature matrix: every case starts the real trainer for a few steps (one process per rank through
-``torch.distributed.run``) and the runner judges the LOG, not just the exit code: a traceback, a NaN / Inf loss, fewer
+``torch.distributed.run``) and the runner reads the LOG, not just the exit code: a traceback, a NaN / Inf loss, fewer
 logged steps than asked, or a timeout fails the case.  A JSON report and one log per case go to the output folder.
 
     python tests/integration/run_matrix.py out/                     every case that fits the visible devices
@@ -107,7 +107,7 @@ _LOSS = re.compile(r"r0\] .*? step:\s+(\d+)\s+loss:\s+([0-9.eE+-]+|nan|inf)", re
 _BENIGN = ("TORCH_NCCL_ASYNC_ERROR_HANDLING", "error_handling", "errors='")
 
 
-def judge(log: str, returncode: int | None, steps: int) -> tuple[bool, str]:
+def assess(log: str, returncode: int | None, steps: int) -> tuple[bool, str]:
     """(passed, reason) from the exit code and the text of a run."""
     if returncode is None:
         return False, "timeout"
@@ -158,7 +158,7 @@ def run_case(case: Case, device: str, out_dir: str, port: int, timeout: int) -> 
         rc = None
     with open(os.path.join(out_dir, f"{case.name}.log"), "w") as f:
         f.write(" ".join(cmd) + "\n" + log)
-    ok, why = judge(log, rc, case.steps)
+    ok, why = assess(log, rc, case.steps)
     return {"case": case.name, "status": "passed" if ok else "failed", "reason": why, "ranks": case.ranks,
             "seconds": round(time.time() - t0, 1)}
 

@@ -1,4 +1,4 @@
-"""The feature-matrix runner itself: its log judge, the case table, and one real case on gloo ranks."""
+"""The feature-matrix runner itself: its log check, the case table, and one real case on gloo ranks."""
 
 import importlib.util
 import os
@@ -15,8 +15,8 @@ def _log(*losses):
     return "\n".join(f"[titan_b200 r0] 10:00:00 INFO step: {i + 1:2d}  loss: {v}  grad_norm: 1.0" for i, v in enumerate(losses))
 
 
-def test_judge_reads_the_log_not_only_the_exit_code():
-    j = run_matrix.judge
+def test_assessment_reads_the_log_not_only_the_exit_code():
+    j = run_matrix.assess
     assert j(_log(8.1, 7.9, 7.5), 0, 3) == (True, "3 steps")
     assert j(_log(8.1, 7.9), 0, 3)[0] is False                       # too few steps
     assert j(_log(8.1, "nan", 7.5), 0, 3) == (False, "loss is NaN / Inf at step 2")
