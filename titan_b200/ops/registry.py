@@ -34,12 +34,13 @@ def _define(schema: str, cuda_impl, fake_impl) -> None:
     _LIB.impl(name, cuda_impl, "CUDA")
     torch.library.register_fake(f"titan_b200::{name}", fake_impl, lib=_LIB)
     _CUDA_IMPLS[name] = cuda_impl
+    _bind(name, cuda_impl)
 
 
 def _nobody_watches(args) -> bool:
     """True when a call can go straight to the launcher: no dispatch mode on the stack (selective checkpointing,
     fake tensors, the memory tracker), no compiler tracing, and a real CUDA tensor in front."""
-    if torch._C._len_torch_dispatch_stack() > 0 or torch.compiler.is_compiling():
+    if torch._C._len_torch_dispatch_stack() > 0:
         return False
     for a in args:
         if isinstance(a, torch.Tensor):
@@ -51,24 +52,27 @@ class _Ops:
     """``ops.<name>(...)``: the dispatcher operator when somebody needs to see the call, the launcher itself otherwise.
     A Python operator call through the dispatcher costs tens of microseconds of host time; launch-bound models (small
     MoE blocks, hyper-connection kernels) feel that, so eager steps without an observer skip it.  ``ops.<name>.op`` is
-    the `torch.ops` overload packet (`.default` for save lists and tests)."""
-
-    def __getattr__(self, name: str):
-        op, impl = getattr(dispatcher_ops, name), _CUDA_IMPLS[name]
-
-        def call(*args, **kwargs):
-            if _nobody_watches(args):
-                return impl(*args, **kwargs)
-            return op(*args, **kwargs)
-
-        call.op = op
-        call.default = op.default
-        call.__name__ = name
-        setattr(self, name, call)
-        return call
+    the `torch.ops` overload packet (`.default` for save lists and tests).  The attributes are created when an
+    operator is defined (nothing is added lazily: a tracer may be looking)."""
 
 
 ops = _Ops()
+
+
+def _bind(name: str, impl) -> None:
+    op = getattr(dispatcher_ops, name)
+
+    def call(*args, **kwargs):
+        if torch.compiler.is_compiling():   # checked first: the tracer folds it and never sees the rest
+            return op(*args, **kwargs)
+        if _nobody_watches(args):
+            return impl(*args, **kwargs)
+        return op(*args, **kwargs)
+
+    call.op = op
+    call.default = op.default
+    call.__name__ = name
+    setattr(ops, name, call)
 
 
 # ---------------------------------------------------------------------------------------------- GEMM
