@@ -250,6 +250,31 @@ def bench_elementwise(iters):
          frac_of_peak=byt / ours / 1e6 / bw_peak, peak=tag)
 
 
+def bench_indexer(iters):
+    """Lightning-indexer scoring + top-k (64 heads of dim 128): the kernel that keeps the query block in shared
+    memory against the generic tiled GEMM's indexer mode, at a cached and at a long key stream."""
+    from titan_b200.ops import dsa
+
+    tf_peak, _, tag = peaks()
+    for S, T in ((4096, 16384), (8192, 32768)):
+        q = torch.randn(1, S, 64, 128, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(1, T, 1, 128, device="cuda", dtype=torch.bfloat16)
+        w = torch.rand(1, S, 64, device="cuda")
+        off = T - S
+        rec = dict(kernel="indexer_scores_topk", S=S, T=T, heads=64, topk=2048)
+        for name, flag in (("resident", True), ("tiled", False)):
+            dsa.RESIDENT_SCORING = flag
+            rec[f"{name}_ms"] = timeit(lambda: dsa.lightning_indexer_topk(q, w, k, 2048, off), iters)
+        dsa.RESIDENT_SCORING = True
+        visible = S * (off + (S + 1) / 2)                     # causal (query, key) pairs
+        fl = 2.0 * visible * 64 * 128
+        rec["resident_tflops_causal"] = fl / rec["resident_ms"] / 1e9
+        rec["frac_of_peak"] = rec["resident_tflops_causal"] / tf_peak
+        rec["peak"] = tag
+        emit(**rec)
+        del q, k, w
+
+
 def bench_moe(iters):
     """Router top-k, routing plan, permute and combine at DeepSeek-16B-like sizes (32768 tokens, dim 2048, 64 experts,
     top-6): CUDA-event time and achieved bytes per kernel."""
@@ -718,6 +743,8 @@ def main():
         bench_sparse_mla(args.iters)
     if "moe" in which:
         bench_moe(args.iters)
+    if "indexer" in which:
+        bench_indexer(args.iters)
     if "elementwise" in which:
         bench_elementwise(args.iters)
     if "attention" in which:

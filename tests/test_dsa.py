@@ -201,3 +201,32 @@ def test_selected_key_indexer_backward_kernel(cuda_device, S, H, T, k):
     for xg, y, name in zip(a, (qr, wr, kr), ("dq", "dw", "dk")):
         torch.testing.assert_close(xg.grad.float(), y.grad.float(), rtol=5e-2, atol=5e-2,
                                    msg=lambda s_, n=name: f"{n}: {s_}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("S,H,T,k,off,ratio", [(257, 64, 900, 128, 643, 1), (130, 16, 512, 64, 0, 1),
+                                               (96, 256, 300, 32, 204, 1), (512, 32, 128, 40, 0, 4)])
+def test_resident_query_scoring_kernel_matches_the_tiled_gemm_form(cuda_device, S, H, T, k, off, ratio):
+    """Head dim 128 takes the kernel that keeps a block of 256 (query, head) rows in shared memory and streams the
+    key tiles past it; the generic tiled GEMM's indexer mode is the oracle (same bf16 inputs, fp32 sums): equal
+    selected values, equal selections up to ties, for several head counts, offsets and a compression ratio."""
+    from titan_b200.ops import _lib, dsa
+
+    torch.manual_seed(4)
+    qi = torch.randn(1, S, H, 128, device="cuda", dtype=torch.bfloat16)
+    ki = torch.randn(1, T, 1, 128, device="cuda", dtype=torch.bfloat16)
+    w = torch.rand(1, S, H, device="cuda")
+    idx, vals = dsa.lightning_indexer_topk(qi, w, ki, k, off, ratio)
+    _lib.shared_status().raise_if_set("indexer_scores_resident")
+    saved = dsa.RESIDENT_SCORING
+    dsa.RESIDENT_SCORING = False
+    try:
+        idx_r, vals_r = dsa.lightning_indexer_topk(qi, w, ki, k, off, ratio)
+    finally:
+        dsa.RESIDENT_SCORING = saved
+    assert ((idx >= 0) == (idx_r >= 0)).all()
+    sv, sr = vals.sort(-1, descending=True)[0], vals_r.sort(-1, descending=True)[0]
+    finite = torch.isfinite(sr)
+    torch.testing.assert_close(sv[finite], sr[finite], rtol=1e-4, atol=1e-3)
+    same = (idx.sort(-1)[0] == idx_r.sort(-1)[0]).float().mean()
+    assert same > 0.98

@@ -69,6 +69,9 @@ def lightning_indexer_topk(q_idx, weights, k_idx, topk: int, pos_offset: int = 0
     return ops.indexer_topk(q_idx.detach(), weights.detach(), k_idx.detach(), topk, pos_offset, ratio)
 
 
+RESIDENT_SCORING = True  # False: the generic tiled GEMM's indexer mode for every shape (the oracle of the other's test)
+
+
 def _indexer_topk_launch(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, ratio: int = 1):
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]
@@ -78,6 +81,7 @@ def _indexer_topk_launch(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, 
     P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     _lib.declare("tb_indexer_scores", [P, P, P, P, I, I, I, I, LL, I, I, I, P, P])
     _lib.declare("tb_topk_select", [P, LL, I, I, I, I, I, P, P, P])
+    _lib.declare("tb_indexer_scores_resident", [P, P, P, P, I, I, I, I, LL, I, I, P, P])
     ld = (T + 3) // 4 * 4
     scores = torch.empty(S, ld, dtype=torch.float32, device=q_idx.device)
     idx = torch.empty(B, S, topk, dtype=torch.int32, device=q_idx.device)
@@ -86,9 +90,14 @@ def _indexer_topk_launch(q_idx, weights, k_idx, topk: int, pos_offset: int = 0, 
         q2 = q_idx[b].reshape(S * H, D).contiguous()
         k2 = k_idx[b].reshape(T, D).contiguous().to(q2.dtype)
         w2 = weights[b].reshape(S * H).float().contiguous()
-        rc = L.tb_indexer_scores(q2.data_ptr(), k2.data_ptr(), w2.data_ptr(), scores.data_ptr(), S, H, T, D, ld,
-                                 pos_offset, ratio, _lib.dtype_code(q2.dtype), _lib.shared_status().ptr,
-                                 _lib.stream_ptr())
+        if RESIDENT_SCORING and D == 128 and q2.dtype == torch.bfloat16 and 16 <= H <= 256 and (H & (H - 1)) == 0:
+            # head dim 128: the query block stays in shared memory and key tiles stream past it
+            rc = L.tb_indexer_scores_resident(q2.data_ptr(), k2.data_ptr(), w2.data_ptr(), scores.data_ptr(), S, H, T,
+                                              D, ld, pos_offset, ratio, _lib.shared_status().ptr, _lib.stream_ptr())
+        else:
+            rc = L.tb_indexer_scores(q2.data_ptr(), k2.data_ptr(), w2.data_ptr(), scores.data_ptr(), S, H, T, D, ld,
+                                     pos_offset, ratio, _lib.dtype_code(q2.dtype), _lib.shared_status().ptr,
+                                     _lib.stream_ptr())
         _lib.check(rc, "indexer_scores")
         rc = L.tb_topk_select(scores.data_ptr(), ld, S, T, topk, pos_offset, ratio, idx[b].data_ptr(),
                               vals[b].data_ptr(), _lib.stream_ptr())
