@@ -81,3 +81,30 @@ def test_backward_matches_autograd_of_the_oracle(cuda_device, kernel_backward, S
     torch.testing.assert_close(kv1.grad.float(), kr.grad, rtol=5e-2, atol=3e-2)
     if sink:
         torch.testing.assert_close(sk1.grad, skr.grad, rtol=5e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("S,H,T,K,dq,dv,sink", [(40, 16, 4096, 2048, 576, 512, False), (24, 32, 2000, 1024, 576, 512, True),
+                                                (16, 16, 900, 384, 512, 512, True), (9, 16, 600, 256, 320, 256, False)])
+def test_pipelined_forward_matches_the_single_tile_kernel(cuda_device, S, H, T, K, dq, dv, sink):
+    """The half-tile ring (two buffers of chunks, copies travelling under the tensor-core and softmax work) against
+    the single-tile kernel: same output, log-sum-exp and teacher distribution, and both against the fp32 oracle."""
+    from titan_b200.ops import _lib, sparse_mla as mod
+
+    q, kv, idx = _case(S, H, T, K, dq, dv, empty=0.15)
+    sk = torch.randn(H, device="cuda") if sink else None
+    scale = dq ** -0.5
+    try:
+        mod.set_pipelined(True)
+        o1, l1, t1 = mod.sparse_mla_forward(q, kv, idx, scale, dv, sk)
+        mod.set_pipelined(False)
+        o0, l0, t0 = mod.sparse_mla_forward(q, kv, idx, scale, dv, sk)
+    finally:
+        mod.set_pipelined(False)
+    _lib.shared_status().raise_if_set("sparse_mla")
+    torch.testing.assert_close(l1, l0, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(o1.float(), o0.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(t1, t0, rtol=1e-3, atol=1e-4)
+    ro, rl, rt = mod.sparse_mla_forward_ref(q, kv, idx, scale, dv, sk)
+    torch.testing.assert_close(l1, rl, rtol=1e-3, atol=2e-3)
+    torch.testing.assert_close(o1.float(), ro.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(t1, rt, rtol=2e-2, atol=2e-3)

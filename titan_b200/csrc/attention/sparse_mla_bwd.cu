@@ -167,12 +167,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
         ctl->valid[tid] = (row >= 0 && row < p.T) ? row : -1;
       }
       __syncthreads();   // valid[] visible; the previous block's MMAs and epilogues have finished with smem / TMEM
-      for (int i = tid; i < BKEYS * qchunks * 8; i += NTHREADS) {
-        const int kr = i / (qchunks * 8), c = i - kr * (qchunks * 8);
-        const int row = ctl->valid[kr];
-        const uint32_t dst = smem_u32(sK) + (c >> 3) * CHUNK_BYTES + kr * 128 + (((c & 7) ^ (kr & 7)) << 4);
-        const __nv_bfloat16* src = row >= 0 ? p.kv + (long long)row * p.dq + c * 8 : p.kv;
-        cp_async16(dst, src, row >= 0 ? 16 : 0);
+      {
+        // Thread = (row lane tid / 8, 16-byte piece tid % 8); it serves rows lane + 32 j of every chunk, so the row
+        // pointers and the swizzled offset are computed once and each copy costs two additions.
+        const int piece = tid & 7, rl = tid >> 3;
+        const uint32_t dst0 = smem_u32(sK) + rl * 128 + ((piece ^ (rl & 7)) << 4);
+        const __nv_bfloat16* src[BKEYS * 8 / NTHREADS];
+        uint32_t nbytes[BKEYS * 8 / NTHREADS];
+#pragma unroll
+        for (int j = 0; j < BKEYS * 8 / NTHREADS; ++j) {
+          const int row = ctl->valid[rl + j * (NTHREADS / 8)];
+          src[j] = p.kv + (row >= 0 ? (long long)row * p.dq : 0ll) + piece * 8;
+          nbytes[j] = row >= 0 ? 16u : 0u;         // an empty slot becomes a zero row
+        }
+        for (int ch = 0; ch < qchunks; ++ch) {
+#pragma unroll
+          for (int j = 0; j < BKEYS * 8 / NTHREADS; ++j)
+            cp_async16(dst0 + ch * CHUNK_BYTES + j * (NTHREADS / 8) * 128, src[j] + ch * 64, nbytes[j]);
+        }
       }
       cp_async_wait_all();
       fence_proxy_async();

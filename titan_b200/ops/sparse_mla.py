@@ -34,7 +34,16 @@ def _declare():
         P, I, Fl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         _lib.declare("tb_sparse_mla_fwd", [P, P, P, P, P, P, P, I, I, I, I, I, I, Fl, P, P])
         _lib.declare("tb_sparse_mla_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, Fl, P, P])
+        _lib.declare("tb_sparse_mla_fwd_set_pipelined", [I])
         _DECLARED = True
+
+
+def set_pipelined(on: bool) -> None:
+    """Forward kernel selection: False (default) is the single-tile kernel; True uses the half-tile ring where it
+    applies (logits fit in tensor memory, value width a multiple of 256).  The ring overlaps the copies with the
+    products but doubles the product / wait round trips and measures slightly slower; it is kept and tested."""
+    _declare()
+    _lib.check(_lib.lib().tb_sparse_mla_fwd_set_pipelined(int(bool(on))), "sparse_mla_fwd_set_pipelined")
 
 
 def sparse_mla_supported(q: torch.Tensor, kv: torch.Tensor, idx: torch.Tensor, dv: int) -> bool:
