@@ -501,8 +501,8 @@ def bench_sparse_mla(iters):
         useful = 2.0 * S * H * K * (dq + dv)   # QK^T over the selected keys + PV
         rec = dict(kernel="sparse_mla_fwd", S=S, T=T, H=H, topk=K, ms=fwd, fwd_bwd_ms=fwdbwd,
                    useful_tflops=useful / fwd / 1e9, frac_of_peak=useful / fwd / 1e9 / tf_peak, peak=tag,
-                   gathered_gbs=2.0 * S * K * dq * 2 / fwd / 1e6,
-                   note="two passes over the keys: the selected rows are gathered twice per query")
+                   gathered_gbs=S * K * (dq + dv) * 2 / fwd / 1e6,
+                   note="two passes over the keys: full rows for the logits, the value columns again for P V")
         if T <= 32768:   # the dense-masked form needs [H, chunk, T] logits: only short streams
             qh = q.transpose(0, 1).contiguous()
             v = kv[:, :dv].contiguous()

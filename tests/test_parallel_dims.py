@@ -45,3 +45,14 @@ def test_single_rank_mesh(gloo_single_rank):
     assert pd.get_optional_mesh("tp") is None and pd.get_optional_mesh("fsdp") is None
     with pytest.raises(ValueError):
         pd.get_mesh("tp")
+
+
+def test_single_process_without_a_process_group_hands_out_no_mesh():
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        pytest.skip("a process group exists in this interpreter")
+    pd = ParallelDims(dp_shard=-1, world_size=1)
+    assert pd.get_optional_mesh("tp") is None and pd.get_optional_mesh("fsdp") is None
+    assert pd.mesh_even_if_trivial("efsdp") is None
+    assert not dist.is_initialized()   # asking did not try to create one

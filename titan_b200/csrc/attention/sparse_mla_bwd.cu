@@ -64,6 +64,11 @@ struct __align__(8) Ctl {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
@@ -231,7 +236,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
         const int c16 = (r & 63) >> 3;
 #pragma unroll
         for (int h = 0; h < HG; ++h) {
-          const float pr = ok ? exp2f(x[h] * p.scale_log2 - ctl->lse2[h]) : 0.f;
+          const float pr = ok ? fast_exp2(x[h] * p.scale_log2 - ctl->lse2[h]) : 0.f;
           const float ds = pr * (dp[h] - ctl->delta[h]) * p.scale;
           const uint32_t a = off + h * 128 + ((c16 ^ (h & 7)) << 4);
           st_shared_b16(smem_u32(sP) + a, pr);

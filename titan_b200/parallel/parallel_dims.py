@@ -210,6 +210,8 @@ class ParallelDims:
 
     def get_optional_mesh(self, name: str) -> DeviceMesh | None:
         if self._dense is None:
+            if self.world_size == 1 and not torch.distributed.is_initialized():
+                return None   # a single process without a process group: every degree is 1, no mesh to hand out
             self.build_mesh()
         if name not in self._meshes or self._meshes[name] is None or not self._enabled(name):
             return None
@@ -218,6 +220,8 @@ class ParallelDims:
     def mesh_even_if_trivial(self, name: str) -> DeviceMesh | None:
         """Like `get_optional_mesh` but also returns meshes of degree 1 (None only if never built)."""
         if self._dense is None:
+            if self.world_size == 1 and not torch.distributed.is_initialized():
+                return None
             self.build_mesh()
         return self._meshes.get(name)
 
