@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
       if (tid < BKEYS) {
         const int row = irow[jb * BKEYS + tid];
         ctl->valid[tid] = (row >= 0 && row < p.T) ? row : -1;
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the last group's rows have left the tile
       }
       __syncthreads();   // valid[] visible; the previous block's MMAs and epilogues have finished with smem / TMEM
       {
@@ -283,6 +284,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
           }
           umma_commit(&ctl->mma_bar);
         }
+        // the previous group's row reductions drain from the staging area while these products run
+        if (tid < BKEYS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         if (!mbar_wait(&ctl->mma_bar, mma_phase, abort_flag)) {
           if (tid == 0 && *abort_flag == 0) { *abort_flag = 1; if (p.status) atomicExch(p.status, TB_ERR_WAIT_TMEM_FULL); }
         }
@@ -319,7 +322,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) sparse_mla_bwd_kernel(const BwdPa
                            : "memory");
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the staging rows may be overwritten
+            // the engine still reads the staging rows: whoever writes that region next (the next group's staging,
+            // the next block's gather) is released by a barrier that follows this thread's wait_group.read
           }
         }
         __syncthreads();   // the group accumulator and the staging area are free again
