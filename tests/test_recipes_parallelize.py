@@ -48,6 +48,20 @@ def _world_size(par) -> int:
     return pp * rep * shard * cp * tp
 
 
+def _assert_fsdp_groups_have_one_dtype(model, label):
+    """FSDP2 refuses, at the first forward, a parameter group whose parameters are stored in different dtypes."""
+    from torch.distributed.fsdp import FSDPModule
+
+    for name, m in model.named_modules():
+        if not isinstance(m, FSDPModule):
+            continue
+        group = getattr(m._get_fsdp_state(), "_fsdp_param_group", None)
+        if group is None:
+            continue
+        dtypes = {getattr(fp, "orig_dtype", fp.sharded_param.dtype) for fp in group.fsdp_params}
+        assert len(dtypes) <= 1, f"{label}: FSDP group {name or '<root>'} stores {sorted(map(str, dtypes))}"
+
+
 @pytest.fixture
 def fake_world():
     made = []
@@ -117,5 +131,6 @@ def test_recipe_parallelizes_on_a_fake_mesh(module, recipe, fake_world):
                                     compile_config=compile_cfg, ac_config=cfg.activation_checkpoint,
                                     dump_folder="/tmp")
         assert sum(p.numel() for p in model.parameters()) > 0
+        _assert_fsdp_groups_have_one_dtype(model, f"{module}:{recipe}")
     finally:
         stash.clear()

@@ -55,6 +55,30 @@ def _find_experts(block: nn.Module):
     return None
 
 
+def _odd_dtype_modules(block: nn.Module, skip: nn.Module | None = None) -> list[nn.Module]:
+    """Submodules of `block` whose own parameters are stored in another dtype than most of the block (by element
+    count).  Modules under `skip` (experts that already form a group) are left out."""
+    skipped = {id(p) for p in skip.parameters()} if skip is not None else set()
+    params = [p for p in block.parameters() if id(p) not in skipped]
+    if not params:
+        return []
+    count: dict[torch.dtype, int] = {}
+    for p in params:
+        count[p.dtype] = count.get(p.dtype, 0) + p.numel()
+    if len(count) == 1:
+        return []
+    major = max(count, key=count.get)
+    odd = []
+    for name, m in block.named_modules():
+        own = [p for p in m.parameters(recurse=False) if id(p) not in skipped]
+        if not own or all(p.dtype == major for p in own):
+            continue
+        if any(p.dtype == major for p in own):
+            raise ValueError(f"module {name!r} mixes {major} parameters with others; FSDP needs one dtype per module")
+        odd.append(m)
+    return odd
+
+
 def apply_fsdp(
     model: nn.Module,
     dp_mesh: DeviceMesh,
@@ -104,6 +128,14 @@ def apply_fsdp(
             fully_shard(experts, **ecfg, reshard_after_forward=reshard, shard_placement_fn=shard_fn)
             if gradient_divide_factor is not None:
                 experts.set_gradient_divide_factor(float(gradient_divide_factor))
+        for odd in _odd_dtype_modules(block, skip=experts):
+            # e.g. an fp32 gate inside a bf16-stored block: FSDP2 wants one storage dtype per group, so the module
+            # becomes a group of its own that keeps its dtype in compute as well (library collectives: it is small)
+            fully_shard(odd, **dict(cfg, mp_policy=MixedPrecisionPolicy(param_dtype=None, reduce_dtype=reduce_dtype)),
+                        reshard_after_forward=reshard)
+            odd._keeps_library_collectives = True
+            if gradient_divide_factor is not None and experts is not None:
+                odd.set_gradient_divide_factor(float(gradient_divide_factor))
         fully_shard(block, **cfg, reshard_after_forward=reshard)
         if gradient_divide_factor is not None and experts is not None:
             block.set_gradient_divide_factor(float(gradient_divide_factor))

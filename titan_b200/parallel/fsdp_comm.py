@@ -227,7 +227,7 @@ def install_peer_all_gather(model: nn.Module, dp_mesh, param_dtype: torch.dtype)
     esize = torch.empty((), dtype=param_dtype).element_size()
     comm = PeerMemoryAllGather(group, reserve_bytes=max_bucket_numel(model, world) * esize)
     for m in model.modules():
-        if not isinstance(m, FSDPModule):
+        if not isinstance(m, FSDPModule) or getattr(m, "_keeps_library_collectives", False):
             continue
         pg = getattr(m._get_fsdp_state(), "_fsdp_param_group", None)
         other = getattr(pg.mesh_info, "shard_process_group", None) if pg is not None else None
@@ -249,7 +249,7 @@ def install_peer_reduce_scatter(model: nn.Module, dp_mesh, wire_dtype: torch.dty
         return None
     comm = PeerMemoryReduceScatter(group, wire_dtype, reserve_numel=max_bucket_numel(model, world), nvls=nvls)
     for m in model.modules():
-        if not isinstance(m, FSDPModule):
+        if not isinstance(m, FSDPModule) or getattr(m, "_keeps_library_collectives", False):
             continue
         state = m._get_fsdp_state()
         pg = getattr(state, "_fsdp_param_group", None)
