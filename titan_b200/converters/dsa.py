@@ -24,7 +24,7 @@ class FusedDSAttention(DSASparseAttention):
             return super().forward(q, k, v, attn_mask, scale, q_indexer, k_indexer, weights, index_topk)
         scale = scale if scale is not None else q.shape[-1] ** -0.5
         prefix = getattr(self, "_values_are_key_prefix", None)
-        if prefix is None and k.shape[1] == 1 and q.is_cuda:
+        if prefix is None and k.shape[1] == 1 and (q.is_cuda or q.is_meta):
             from titan_b200.ops.dsa import _values_are_key_prefix
 
             # MLA absorb: the values are the latent part of the keys; decided once per module (a layout property)

@@ -84,7 +84,7 @@ class FusedGroupedExperts(Module):
         if mx is not None:
             h13 = self.mx_grouped_mm(x, w13.to(x.dtype), offs, mx)
             return self.mx_grouped_mm(swiglu_fused(h13, None, self.swiglu_limit), w2.to(x.dtype), offs, mx)
-        if x.is_cuda:
+        if x.is_cuda or x.is_meta:
             h13 = torch._grouped_mm(x.bfloat16(), w13.bfloat16().transpose(-2, -1), offs=offs)
             h = swiglu_fused(h13, None, self.swiglu_limit)
             return torch._grouped_mm(h, w2.bfloat16().transpose(-2, -1), offs=offs).to(x.dtype)

@@ -80,7 +80,7 @@ def mx_dequantize_ref(q: torch.Tensor, scales: torch.Tensor, axis: int = -1, dty
 
 
 def _kernel_ok(x: torch.Tensor, axis: int) -> bool:
-    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 2 and x.is_contiguous()
+    return ((x.is_cuda or x.is_meta) and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 2 and x.is_contiguous()
             and x.shape[1] % 8 == 0 and x.shape[-1 if axis == -1 else -2] % BLOCK == 0
             and (axis == -1 or x.shape[0] // BLOCK <= 65535))
 
@@ -92,10 +92,12 @@ def mx_quantize(x: torch.Tensor, axis: int = -1, round_mode: str = "rceil"):
         return q.view(x.shape), s.view(*x.shape[:-1], -1)
     if not _kernel_ok(x, axis):
         return mx_quantize_ref(x, axis, round_mode)
-    _declare()
     rows, cols = x.shape
     q = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
     s = torch.empty((rows, cols // BLOCK) if axis == -1 else (rows // BLOCK, cols), dtype=torch.uint8, device=x.device)
+    if x.is_meta:   # shapes only (memory simulation)
+        return q.view(torch.float8_e4m3fn), s
+    _declare()
     rc = _lib.lib().tb_mx_quantize(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, cols, axis,
                                    {"floor": 0, "rceil": 1}[round_mode], _lib.dtype_code(x.dtype), _lib.stream_ptr())
     _lib.check(rc, "mx_quantize")
@@ -117,7 +119,7 @@ def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool =
         raise ValueError("mx_quantize_dual: ask for at least one view")
     if atoms and (x.shape[0] % 128 or x.shape[1] % 128):
         raise ValueError("mx_quantize_dual(atoms=True) needs both dims to be multiples of 128")
-    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)):
+    if not ((x.is_cuda or x.is_meta) and x.dtype in (torch.bfloat16, torch.float16)):
         q1, s1 = mx_quantize_ref(x, -1, round_mode) if rows else (None, None)
         q2t, s2t = mx_quantize_ref(x.t().contiguous(), -1, round_mode) if transposed else (None, None)
         if atoms:
@@ -126,7 +128,8 @@ def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool =
             s1 = pack_scale_atoms(s1) if rows else None
             s2t = pack_scale_atoms(s2t) if transposed else None
         return q1, s1, q2t, s2t
-    _declare()
+    if not x.is_meta:
+        _declare()
     x = x.contiguous()
     R, C = x.shape
     u8 = dict(dtype=torch.uint8, device=x.device)
@@ -138,21 +141,26 @@ def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool =
     else:
         s1 = torch.empty(R, C // BLOCK, **u8) if rows else None
         s2t = torch.empty(C, R // BLOCK, **u8) if transposed else None
+    f8 = lambda t: t.view(torch.float8_e4m3fn) if t is not None else None  # noqa: E731
+    if x.is_meta:   # shapes only (memory simulation)
+        return f8(q1), s1, f8(q2t), s2t
     p = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
     rc = _lib.lib().tb_mx_quantize_dual(x.data_ptr(), p(q1), p(s1), p(q2t), p(s2t), R, C,
                                         {"floor": 0, "rceil": 1}[round_mode], _lib.dtype_code(x.dtype), int(atoms),
                                         _lib.stream_ptr())
     _lib.check(rc, "mx_quantize_dual")
-    f8 = lambda t: t.view(torch.float8_e4m3fn) if t is not None else None  # noqa: E731
     return f8(q1), s1, f8(q2t), s2t
 
 
 def mx_dequantize(q: torch.Tensor, scales: torch.Tensor, axis: int = -1, dtype=torch.bfloat16):
-    if not (q.is_cuda and q.dim() == 2 and q.is_contiguous() and dtype == torch.bfloat16 and q.shape[1] % 8 == 0):
+    if not ((q.is_cuda or q.is_meta) and q.dim() == 2 and q.is_contiguous() and dtype == torch.bfloat16
+            and q.shape[1] % 8 == 0):
         return mx_dequantize_ref(q, scales, axis, dtype)
-    _declare()
     rows, cols = q.shape
     out = torch.empty(rows, cols, dtype=torch.bfloat16, device=q.device)
+    if q.is_meta:   # shapes only (memory simulation)
+        return out
+    _declare()
     rc = _lib.lib().tb_mx_dequantize(q.view(torch.uint8).data_ptr(), scales.contiguous().data_ptr(), out.data_ptr(),
                                      rows, cols, axis, _lib.stream_ptr())
     _lib.check(rc, "mx_dequantize")

@@ -48,7 +48,7 @@ def _fq(t: torch.Tensor, axis: int, round_mode: str) -> torch.Tensor:
 
 def _mm_mx(a: torch.Tensor, b_t: torch.Tensor, round_mode: str) -> torch.Tensor:
     """``mx(a, K) · mx(b_t, K)ᵀ`` for a [M, K], b_t [N, K], both quantised in 1×32 blocks along K."""
-    if a.is_cuda and a.dtype == torch.bfloat16 and b_t.dtype == torch.bfloat16:
+    if (a.is_cuda or a.is_meta) and a.dtype == torch.bfloat16 and b_t.dtype == torch.bfloat16:
         from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, mxfp8_gemm_supported
 
         if mxfp8_gemm_supported(a.shape[0], b_t.shape[0], a.shape[1]):
@@ -69,7 +69,7 @@ def _mm(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
 
 def _gemm_q(aq, sa, bq, sb, dtype) -> torch.Tensor:
     """``dequant(aq, sa) · dequant(bq, sb)ᵀ`` for operands already quantised along their shared last dim."""
-    if aq.is_cuda:
+    if aq.is_cuda or aq.is_meta:
         from titan_b200.ops.mxfp8_gemm import mxfp8_gemm, mxfp8_gemm_supported
 
         if sa.dim() == 3:  # scales already in the GEMM's atom order (only produced for shapes the kernel takes)
@@ -85,7 +85,7 @@ def _once_ok(*dims: int) -> bool:
 
 def _atoms_ok(t: torch.Tensor, *dims: int) -> bool:
     """The quantiser can emit the GEMM's scale layout directly: CUDA 16-bit input, every dim a multiple of 128."""
-    return t.is_cuda and t.dtype in (torch.bfloat16, torch.float16) and all(d % 128 == 0 for d in dims)
+    return (t.is_cuda or t.is_meta) and t.dtype in (torch.bfloat16, torch.float16) and all(d % 128 == 0 for d in dims)
 
 
 def _mx_linear_fwd(x2, w, round_mode: str, need_wgrad: bool, atoms: bool):
@@ -105,7 +105,7 @@ class MXFP8MM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, round_mode: str = "rceil"):
         x2 = x.reshape(-1, x.shape[-1])
-        if x2.dtype == torch.float32 and x2.is_cuda:
+        if x2.dtype == torch.float32 and (x2.is_cuda or x2.is_meta):
             x2 = x2.to(torch.bfloat16)
         wq = w.to(x2.dtype)
         ctx.meta = (x.shape, x.dtype, w.dtype, round_mode)
@@ -241,7 +241,8 @@ class _MXGroupedMMAligned(torch.autograd.Function):
 
 
 def _aligned_ok(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor) -> bool:
-    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and offs.is_cuda
+    return ((x.is_cuda or x.is_meta) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and (offs.is_cuda or offs.is_meta)
             and x.shape[0] >= 128 and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0)
 
 
@@ -287,6 +288,6 @@ def mx_grouped_mm(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, round_mo
     caller's promise that every group is a multiple of 128 rows (the padded expert-major layout): on CUDA that form runs
     as one grouped tensor-core launch per product instead of a loop over experts.  ``weight_key`` (any hashable that
     names the weight) keeps the weight's quantised views between optimizer steps (see `invalidate_weight_cache`)."""
-    if aligned and _aligned_ok(x, w, offs):
+    if (aligned or x.is_meta) and _aligned_ok(x, w, offs):   # meta: shapes only, the host loop would read offs
         return _MXGroupedMMAligned.apply(x, w, offs.to(torch.int32), round_mode, weight_key)
     return _MXGroupedMM.apply(x, w, offs, round_mode)

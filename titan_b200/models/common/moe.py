@@ -200,7 +200,7 @@ class GroupedExperts(Module):
             if self.swiglu_limit > 0:
                 g, u = g.clamp(max=self.swiglu_limit), u.clamp(min=-self.swiglu_limit, max=self.swiglu_limit)
             return self.mx_grouped_mm(F.silu(g) * u, w2.to(x.dtype), offs, mx)
-        if self.use_grouped_mm and x.is_cuda:
+        if (self.use_grouped_mm and x.is_cuda) or x.is_meta:   # meta: shapes only (no host read of the counts)
             return run_experts_grouped_mm(w1, w2, w3, x, counts.to(torch.int32), self.swiglu_limit)
         return run_experts_for_loop(w1, w2, w3, x, counts.long(), self.swiglu_limit)
 

@@ -64,7 +64,7 @@ def hadamard_transform(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
 
 
 def rotate_activation(x: torch.Tensor) -> torch.Tensor:
-    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.size(-1) in (64, 128, 256, 512):
+    if (x.is_cuda or x.is_meta) and x.dtype in (torch.bfloat16, torch.float16) and x.size(-1) in (64, 128, 256, 512):
         from titan_b200.ops.hadamard import hadamard
 
         return hadamard(x)  # FWHT kernel: one warp per row, butterflies in registers + shuffles

@@ -80,19 +80,77 @@ def _declare(L) -> None:
         fn.restype = c_int
 
 
+class _NoLaunchLibrary:
+    """Stands in for the kernel library while shapes are traced on meta tensors: every entry point returns 0."""
+
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        fn = lambda *a, **k: 0  # noqa: E731
+        fn.argtypes, fn.restype = None, None
+        return fn
+
+
+class _NoLaunchStatus:
+    ptr = None
+
+    def read(self) -> int:
+        return 0
+
+    def raise_if_set(self, what: str) -> None:
+        return None
+
+
+_NO_LAUNCH = {"depth": 0}
+_PENDING_DECLARATIONS: dict[str, list] = {}
+
+
+class no_launch:
+    """``with no_launch():`` the wrappers run their device code paths (buffers, saved tensors, autograd nodes) on
+    meta tensors and no kernel is launched: `lib()` hands out a stand-in, `stream_ptr()` is 0, the status word is
+    inert.  The memory simulator measures a step this way."""
+
+    def __enter__(self):
+        _NO_LAUNCH["depth"] += 1
+        return self
+
+    def __exit__(self, *exc):
+        _NO_LAUNCH["depth"] -= 1
+        return False
+
+
+def launches_disabled() -> bool:
+    return _NO_LAUNCH["depth"] > 0
+
+
+def on_device(t: torch.Tensor) -> bool:
+    """True for tensors that take the kernel code paths: CUDA tensors, and meta tensors inside `no_launch()`."""
+    return t.is_cuda or (t.is_meta and _NO_LAUNCH["depth"] > 0)
+
+
 def lib():
     global _LIB
+    if _NO_LAUNCH["depth"] > 0:
+        return _NoLaunchLibrary()
     if _LIB is None:
         if not os.path.exists(LIB_PATH):
             raise KernelError(
                 f"{LIB_PATH} is missing: run `python -m titan_b200.csrc.build` (needs nvcc; no GPU required)")
         _LIB = ctypes.CDLL(LIB_PATH)
         _declare(_LIB)
+    if _PENDING_DECLARATIONS:
+        for name, argtypes in list(_PENDING_DECLARATIONS.items()):
+            fn = getattr(_LIB, name)
+            fn.argtypes, fn.restype = argtypes, c_int
+        _PENDING_DECLARATIONS.clear()
     return _LIB
 
 
 def declare(name: str, argtypes: list) -> None:
     """Late declaration for entry points added by optional source files."""
+    if _NO_LAUNCH["depth"] > 0:
+        _PENDING_DECLARATIONS[name] = argtypes   # callers remember "declared": applied when the real library is used
+        return
     fn = getattr(lib(), name)
     fn.argtypes = argtypes
     fn.restype = c_int
@@ -129,6 +187,8 @@ _TLS = threading.local()
 
 def stream_ptr() -> int:
     """Current stream handle; also binds the calling thread to the current device inside the library."""
+    if _NO_LAUNCH["depth"] > 0:
+        return 0
     dev = torch.cuda.current_device()
     if getattr(_TLS, "device", None) != dev:
         fn = lib().tb_bind_device
@@ -177,6 +237,8 @@ _STATUS_CACHE: dict[int, StatusWord] = {}
 
 def shared_status() -> StatusWord:
     """One status word per device, checked lazily (e.g. at log steps) to avoid per-op syncs."""
+    if _NO_LAUNCH["depth"] > 0:
+        return _NoLaunchStatus()
     dev = torch.cuda.current_device()
     if dev not in _STATUS_CACHE:
         _STATUS_CACHE[dev] = StatusWord()

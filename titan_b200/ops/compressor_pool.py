@@ -80,6 +80,6 @@ class _PoolFn(torch.autograd.Function):
 def compressor_pool(kv: torch.Tensor, score: torch.Tensor, ape: torch.Tensor, ratio: int, head_dim: int,
                     overlap: bool) -> torch.Tensor:
     """kv, score [B, S, width] fp32, ape [ratio, width] fp32 → pooled [B, S / ratio, head_dim] fp32."""
-    if kv.is_cuda and kv.dtype == torch.float32 and score.dtype == torch.float32 and head_dim % 4 == 0:
+    if _lib.on_device(kv) and kv.dtype == torch.float32 and score.dtype == torch.float32 and head_dim % 4 == 0:
         return _PoolFn.apply(kv, score, ape.float(), ratio, head_dim, overlap)
     return compressor_pool_ref(kv, score, ape.float(), ratio, head_dim, overlap)

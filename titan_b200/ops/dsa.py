@@ -51,7 +51,7 @@ def lightning_indexer_topk_ref(q_idx, weights, k_idx, topk: int, pos_offset: int
 
 def _scoring_kernels_take(q_idx) -> bool:
     heads = q_idx.shape[2]
-    return (q_idx.is_cuda and q_idx.dtype in (torch.bfloat16, torch.float16) and heads <= 256
+    return ((q_idx.is_cuda or q_idx.is_meta) and q_idx.dtype in (torch.bfloat16, torch.float16) and heads <= 256
             and heads & (heads - 1) == 0 and q_idx.shape[3] % 8 == 0)
 
 
@@ -190,7 +190,7 @@ SELECTED_BACKWARD = True  # False: the dense chunked backward below (the oracle 
 
 
 def _selected_backward_takes(q_idx, k_idx) -> bool:
-    return (q_idx.is_cuda and q_idx.dtype == torch.bfloat16 and q_idx.shape[-1] == 128
+    return ((q_idx.is_cuda or q_idx.is_meta) and q_idx.dtype == torch.bfloat16 and q_idx.shape[-1] == 128
             and q_idx.shape[2] in (16, 32, 64))
 
 
@@ -202,7 +202,9 @@ def _indexer_selected_backward(q_idx, weights, k_idx, idx, g):
     B, S, H, D = q_idx.shape
     T, kk = k_idx.shape[1], idx.shape[-1]
     P, I = ctypes.c_void_p, ctypes.c_int
-    _lib.declare("tb_indexer_sel_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, P, P])
+    meta = q_idx.is_meta   # shapes only (memory simulation): same buffers, no launches
+    if not meta:
+        _lib.declare("tb_indexer_sel_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, P, P])
     pad = (-kk) % 128
     if pad:
         idx, g = F.pad(idx, (0, pad), value=-1), F.pad(g, (0, pad))
@@ -215,6 +217,8 @@ def _indexer_selected_backward(q_idx, weights, k_idx, idx, g):
         qb = q_idx[b].contiguous()
         kb = k_idx[b, :, 0].contiguous().to(qb.dtype)
         wb = weights[b].float().contiguous()
+        if meta:
+            continue
         rc = _lib.lib().tb_indexer_sel_bwd(qb.data_ptr(), kb.data_ptr(), idx[b].data_ptr(), g[b].data_ptr(),
                                            wb.data_ptr(), dq[b].data_ptr(), dw[b].data_ptr(), dk[b].data_ptr(),
                                            S, H, T, kk + pad, D, _lib.shared_status().ptr, _lib.stream_ptr())
@@ -231,7 +235,9 @@ def _indexer_dense_backward(q_idx, weights, k_idx, idx, g, chunk):
     B, S, H, D = q_idx.shape
     T = k_idx.shape[1]
     P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-    _lib.declare("tb_indexer_relu_bwd", [P, P, P, P, P, LL, I, I, I, P])
+    meta = q_idx.is_meta   # shapes only (memory simulation): same buffers, no launches
+    if not meta:
+        _lib.declare("tb_indexer_relu_bwd", [P, P, P, P, P, LL, I, I, I, P])
     safe = idx.clamp_min(0).long()
     dq = torch.empty_like(q_idx)
     dw = torch.empty(B, S, H, dtype=torch.float32, device=q_idx.device)
@@ -248,10 +254,11 @@ def _indexer_dense_backward(q_idx, weights, k_idx, idx, g, chunk):
             dx = torch.empty_like(x)
             dwc = torch.empty(sc * H, dtype=torch.float32, device=x.device)
             wc = weights[b, s0:s1].float().contiguous()
-            rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dense_g.data_ptr(), wc.data_ptr(), dx.data_ptr(),
-                                                dwc.data_ptr(), sc * H, H, T, _lib.dtype_code(x.dtype),
-                                                _lib.stream_ptr())
-            _lib.check(rc, "indexer_relu_bwd")
+            if not meta:
+                rc = _lib.lib().tb_indexer_relu_bwd(x.data_ptr(), dense_g.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+                                                    dwc.data_ptr(), sc * H, H, T, _lib.dtype_code(x.dtype),
+                                                    _lib.stream_ptr())
+                _lib.check(rc, "indexer_relu_bwd")
             dq[b, s0:s1] = torch.matmul(dx, kb).view(sc, H, D)
             dk[b] += torch.matmul(dx.t(), qc).float()
             dw[b, s0:s1] = dwc.view(sc, H)
@@ -305,6 +312,8 @@ def _values_are_key_prefix(k: torch.Tensor, v: torch.Tensor) -> bool:
     (one small device-to-host read; callers cache the answer per module)."""
     if v.shape[-1] > k.shape[-1] or v.shape[:-1] != k.shape[:-1]:
         return False
+    if k.is_meta:
+        return True   # shapes only (memory simulation): the absorb layout is the one that passes the shape test
     dv, t = v.shape[-1], k.shape[2]
     rows = sorted({0, t // 2, t - 1})
     with torch.no_grad():   # a probe, not part of the graph (under activation checkpointing it runs only once)
@@ -335,7 +344,7 @@ def sparse_mla_attention(q, k, v, idx, scale: float, chunk: int = 256, want_lse:
     that ``v`` is the latent part of ``k`` (None = check a few rows)."""
     B, H, S, _ = q.shape
     T, dv = k.shape[2], v.shape[-1]
-    if T >= KERNEL_RATIO * idx.shape[-1] and q.is_cuda:
+    if T >= KERNEL_RATIO * idx.shape[-1] and (q.is_cuda or q.is_meta):
         from titan_b200.ops.sparse_mla import sparse_mla_supported
 
         if sparse_mla_supported(q[0].transpose(0, 1), k[0, 0], F.pad(idx[0], (0, (-idx.shape[-1]) % 128)), dv):

@@ -28,7 +28,7 @@ def gemm_ref(a, b, a_mn=False, b_mn=False, out_dtype=None):
 
 
 def supported(a: torch.Tensor, b: torch.Tensor) -> bool:
-    return (a.is_cuda and a.dtype in (torch.bfloat16, torch.float16) and a.dtype == b.dtype
+    return (_lib.on_device(a) and a.dtype in (torch.bfloat16, torch.float16) and a.dtype == b.dtype
             and a.dim() == 2 and b.dim() == 2)
 
 
@@ -81,7 +81,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if b.stride(0) % 8 or b.data_ptr() % 16:
         b = _aligned_copy(b)
     status = _lib.shared_status()
-    ws = _workspace(a.device) if split_tail and policy != "single" else None
+    ws = _workspace(a.device) if split_tail and policy != "single" and a.is_cuda else None
     rc = _lib.lib().tb_gemm_auto(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                                  out.stride(0), int(a_mn), int(b_mn), _lib.dtype_code(a.dtype),
                                  int(out_dtype == torch.float32), int(accumulate), _POLICY[policy],

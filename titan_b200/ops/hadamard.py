@@ -42,6 +42,8 @@ class _HadamardFn(torch.autograd.Function):
 
 def _run(x: torch.Tensor, scale: float) -> torch.Tensor:
     global _DECLARED
+    if x.is_meta:   # shapes only (memory simulation)
+        return torch.empty_like(x.contiguous())
     if not _DECLARED:
         P = ctypes.c_void_p
         _lib.declare("tb_hadamard", [P, P, ctypes.c_longlong, ctypes.c_int, ctypes.c_float, ctypes.c_int, P])
@@ -59,6 +61,6 @@ def hadamard(x: torch.Tensor, scale: float | None = None) -> torch.Tensor:
     """``x @ H_n · scale`` over the last dim (default scale ``n^-0.5``: an orthonormal rotation)."""
     n = x.shape[-1]
     scale = n ** -0.5 if scale is None else scale
-    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and n in (64, 128, 256, 512):
+    if (x.is_cuda or x.is_meta) and x.dtype in (torch.bfloat16, torch.float16) and n in (64, 128, 256, 512):
         return _HadamardFn.apply(x, scale)
     return hadamard_ref(x, scale)

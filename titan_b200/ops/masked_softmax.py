@@ -76,7 +76,7 @@ def masked_softmax(s: torch.Tensor, allowed: torch.Tensor, scale: float = 1.0,
     """s [H, Sc, T] logits, allowed [Sc, T] bool, sink [H] | None → probabilities [H, Sc, T] in s.dtype."""
     T = s.shape[-1]
     vec = 4 if s.dtype == torch.float32 else 8
-    if s.is_cuda and s.dim() == 3 and s.dtype in _DTYPES and T % vec == 0 \
+    if _lib.on_device(s) and s.dim() == 3 and s.dtype in _DTYPES and T % vec == 0 \
             and allowed.dtype == torch.bool and allowed.shape == s.shape[1:]:
         return _MaskedSoftmax.apply(s, allowed, scale, sink)
     return masked_softmax_ref(s, allowed, scale, sink)

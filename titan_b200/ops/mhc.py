@@ -22,6 +22,8 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
+from titan_b200.ops import _lib
+
 __all__ = ["hc_split_sinkhorn", "hc_pre", "hc_post", "hc_head", "hc_pre_ref", "hc_post_ref", "hc_head_ref", "set_fused"]
 
 _FUSED = {"pre": False, "post": False}
@@ -82,7 +84,7 @@ def hc_pre(x, hc_fn, hc_scale, hc_base, hc_mult: int = 4, sinkhorn_iters: int = 
            norm_eps: float = 1e-6):
     """x [.., hc, D] → (y [.., D] in x.dtype, post [.., hc] fp32, comb [.., hc, hc] fp32)."""
     hc_fn, hc_scale, hc_base = _local(hc_fn), _local(hc_scale), _local(hc_base)
-    if _FUSED["pre"] and x.is_cuda and x.dtype == torch.bfloat16 and hc_mult == 4 and x.shape[-1] % 8 == 0:
+    if _FUSED["pre"] and _lib.on_device(x) and x.dtype == torch.bfloat16 and hc_mult == 4 and x.shape[-1] % 8 == 0:
         from titan_b200.ops import mhc_cuda
 
         return mhc_cuda.mhc_pre(x, hc_fn, hc_scale, hc_base, sinkhorn_iters, hc_eps, norm_eps)
@@ -91,7 +93,8 @@ def hc_pre(x, hc_fn, hc_scale, hc_base, hc_mult: int = 4, sinkhorn_iters: int = 
 
 def hc_post(x, residual, post, comb):
     """x [.., D], residual [.., hc, D], post [.., hc], comb [.., hc, hc] → [.., hc, D]."""
-    if _FUSED["post"] and x.is_cuda and x.dtype == torch.bfloat16 and residual.shape[-2] == 4 and x.shape[-1] % 8 == 0:
+    if (_FUSED["post"] and _lib.on_device(x) and x.dtype == torch.bfloat16 and residual.shape[-2] == 4
+            and x.shape[-1] % 8 == 0):
         from titan_b200.ops import mhc_cuda
 
         return mhc_cuda.mhc_post(x, residual, post, comb)
@@ -101,7 +104,7 @@ def hc_post(x, residual, post, comb):
 def hc_head(x, head_fn, head_scale, head_base, hc_eps: float = 1e-6, norm_eps: float = 1e-6):
     """Collapse the streams: x [.., hc, D] → [.., D] with weights ``sigmoid(mix·scale + base) + eps``."""
     head_fn, head_scale, head_base = _local(head_fn), _local(head_scale), _local(head_base)
-    if (_FUSED["pre"] and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-2] == 4 and x.shape[-1] % 8 == 0
+    if (_FUSED["pre"] and _lib.on_device(x) and x.dtype == torch.bfloat16 and x.shape[-2] == 4 and x.shape[-1] % 8 == 0
             and x.shape[-1] <= 8192):
         # the collapse is the "pre" third of `hc_pre` (same RMS, same sigmoid weights, same weighted sum) with no
         # post / comb outputs: run the fused kernel on parameters padded with zero rows (one Sinkhorn pass on zeros)

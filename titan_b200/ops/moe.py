@@ -31,6 +31,12 @@ ALIGN = 128
 _SCORE = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
 
 
+def _on_device(t: torch.Tensor) -> bool:
+    """CUDA tensors run the kernels; meta tensors follow the same path with the launches skipped, so shapes, saved
+    tensors and buffer sizes are those of a GPU run (the memory simulator relies on it)."""
+    return t.is_cuda or t.is_meta
+
+
 def capacity_for(num_pairs: int, num_experts: int) -> int:
     return (num_pairs + (ALIGN - 1) * num_experts + ALIGN - 1) // ALIGN * ALIGN
 
@@ -70,7 +76,7 @@ class _RouterFn(torch.autograd.Function):
         gate = torch.empty(T, k, dtype=torch.float32, device=logits.device)
         idx = torch.empty(T, k, dtype=torch.int64, device=logits.device)
         counts = torch.zeros(E, dtype=torch.int32, device=logits.device)
-        rc = _lib.lib().tb_router_topk(
+        rc = 0 if logits.is_meta else _lib.lib().tb_router_topk(
             logits.data_ptr(), _lib.ptr(bias.float().contiguous() if bias is not None else None),
             _lib.ptr(forced_idx.contiguous() if forced_idx is not None else None), gate.data_ptr(), idx.data_ptr(),
             counts.data_ptr(), None, T, E, k, _SCORE[score_func], int(route_norm), float(route_scale),
@@ -98,7 +104,7 @@ class _RouterFn(torch.autograd.Function):
 
 def router_topk(logits, k, *, bias=None, score_func="sigmoid", route_norm=False, route_scale=1.0, forced_idx=None):
     """→ (gate [T,k] fp32, idx [T,k] int64, counts [E] int32)."""
-    if not logits.is_cuda:
+    if not _on_device(logits):
         return router_topk_ref(logits, k, bias=bias, score_func=score_func, route_norm=route_norm,
                                route_scale=route_scale, forced_idx=forced_idx)
     return _RouterFn.apply(logits, bias, forced_idx, k, score_func, route_norm, route_scale)
@@ -131,11 +137,15 @@ def make_plan(idx: torch.Tensor, num_experts: int, capacity: int | None = None) 
     T, k = idx.shape
     P = T * k
     capacity = capacity or capacity_for(P, num_experts)
-    if not idx.is_cuda:
+    if not _on_device(idx):
         dest, counts, starts, offs = _plan_ref(idx, num_experts, capacity)
         return MoePlan(dest, counts, starts, offs, capacity, num_experts, k)
-    L = _lib.lib()
     dev = idx.device
+    if idx.is_meta:
+        dest = torch.empty(P, dtype=torch.int32, device=dev)
+        counts, starts, offs = (torch.empty(num_experts, dtype=torch.int32, device=dev) for _ in range(3))
+        return MoePlan(dest, counts, starts, offs, capacity, num_experts, k)
+    L = _lib.lib()
     nb = L.tb_moe_plan_blocks(P)
     scratch = torch.empty(max(nb, 1) * num_experts, dtype=torch.int32, device=dev)
     dest = torch.empty(P, dtype=torch.int32, device=dev)
@@ -156,6 +166,8 @@ def _ptr_array(tensors):
 
 def _gather_raw(x, plan: MoePlan, scale):
     buf = torch.empty(plan.capacity, x.shape[1], dtype=x.dtype, device=x.device)
+    if x.is_meta:
+        return buf
     L = _lib.lib()
     P = plan.dest.numel()
     rc = L.tb_moe_gather(x.data_ptr(), plan.dest.data_ptr(), _lib.ptr(scale), _ptr_array([buf]), 1, P, plan.top_k,
@@ -169,6 +181,8 @@ def _gather_raw(x, plan: MoePlan, scale):
 
 def _combine_raw(buf, plan: MoePlan, w, base, T):
     out = torch.empty(T, buf.shape[1], dtype=buf.dtype, device=buf.device)
+    if buf.is_meta:
+        return out
     rc = _lib.lib().tb_moe_combine(_ptr_array([buf]), 1, plan.dest.data_ptr(), _lib.ptr(w), _lib.ptr(base),
                                    out.data_ptr(), T, plan.top_k, buf.shape[1], plan.capacity,
                                    _lib.dtype_code(buf.dtype), _lib.stream_ptr())
@@ -179,6 +193,8 @@ def _combine_raw(buf, plan: MoePlan, w, base, T):
 def _pair_dot_raw(buf, plan: MoePlan, g):
     P = plan.dest.numel()
     d = torch.empty(P, dtype=torch.float32, device=buf.device)
+    if buf.is_meta:
+        return d
     rc = _lib.lib().tb_moe_pair_dot(_ptr_array([buf]), 1, plan.dest.data_ptr(), g.data_ptr(), d.data_ptr(), P,
                                     plan.top_k, buf.shape[1], plan.capacity, _lib.dtype_code(buf.dtype),
                                     _lib.stream_ptr())
@@ -230,7 +246,7 @@ class _CombineFn(torch.autograd.Function):
 
 def permute(x: torch.Tensor, plan: MoePlan, scale: torch.Tensor | None = None) -> torch.Tensor:
     """x [T, D] → padded expert-major [cap, D]; `scale` [T, k] multiplies every routed copy."""
-    if not x.is_cuda:
+    if not _on_device(x):
         buf = x.new_zeros(plan.capacity, x.shape[1])
         rows = x.repeat_interleave(plan.top_k, dim=0)
         if scale is not None:
@@ -242,7 +258,7 @@ def permute(x: torch.Tensor, plan: MoePlan, scale: torch.Tensor | None = None) -
 def combine(buf: torch.Tensor, plan: MoePlan, num_tokens: int, weights: torch.Tensor | None = None,
             base: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = base[t] + Σ_j buf[dest[t,j]] · weights[t,j]."""
-    if not buf.is_cuda:
+    if not _on_device(buf):
         rows = buf[plan.dest.long()].float()
         if weights is not None:
             rows = rows * weights.reshape(-1, 1).float()
@@ -312,6 +328,6 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor) -> torc
 
     Rows at or beyond ``offs[-1]`` are unused capacity: forward leaves them unwritten and backward ignores
     them, so callers must not read them (the MoE path never does: `combine` only follows `dest`)."""
-    if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16):
+    if not _on_device(x) or x.dtype not in (torch.bfloat16, torch.float16):
         return grouped_linear_ref(x, w, offs)
     return _GroupedLinearFn.apply(x, w, offs)

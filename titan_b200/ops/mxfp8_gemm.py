@@ -64,6 +64,8 @@ def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.T
     global _DECLARED
     M, K = aq.shape
     N = bq.shape[0]
+    if aq.is_meta and mxfp8_gemm_supported(M, N, K):   # shapes only (memory simulation)
+        return torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
     if not (aq.is_cuda and mxfp8_gemm_supported(M, N, K)):
         raise ValueError(f"mxfp8_gemm: unsupported problem M={M} N={N} K={K} on {aq.device}")
     if not _DECLARED:
@@ -95,7 +97,7 @@ def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb:
     (bf16, contiguous, at least as many rows as the result) receives the result in its leading rows."""
     global _GROUPED_DECLARED
     E = offs.numel()
-    if offs.dtype != torch.int32 or not offs.is_cuda:
+    if offs.dtype != torch.int32 or not (offs.is_cuda or offs.is_meta):
         raise ValueError("mxfp8_grouped_gemm: offs must be an int32 tensor on the device")
     M, K = aq.shape
     if mode == GROUP_B_ROWS:
@@ -109,6 +111,8 @@ def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb:
         ok = bq.shape[1] == K
     else:
         raise ValueError(f"mxfp8_grouped_gemm: unknown mode {mode}")
+    if ok and aq.is_meta and mxfp8_gemm_supported(M, N, K):   # shapes only (memory simulation)
+        return out if out is not None else torch.empty(rows_out, N, dtype=torch.bfloat16, device=aq.device)
     if not (ok and aq.is_cuda and mxfp8_gemm_supported(M, N, K)):
         raise ValueError(f"mxfp8_grouped_gemm: unsupported problem mode={mode} A={tuple(aq.shape)} B={tuple(bq.shape)} E={E}")
     if not _GROUPED_DECLARED:

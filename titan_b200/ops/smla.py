@@ -28,6 +28,7 @@ from torch.utils.checkpoint import checkpoint
 __all__ = ["smla_attention", "li_select"]
 
 
+from titan_b200.ops import _lib
 from titan_b200.ops.dsa import gather_rows
 
 DENSE_RATIO = 64  # a compressed stream at most this many times longer than k is attended densely with a mask
@@ -39,7 +40,7 @@ def _kernel_takes(q, kv_compress, compress_idx, window: int, ratio: int) -> bool
     sink when the head dim is a multiple of 128 (keys are values here: dq = dv = hd) and the compressed stream is long
     compared with what a query actually attends to."""
     hd, H = q.shape[-1], q.shape[2]
-    if not (q.is_cuda and q.dtype == torch.bfloat16 and H % 16 == 0 and hd % 128 == 0 and hd <= 512):
+    if not (_lib.on_device(q) and q.dtype == torch.bfloat16 and H % 16 == 0 and hd % 128 == 0 and hd <= 512):
         return False
     if kv_compress is None or ratio <= 1:
         return False
@@ -85,7 +86,7 @@ def _chunk(q, kv, sink, kvc, cidx, s0: int, koff: int, qpos0: int, window: int, 
     tpos = torch.arange(t0, s1 + koff, device=q.device).unsqueeze(0)
     outside = (tpos > kpos) | (tpos <= kpos - window)  # [Sc, W]
     dense_ok = cidx is None or (kvc is not None and kvc.shape[0] <= DENSE_RATIO * cidx.shape[1])
-    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and dense_ok:
+    if _lib.on_device(q) and q.dtype in (torch.bfloat16, torch.float16) and dense_ok:
         # One GEMM over [window keys | compressed keys], one kernel for mask + sink + softmax, one GEMM back: the shared
         # KV latent is key and value at once, so the concatenated key block serves both products.
         from titan_b200.ops.masked_softmax import masked_softmax

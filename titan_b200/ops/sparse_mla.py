@@ -49,7 +49,7 @@ def set_pipelined(on: bool) -> None:
 def sparse_mla_supported(q: torch.Tensor, kv: torch.Tensor, idx: torch.Tensor, dv: int) -> bool:
     """q [S, H, Dq], kv [T, Dq], idx [S, K]."""
     H, dq = q.shape[1], q.shape[2]
-    return (q.is_cuda and q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and H % 16 == 0
+    return ((q.is_cuda or q.is_meta) and q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and H % 16 == 0
             and dq % 64 == 0 and dq <= 576 and dv % 128 == 0 and dv <= min(512, dq) and idx.shape[1] % 128 == 0)
 
 
@@ -124,13 +124,16 @@ KERNEL_BACKWARD = True  # False: the chunked PyTorch backward below (the oracle 
 def sparse_mla_backward(q, kv, idx, g_out, lse, delta, scale: float, dv: int):
     """Gradients of queries and latent on the tensor cores (`csrc/attention/sparse_mla_bwd.cu`):
     → (dq [S, H, Dq] bf16, dkv [T, Dq] fp32)."""
-    _declare()
+    if not q.is_meta:
+        _declare()
     S, H, dq = q.shape
     T, K = kv.shape[0], idx.shape[1]
     q, kv, g_out = q.contiguous(), kv.contiguous(), g_out.contiguous()
     idx = idx.to(torch.int32).contiguous()
     dq_ = torch.empty_like(q)
     dkv = torch.zeros(T, dq, dtype=torch.float32, device=kv.device)
+    if q.is_meta:   # shapes only (memory simulation)
+        return dq_, dkv
     rc = _lib.lib().tb_sparse_mla_bwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), g_out.data_ptr(),
                                       lse.contiguous().data_ptr(), delta.contiguous().data_ptr(), dq_.data_ptr(),
                                       dkv.data_ptr(), S, H, T, K, dq, dv, float(scale),

@@ -8,7 +8,8 @@ checkpoint mode.  Static terms (parameter, gradient and optimizer shards, FSDP a
 reduce-scatter buffers) follow from `ParallelDims` arithmetic:
 
     params    Σ numel / shard(p) · store bytes          shard = fsdp·tp (dense), efsdp·ep·etp (experts), / pp
-    optim     2 · 4 B · local params (AdamW fp32 moments); 0 on the device with Swap/Virtual optimizers
+    optim     2 moments · local params: fp32 with the framework's fused AdamW, the storage dtype with the library
+              implementations; 0 on the device with Swap/Virtual optimizers
     gathered  FSDP only: unsharded compute copies that stay resident: every unit with
               ``fsdp_reshard_after_forward = never``, two units (current + prefetched) otherwise
     fsdp buf  all-gather output of the next unit + the gradient bucket of one unit (wire dtype of the chosen
@@ -43,6 +44,27 @@ from torch.utils._pytree import tree_flatten
 __all__ = ["MetaMemoryTracker", "MemoryReport", "estimate", "run_from_config"]
 
 GIB = 1024 ** 3
+
+
+def _meta_bincount(x, weights=None, minlength=0):
+    return torch.empty(max(int(minlength), 1), dtype=torch.int64 if weights is None else weights.dtype, device=x.device)
+
+
+def _meta_histc(x, bins=100, min=0, max=0):
+    return torch.empty(int(bins), dtype=x.dtype, device=x.device)
+
+
+def _meta_nonzero(x):
+    return torch.empty(x.numel(), x.dim(), dtype=torch.int64, device=x.device)   # upper bound: every element
+
+
+# Operators whose output shape depends on values have no meta kernel; the tracker only needs shapes, and for these
+# the shape (or a safe upper bound of it) follows from the arguments.
+_META_STAND_INS = {
+    torch.ops.aten.bincount.default: _meta_bincount,
+    torch.ops.aten.histc.default: _meta_histc,
+    torch.ops.aten.nonzero.default: _meta_nonzero,
+}
 
 
 class MetaMemoryTracker(TorchDispatchMode):
@@ -88,7 +110,13 @@ class MetaMemoryTracker(TorchDispatchMode):
         self.current -= n - new
 
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
-        out = func(*args, **(kwargs or {}))
+        try:
+            out = func(*args, **(kwargs or {}))
+        except NotImplementedError:
+            stand_in = _META_STAND_INS.get(func)
+            if stand_in is None:
+                raise
+            out = stand_in(*args, **(kwargs or {}))
         # storages that came IN with the arguments are not allocations of this op: a view of a parameter (``w.t()``)
         # shares the parameter's storage, which the static terms already count
         for leaf in tree_flatten((args, kwargs or {}))[0]:
@@ -189,14 +217,18 @@ def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad
     import torch.nn.functional as F
 
     b, s = training.local_batch_size, training.seq_len
-    tokens = torch.empty(b, s, dtype=torch.int64, device="meta")
+    tokens = torch.empty(b, s + num_mtp, dtype=torch.int64, device="meta")   # MTP depths read the look-ahead tokens
     labels = torch.empty(b, s + num_mtp, dtype=torch.int64, device="meta")
     real_sdpa = F.scaled_dot_product_attention
     F.scaled_dot_product_attention = _sdpa_stand_in
     hooks = []
     grads_live = {"bytes": 0, "at_peak": 0, "peak": 0}
+    from titan_b200.ops import _lib
+
     try:
-        with MetaMemoryTracker() as tr:
+        # the wrappers take their kernel code paths on the meta tensors (same buffers and saved tensors as on a GPU)
+        # with every launch a no-op
+        with _lib.no_launch(), MetaMemoryTracker() as tr:
             def on_grad(p):
                 keep = grad_keep.get(p, 1.0)
                 n = p.grad.numel() * p.grad.element_size()
@@ -278,7 +310,10 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
     rb = torch.empty((), dtype=_DT[cfg.training.mixed_precision_reduce]).element_size()
     bytes_params = int(local * sb)
     bytes_grads = int(local * sb)
-    opt_bytes = int(local * 8)  # two fp32 moments
+    # two moments: fp32 for the framework's fused AdamW, the parameters' storage dtype for the library implementations
+    # (`torch.optim.AdamW` allocates its state with `zeros_like(param)`)
+    moment_bytes = 4 if cfg.optimizer.implementation == "b200_fused" else sb
+    opt_bytes = int(local * 2 * moment_bytes)
     if cfg.optimizer.name == "Muon":
         opt_bytes = int(local * 4)
         notes.append("Muon keeps one momentum buffer for matrix params (AdamW moments for the rest are a few %)")
@@ -315,7 +350,28 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         else:
             shard = fsdp * (pd.tp if (p.dim() >= 2 and pd.tp_enabled) else 1)
         grad_keep[p] = 1.0 / shard
+    if fsdp > 1 and store_dt != param_dt:
+        model.to(param_dt)   # FSDP computes on gathered copies in the parameter dtype: so do the activations
     grads_at_peak = 0
+    # Fused expert parallelism sizes every expert-major buffer of a layer for the rows an owner rank may receive
+    # (capacity factor x the balanced load), not for the balanced load itself, and keeps two receive buffers of that
+    # size in symmetric memory.  The meta model routes locally, so its row capacity is replaced for the run.
+    from titan_b200.ops import moe as moe_ops
+
+    real_capacity = moe_ops.capacity_for
+    bytes_ep_workspace = 0
+    fused_ep = pd.ep_enabled and par.expert_parallel_comm_backend == "fused_p2p"
+    if fused_ep:
+        from titan_b200.ops.moe_comm import capacity_per_owner
+
+        factor = float(par.expert_parallel_capacity_factor)
+        moe_ops.capacity_for = lambda pairs, experts: capacity_per_owner(pairs, max(experts // pd.ep, 1), pd.ep, factor)
+        tok = cfg.training.local_batch_size * cfg.training.seq_len // max(pd.cp * pd.tp, 1)
+        topk = getattr(getattr(mc, "moe_args", None), "top_k", getattr(mc, "top_k", 1))
+        n_exp = getattr(getattr(mc, "moe_args", None), "num_experts", getattr(mc, "num_experts", pd.ep))
+        bytes_ep_workspace = 2 * moe_ops.capacity_for(tok * topk, n_exp) * mc.dim * pb
+        notes.append(f"fused expert parallelism: expert-major buffers hold {factor:g}x the balanced rows; "
+                     f"{bytes_ep_workspace / GIB:.2f} GiB of symmetric receive buffers")
     try:
         dyn, grads_at_peak = _measure_timeline(model, mc, cfg.training, loss_fn, cfg.training.num_mtp_modules,
                                                grad_keep)
@@ -326,6 +382,8 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         per_layer_act = {"full": 1, "selective": 10, "none": 24}[cfg.activation_checkpoint.mode]
         act = int(tok * d * pb * per_layer_act * L + tok * mc.vocab_size * (pb + 4))
         notes.append(f"activation term from the closed-form bound ({type(e).__name__}: {str(e)[:80]})")
+    finally:
+        moe_ops.capacity_for = real_capacity
     act = int(act / (pd.tp * pd.cp) / pd.pp)
     grads_at_peak = int(grads_at_peak / pd.pp)
     dyn_peak = act + grads_at_peak
@@ -355,6 +413,7 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
 
     # the optimizer step runs after backward with every local gradient present and no activation left
     at_step = bytes_params + bytes_grads + bytes_opt_dev
+    bytes_fsdp += bytes_ep_workspace
     total_bytes = max(bytes_params + bytes_opt_dev + bytes_fsdp + bytes_gathered + dyn_peak, at_step)
     budget = int(cfg.memory_sim.hbm_budget_gib * 1e9)
     return MemoryReport(
