@@ -431,7 +431,13 @@ def run_from_config(trainer_config) -> MemoryReport:
     import os
 
     world = int(os.environ.get("NGPU", os.environ.get("WORLD_SIZE", "1")))
-    rep = estimate(trainer_config, world)
+    try:
+        rep = estimate(trainer_config, world)
+    except ValueError as e:
+        if "world_size" in str(e) and "NGPU" not in os.environ and "WORLD_SIZE" not in os.environ:
+            raise ValueError(f"{e}; the memory estimate takes the job size from NGPU (or WORLD_SIZE): "
+                             f"e.g. NGPU=8 python -m titan_b200.entry ... --memory_sim.enable") from None
+        raise
     path = trainer_config.memory_sim.report_path
     if path:
         os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
