@@ -42,6 +42,19 @@ def test_async_tp2_reproduces_single_rank_step(tmp_path):
     assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)
 
 
+def test_async_tp2_with_two_sequences_per_rank_reproduces_single_rank_step(tmp_path):
+    """A local batch of several sequences runs the fused operators once per sequence."""
+    folder = str(tmp_path / "run")
+    common = ["--module", "llama3", "--config", "llama3_debugmodel", "--training.seq_len", "256", "--comm.backend",
+              "gloo", "--training.local_batch_size", "2", "--job.dump_folder", folder, "--checkpoint.enable",
+              "--checkpoint.interval", "1", "--training.steps", "2"]
+    ref = step_line(launch(common, 1, 29663), 2)
+    got = step_line(launch([*common, "--checkpoint.load_step", "1", "--parallelism.data_parallel_shard_degree", "1",
+                            "--parallelism.tensor_parallel_degree", "2",
+                            "--parallelism.enable_async_tensor_parallel"], 2, 29664), 2)
+    assert abs(got[0] - ref[0]) < 2e-3 and abs(got[1] - ref[1]) < 2e-3 * max(ref[1], 1.0), (got, ref)
+
+
 import pytest
 
 

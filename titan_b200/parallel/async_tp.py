@@ -30,7 +30,7 @@ import torch.nn.functional as F
 
 from titan_b200.ops import fused_comm
 
-__all__ = ["ag_multi_linear", "linear_rs", "enable_for_llama"]
+__all__ = ["ag_multi_linear", "linear_rs", "ag_multi_linear_batched", "linear_rs_batched", "enable_for_llama"]
 
 
 def _mm(a, b_t):
@@ -95,6 +95,22 @@ def linear_rs(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
     return _LinearRS.apply(x, w, group)
 
 
+def ag_multi_linear_batched(x: torch.Tensor, weights: list[torch.Tensor], group) -> list[torch.Tensor]:
+    """x [B, S/tp, K] → outputs [B, S, N_i].  The fused kernel gathers one sequence's rows in rank order, so a batch
+    runs one launch per sequence (a single sequence adds no copy)."""
+    if x.shape[0] == 1:
+        return [y.unsqueeze(0) for y in ag_multi_linear(x[0], weights, group)]
+    per_seq = [ag_multi_linear(x[b], weights, group) for b in range(x.shape[0])]
+    return [torch.stack([seq[i] for seq in per_seq]) for i in range(len(weights))]
+
+
+def linear_rs_batched(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
+    """x [B, S, K_local] → reduce-scattered [B, S/tp, N], one launch per sequence."""
+    if x.shape[0] == 1:
+        return linear_rs(x[0], w, group).unsqueeze(0)
+    return torch.stack([linear_rs(x[b], w, group) for b in range(x.shape[0])])
+
+
 def _local(p):
     return p.to_local() if hasattr(p, "to_local") else p
 
@@ -108,25 +124,21 @@ def enable_for_llama(model, tp_mesh) -> int:
     fused_comm.enable_for_group(group)
 
     def attn_forward(self, x, freqs_cis, attention_masks=None, positions=None):
-        if x.shape[0] != 1:
-            raise NotImplementedError("async tensor parallelism runs one sequence per rank (local batch size 1)")
-        xq, xk, xv = ag_multi_linear(x[0], [_local(self.wq.weight), _local(self.wk.weight), _local(self.wv.weight)],
-                                     group)
-        s = xq.shape[0]
-        xq = xq.view(1, s, -1, self.head_dim)
-        xk = xk.view(1, s, -1, self.head_dim)
-        xv = xv.view(1, s, -1, self.head_dim)
+        xq, xk, xv = ag_multi_linear_batched(
+            x, [_local(self.wq.weight), _local(self.wk.weight), _local(self.wv.weight)], group)
+        b, s = xq.shape[0], xq.shape[1]
+        xq = xq.view(b, s, -1, self.head_dim)
+        xk = xk.view(b, s, -1, self.head_dim)
+        xv = xv.view(b, s, -1, self.head_dim)
         xq, xk = apply_rotary_emb_complex(xq, xk, freqs_cis, positions)
         out = self.inner_attention(xq.transpose(1, 2), xk.transpose(1, 2), xv.transpose(1, 2),
                                    attn_mask=attention_masks)
-        out = out.transpose(1, 2).reshape(s, -1)
-        return linear_rs(out, _local(self.wo.weight), group).unsqueeze(0)
+        out = out.transpose(1, 2).reshape(b, s, -1)
+        return linear_rs_batched(out, _local(self.wo.weight), group)
 
     def ffn_forward(self, x):
-        if x.shape[0] != 1:
-            raise NotImplementedError("async tensor parallelism runs one sequence per rank (local batch size 1)")
-        g, u = ag_multi_linear(x[0], [_local(self.w1.weight), _local(self.w3.weight)], group)
-        return linear_rs(F.silu(g) * u, _local(self.w2.weight), group).unsqueeze(0)
+        g, u = ag_multi_linear_batched(x, [_local(self.w1.weight), _local(self.w3.weight)], group)
+        return linear_rs_batched(F.silu(g) * u, _local(self.w2.weight), group)
 
     n = 0
     for block in model.layers.values():

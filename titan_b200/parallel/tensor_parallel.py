@@ -212,8 +212,8 @@ class FusedRowwiseParallel(ParallelStyle):
     """`RowwiseParallel(output_layouts=Shard(1))` with the reduce-scatter fused into the GEMM: the weight keeps its
     input-feature shard, the forward multiplies the local activations and the epilogue of the GEMM stores every tile
     into the staging slot of the rank that owns those sequence rows (`titan_b200.parallel.async_tp.linear_rs`).
-    One sequence per rank takes the fused kernel; other batch shapes, biased linears and non-linear modules (the
-    embedding) fall back to the wrapped style or to a library reduce-scatter with the same result."""
+    [batch, sequence, features] inputs take the fused kernel, one launch per sequence; other shapes, biased linears
+    and non-linear modules (the embedding) fall back to the wrapped style or to a library reduce-scatter with the same result."""
 
     def __init__(self, fallback: ParallelStyle):
         super().__init__()
@@ -229,13 +229,13 @@ class FusedRowwiseParallel(ParallelStyle):
         group = device_mesh.get_group()
 
         def forward(x, _m=module):
-            from titan_b200.parallel.async_tp import linear_rs
+            from titan_b200.parallel.async_tp import linear_rs_batched
 
             w = _m.weight.to_local()
             if isinstance(x, DTensor):
                 x = x.to_local()
-            if x.dim() == 3 and x.shape[0] == 1:
-                return linear_rs(x[0].to(w.dtype), w, group).unsqueeze(0)
+            if x.dim() == 3:
+                return linear_rs_batched(x.to(w.dtype), w, group)   # one fused launch per sequence
             y = torch.nn.functional.linear(x, w)
             return DTensor.from_local(y, device_mesh, [Partial()]).redistribute(placements=[Shard(1)]).to_local()
 
