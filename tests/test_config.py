@@ -98,7 +98,12 @@ def test_example_scripts_parse_with_the_real_config_parser(tmp_path):
                PYTHONPATH=root)
     scripts = sorted(glob.glob(os.path.join(root, "examples", "*", "*.sh")))
     assert len(scripts) >= 10
-    for sh in scripts:
-        out = subprocess.run(["bash", sh], env=env, capture_output=True, text=True, cwd=str(tmp_path))
-        assert out.returncode == 0, f"{sh}:\n{out.stdout[-2000:]}\n{out.stderr[-2000:]}"
-        assert '"_type": "TrainerConfig"' in out.stdout, sh
+    from concurrent.futures import ThreadPoolExecutor
+
+    def run(sh):   # the scripts are independent: a few at a time (each child spends seconds importing torch)
+        return sh, subprocess.run(["bash", sh], env=env, capture_output=True, text=True, cwd=str(tmp_path))
+
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        for sh, out in pool.map(run, scripts):
+            assert out.returncode == 0, f"{sh}:\n{out.stdout[-2000:]}\n{out.stderr[-2000:]}"
+            assert '"_type": "TrainerConfig"' in out.stdout, sh
