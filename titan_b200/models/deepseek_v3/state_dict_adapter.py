@@ -19,7 +19,7 @@ import re
 from typing import Any
 
 import torch
-from torch.distributed.tensor import DTensor, Shard
+from torch.distributed.tensor import DTensor, Replicate, Shard
 
 from titan_b200.protocols.state_dict_adapter import StateDictAdapter
 
@@ -37,16 +37,22 @@ class MoEStateDictAdapter(StateDictAdapter):
 
     @staticmethod
     def _local_expert_range(t) -> tuple[int, int, Any]:
-        """(first expert, count, local tensor) for a possibly dim-0-sharded DTensor."""
+        """(first expert, count, local tensor) for a possibly sharded DTensor.  Shards of the expert dim (0) stay
+        local: every rank exports its own experts.  A weight that is also split inside the expert (expert tensor
+        parallelism, or FSDP on dim 1 when a rank has fewer experts than shard ranks) is gathered over those mesh
+        dims first (a collective: every rank of the mesh exports together, as it does under DCP)."""
         if isinstance(t, DTensor):
+            inner = [isinstance(pl, Shard) and pl.dim != 0 for pl in t.placements]
+            if any(inner):
+                t = t.redistribute(placements=[Replicate() if g else pl for g, pl in zip(inner, t.placements)])
             local = t.to_local()
             first = 0
-            for mesh_dim, pl in enumerate(t.placements):
+            stride = 1   # several mesh dims may split the expert dim: the last one varies fastest
+            for mesh_dim in reversed(range(len(t.placements))):
+                pl = t.placements[mesh_dim]
                 if isinstance(pl, Shard) and pl.dim == 0:
-                    per = t.shape[0] // t.device_mesh.size(mesh_dim)
-                    first = t.device_mesh.get_local_rank(mesh_dim) * per
-                elif isinstance(pl, Shard):
-                    raise NotImplementedError("HF export of experts sharded beyond dim 0 needs a full_tensor() first")
+                    first += t.device_mesh.get_local_rank(mesh_dim) * stride * local.shape[0]
+                    stride *= t.device_mesh.size(mesh_dim)
             return first, local.shape[0], local
         return 0, t.shape[0], t
 
