@@ -100,6 +100,20 @@ def test_no_launch_mode_restores_the_library_and_keeps_declarations():
     _lib._PENDING_DECLARATIONS.pop("tb_example_entry")
 
 
+def test_tracker_gives_value_dependent_ops_a_shape_on_meta_tensors():
+    from titan_b200.simulator.memory import MetaMemoryTracker
+
+    idx = torch.empty(64, dtype=torch.int64, device="meta")
+    with MetaMemoryTracker() as tr:
+        counts = torch.bincount(idx, minlength=8)
+        hist = torch.histc(torch.empty(64, device="meta"), bins=16, min=0, max=15)
+        where = torch.nonzero(torch.empty(4, 5, device="meta"))
+        assert counts.shape == (8,) and hist.shape == (16,) and where.shape == (20, 2)   # nonzero: upper bound
+        assert tr.current == 8 * 8 + 16 * 4 + 20 * 2 * 8
+    with pytest.raises(NotImplementedError), MetaMemoryTracker():
+        torch.empty(3, device="meta").tolist()   # a host read has no stand-in: callers must not need the values
+
+
 def test_peak_is_not_activations_plus_gradients():
     """On one GPU the peak sits at the start of backward: hardly any gradient exists there."""
     from titan_b200.config.manager import resolve_recipe
