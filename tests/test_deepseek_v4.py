@@ -427,3 +427,43 @@ def test_kernel_path_key_lists_match_the_dense_oracle_on_cpu(monkeypatch):
     cmp = probs[..., S:].sum(dim=1) / H
     want = torch.gather(cmp, -1, (idx - S).clamp(min=0)).masked_fill(idx < 0, 0.0)
     torch.testing.assert_close(dist, want.to(dist.dtype), rtol=1e-4, atol=1e-6)
+
+
+def test_compile_plan_reproduces_the_eager_steps_under_fsdp(tmp_path):
+    """`--compile.enable` compiles the projections around the attention cores and the router / shared experts in
+    place (the cores and the routed experts stay eager): two FSDP ranks must log the losses of the eager run, and the
+    checkpoint keeps its parameter names."""
+    common = [*_BASE, "--training.steps", "2", "--metrics.log_freq", "1", "--debug.seed", "0"]
+    eager = _launch([*common, "--job.dump_folder", str(tmp_path / "eager")], 2, 29566)
+    comp = _launch([*common, "--job.dump_folder", str(tmp_path / "compiled"), "--compile.enable",
+                    "--compile.backend", "aot_eager"], 2, 29567)
+    assert "compiled" in comp and "DeepSeek-V4 submodules" in comp
+    a, b = _losses(eager), _losses(comp)
+    assert len(a) == 2 and len(b) == 2
+    assert all(abs(x - y) < 1e-3 for x, y in zip(a, b)), (a, b)
+
+
+def test_compile_plan_skips_cores_experts_and_norms():
+    from types import SimpleNamespace
+
+    from titan_b200.models.deepseek_v4.parallelize import apply_compile
+    from titan_b200.protocols.model_spec import get_model_spec
+
+    spec = get_model_spec("deepseek_v4", "smoketest")
+    with torch.device("meta"):
+        model = spec.model.build()
+    compiled = []
+    import torch.nn as nn
+
+    real = nn.Module.compile
+    nn.Module.compile = lambda self, *a, **k: compiled.append(self)
+    try:
+        n = apply_compile(model, SimpleNamespace(backend="eager"))
+        n_tnd = apply_compile(model, SimpleNamespace(backend="eager"), use_global_tnd=True)
+    finally:
+        nn.Module.compile = real
+    names = {type(m).__name__ for m in compiled}
+    assert n == len(compiled) - n_tnd and n > n_tnd > 0
+    assert "InnerAttention" not in names and not any("Experts" in t and "Shared" not in t for t in names), names
+    assert not any("norm" in t.lower() for t in names), names
+    assert {"PreAttention", "PostAttention"} <= names

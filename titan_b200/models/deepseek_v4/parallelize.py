@@ -43,6 +43,7 @@ from titan_b200.parallel.tensor_parallel import (
     parallelize_module,
 )
 from titan_b200.protocols.converter import has_converter
+from titan_b200.utils.logging import logger
 
 __all__ = ["parallelize_deepseekv4", "apply_non_moe_tp", "validate_parallelism"]
 
@@ -134,6 +135,35 @@ def apply_non_moe_tp(model: nn.Module, tp_mesh, *, loss_parallel: bool) -> None:
         parallelize_module(block, tp_mesh, plan)
 
 
+def apply_compile(model: nn.Module, compile_config, *, use_global_tnd: bool = False) -> int:
+    """Per-submodule compile plan (opt-in, `--compile.enable`): inside every block the projections around the attention
+    core (`pre_attention`, `post_attention`) and the MoE's router and shared experts are compiled in place; the
+    attention core and the routed experts are not (hand-written kernels with data-dependent shapes, and the experts
+    carry FSDP hooks that a compiled region must not swallow), nor are the norms (kernel converters) and the
+    hyper-connection mixing, which the block runs itself.  With packed streams (`use_global_tnd`) the stream layout
+    is data dependent in `pre_attention`, which then stays eager as well.  `nn.Module.compile` keeps the module
+    objects, so parameter names and checkpoints do not change.  Returns the number of compiled submodules.
+
+    Parity: torchtitan_npu/models/deepseek_v4/parallelize.py:958-1044 (compile around the experts' hooks, skip the
+    inner attention, the hyper-connection pre step and the fused norms)."""
+    skip = {"attention": {"inner_attention"} | ({"pre_attention"} if use_global_tnd else set()), "moe": {"experts"}}
+    count = 0
+    for block in model.layers.values():
+        if block is None:
+            continue
+        inner = getattr(block, "_checkpoint_wrapped_module", block)
+        for parent_name, skipped in skip.items():
+            parent = getattr(inner, parent_name, None)
+            if parent is None:
+                continue
+            for name, child in parent.named_children():
+                if name in skipped or "norm" in type(child).__name__.lower():
+                    continue
+                child.compile(backend=compile_config.backend, fullgraph=False)
+                count += 1
+    return count
+
+
 def parallelize_deepseekv4(model: nn.Module, *, parallel_dims, training, model_converters=None, parallelism=None,
                            compile_config=None, ac_config=None, dump_folder: str = ""):
     pd = parallel_dims
@@ -165,8 +195,8 @@ def parallelize_deepseekv4(model: nn.Module, *, parallel_dims, training, model_c
     if ac_config is not None and ac_config.mode != "none":
         apply_ac(model, ac_config)
     if compile_config is not None and compile_config.enable and "model" in compile_config.components:
-        raise NotImplementedError("DeepSeek-V4 blocks run as eager PyTorch + CUDA kernels; a tracing compiler is not "
-                                  "part of this path")
+        n = apply_compile(model, compile_config, use_global_tnd=bool(getattr(model.config, "use_global_tnd", False)))
+        logger.info("compiled %d DeepSeek-V4 submodules around the attention cores and the experts", n)
     if pd.fsdp_enabled or pd.ep_enabled:
         names = ("dp_replicate", "fsdp") if pd.dp_replicate_enabled else None
         dp_mesh = pd.get_mesh(names) if names else pd.get_optional_mesh("fsdp")
