@@ -98,6 +98,9 @@ CASES: tuple[Case, ...] = (
     _c("deepseek_v4_fsdp_ep", "deepseek_v4", "deepseek_v4_smoketest",
        ("--parallelism.expert_parallel_degree", "2"), cpu_ok=True),
     _c("deepseek_v4_muon", "deepseek_v4", "deepseek_v4_smoketest", ("--optimizer.name", "Muon"), cpu_ok=True),
+    _c("deepseek_v4_compile", "deepseek_v4", "deepseek_v4_smoketest",
+       ("--compile.enable", "--compile.backend", "aot_eager"), cpu_ok=True,
+       note="per-submodule compile plan around the attention cores and the experts"),
     # ---- Qwen3
     _c("qwen3_base", "qwen3", "qwen3_debugmodel", cpu_ok=True),
     _c("qwen3_moe_ep", "qwen3", "qwen3_debugmodel_moe", ("--parallelism.expert_parallel_degree", "2"), cpu_ok=True),
