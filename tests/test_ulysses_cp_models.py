@@ -12,8 +12,8 @@ def _common(module, config, folder):
             "--checkpoint.interval", "1", "--training.steps", "2"]
 
 
-@pytest.mark.parametrize("module,config,port", [("llama3", "llama3_debugmodel", 29760),
-                                                ("qwen3", "qwen3_debugmodel", 29770)])
+# Qwen3 under CP2 is covered by tests/test_qwen3.py (same two-launch comparison)
+@pytest.mark.parametrize("module,config,port", [("llama3", "llama3_debugmodel", 29760)])
 def test_cp2_reproduces_single_rank(tmp_path, module, config, port):
     common = _common(module, config, str(tmp_path / "run"))
     ref = step_line(launch(common, 1, port), 2)
