@@ -86,6 +86,73 @@ def test_estimate_matches_measured_peak_of_other_models(module, recipe, edit, wo
     assert not any("closed-form" in n for n in rep.notes), rep.notes
 
 
+def _llama_noac(cfg):
+    cfg.activation_checkpoint.mode = "none"
+
+
+# (module, recipe, edit, world, measured ms per step on B200s, relative band)
+MEASURED_STEPS = [
+    ("llama3", "llama3_8b", None, 1, 444.0, 0.08),
+    ("llama3", "llama3_8b", _llama_noac, 1, 435.0, 0.08),
+    ("llama3", "llama3_8b_mxfp8", None, 1, 347.5, 0.08),
+    ("llama3", "llama3_8b", None, 8, 452.0, 0.10),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(8192, 1), 1, 535.0, 0.10),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(32768, 1), 1, 2080.0, 0.10),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(65536, 2), 2, 2411.0, 0.10),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(131072, 4), 4, 3060.0, 0.10),
+    ("deepseek_v4", "debug_deepseek_v4_single_node_1b", _v4_mini_as_benchmarked, 1, 259.0, 0.15),
+]
+
+
+@pytest.mark.parametrize("module,recipe,edit,world,want_ms,band", MEASURED_STEPS,
+                         ids=[f"{r}-{getattr(e, '__name__', 'as_is') if e else 'as_is'}-{w}gpu-{int(ms)}ms"
+                              for _, r, e, w, ms, _ in MEASURED_STEPS])
+def test_step_time_estimate_matches_measured_steps(module, recipe, edit, world, want_ms, band):
+    """Constants of the cost model are calibrated on kernel timings of these runs; the band says how far the whole-step
+    estimate may drift from the measured step."""
+    from titan_b200.config.manager import resolve_recipe
+    from titan_b200.simulator.memory import estimate
+
+    cfg = resolve_recipe(module, recipe)
+    if edit is not None:
+        edit(cfg)
+    rep = estimate(cfg, world)
+    got = rep.step_seconds_estimate * 1e3
+    assert abs(got / want_ms - 1) < band, (got, want_ms, rep.summary())
+    tokens = cfg.training.local_batch_size * cfg.training.seq_len * world // max(
+        cfg.parallelism.context_parallel_degree * cfg.parallelism.tensor_parallel_degree, 1)
+    assert abs(rep.tokens_per_second_estimate / (tokens / rep.step_seconds_estimate) - 1) < 1e-6
+
+
+def test_step_time_of_expert_parallel_recipes_is_a_lower_bound():
+    from titan_b200.config.manager import resolve_recipe
+    from titan_b200.simulator.memory import estimate
+
+    rep = estimate(resolve_recipe("deepseek_v3", "deepseek_v3_16b_ep8"), 8)
+    assert 0.4 * 415.0 < rep.step_seconds_estimate * 1e3 < 415.0      # measured: 415 ms on 8 B200s
+    assert any("lower bound" in n for n in rep.notes)
+
+
+def test_cost_model_prices_contractions_views_and_skipped_launches():
+    from titan_b200.ops import _lib
+    from titan_b200.simulator.cost import Peaks, StepCost
+    from titan_b200.simulator.memory import MetaMemoryTracker
+
+    cost = StepCost(Peaks())
+    a = torch.empty(4096, 4096, dtype=torch.bfloat16, device="meta")
+    with _lib.no_launch(on_call=cost.on_library_call), MetaMemoryTracker(cost):
+        b = a @ a                      # 137 GFLOP
+        _ = b.t()                      # a view: free, but the host dispatches it
+        _ = b + 1                      # 64 MiB moved
+        _lib.lib().tb_gemm_auto(0, 0, 0, 4096, 4096, 4096)
+        _lib.note_skipped_launch("tb_sparse_mla_bwd", (None,) * 8 + (4096, 16, 8192, 2048, 576, 512))
+    p = cost.peaks
+    assert abs(cost.by_kind["matmul"] - 2 * 4096 ** 3 / (p.bf16_tflops * 1e12 * p.gemm_efficiency)) < 1e-9
+    assert abs(cost.by_kind["gemm_tcgen05"] - cost.by_kind["matmul"]) < 1e-9
+    assert abs(cost.by_kind["sparse_attention"] - 7.6e-3) < 1e-6
+    assert cost.free_ops >= 1 and cost.by_kind["elementwise"] > 0
+
+
 def test_no_launch_mode_restores_the_library_and_keeps_declarations():
     from titan_b200.ops import _lib
 

@@ -96,6 +96,7 @@ def mx_quantize(x: torch.Tensor, axis: int = -1, round_mode: str = "rceil"):
     q = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
     s = torch.empty((rows, cols // BLOCK) if axis == -1 else (rows // BLOCK, cols), dtype=torch.uint8, device=x.device)
     if x.is_meta:   # shapes only (memory simulation)
+        _lib.note_skipped_launch("tb_mx_quantize", (None, None, None, rows, cols))
         return q.view(torch.float8_e4m3fn), s
     _declare()
     rc = _lib.lib().tb_mx_quantize(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, cols, axis,
@@ -143,6 +144,7 @@ def mx_quantize_dual(x: torch.Tensor, round_mode: str = "rceil", *, rows: bool =
         s2t = torch.empty(C, R // BLOCK, **u8) if transposed else None
     f8 = lambda t: t.view(torch.float8_e4m3fn) if t is not None else None  # noqa: E731
     if x.is_meta:   # shapes only (memory simulation)
+        _lib.note_skipped_launch("tb_mx_quantize_dual", (None, None, None, None, None, R, C))
         return f8(q1), s1, f8(q2t), s2t
     p = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
     rc = _lib.lib().tb_mx_quantize_dual(x.data_ptr(), p(q1), p(s1), p(q2t), p(s2t), R, C,
@@ -159,6 +161,7 @@ def mx_dequantize(q: torch.Tensor, scales: torch.Tensor, axis: int = -1, dtype=t
     rows, cols = q.shape
     out = torch.empty(rows, cols, dtype=torch.bfloat16, device=q.device)
     if q.is_meta:   # shapes only (memory simulation)
+        _lib.note_skipped_launch("tb_mx_dequantize", (None, None, None, rows, cols))
         return out
     _declare()
     rc = _lib.lib().tb_mx_dequantize(q.view(torch.uint8).data_ptr(), scales.contiguous().data_ptr(), out.data_ptr(),

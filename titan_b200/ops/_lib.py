@@ -86,7 +86,13 @@ class _NoLaunchLibrary:
     def __getattr__(self, name):
         if name.startswith("__"):
             raise AttributeError(name)
-        fn = lambda *a, **k: 0  # noqa: E731
+
+        def fn(*args, **kwargs):
+            sink = _NO_LAUNCH.get("sink")
+            if sink is not None:
+                sink(name, args)            # a cost model may price the launch from its name and integer arguments
+            return 0
+
         fn.argtypes, fn.restype = None, None
         return fn
 
@@ -110,13 +116,28 @@ class no_launch:
     meta tensors and no kernel is launched: `lib()` hands out a stand-in, `stream_ptr()` is 0, the status word is
     inert.  The memory simulator measures a step this way."""
 
+    def __init__(self, on_call=None):
+        self.on_call = on_call              # optional ``(entry point name, args)`` callback for every skipped launch
+
     def __enter__(self):
         _NO_LAUNCH["depth"] += 1
+        self._outer_sink = _NO_LAUNCH.get("sink")
+        if self.on_call is not None:
+            _NO_LAUNCH["sink"] = self.on_call
         return self
 
     def __exit__(self, *exc):
         _NO_LAUNCH["depth"] -= 1
+        _NO_LAUNCH["sink"] = self._outer_sink
         return False
+
+
+def note_skipped_launch(name: str, args: tuple) -> None:
+    """A wrapper that returns early on meta tensors reports the launch it skipped (same form as the stand-in
+    library: entry point name and its arguments, pointers may be None)."""
+    sink = _NO_LAUNCH.get("sink")
+    if sink is not None:
+        sink(name, args)
 
 
 def launches_disabled() -> bool:

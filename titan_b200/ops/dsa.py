@@ -218,6 +218,7 @@ def _indexer_selected_backward(q_idx, weights, k_idx, idx, g):
         kb = k_idx[b, :, 0].contiguous().to(qb.dtype)
         wb = weights[b].float().contiguous()
         if meta:
+            _lib.note_skipped_launch("tb_indexer_sel_bwd", (None,) * 8 + (S, H, T, kk + pad, D))
             continue
         rc = _lib.lib().tb_indexer_sel_bwd(qb.data_ptr(), kb.data_ptr(), idx[b].data_ptr(), g[b].data_ptr(),
                                            wb.data_ptr(), dq[b].data_ptr(), dw[b].data_ptr(), dk[b].data_ptr(),

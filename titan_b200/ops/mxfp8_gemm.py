@@ -65,6 +65,7 @@ def mxfp8_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.T
     M, K = aq.shape
     N = bq.shape[0]
     if aq.is_meta and mxfp8_gemm_supported(M, N, K):   # shapes only (memory simulation)
+        _lib.note_skipped_launch("tb_mxfp8_gemm", (None, None, None, None, None, M, N, K))
         return torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
     if not (aq.is_cuda and mxfp8_gemm_supported(M, N, K)):
         raise ValueError(f"mxfp8_gemm: unsupported problem M={M} N={N} K={K} on {aq.device}")
@@ -112,6 +113,7 @@ def mxfp8_grouped_gemm(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb:
     else:
         raise ValueError(f"mxfp8_grouped_gemm: unknown mode {mode}")
     if ok and aq.is_meta and mxfp8_gemm_supported(M, N, K):   # shapes only (memory simulation)
+        _lib.note_skipped_launch("tb_mxfp8_grouped_gemm", (None, None, None, None, None, M, N, K))
         return out if out is not None else torch.empty(rows_out, N, dtype=torch.bfloat16, device=aq.device)
     if not (ok and aq.is_cuda and mxfp8_gemm_supported(M, N, K)):
         raise ValueError(f"mxfp8_grouped_gemm: unsupported problem mode={mode} A={tuple(aq.shape)} B={tuple(bq.shape)} E={E}")

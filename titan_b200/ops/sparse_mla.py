@@ -133,6 +133,7 @@ def sparse_mla_backward(q, kv, idx, g_out, lse, delta, scale: float, dv: int):
     dq_ = torch.empty_like(q)
     dkv = torch.zeros(T, dq, dtype=torch.float32, device=kv.device)
     if q.is_meta:   # shapes only (memory simulation)
+        _lib.note_skipped_launch("tb_sparse_mla_bwd", (None,) * 8 + (S, H, T, K, dq, dv))
         return dq_, dkv
     rc = _lib.lib().tb_sparse_mla_bwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), g_out.data_ptr(),
                                       lse.contiguous().data_ptr(), delta.contiguous().data_ptr(), dq_.data_ptr(),

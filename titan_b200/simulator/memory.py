@@ -70,11 +70,12 @@ _META_STAND_INS = {
 class MetaMemoryTracker(TorchDispatchMode):
     """Tracks live bytes of storages created while the mode is active (works on meta tensors)."""
 
-    def __init__(self):
+    def __init__(self, cost=None):
         super().__init__()
         self.current = 0
         self.peak = 0
         self._seen: dict[int, int] = {}
+        self.cost = cost   # optional `simulator.cost.StepCost`: prices every operator that passes through
 
     def _release(self, key: int) -> None:
         self.current -= self._seen.pop(key, 0)
@@ -117,6 +118,8 @@ class MetaMemoryTracker(TorchDispatchMode):
             if stand_in is None:
                 raise
             out = stand_in(*args, **(kwargs or {}))
+        if self.cost is not None:
+            self.cost.on_op(func, args, kwargs or {}, out)
         # storages that came IN with the arguments are not allocations of this op: a view of a parameter (``w.t()``)
         # shares the parameter's storage, which the static terms already count
         for leaf in tree_flatten((args, kwargs or {}))[0]:
@@ -155,6 +158,11 @@ class MemoryReport:
     bytes_gathered_params: int = 0
     bytes_dynamic_peak: int = 0
     bytes_grads_at_peak: int = 0
+    step_seconds_estimate: float = 0.0       # 0 when the step could not be traced
+    tokens_per_second_estimate: float = 0.0  # whole job
+    flops_per_rank_step: float = 0.0
+    seconds_by_kind: dict = field(default_factory=dict)
+    operators_per_step: int = 0              # dispatched operators + library launches of the traced step
 
     def summary(self) -> str:
         g = lambda b: f"{b / GIB:8.2f} GiB"  # noqa: E731
@@ -170,6 +178,11 @@ class MemoryReport:
             f"  link traffic/step {json.dumps({k: round(v / GIB, 3) for k, v in self.comm_bytes_per_step.items()})} GiB"
             f" ≈ {self.comm_seconds_per_step * 1e3:.1f} ms at link rate",
         ]
+        if self.step_seconds_estimate > 0:
+            top = ", ".join(f"{k} {v * 1e3:.0f} ms" for k, v in list(self.seconds_by_kind.items())[:6])
+            lines.append(f"  step time (est.)  {self.step_seconds_estimate * 1e3:8.1f} ms   "
+                         f"{self.tokens_per_second_estimate:,.0f} tokens/s for the job   "
+                         f"{self.flops_per_rank_step / 1e12:.0f} TFLOP per rank   ({top})")
         return "\n".join(lines + [f"  note: {n}" for n in self.notes])
 
     def to_json(self) -> str:
@@ -181,6 +194,9 @@ _DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.fl
 
 def _is_expert(name: str) -> bool:
     return ".experts." in name and "shared_experts" not in name
+
+
+_ACTIVE_COST: list = [None]   # the step-cost model of the run in progress (the attention stand-in reports to it)
 
 
 class _FlashStandIn(torch.autograd.Function):
@@ -198,11 +214,15 @@ class _FlashStandIn(torch.autograd.Function):
             out = torch.empty(*q.shape[:-1], v.shape[-1], dtype=q.dtype, device=q.device)
         lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
         ctx.save_for_backward(q, k, v, out, lse)
+        if _ACTIVE_COST[0] is not None:
+            _ACTIVE_COST[0].on_dense_attention(q, k, backward=False)
         return out
 
     @staticmethod
     def backward(ctx, g):
         q, k, v, _, _ = ctx.saved_tensors
+        if _ACTIVE_COST[0] is not None:
+            _ACTIVE_COST[0].on_dense_attention(q, k, backward=True)
         return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
@@ -210,7 +230,8 @@ def _sdpa_stand_in(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scal
     return _FlashStandIn.apply(q, k, v)
 
 
-def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad_keep: dict) -> tuple[int, int]:
+def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad_keep: dict,
+                      cost=None) -> tuple[int, int]:
     """One forward + backward on meta tensors.  Returns (peak bytes of activations + gradients-so-far, gradient
     bytes inside that peak).  ``grad_keep[param] = fraction`` of a parameter's gradient that stays on this rank once
     it has been reduced (1 on one GPU, 1 / fsdp under FSDP, ...)."""
@@ -228,7 +249,9 @@ def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad
     try:
         # the wrappers take their kernel code paths on the meta tensors (same buffers and saved tensors as on a GPU)
         # with every launch a no-op
-        with _lib.no_launch(), MetaMemoryTracker() as tr:
+        _ACTIVE_COST[0] = cost
+        with _lib.no_launch(on_call=cost.on_library_call if cost is not None else None), \
+                MetaMemoryTracker(cost) as tr:
             def on_grad(p):
                 keep = grad_keep.get(p, 1.0)
                 n = p.grad.numel() * p.grad.element_size()
@@ -247,6 +270,7 @@ def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad
             loss.backward()
             peak = tr.peak
     finally:
+        _ACTIVE_COST[0] = None
         F.scaled_dot_product_attention = real_sdpa
         for h in hooks:
             h.remove()
@@ -372,9 +396,16 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         bytes_ep_workspace = 2 * moe_ops.capacity_for(tok * topk, n_exp) * mc.dim * pb
         notes.append(f"fused expert parallelism: expert-major buffers hold {factor:g}x the balanced rows; "
                      f"{bytes_ep_workspace / GIB:.2f} GiB of symmetric receive buffers")
+    from titan_b200.simulator.cost import StepCost
+
+    cost = StepCost()
+    if fused_ep:
+        # the grouped products only touch the rows in use, not the capacity the buffers are sized for
+        tok_pairs = cfg.training.local_batch_size * cfg.training.seq_len * max(int(topk), 1)
+        cost.grouped_rows_scale = real_capacity(tok_pairs, n_exp) / max(moe_ops.capacity_for(tok_pairs, n_exp), 1)
     try:
         dyn, grads_at_peak = _measure_timeline(model, mc, cfg.training, loss_fn, cfg.training.num_mtp_modules,
-                                               grad_keep)
+                                               grad_keep, cost)
         act = max(dyn - grads_at_peak, 0)
     except Exception as e:  # an op without a meta kernel: fall back to a closed-form bound
         L, d = mc.n_layers, mc.dim
@@ -382,6 +413,7 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         per_layer_act = {"full": 1, "selective": 10, "none": 24}[cfg.activation_checkpoint.mode]
         act = int(tok * d * pb * per_layer_act * L + tok * mc.vocab_size * (pb + 4))
         notes.append(f"activation term from the closed-form bound ({type(e).__name__}: {str(e)[:80]})")
+        cost = None   # no traced step: no step-time estimate either
     finally:
         moe_ops.capacity_for = real_capacity
     act = int(act / (pd.tp * pd.cp) / pd.pp)
@@ -414,6 +446,40 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
     # the optimizer step runs after backward with every local gradient present and no activation left
     at_step = bytes_params + bytes_grads + bytes_opt_dev
     bytes_fsdp += bytes_ep_workspace
+    # ---- step time: traced operators (sequence- / context- / pipeline-parallel ranks share them), optimizer, the
+    #      part of the collectives that compute does not hide
+    step_s = tok_s = 0.0
+    by_kind: dict = {}
+    flops_rank = 0.0
+    n_ops = 0
+    if cost is not None:
+        share = pd.tp * pd.cp * pd.pp
+        compute_s = cost.seconds / share
+        by_kind = {k: v / share for k, v in cost.by_kind.items()}
+        if pd.cp > 1 and "indexer scoring" in by_kind:
+            # all-gather context parallelism: rank r scores its queries against (r + 1) / cp of the keys, and the
+            # step waits for the last rank, which has (2 - 1 / cp) times the average number of pairs
+            extra = by_kind["indexer scoring"] * (1.0 - 1.0 / pd.cp)
+            by_kind["indexer scoring"] += extra
+            compute_s += extra
+        flops_rank = cost.flops / share
+        n_ops = cost.launches + cost.free_ops
+        cost.seconds, cost.by_kind = 0.0, {}
+        cost.add_optimizer_step(local, sb, 4 if cfg.optimizer.implementation == "b200_fused" else sb)
+        cost.exposed_collectives(comm, link_gbs)
+        by_kind.update(cost.by_kind)
+        device_s = compute_s + cost.seconds
+        host_s = n_ops * cost.peaks.host_s_per_operator
+        step_s = max(device_s, host_s)
+        if host_s > device_s:
+            by_kind = {"host (operator dispatch)": host_s, **by_kind}
+            notes.append(f"the step is host-bound: {n_ops:,} operators at "
+                         f"{cost.peaks.host_s_per_operator * 1e6:.0f} us each exceed {device_s * 1e3:.0f} ms of kernels")
+        if pd.ep_enabled:
+            notes.append("step time excludes the waits between expert-parallel ranks at every dispatch / combine: "
+                         "a lower bound for expert-parallel recipes")
+        tokens = cfg.training.local_batch_size * cfg.training.seq_len * pd.dp_replicate * pd.dp_shard
+        tok_s = tokens / step_s if step_s > 0 else 0.0
     total_bytes = max(bytes_params + bytes_opt_dev + bytes_fsdp + bytes_gathered + dyn_peak, at_step)
     budget = int(cfg.memory_sim.hbm_budget_gib * 1e9)
     return MemoryReport(
@@ -424,7 +490,10 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         bytes_optimizer_device=bytes_opt_dev, bytes_optimizer_host=bytes_opt_host, bytes_fsdp_buffers=bytes_fsdp,
         bytes_activations=act, bytes_total=total_bytes, budget_bytes=budget, fits=total_bytes <= budget,
         bytes_gathered_params=bytes_gathered, bytes_dynamic_peak=dyn_peak, bytes_grads_at_peak=grads_at_peak,
-        comm_bytes_per_step={k: float(v) for k, v in comm.items()}, comm_seconds_per_step=seconds, notes=notes)
+        comm_bytes_per_step={k: float(v) for k, v in comm.items()}, comm_seconds_per_step=seconds, notes=notes,
+        step_seconds_estimate=step_s, tokens_per_second_estimate=tok_s, flops_per_rank_step=flops_rank,
+        seconds_by_kind={k: round(v, 6) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])},
+        operators_per_step=n_ops)
 
 
 def run_from_config(trainer_config) -> MemoryReport:
