@@ -63,6 +63,7 @@ class Peaks:
     exposed_fsdp: float = 0.5            # share of the FSDP traffic time (at link rate) that compute does not hide,
                                          # including what the collectives take from the GEMMs that run beside them
     exposed_tp: float = 1.0
+    pcie_gbs: float = 50.0               # pinned host <-> device, per direction (Swap optimizer streams its state)
     exposed_ep: float = 0.6
 
     @classmethod
@@ -222,7 +223,9 @@ class StepCost:
             self._contraction("gemm_tcgen05", 2.0 * m * n * k, 2.0 * (m * k + n * k + m * n))
         elif name in ("tb_mxfp8_gemm", "tb_mxfp8_grouped_gemm") and len(args) >= 8:
             m, n, k = (int(v) for v in args[5:8])
-            self._contraction("mxfp8_gemm", 2.0 * m * n * k, 1.0 * (m * k + n * k) + 2.0 * m * n, p.fp8_factor)
+            g = self.grouped_rows_scale if name == "tb_mxfp8_grouped_gemm" else 1.0   # rows in use, not capacity
+            self._contraction("mxfp8_gemm", 2.0 * m * n * k * g, (1.0 * (m * k + n * k) + 2.0 * m * n) * g,
+                              p.fp8_factor)
         elif name == "tb_sparse_mla_bwd" and len(args) >= 14:
             s, h, t, kk, dq = (int(v) for v in args[8:13])
             big = p.sparse_bwd_large_stream if t * dq * 4 > 100e6 else 1.0
@@ -245,6 +248,13 @@ class StepCost:
         self._add("optimizer", step / (p.hbm_gbs * 1e9 * p.optimizer_efficiency), 0.0, step)
         norm = local_params * param_bytes
         self._add("gradient norm", norm / (p.hbm_gbs * 1e9 * 0.4), 0.0, norm)
+
+    def add_optimizer_swap(self, host_state_bytes: float) -> None:
+        """Swap optimizer: every step the state travels to the device and back; the two directions overlap."""
+        if host_state_bytes > 0:
+            t = host_state_bytes / (self.peaks.pcie_gbs * 1e9)
+            self.seconds += t
+            self.by_kind["optimizer state swap"] = self.by_kind.get("optimizer state swap", 0.0) + t
 
     def exposed_collectives(self, comm_bytes: dict, link_gbs: float) -> float:
         share = {"fsdp_all_gather": self.peaks.exposed_fsdp, "fsdp_reduce_scatter": self.peaks.exposed_fsdp,

@@ -466,6 +466,8 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         n_ops = cost.launches + cost.free_ops
         cost.seconds, cost.by_kind = 0.0, {}
         cost.add_optimizer_step(local, sb, 4 if cfg.optimizer.implementation == "b200_fused" else sb)
+        if cfg.optimizer.swap_optimizer:
+            cost.add_optimizer_swap(bytes_opt_host)
         cost.exposed_collectives(comm, link_gbs)
         by_kind.update(cost.by_kind)
         device_s = compute_s + cost.seconds
