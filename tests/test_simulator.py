@@ -153,6 +153,17 @@ def test_cost_model_prices_contractions_views_and_skipped_launches():
     assert cost.free_ops >= 1 and cost.by_kind["elementwise"] > 0
 
 
+def test_command_line_prints_the_report_and_signals_a_budget_miss(capsys):
+    from titan_b200.simulator.__main__ import main
+
+    assert main(["--world", "1", "--module", "llama3", "--config", "llama3_debugmodel"]) == 0
+    out = capsys.readouterr().out
+    assert "memory estimate per rank (1 ranks" in out and "step time (est.)" in out
+    rc = main(["--world=1", "--json", "--module", "llama3", "--config", "llama3_8b",
+               "--memory_sim.hbm_budget_gib", "40"])
+    assert rc == 3 and '"fits": false' in capsys.readouterr().out
+
+
 def test_no_launch_mode_restores_the_library_and_keeps_declarations():
     from titan_b200.ops import _lib
 
