@@ -31,6 +31,12 @@ def test_estimate_matches_measured_peak(recipe, world):
     assert not any("closed-form" in n for n in rep.notes), rep.notes   # the converted model ran on meta tensors
 
 
+def _moe_five_layers_local_experts(cfg):
+    cfg.model.flavor = "16B_mla_5l"
+    cfg.parallelism.expert_parallel_degree = 1
+    cfg.debug.moe_force_load_balance = True
+
+
 def _v32_sparse(seq_len, cp):
     def edit(cfg):
         cfg.training.seq_len = seq_len
@@ -67,6 +73,8 @@ MEASURED_MORE = [
     ("llama3", "llama3_8b", _llama_selective_without_swiglu_keep, 8, 52.5),
     ("llama3", "llama3_8b_mxfp8", None, 1, 110.8),
     ("llama3", "llama3_8b_baseline", None, 1, 81.8),
+    ("deepseek_v3", "deepseek_v3_16b_ep8", _moe_five_layers_local_experts, 1, 39.4),
+    ("deepseek_v3", "deepseek_v3_16b_ep8_mxfp8", _moe_five_layers_local_experts, 1, 41.5),
 ]
 
 
@@ -101,6 +109,9 @@ MEASURED_STEPS = [
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(65536, 2), 2, 2411.0, 0.10),
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(131072, 4), 4, 3060.0, 0.10),
     ("deepseek_v4", "debug_deepseek_v4_single_node_1b", _v4_mini_as_benchmarked, 1, 259.0, 0.15),
+    # not used for calibration: 5 layers of the 16B MoE with all 64 experts on one GPU, bf16 and MXFP8 experts
+    ("deepseek_v3", "deepseek_v3_16b_ep8", _moe_five_layers_local_experts, 1, 64.07, 0.10),
+    ("deepseek_v3", "deepseek_v3_16b_ep8_mxfp8", _moe_five_layers_local_experts, 1, 66.42, 0.10),
 ]
 
 
