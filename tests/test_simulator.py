@@ -103,7 +103,8 @@ MEASURED_STEPS = [
     ("llama3", "llama3_8b", None, 1, 444.0, 0.08),
     ("llama3", "llama3_8b", _llama_noac, 1, 435.0, 0.08),
     ("llama3", "llama3_8b_mxfp8", None, 1, 347.5, 0.08),
-    ("llama3", "llama3_8b", None, 8, 452.0, 0.10),
+    ("llama3", "llama3_8b", None, 4, 443.5, 0.06),
+    ("llama3", "llama3_8b", None, 8, 452.0, 0.06),
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(8192, 1), 1, 535.0, 0.10),
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(32768, 1), 1, 2080.0, 0.10),
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(65536, 2), 2, 2411.0, 0.10),
@@ -173,6 +174,17 @@ def test_command_line_prints_the_report_and_signals_a_budget_miss(capsys):
     rc = main(["--world=1", "--json", "--module", "llama3", "--config", "llama3_8b",
                "--memory_sim.hbm_budget_gib", "40"])
     assert rc == 3 and '"fits": false' in capsys.readouterr().out
+
+
+def test_command_line_table_over_job_sizes(capsys):
+    from titan_b200.simulator.__main__ import main
+
+    assert main(["--worlds", "1,2,3", "--module", "llama3", "--config", "llama3_debugmodel",
+                 "--parallelism.tensor_parallel_degree", "2"]) == 0
+    out = capsys.readouterr().out.splitlines()
+    assert out[0].split()[:3] == ["GPUs", "peak", "GiB"]
+    assert "skipped" in out[1] and "skipped" in out[3]        # 1 and 3 ranks cannot hold a tensor-parallel pair
+    assert out[2].split()[0] == "2" and out[2].split()[2] == "yes"
 
 
 def test_no_launch_mode_restores_the_library_and_keeps_declarations():

@@ -60,8 +60,10 @@ class Peaks:
     indexer_sel_bwd_s: float = 1.35e-3 / (2048 * 2048 * 64)  # per (query x selected key x head)
     host_s_per_operator: float = 10e-6   # eager dispatch + autograd bookkeeping per operator: a step cannot be shorter
                                          # than the host needs to issue it (DeepSeek-V4 mini: 26 k operators, 259 ms)
-    exposed_fsdp: float = 0.5            # share of the FSDP traffic time (at link rate) that compute does not hide,
-                                         # including what the collectives take from the GEMMs that run beside them
+    exposed_fsdp: float = 1.0            # the FSDP traffic time at link rate shows up in full, partly as waits and
+                                         # partly as GEMMs that slow down beside the collectives: Llama-3 8B goes
+                                         # from 438 ms on one GPU to 444 / 452 ms on 4 / 8 although the optimizer
+                                         # step shrinks by 31 ms
     exposed_tp: float = 1.0
     pcie_gbs: float = 50.0               # pinned host <-> device, per direction (Swap optimizer streams its state)
     exposed_ep: float = 0.6
