@@ -66,7 +66,8 @@ class Peaks:
                                          # step shrinks by 31 ms
     exposed_tp: float = 1.0
     pcie_gbs: float = 50.0               # pinned host <-> device, per direction (Swap optimizer streams its state)
-    exposed_ep: float = 0.6
+    exposed_ep: float = 1.5              # dispatch / combine run inside the layer at about two thirds of the link rate,
+                                         # plus the staging copies on either side
 
     @classmethod
     def load(cls) -> "Peaks":
