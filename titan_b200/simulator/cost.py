@@ -101,6 +101,7 @@ class StepCost:
     bytes: float = 0.0
     launches: int = 0
     by_kind: dict = field(default_factory=dict)
+    unpriced: int = 0                 # operators whose pricing rule failed (counted, not fatal)
     free_ops: int = 0                 # views and allocations: no device time, but the host still dispatches them
     grouped_rows_scale: float = 1.0   # rows in use / rows the expert-major buffers are sized for
 
@@ -219,6 +220,12 @@ class StepCost:
 
     # ------------------------------------------------------------------ kernels launched through ctypes
     def on_library_call(self, name: str, args: tuple) -> None:
+        try:
+            self._price_library_call(name, args)
+        except Exception:
+            self.unpriced += 1
+
+    def _price_library_call(self, name: str, args: tuple) -> None:
         ints = [a for a in args if isinstance(a, int) and not isinstance(a, bool)]
         p = self.peaks
         if name == "tb_gemm_auto" and len(args) >= 6:

@@ -119,7 +119,10 @@ class MetaMemoryTracker(TorchDispatchMode):
                 raise
             out = stand_in(*args, **(kwargs or {}))
         if self.cost is not None:
-            self.cost.on_op(func, args, kwargs or {}, out)
+            try:
+                self.cost.on_op(func, args, kwargs or {}, out)
+            except Exception:   # pricing an operator must never break the memory estimate
+                self.cost.unpriced += 1
         # storages that came IN with the arguments are not allocations of this op: a view of a parameter (``w.t()``)
         # shares the parameter's storage, which the static terms already count
         for leaf in tree_flatten((args, kwargs or {}))[0]:
