@@ -480,6 +480,8 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
             by_kind = {"host (operator dispatch)": host_s, **by_kind}
             notes.append(f"the step is host-bound: {n_ops:,} operators at "
                          f"{cost.peaks.host_s_per_operator * 1e6:.0f} us each exceed {device_s * 1e3:.0f} ms of kernels")
+        if cost.unpriced:
+            notes.append(f"{cost.unpriced} operators could not be priced and count as free in the step time")
         if pd.ep_enabled:
             notes.append("step time excludes the waits between expert-parallel ranks at every dispatch / combine: "
                          "a lower bound for expert-parallel recipes")
