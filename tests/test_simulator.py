@@ -179,7 +179,8 @@ def test_command_line_prints_the_report_and_signals_a_budget_miss(capsys):
 @pytest.mark.parametrize("module,recipe,world", [("deepseek_v3", "deepseek_v3_671b_61layers_4k", 128),
                                                  ("deepseek_v4", "debug_deepseek_v4_pro_single_node", 16),
                                                  ("qwen3", "sft_qwen3_30ba3b_gsm8k", 8),
-                                                 ("llama3", "llama3_405b", 8)])
+                                                 ("llama3", "llama3_405b", 8),
+                                                 ("vlm", "vlm_debugmodel", 1)])
 def test_large_recipes_trace_their_step_on_meta_tensors(module, recipe, world):
     """Cluster-sized recipes (pipeline / expert / tensor / context parallel degrees, MTP, fp32 storage with bf16
     compute) run their step on meta tensors: no closed-form fallback, a step time and a per-kind breakdown."""
@@ -188,7 +189,7 @@ def test_large_recipes_trace_their_step_on_meta_tensors(module, recipe, world):
 
     rep = estimate(resolve_recipe(module, recipe), world)
     assert not any("closed-form" in n for n in rep.notes), rep.notes
-    assert rep.step_seconds_estimate > 0 and rep.operators_per_step > 1000 and rep.seconds_by_kind
+    assert rep.step_seconds_estimate > 0 and rep.operators_per_step > 500 and rep.seconds_by_kind
     assert rep.bytes_activations > 0 and rep.world_size == world
 
 

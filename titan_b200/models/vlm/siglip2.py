@@ -28,6 +28,10 @@ def resize_positional_embeddings_zero_padded(pos_embeddings: torch.Tensor, spati
                                              max_length: int) -> torch.Tensor:
     """pos_embeddings ``(h, w, d)``; spatial_shapes ``(images, 2)`` → ``(images, max_length, d)``."""
     out = pos_embeddings.new_zeros((spatial_shapes.shape[0], max_length, pos_embeddings.shape[-1]))
+    if spatial_shapes.is_meta:
+        # shapes only (memory simulation): the grid sizes are values; the result depends on the table through one
+        # interpolation per distinct size, which the differentiable stand-in below represents
+        return out + pos_embeddings.reshape(-1, pos_embeddings.shape[-1]).sum(0)
     table = pos_embeddings.permute(2, 0, 1).unsqueeze(0)  # 1 d h w
     by_shape: dict[tuple[int, int], list[int]] = defaultdict(list)
     for i, (h, w) in enumerate(spatial_shapes.tolist()):

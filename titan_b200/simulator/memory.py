@@ -60,10 +60,19 @@ def _meta_nonzero(x):
 
 # Operators whose output shape depends on values have no meta kernel; the tracker only needs shapes, and for these
 # the shape (or a safe upper bound of it) follows from the arguments.
+def _meta_masked_select(x, mask):
+    shape = torch.broadcast_shapes(x.shape, mask.shape)
+    n = 1
+    for d in shape:
+        n *= d
+    return torch.empty(n, dtype=x.dtype, device=x.device)   # upper bound: every element selected
+
+
 _META_STAND_INS = {
     torch.ops.aten.bincount.default: _meta_bincount,
     torch.ops.aten.histc.default: _meta_histc,
     torch.ops.aten.nonzero.default: _meta_nonzero,
+    torch.ops.aten.masked_select.default: _meta_masked_select,
 }
 
 
@@ -233,8 +242,23 @@ def _sdpa_stand_in(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scal
     return _FlashStandIn.apply(q, k, v)
 
 
+def _example_inputs_on_meta(trainer_config, model_config):
+    """For loaders that feed more than tokens (images): one batch from the recipe's own SYNTHETIC loader, shapes only.
+    → (input dict on the meta device, labels on the meta device) or None when tokens alone are the input."""
+    dl = trainer_config.dataloader
+    if getattr(dl, "dataset", None) != "synthetic" or not type(dl).__name__.startswith("MultiModal"):
+        return None
+    from titan_b200.data.synthetic import build_dataloader
+
+    loader = build_dataloader(dl, model_config=model_config, training=trainer_config.training, dp_rank=0,
+                              dp_world_size=1)
+    batch, labels = next(iter(loader))
+    to_meta = lambda t: torch.empty_like(t, device="meta") if isinstance(t, torch.Tensor) else t   # noqa: E731
+    return {k: to_meta(v) for k, v in batch.items()}, to_meta(labels)
+
+
 def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad_keep: dict,
-                      cost=None) -> tuple[int, int]:
+                      cost=None, example=None) -> tuple[int, int]:
     """One forward + backward on meta tensors.  Returns (peak bytes of activations + gradients-so-far, gradient
     bytes inside that peak).  ``grad_keep[param] = fraction`` of a parameter's gradient that stays on this rank once
     it has been reduced (1 on one GPU, 1 / fsdp under FSDP, ...)."""
@@ -267,7 +291,12 @@ def _measure_timeline(model, model_config, training, loss_fn, num_mtp: int, grad
             for p in model.parameters():
                 if p.requires_grad:
                     hooks.append(p.register_post_accumulate_grad_hook(on_grad))
-            out = model(tokens)
+            if example is not None:
+                batch, labels = example
+                batch = dict(batch)
+                out = model(batch.pop("input"), **batch)
+            else:
+                out = model(tokens)
             loss = loss_fn(out, labels)
             del out
             loss.backward()
@@ -408,7 +437,7 @@ def estimate(trainer_config, world_size: int, *, link_gbs: float = 770.0) -> Mem
         cost.grouped_rows_scale = real_capacity(tok_pairs, n_exp) / max(moe_ops.capacity_for(tok_pairs, n_exp), 1)
     try:
         dyn, grads_at_peak = _measure_timeline(model, mc, cfg.training, loss_fn, cfg.training.num_mtp_modules,
-                                               grad_keep, cost)
+                                               grad_keep, cost, _example_inputs_on_meta(cfg, mc))
         act = max(dyn - grads_at_peak, 0)
     except Exception as e:  # an op without a meta kernel: fall back to a closed-form bound
         L, d = mc.n_layers, mc.dim
