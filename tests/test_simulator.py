@@ -45,6 +45,14 @@ def _v32_sparse(seq_len, cp):
     return edit
 
 
+def _v32_sparse_full_recompute(seq_len):
+    def edit(cfg):
+        _v32_sparse(seq_len, 1)(cfg)
+        cfg.activation_checkpoint.mode = "full"
+    edit.__name__ = f"full_recompute_{seq_len}"
+    return edit
+
+
 def _llama_selective_without_swiglu_keep(cfg):
     cfg.activation_checkpoint.selective_keep_swiglu = False
 
@@ -65,6 +73,9 @@ MEASURED_MORE = [
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(32768, 1), 1, 166.5),
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(65536, 2), 2, 133.7),
     ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse(131072, 4), 4, 117.2),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse_full_recompute(8192), 1, 81.0),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse_full_recompute(16384), 1, 85.9),
+    ("deepseek_v32", "deepseek_v32_sparse_cp8", _v32_sparse_full_recompute(32768), 1, 105.5),
     ("deepseek_v3", "deepseek_v3_16b_ep8", None, 8, 81.5),
     ("deepseek_v4", "debug_deepseek_v4_single_node_1b", _v4_mini_as_benchmarked, 1, 18.7),
     ("llama3", "llama3_8b", None, 1, 110.0),
@@ -191,6 +202,17 @@ def test_large_recipes_trace_their_step_on_meta_tensors(module, recipe, world):
     assert not any("closed-form" in n for n in rep.notes), rep.notes
     assert rep.step_seconds_estimate > 0 and rep.operators_per_step > 500 and rep.seconds_by_kind
     assert rep.bytes_activations > 0 and rep.world_size == world
+
+
+def test_command_line_checkpointing_table_marks_the_fastest_mode_that_fits(capsys):
+    from titan_b200.simulator.__main__ import main
+
+    rc = main(["--checkpointing", "--world", "1", "--module", "llama3", "--config", "llama3_8b",
+               "--memory_sim.hbm_budget_gib", "118"])
+    lines = capsys.readouterr().out.splitlines()
+    assert rc == 0 and [ln.split()[0] for ln in lines[1:]] == ["none", "selective", "full"]
+    assert sum("fastest that fits" in ln for ln in lines) == 1
+    assert "fastest that fits" in lines[2]      # without recomputation 111.9 GiB misses the 110 GiB (118 GB) budget
 
 
 def test_command_line_table_over_job_sizes(capsys):
